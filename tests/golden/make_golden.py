@@ -1,0 +1,211 @@
+"""Generate the golden vectors in this directory by running the REFERENCE's own code.
+
+Run where the reference checkout is available:
+
+    PYTHONDONTWRITEBYTECODE=1 MEGABENCH_ROOT=<reference checkout> python tests/golden/make_golden.py
+
+It imports ``megabench.tasks.{quantization,frontier,megamoe}`` from that checkout and stores
+inputs and outputs of its quantisers, routers and of the MoE layer composed from its
+primitives. The stored files are what ``tests/test_oracle_golden.py`` pins the oracle to; the
+reference is not needed to run the tests.
+
+Layer composition (only reference functions do arithmetic): per token
+``frontier.route(router.float() @ x.float(), ...)`` or the stable softmax rule of
+``tasks/distributed.py:174-176``; rows grouped per expert with the stable sort of
+``megamoe.experts``; per expert ``unpack(pack_fp8_activation(x)).bf16 @ unpack_fp8_weight.bf16.T``,
+fp32 ``g/(1+exp(-g))*u``, ``pack/unpack_fp8_activation``, ``@ down.T``; fp32 slot-order weighted
+sum plus the shared expert, one bf16 rounding.
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+REPO = HERE.parent.parent
+sys.path.insert(0, os.environ.get("MEGABENCH_ROOT", "/root/reference"))
+sys.path.insert(0, str(REPO))
+
+from megabench.tasks import frontier, quantization as Q  # noqa: E402
+from megabench.tasks.oracle import WidenBf16  # noqa: E402
+
+from vibe_megakernel_b200 import synthetic  # noqa: E402
+
+
+def u8(t):
+    return t.view(torch.uint8).numpy()
+
+
+def bf16_bits(t):
+    return t.contiguous().view(torch.int16).numpy()
+
+
+def quantizer_vectors():
+    out = {}
+    torch.manual_seed(13)
+    value = torch.randn(137, 259).to(torch.bfloat16)          # megabench/tests/test_frontier.py:225-226
+    out["w_in"] = bf16_bits(value)
+    for power in (False, True):
+        p, s = Q.pack_fp8_weight(value, power_of_two=power)
+        out[f"w_q_{int(power)}"], out[f"w_s_{int(power)}"] = u8(p), s.numpy()
+        out[f"w_deq_{int(power)}"] = Q.unpack_fp8_weight(p, s).numpy()
+        p, s = Q.pack_fp8_activation(value, power_of_two=power)
+        out[f"wa_q_{int(power)}"], out[f"wa_s_{int(power)}"] = u8(p), s.numpy()
+    value = torch.randn((3, 300), generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+    out["a_in"] = bf16_bits(value)                            # megabench/tests/test_megamoe.py:73
+    for power in (False, True):
+        p, s = Q.pack_fp8_activation(value, power_of_two=power)
+        out[f"a_q_{int(power)}"], out[f"a_s_{int(power)}"] = u8(p), s.numpy()
+        out[f"a_deq_{int(power)}"] = Q.unpack_fp8_activation(p, s).numpy()
+    generator = torch.Generator().manual_seed(3)              # megabench/tests/test_megamoe.py:57-61
+    value = torch.randn((64, 256), generator=generator) * torch.logspace(-6, 3, 64)[:, None]
+    edges = torch.tensor([448., 448.00003, 447.99997, 224., 1e-4, 1e-6, 0., 2. ** -22 * 448, 896.])
+    value[:len(edges), 0] = edges
+    out["e_in"] = value.numpy()
+    p, s = Q.pack_fp8_activation(value, block=32, scale_format="e8m0")
+    out["e_q"], out["e_s"] = u8(p), s.numpy()
+    out["e_deq"] = Q.unpack_fp8_activation(p, s, block=32).numpy()
+    p, s = Q.pack_fp8_activation(value)                       # float scales on the same edge rows
+    out["ef_q"], out["ef_s"] = u8(p), s.numpy()
+    # fp32 input (SwiGLU output is fp32 when it is requantised, megamoe.py:125-128)
+    value = torch.randn((5, 512), generator=torch.Generator().manual_seed(11)) * 3
+    value[1] = 0
+    value[2, :128] = 1e-7
+    out["f_in"] = value.numpy()
+    p, s = Q.pack_fp8_activation(value)
+    out["f_q"], out["f_s"] = u8(p), s.numpy()
+    np.savez_compressed(HERE / "quantizers.npz", **out)
+
+
+def softmax_route(scores, topk):
+    ids = torch.argsort(scores, descending=True, stable=True)[:topk]   # tasks/distributed.py:175
+    return ids, scores[ids].softmax(-1)                                # tasks/distributed.py:176
+
+
+def router_vectors():
+    out = {}
+    gen = torch.Generator().manual_seed(21)
+    cases = []
+    for name, e, topk, groups, top_groups, scaling in (("ds", 256, 8, 8, 4, 2.5), ("kimi", 384, 8, 1, 1, 2.827),
+                                                       ("small", 16, 4, 4, 2, 1.0), ("pair", 8, 2, 2, 1, 2.5)):
+        scores = torch.randn((12, e), generator=gen)
+        bias = torch.randn((e,), generator=gen) * 0.05
+        ids = torch.empty((12, topk), dtype=torch.int64)
+        ws = torch.empty((12, topk))
+        for t in range(12):
+            ids[t], ws[t] = frontier.route(scores[t], bias, topk, groups, top_groups, scaling)
+        out[f"{name}_scores"], out[f"{name}_bias"] = scores.numpy(), bias.numpy()
+        out[f"{name}_ids"], out[f"{name}_w"] = ids.numpy(), ws.numpy()
+        cases.append((name, e, topk, groups, top_groups, scaling))
+    out["sig_cases"] = np.array([[e, k, g, tg] for _, e, k, g, tg, _ in cases], dtype=np.int64)
+    out["sig_scaling"] = np.array([s for *_, s in cases], dtype=np.float64)
+    # ties: all-zero scores pick the lowest ids (megabench/tests/test_frontier.py:297-299)
+    ids, ws = frontier.route(torch.zeros(8), torch.zeros(8), 2, 2, 1)
+    out["tie_ids"], out["tie_w"] = ids.numpy(), ws.numpy()
+    # ties inside and across groups, and more picks than live experts
+    scores = torch.tensor([0.5, 0.5, -1.0, 0.5, 0.5, 0.5, -1.0, 0.5, 2.0, -3.0, -3.0, -3.0, 0.5, 0.5, 0.5, 0.5])
+    ids, ws = frontier.route(scores, torch.zeros(16), 6, 4, 2, 1.0)
+    out["tie2_scores"], out["tie2_ids"], out["tie2_w"] = scores.numpy(), ids.numpy(), ws.numpy()
+    ids, ws = frontier.route(scores, torch.zeros(16), 6, 4, 1, 1.0)
+    out["tie3_ids"], out["tie3_w"] = ids.numpy(), ws.numpy()
+    for name, e, topk in (("sm16", 16, 4), ("sm128", 128, 8), ("sm8", 8, 2)):
+        scores = torch.randn((12, e), generator=gen)
+        scores[3, 1] = scores[3, 5]          # an exact tie
+        ids = torch.empty((12, topk), dtype=torch.int64)
+        ws = torch.empty((12, topk))
+        for t in range(12):
+            ids[t], ws[t] = softmax_route(scores[t], topk)
+        out[f"{name}_scores"], out[f"{name}_ids"], out[f"{name}_w"] = scores.numpy(), ids.numpy(), ws.numpy()
+    np.savez_compressed(HERE / "routers.npz", **out)
+
+
+def reference_layer(geo, values, *, widen=False):
+    """The layer composed from reference primitives only."""
+    x = values["x"]
+    tokens = x.shape[0]
+    bf16 = torch.bfloat16
+    ids, ws = [], []
+    for row in x:
+        scores = values["router"].float() @ row.float()                 # frontier.py:343
+        if geo.scoring == "sigmoid":
+            i, w = frontier.route(scores, values["router_bias"], geo.topk, geo.n_group, geo.topk_group, geo.scaling)
+        else:
+            i, w = softmax_route(scores, geo.topk)
+        ids.append(i)
+        ws.append(w)
+    ids, ws = torch.stack(ids), torch.stack(ws)
+    flat = ids.flatten()
+    order = torch.sort(flat, stable=True).indices                       # megamoe.py:137
+    counts = torch.bincount(flat, minlength=geo.experts).tolist()       # megamoe.py:138
+    source = torch.div(order, geo.topk, rounding_mode="floor")          # megamoe.py:165
+
+    def mlp(rows, gate, gs, up, us, down, ds):
+        xa = Q.unpack_fp8_activation(*Q.pack_fp8_activation(rows)).to(bf16)      # megamoe.py:146
+        g = xa @ Q.unpack_fp8_weight(gate, gs).to(bf16).T                      # megamoe.py:147,149
+        u = xa @ Q.unpack_fp8_weight(up, us).to(bf16).T
+        g32, u32 = g.float(), u.float()
+        a = g32 / (1 + torch.exp(-g32)) * u32                                   # megamoe.py:119-122
+        a = Q.unpack_fp8_activation(*Q.pack_fp8_activation(a)).to(bf16)         # megamoe.py:125-128
+        return a @ Q.unpack_fp8_weight(down, ds).to(bf16).T                     # megamoe.py:148-149
+
+    output = torch.empty((flat.numel(), geo.hidden), dtype=bf16)
+    start = 0
+    for expert, count in enumerate(counts):
+        if not count:
+            continue
+        selected = order[start:start + count]
+        rows = x[source[start:start + count]]
+        start += count
+        output[selected] = mlp(rows, values["gate"][expert], values["gate_scale"][expert],
+                               values["up"][expert], values["up_scale"][expert],
+                               values["down"][expert], values["down_scale"][expert])
+    slots = output.view(tokens, geo.topk, -1)
+    combined = torch.zeros((tokens, geo.hidden), dtype=torch.float32)
+    for slot in range(geo.topk):
+        combined = combined + slots[:, slot].float() * ws[:, slot:slot + 1]       # frontier.py:352
+    if geo.shared:
+        combined = combined + mlp(x, values["shared_gate"], values["shared_gate_scale"],
+                                  values["shared_up"], values["shared_up_scale"],
+                                  values["shared_down"], values["shared_down_scale"]).float()   # frontier.py:353
+    return {"y": combined if widen else combined.to(bf16), "expert_ids": ids, "topk_weights": ws, "order": order}
+
+
+def layer_vectors():
+    """Small layers whose inputs the seeded generator of the package re-creates bit for bit."""
+    import dataclasses
+    out = {}
+    specs = {
+        "tiny": (synthetic.GEOMETRIES["tiny"], 4, 0),
+        "ds_small": (dataclasses.replace(synthetic.GEOMETRIES["deepseek_v3"], name="ds_small", hidden=512, inter=256,
+                                         experts=32, topk=4, n_group=4, topk_group=2), 6, 0),
+        "qwen_small": (dataclasses.replace(synthetic.GEOMETRIES["qwen3_30b_a3b"], name="qwen_small", hidden=256,
+                                           inter=128, experts=8, topk=2), 5, 0),
+    }
+    for name, (geo, tokens, seed) in specs.items():
+        values = synthetic.make_inputs(geo, tokens, seed, "cpu")
+        got = reference_layer(geo, values)
+        with torch.no_grad(), WidenBf16():
+            wide = reference_layer(geo, values, widen=True)
+        out[f"{name}_y"] = bf16_bits(got["y"])
+        out[f"{name}_y_fp32"] = wide["y"].float().numpy()
+        out[f"{name}_ids"] = got["expert_ids"].numpy()
+        out[f"{name}_w"] = got["topk_weights"].numpy()
+        out[f"{name}_order"] = got["order"].numpy()
+        out[f"{name}_x_sum"] = np.array([float(values["x"].float().sum()), float(values["router"].sum()),
+                                         float(values["gate"].float().sum()), float(values["down_scale"].sum())])
+        out[f"{name}_geo"] = np.array([geo.hidden, geo.inter, geo.experts, geo.topk, geo.shared,
+                                       geo.n_group, geo.topk_group, tokens, seed], dtype=np.int64)
+    np.savez_compressed(HERE / "layers.npz", **out)
+
+
+if __name__ == "__main__":
+    quantizer_vectors()
+    router_vectors()
+    layer_vectors()
+    for f in sorted(HERE.glob("*.npz")):
+        print(f.name, f.stat().st_size)

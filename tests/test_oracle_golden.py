@@ -1,0 +1,131 @@
+"""Pins the CPU oracle to vectors produced by the reference's own code (tests/golden)."""
+
+import dataclasses
+
+import numpy as np
+import torch
+
+from oracle import moe_oracle as O
+from vibe_megakernel_b200 import synthetic
+
+
+def bf16(bits):
+    return torch.from_numpy(bits.copy()).view(torch.bfloat16)
+
+
+def q_bytes(t):
+    return t.view(torch.uint8).numpy()
+
+
+def test_weight_and_activation_block_scales(golden_dir):
+    g = np.load(golden_dir / "quantizers.npz")
+    value = bf16(g["w_in"])
+    for power in (0, 1):
+        q, s = O.quantize_weight(value, power_of_two=bool(power))
+        assert np.array_equal(q_bytes(q), g[f"w_q_{power}"])
+        assert np.array_equal(s.numpy(), g[f"w_s_{power}"])
+        assert np.array_equal(O.dequantize_weight(q, s).numpy(), g[f"w_deq_{power}"])
+        q, s = O.quantize_activation(value, power_of_two=bool(power))
+        assert np.array_equal(q_bytes(q), g[f"wa_q_{power}"])
+        assert np.array_equal(s.numpy(), g[f"wa_s_{power}"])
+    value = bf16(g["a_in"])
+    for power in (0, 1):
+        q, s = O.quantize_activation(value, power_of_two=bool(power))
+        assert np.array_equal(q_bytes(q), g[f"a_q_{power}"])
+        assert np.array_equal(s.numpy(), g[f"a_s_{power}"])
+        assert np.array_equal(O.dequantize_activation(q, s).numpy(), g[f"a_deq_{power}"])
+
+
+def test_scale_edge_values(golden_dir):
+    g = np.load(golden_dir / "quantizers.npz")
+    value = torch.from_numpy(g["e_in"])
+    q, s = O.quantize_activation(value, group=32, scale_format="e8m0")
+    assert np.array_equal(q_bytes(q), g["e_q"])
+    assert np.array_equal(s.numpy(), g["e_s"])
+    assert np.array_equal(O.dequantize_activation(q, s, group=32).numpy(), g["e_deq"])
+    q, s = O.quantize_activation(value)
+    assert np.array_equal(q_bytes(q), g["ef_q"])
+    assert np.array_equal(s.numpy(), g["ef_s"])
+    value = torch.from_numpy(g["f_in"])
+    q, s = O.quantize_activation(value)
+    assert np.array_equal(q_bytes(q), g["f_q"])
+    assert np.array_equal(s.numpy(), g["f_s"])
+    # an all-zero row takes the 1e-4 floor
+    assert float(s[1, 0]) == np.float32(1e-4) / np.float32(448)
+
+
+def test_sigmoid_group_router(golden_dir):
+    g = np.load(golden_dir / "routers.npz")
+    for name, (e, k, groups, top_groups), scaling in zip(("ds", "kimi", "small", "pair"), g["sig_cases"], g["sig_scaling"]):
+        scores, bias = torch.from_numpy(g[f"{name}_scores"]), torch.from_numpy(g[f"{name}_bias"])
+        for t in range(scores.shape[0]):
+            ids, w = O.route_sigmoid_grouped(scores[t], bias, int(k), int(groups), int(top_groups), float(scaling))
+            assert np.array_equal(ids.numpy(), g[f"{name}_ids"][t])
+            assert np.array_equal(w.numpy(), g[f"{name}_w"][t])
+    ids, w = O.route_sigmoid_grouped(torch.zeros(8), torch.zeros(8), 2, 2, 1, 2.5)
+    assert ids.tolist() == [0, 1] == g["tie_ids"].tolist()
+    assert w.tolist() == [1.25, 1.25] == g["tie_w"].tolist()
+    scores = torch.from_numpy(g["tie2_scores"])
+    ids, w = O.route_sigmoid_grouped(scores, torch.zeros(16), 6, 4, 2, 1.0)
+    assert np.array_equal(ids.numpy(), g["tie2_ids"]) and np.array_equal(w.numpy(), g["tie2_w"])
+    ids, w = O.route_sigmoid_grouped(scores, torch.zeros(16), 6, 4, 1, 1.0)
+    assert np.array_equal(ids.numpy(), g["tie3_ids"]) and np.array_equal(w.numpy(), g["tie3_w"])
+
+
+def test_softmax_router(golden_dir):
+    g = np.load(golden_dir / "routers.npz")
+    for name, k in (("sm16", 4), ("sm128", 8), ("sm8", 2)):
+        scores = torch.from_numpy(g[f"{name}_scores"])
+        for t in range(scores.shape[0]):
+            ids, w = O.route_softmax(scores[t], k)
+            assert np.array_equal(ids.numpy(), g[f"{name}_ids"][t])
+            assert np.array_equal(w.numpy(), g[f"{name}_w"][t])
+
+
+def small_layers():
+    return {
+        "tiny": synthetic.GEOMETRIES["tiny"],
+        "ds_small": dataclasses.replace(synthetic.GEOMETRIES["deepseek_v3"], name="ds_small", hidden=512, inter=256,
+                                        experts=32, topk=4, n_group=4, topk_group=2),
+        "qwen_small": dataclasses.replace(synthetic.GEOMETRIES["qwen3_30b_a3b"], name="qwen_small", hidden=256,
+                                          inter=128, experts=8, topk=2),
+    }
+
+
+def spec_of(geo):
+    return O.LayerSpec(geo.hidden, geo.inter, geo.experts, geo.topk, geo.shared, geo.scoring,
+                       geo.n_group, geo.topk_group, geo.scaling)
+
+
+def test_layer_matches_reference_composition(golden_dir):
+    g = np.load(golden_dir / "layers.npz")
+    for name, geo in small_layers().items():
+        tokens, seed = int(g[f"{name}_geo"][7]), int(g[f"{name}_geo"][8])
+        values = synthetic.make_inputs(geo, tokens, seed, "cpu")
+        sums = np.array([float(values["x"].float().sum()), float(values["router"].sum()),
+                         float(values["gate"].float().sum()), float(values["down_scale"].sum())])
+        assert np.array_equal(sums, g[f"{name}_x_sum"]), "seeded generator changed"
+        got = O.moe_layer(spec_of(geo), values)
+        assert np.array_equal(got["expert_ids"].numpy(), g[f"{name}_ids"])
+        assert np.array_equal(got["topk_weights"].numpy(), g[f"{name}_w"])
+        assert np.array_equal(got["order"].numpy(), g[f"{name}_order"])
+        assert np.array_equal(got["y"].view(torch.int16).numpy(), g[f"{name}_y"])
+        wide = O.moe_layer(spec_of(geo), values, compute=torch.float32)
+        assert np.array_equal(wide["y_fp32"].numpy(), g[f"{name}_y_fp32"])
+
+
+def test_weight_generator_uses_the_reference_block_format():
+    w = torch.randn((256, 384), generator=torch.Generator().manual_seed(2)) * 0.02
+    q, s = synthetic.block_quantize_weight(w)
+    q2, s2 = O.quantize_weight(w)
+    assert torch.equal(q.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(s, s2)
+
+
+def test_margin_audit_flags_ties():
+    geo = small_layers()["ds_small"]
+    spec = spec_of(geo)
+    x = torch.zeros((1, geo.hidden), dtype=torch.bfloat16)
+    router = torch.zeros((geo.experts, geo.hidden))
+    assert O.decision_margins(spec, x, router, torch.zeros(geo.experts)) == 0.0
+    values = synthetic.make_inputs(geo, 6, 0, "cpu")
+    assert O.decision_margins(spec, values["x"], values["router"], values["router_bias"]) > 0
