@@ -1,0 +1,149 @@
+/*
+ * C ABI of the B200 FP8 mixture-of-experts decode layer.
+ *
+ * Every entry point takes plain device pointers and sizes; none allocates device memory: the
+ * caller owns inputs, outputs and the scratch workspace. All work is enqueued on `stream`
+ * (a cudaStream_t passed as void*). Return value: 0 = ok, > 0 = a cudaError_t, < 0 = one of
+ * the MOE_ERR_* codes below. Kernels never trap: a bounded on-device wait that runs out is
+ * reported through moe_device_status().
+ *
+ * The reference these replace is megabench's PyTorch MoE layer (kamahori/vibe-megakernel);
+ * each declaration cites the reference lines whose arithmetic it reproduces. Paths are
+ * relative to the reference project root.
+ */
+#ifndef MOE_B200_H_
+#define MOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOE_OK 0
+#define MOE_ERR_BAD_ARG (-1)
+#define MOE_ERR_UNSUPPORTED (-2)
+#define MOE_ERR_WORKSPACE (-3)
+#define MOE_ERR_DEVICE_TIMEOUT (-4)
+#define MOE_ERR_DRIVER (-5)
+#define MOE_ERR_DEVICE_BOUNDS (-6)
+
+#define MOE_SCORING_SOFTMAX 0 /* stable top-k of the logits, softmax over the selection */
+#define MOE_SCORING_SIGMOID 1 /* sigmoid + selection bias, group-limited, normalised, scaled */
+
+#define MOE_GEMM_TCGEN05 0 /* tcgen05 FP8 MMA, TMEM accumulators, TMA-fed (the product path) */
+#define MOE_GEMM_SIMT 1    /* plain CUDA-core check arm used by the tests to localise faults */
+
+#define MOE_MAX_EXPERTS 512
+#define MOE_MAX_TOPK 16
+
+typedef struct moe_config {
+  int32_t hidden;         /* H, multiple of 128 */
+  int32_t inter;          /* I, multiple of 128 */
+  int32_t n_experts;      /* routed experts in the whole layer */
+  int32_t topk;
+  int32_t n_shared;       /* 0 or 1 shared expert of width I */
+  int32_t scoring;        /* MOE_SCORING_* */
+  int32_t n_group;        /* router groups (1 = no group limit) */
+  int32_t topk_group;     /* groups kept */
+  float routed_scaling;   /* multiplies the normalised sigmoid weights */
+  int32_t ep_world;       /* expert-parallel ranks; rank r owns experts [r*E/world, (r+1)*E/world) */
+  int32_t ep_rank;
+  int32_t gemm_impl;      /* MOE_GEMM_* */
+} moe_config_t;
+
+/* Device pointers. Layouts are the MoE-block tensors of megabench/tasks/frontier.py:157-176:
+ * gate/up e4m3 [E_local, I, H] with fp32 scales [E_local, I/128, H/128]; down e4m3
+ * [E_local, H, I] with scales [E_local, H/128, I/128]; shared_* the same without the expert
+ * axis; router fp32 [E, H]; router_bias fp32 [E] (may be NULL: treated as zeros). */
+typedef struct moe_weights {
+  const float* router;
+  const float* router_bias;
+  const uint8_t* gate;
+  const float* gate_scale;
+  const uint8_t* up;
+  const float* up_scale;
+  const uint8_t* down;
+  const float* down_scale;
+  const uint8_t* shared_gate;
+  const float* shared_gate_scale;
+  const uint8_t* shared_up;
+  const float* shared_up_scale;
+  const uint8_t* shared_down;
+  const float* shared_down_scale;
+} moe_weights_t;
+
+/* Byte offsets of the scratch arrays inside the workspace (tests read intermediates here). */
+typedef struct moe_workspace_layout {
+  uint64_t total_bytes;
+  uint64_t status;        /* int32[8]: [0] device status, [1] detail */
+  uint64_t logits;        /* fp32 [T, E] */
+  uint64_t topk_ids;      /* int32 [T, topk] */
+  uint64_t topk_weights;  /* fp32 [T, topk] */
+  uint64_t counts;        /* int32 [E_local + 1] rows per local expert (+ shared) */
+  uint64_t offsets;       /* int32 [E_local + 2] exclusive prefix of counts */
+  uint64_t n_chunks;      /* int32: number of (expert, row chunk) work items */
+  uint64_t chunks;        /* int32 [max_chunks][4]: expert, first row, rows, reserved */
+  uint64_t row_token;     /* int32 [rows]: source token of every grouped row */
+  uint64_t row_dest;      /* int32 [rows]: output slot row (token*topk+slot; shared: T*topk+token) */
+  uint64_t xq;            /* e4m3 [rows, H] grouped activation rows */
+  uint64_t xs;            /* fp32 [rows, H/128] */
+  uint64_t aq;            /* e4m3 [rows, I] requantised SwiGLU output */
+  uint64_t as;            /* fp32 [rows, I/128] */
+  uint64_t slots;         /* bf16 [T*topk + T, H] down-projection rows in slot order */
+  int32_t rows;           /* T*topk + T*n_shared */
+  int32_t max_chunks;
+  int32_t token_tile;     /* tokens per MMA tile (16, 32 or 64) chosen for this T */
+  int32_t reserved;
+} moe_workspace_layout_t;
+
+/* Scratch a call with `tokens` rows needs; fills *layout when it is not NULL. */
+int moe_workspace_layout(const moe_config_t* cfg, int32_t tokens, moe_workspace_layout_t* layout);
+
+/* Router: fp32 logits (fp64 accumulation) and top-k selection for `tokens` bf16 rows.
+ * Replaces `router.float() @ x.float()` + frontier.route (megabench/tasks/frontier.py:229-242,343)
+ * and the stable softmax top-k of megabench/tasks/distributed.py:174-176.
+ * expert_ids int64 [T, topk] in choice order; weights fp32 [T, topk]; either may be NULL.
+ * Uses the logits / topk_ids / topk_weights arrays of `workspace`. */
+int moe_route(const moe_config_t* cfg, const void* x_bf16, const float* router, const float* router_bias,
+              int32_t tokens, int64_t* expert_ids, float* weights, void* workspace, size_t workspace_bytes,
+              void* stream);
+
+/* Per-row, per-128-channel e4m3 quantiser: scale = max(amax, 1e-4)/448, q = RNE(x/scale).
+ * Replaces pack_fp8_activation(..., scale_format="float") (megabench/tasks/quantization.py:87-109).
+ * dtype: 0 = bf16 input, 1 = fp32 input. `width` need not be a multiple of 128 (zero padding).
+ * gather (int32[rows], may be NULL) selects the input row of every output row. */
+int moe_quantize_rows(const void* x, int32_t dtype, int32_t rows, int32_t width, const int32_t* gather,
+                      uint8_t* q, float* scales, void* stream);
+
+/* Stable grouping of `n` routed rows by expert id (the token->expert permutation).
+ * Replaces `torch.sort(ids, stable=True)` + `bincount` (megabench/tasks/megamoe.py:137-138,161-165).
+ * ids int64 [n]; rows whose id is outside [id_base, id_base + n_local) are dropped.
+ * order int64 [n] (grouped position -> input row; unused tail = -1), counts int32 [n_local + 1]
+ * (rows per expert; the last entry is reserved and written as 0). */
+int moe_group_rows(const int64_t* ids, int32_t n, int32_t id_base, int32_t n_local, int64_t* order,
+                   int32_t* counts, void* stream);
+
+/* Whole layer on one GPU (ep_world == 1): router, permutation, activation quantiser, grouped
+ * gate/up GEMM with SwiGLU + requantisation, grouped down GEMM, shared expert, weighted combine.
+ * Replaces the MoE block of megabench/tasks/frontier.py:343-353 batched over tokens with the
+ * permutation/combine order of megabench/tasks/megamoe.py:153-182.
+ * x bf16 [T, H] -> y bf16 [T, H]; expert_ids int64 [T, topk], topk_weights fp32 [T, topk],
+ * order int64 [T*topk] are optional outputs (NULL to skip). Inputs are not modified. */
+int moe_layer_forward(const moe_config_t* cfg, const moe_weights_t* weights, const void* x_bf16, int32_t tokens,
+                      void* y_bf16, int64_t* expert_ids, float* topk_weights, int64_t* order, void* workspace,
+                      size_t workspace_bytes, void* stream);
+
+/* Synchronises `stream` and returns the device status word of the workspace: MOE_OK, or
+ * MOE_ERR_DEVICE_TIMEOUT / MOE_ERR_DEVICE_BOUNDS when a kernel gave up on a bounded wait or
+ * refused an out-of-range index. *detail (may be NULL) receives a code naming the place. */
+int moe_device_status(const void* workspace, void* stream, int32_t* detail);
+
+/* Number of kernels the last moe_layer_forward call on this thread launched. */
+int moe_last_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOE_B200_H_ */

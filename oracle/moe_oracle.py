@@ -105,7 +105,7 @@ def quantize_weight(w: torch.Tensor, *, power_of_two: bool = False):
     """
     r, c = w.shape
     pr, pc = (-r) % GROUP, (-c) % GROUP
-    v = torch.zeros((r + pr, c + pc), dtype=torch.float32)
+    v = torch.zeros((r + pr, c + pc), dtype=torch.float32, device=w.device)
     v[:r, :c] = w.to(torch.float32)
     blocks = v.reshape((r + pr) // GROUP, GROUP, (c + pc) // GROUP, GROUP)
     scales = scale_from_amax(blocks.abs().amax(dim=(1, 3)), power_of_two)
@@ -139,7 +139,7 @@ def route_sigmoid_grouped(scores: torch.Tensor, bias: torch.Tensor, topk: int, n
         g = c.reshape(n_group, -1)
         best_two = torch.sort(g, dim=-1, descending=True, stable=True).values[:, :2].sum(dim=-1)
         keep = torch.argsort(best_two, descending=True, stable=True)[:topk_group]
-        alive = torch.zeros(n_group, dtype=torch.bool)
+        alive = torch.zeros(n_group, dtype=torch.bool, device=scores.device)
         alive[keep] = True
         c = torch.where(alive[:, None], g, torch.full_like(g, -math.inf)).reshape(-1)
     ids = torch.argsort(c, descending=True, stable=True)[:topk]
@@ -260,7 +260,7 @@ def moe_layer(spec: LayerSpec, values: dict, *, compute=torch.bfloat16, keep_int
     order, counts = expert_order(flat, spec.experts)
     xq, xs = quantize_activation(x.to(torch.bfloat16))
     src = torch.div(order, spec.topk, rounding_mode="floor")
-    out_rows = torch.empty((flat.numel(), h), dtype=compute)
+    out_rows = torch.empty((flat.numel(), h), dtype=compute, device=x.device)
     inter = {}
     start = 0
     for e, n in enumerate(counts.tolist()):
@@ -275,7 +275,7 @@ def moe_layer(spec: LayerSpec, values: dict, *, compute=torch.bfloat16, keep_int
         out_rows[sel] = res
         if keep_intermediates:
             inter[e] = (aq, a_s)
-    acc = torch.zeros((t, h), dtype=torch.float32)
+    acc = torch.zeros((t, h), dtype=torch.float32, device=x.device)
     slots = out_rows.reshape(t, spec.topk, h)
     for s in range(spec.topk):
         acc = acc + slots[:, s].to(torch.float32) * ws[:, s:s + 1]
@@ -313,7 +313,7 @@ def decision_margins(spec: LayerSpec, x: torch.Tensor, router: torch.Tensor, bia
                 worst = min(worst, float(ss[spec.topk_group - 1] - ss[spec.topk_group]))
                 # within-group top-2 membership does not change ids, only the sum
                 keep = torch.argsort(sc, descending=True)[:spec.topk_group]
-                alive = torch.zeros(spec.n_group, dtype=torch.bool)
+                alive = torch.zeros(spec.n_group, dtype=torch.bool, device=x.device)
                 alive[keep] = True
                 c = torch.where(alive[:, None], g, torch.full_like(g, -math.inf)).reshape(-1)
         else:

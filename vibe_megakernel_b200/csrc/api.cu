@@ -1,0 +1,254 @@
+// C ABI: argument checks, workspace layout and the launch sequence of one layer call.
+#include <algorithm>
+#include <cstring>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace {
+
+thread_local int g_last_launches = 0;
+
+inline uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+int check_config(const moe_config_t* c) {
+  if (!c) return MOE_ERR_BAD_ARG;
+  if (c->hidden <= 0 || c->inter <= 0 || c->n_experts <= 0 || c->topk <= 0) return MOE_ERR_BAD_ARG;
+  if (c->hidden % 128 || c->inter % 128) return MOE_ERR_UNSUPPORTED;
+  if (c->n_experts > MOE_MAX_EXPERTS || c->topk > MOE_MAX_TOPK || c->topk > c->n_experts) return MOE_ERR_UNSUPPORTED;
+  if (c->n_shared < 0 || c->n_shared > 1) return MOE_ERR_UNSUPPORTED;
+  if (c->scoring != MOE_SCORING_SOFTMAX && c->scoring != MOE_SCORING_SIGMOID) return MOE_ERR_BAD_ARG;
+  if (c->n_group < 1 || c->n_group > 32 || c->n_experts % c->n_group) return MOE_ERR_BAD_ARG;
+  if (c->topk_group < 1 || c->topk_group > c->n_group) return MOE_ERR_BAD_ARG;
+  if (c->ep_world < 1 || c->ep_rank < 0 || c->ep_rank >= c->ep_world || c->n_experts % c->ep_world) return MOE_ERR_BAD_ARG;
+  if (c->gemm_impl != MOE_GEMM_TCGEN05 && c->gemm_impl != MOE_GEMM_SIMT) return MOE_ERR_BAD_ARG;
+  if (c->hidden / 128 > 112 || c->inter / 128 > 112) return MOE_ERR_UNSUPPORTED;
+  return MOE_OK;
+}
+
+int token_tile(int tokens) { return tokens <= 16 ? 16 : tokens <= 32 ? 32 : 64; }
+
+int layout_of(const moe_config_t* c, int tokens, moe_workspace_layout_t* L) {
+  const int rc = check_config(c);
+  if (rc) return rc;
+  if (tokens < 1 || static_cast<int64_t>(tokens) * c->topk > 32768) return MOE_ERR_UNSUPPORTED;
+  const int n_local = c->n_experts / c->ep_world;
+  const int routed = tokens * c->topk;
+  const int rows = routed + tokens * c->n_shared;
+  const int tile = token_tile(tokens);
+  const int max_chunks = std::min(routed, n_local) + routed / tile + (tokens + tile - 1) / tile + 1;
+  const uint64_t H = c->hidden, I = c->inter;
+  uint64_t off = 0;
+  auto take = [&](uint64_t bytes) { const uint64_t at = off; off = align_up(off + bytes, 256); return at; };
+  moe_workspace_layout_t l;
+  std::memset(&l, 0, sizeof(l));
+  l.status = take(8 * 4);
+  l.logits = take(4ull * tokens * c->n_experts);
+  l.topk_ids = take(4ull * routed);
+  l.topk_weights = take(4ull * routed);
+  l.counts = take(4ull * (n_local + 1));
+  l.offsets = take(4ull * (n_local + 2));
+  l.n_chunks = take(4);
+  l.chunks = take(16ull * max_chunks);
+  l.row_token = take(4ull * rows);
+  l.row_dest = take(4ull * rows);
+  l.xq = take(static_cast<uint64_t>(rows) * H);
+  l.xs = take(4ull * rows * (H / 128));
+  l.aq = take(static_cast<uint64_t>(rows) * I);
+  l.as = take(4ull * rows * (I / 128));
+  l.slots = take(2ull * rows * H);
+  l.total_bytes = off;
+  l.rows = rows;
+  l.max_chunks = max_chunks;
+  l.token_tile = tile;
+  if (L) *L = l;
+  return MOE_OK;
+}
+
+inline int from_cuda(cudaError_t e) { return e == cudaSuccess ? MOE_OK : static_cast<int>(e); }
+
+}  // namespace
+
+extern "C" {
+
+int moe_workspace_layout(const moe_config_t* cfg, int32_t tokens, moe_workspace_layout_t* layout) {
+  return layout_of(cfg, tokens, layout);
+}
+
+int moe_route(const moe_config_t* cfg, const void* x_bf16, const float* router, const float* router_bias,
+              int32_t tokens, int64_t* expert_ids, float* weights, void* workspace, size_t workspace_bytes,
+              void* stream) {
+  moe_workspace_layout_t L;
+  const int rc = layout_of(cfg, tokens, &L);
+  if (rc) return rc;
+  if (!x_bf16 || !router || !workspace) return MOE_ERR_BAD_ARG;
+  if (workspace_bytes < L.total_bytes) return MOE_ERR_WORKSPACE;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  int launches = 0;
+  return from_cuda(moe::launch_router(*cfg, static_cast<const __nv_bfloat16*>(x_bf16), router, router_bias, tokens,
+                                      reinterpret_cast<float*>(ws + L.logits),
+                                      reinterpret_cast<int32_t*>(ws + L.topk_ids),
+                                      reinterpret_cast<float*>(ws + L.topk_weights), expert_ids, weights,
+                                      static_cast<cudaStream_t>(stream), &launches));
+}
+
+int moe_quantize_rows(const void* x, int32_t dtype, int32_t rows, int32_t width, const int32_t* gather, uint8_t* q,
+                      float* scales, void* stream) {
+  if (!x || !q || !scales || rows < 0 || width < 1 || (dtype != 0 && dtype != 1)) return MOE_ERR_BAD_ARG;
+  int launches = 0;
+  return from_cuda(moe::launch_quantize(x, dtype, rows, width, gather, q, scales, static_cast<cudaStream_t>(stream),
+                                        &launches));
+}
+
+int moe_group_rows(const int64_t* ids, int32_t n, int32_t id_base, int32_t n_local, int64_t* order, int32_t* counts,
+                   void* stream) {
+  if (!ids || !order || !counts || n < 0 || n_local < 1 || n_local > MOE_MAX_EXPERTS || n > 32768) return MOE_ERR_BAD_ARG;
+  moe::GroupArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.ids64 = ids;
+  a.n = n;
+  a.id_base = id_base;
+  a.n_local = n_local;
+  a.topk = 1;
+  a.tile = 1;
+  a.counts = counts;
+  a.order = order;
+  int launches = 0;
+  return from_cuda(moe::launch_group_rows(a, static_cast<cudaStream_t>(stream), &launches));
+}
+
+int moe_layer_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* x_bf16, int32_t tokens,
+                      void* y_bf16, int64_t* expert_ids, float* topk_weights, int64_t* order, void* workspace,
+                      size_t workspace_bytes, void* stream_) {
+  moe_workspace_layout_t L;
+  const int rc = layout_of(cfg, tokens, &L);
+  if (rc) return rc;
+  if (cfg->ep_world != 1) return MOE_ERR_UNSUPPORTED;
+  if (!w || !x_bf16 || !y_bf16 || !workspace) return MOE_ERR_BAD_ARG;
+  if (!w->router || !w->gate || !w->gate_scale || !w->up || !w->up_scale || !w->down || !w->down_scale) return MOE_ERR_BAD_ARG;
+  if (cfg->n_shared && (!w->shared_gate || !w->shared_gate_scale || !w->shared_up || !w->shared_up_scale ||
+                        !w->shared_down || !w->shared_down_scale))
+    return MOE_ERR_BAD_ARG;
+  if (workspace_bytes < L.total_bytes) return MOE_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return MOE_ERR_BAD_ARG;
+
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  int32_t* status = reinterpret_cast<int32_t*>(ws + L.status);
+  float* logits = reinterpret_cast<float*>(ws + L.logits);
+  int32_t* ids32 = reinterpret_cast<int32_t*>(ws + L.topk_ids);
+  float* tw = reinterpret_cast<float*>(ws + L.topk_weights);
+  moe::Chunk* chunks = reinterpret_cast<moe::Chunk*>(ws + L.chunks);
+  int32_t* n_chunks = reinterpret_cast<int32_t*>(ws + L.n_chunks);
+  int32_t* row_token = reinterpret_cast<int32_t*>(ws + L.row_token);
+  int32_t* row_dest = reinterpret_cast<int32_t*>(ws + L.row_dest);
+  uint8_t* xq = ws + L.xq;
+  float* xs = reinterpret_cast<float*>(ws + L.xs);
+  uint8_t* aq = ws + L.aq;
+  float* as = reinterpret_cast<float*>(ws + L.as);
+  __nv_bfloat16* slots = reinterpret_cast<__nv_bfloat16*>(ws + L.slots);
+
+  const int n_local = cfg->n_experts;
+  const int routed = tokens * cfg->topk;
+  int launches = 0;
+  cudaError_t e = cudaMemsetAsync(status, 0, 32, stream);
+  if (e != cudaSuccess) return from_cuda(e);
+
+  // 1. router
+  e = moe::launch_router(*cfg, static_cast<const __nv_bfloat16*>(x_bf16), w->router, w->router_bias, tokens, logits,
+                         ids32, tw, expert_ids, topk_weights, stream, &launches);
+  if (e != cudaSuccess) return from_cuda(e);
+
+  // 2. token -> expert permutation and the work list of the GEMMs
+  moe::GroupArgs g;
+  std::memset(&g, 0, sizeof(g));
+  g.ids32 = ids32;
+  g.n = routed;
+  g.id_base = 0;
+  g.n_local = n_local;
+  g.topk = cfg->topk;
+  g.shared_rows = cfg->n_shared ? tokens : 0;
+  g.tile = L.token_tile;
+  g.max_chunks = L.max_chunks;
+  g.counts = reinterpret_cast<int32_t*>(ws + L.counts);
+  g.offsets = reinterpret_cast<int32_t*>(ws + L.offsets);
+  g.n_chunks = n_chunks;
+  g.chunks = chunks;
+  g.row_token = row_token;
+  g.row_dest = row_dest;
+  g.order = order;
+  g.status = status;
+  e = moe::launch_group_rows(g, stream, &launches);
+  if (e != cudaSuccess) return from_cuda(e);
+
+  // 3. activation quantiser, gathering each grouped row from its token
+  e = moe::launch_quantize(x_bf16, 0, L.rows, cfg->hidden, row_token, xq, xs, stream, &launches);
+  if (e != cudaSuccess) return from_cuda(e);
+
+  // 4. gate/up GEMM + SwiGLU + requantisation; 5. down GEMM into slot rows
+  moe::GemmArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.tile = L.token_tile;
+  a.n_local = n_local;
+  a.total_rows = L.rows;
+  a.chunks = chunks;
+  a.n_chunks = n_chunks;
+  a.status = status;
+  int driver_error = 0;
+
+  a.dual = true;
+  a.k = cfg->hidden;
+  a.m = cfg->inter;
+  a.max_units = L.max_chunks * (cfg->inter / 128);
+  a.act = xq;
+  a.act_scale = xs;
+  a.w_a = w->gate; a.w_a_scale = w->gate_scale;
+  a.w_b = w->up; a.w_b_scale = w->up_scale;
+  a.s_a = w->shared_gate; a.s_a_scale = w->shared_gate_scale;
+  a.s_b = w->shared_up; a.s_b_scale = w->shared_up_scale;
+  a.aq = aq;
+  a.as = as;
+  e = cfg->gemm_impl == MOE_GEMM_TCGEN05 ? moe::launch_gemm_tc(a, stream, &launches, &driver_error)
+                                         : moe::launch_gemm_simt(a, stream, &launches);
+  if (driver_error) return MOE_ERR_DRIVER;
+  if (e != cudaSuccess) return from_cuda(e);
+
+  a.dual = false;
+  a.k = cfg->inter;
+  a.m = cfg->hidden;
+  a.max_units = L.max_chunks * (cfg->hidden / 128);
+  a.act = aq;
+  a.act_scale = as;
+  a.w_a = w->down; a.w_a_scale = w->down_scale;
+  a.w_b = nullptr; a.w_b_scale = nullptr;
+  a.s_a = w->shared_down; a.s_a_scale = w->shared_down_scale;
+  a.s_b = nullptr; a.s_b_scale = nullptr;
+  a.aq = nullptr;
+  a.as = nullptr;
+  a.out = slots;
+  a.row_dest = row_dest;
+  e = cfg->gemm_impl == MOE_GEMM_TCGEN05 ? moe::launch_gemm_tc(a, stream, &launches, &driver_error)
+                                         : moe::launch_gemm_simt(a, stream, &launches);
+  if (driver_error) return MOE_ERR_DRIVER;
+  if (e != cudaSuccess) return from_cuda(e);
+
+  // 6. weighted combine in slot order, plus the shared expert's row
+  e = moe::launch_combine(slots, tw, tokens, cfg->topk, cfg->hidden, cfg->n_shared, static_cast<__nv_bfloat16*>(y_bf16),
+                          stream, &launches);
+  g_last_launches = launches;
+  return from_cuda(e);
+}
+
+int moe_device_status(const void* workspace, void* stream, int32_t* detail) {
+  if (!workspace) return MOE_ERR_BAD_ARG;
+  int32_t host[2] = {0, 0};
+  cudaError_t e = cudaMemcpyAsync(host, workspace, sizeof(host), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (detail) *detail = host[1];
+  return host[0];
+}
+
+int moe_last_launch_count(void) { return g_last_launches; }
+
+}  // extern "C"

@@ -1,0 +1,52 @@
+// Weighted combine / un-permute: y[t] = bf16( sum over slots, in slot order, of row*weight, then
+// the shared expert's row ), all in fp32 with a separate multiply and add per slot.
+//
+// Reference: megabench/tasks/frontier.py:349-354 (`output + down.float()*weights[slot]`, then the
+// shared expert) and the slot-order fp32 sum with one bf16 rounding of
+// megabench/tasks/megamoe.py:176-182. The down-projection rows are already stored in slot order
+// (row token*topk+slot), which is the reference's `slots[order] = output` un-permutation.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace moe {
+
+__global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __restrict__ slots,
+                                                      const float* __restrict__ weights, int tokens, int topk,
+                                                      int hidden, int shared, __nv_bfloat16* __restrict__ y) {
+  const int t = blockIdx.y;
+  const int c = (blockIdx.x * 256 + threadIdx.x) * 8;
+  if (c >= hidden) return;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int s = 0; s < topk; ++s) {
+    const size_t row = static_cast<size_t>(t) * topk + s;
+    const float w = weights[row];
+    const uint4 raw = *reinterpret_cast<const uint4*>(slots + row * hidden + c);
+    const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(__bfloat162float(v[i]), w));
+  }
+  if (shared) {
+    const size_t row = static_cast<size_t>(tokens) * topk + t;
+    const uint4 raw = *reinterpret_cast<const uint4*>(slots + row * hidden + c);
+    const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __bfloat162float(v[i]));
+  }
+  uint4 packed;
+  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&packed);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i] = __float2bfloat16_rn(acc[i]);
+  *reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * hidden + c) = packed;
+}
+
+cudaError_t launch_combine(const __nv_bfloat16* slots, const float* weights, int tokens, int topk, int hidden,
+                           int shared, __nv_bfloat16* y, cudaStream_t stream, int* launches) {
+  dim3 grid((hidden / 8 + 255) / 256, tokens);
+  combine_kernel<<<grid, 256, 0, stream>>>(slots, weights, tokens, topk, hidden, shared, y);
+  if (launches) *launches += 1;
+  return cudaGetLastError();
+}
+
+}  // namespace moe

@@ -1,0 +1,365 @@
+// Persistent grouped FP8 GEMM for the expert MLPs on tcgen05 tensor cores.
+//
+// Orientation: the weights are the MMA's M side (128 output channels per tile) and the tokens
+// of one expert are the N side (16, 32 or 64 per tile), so a decode batch streams every weight
+// byte exactly once through TMA while the token rows stay L2-resident.
+//
+//   D[m, n] = sum_k W[m, k] * X[n, k]       e4m3 x e4m3 -> fp32 in TMEM, kind::f8f6f4
+//
+// Block scales: W has one fp32 scale per 128x128 block, X one per token per 128 channels
+// (megabench/tasks/quantization.py:87-131). They are not powers of two, so each 128-deep K block
+// is accumulated into a fresh TMEM accumulator and the epilogue warps fold it into fp32
+// registers as acc += D * (w_scale * x_scale[n]); a second TMEM accumulator stage lets the
+// next K block's MMAs run meanwhile.
+//
+// Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2-5 =
+// epilogue (thread = one TMEM lane = one output channel). Work items (expert, row chunk, channel
+// tile) are taken round-robin by a persistent grid; their list is produced on the device by the
+// permutation kernel, so no host synchronisation is needed between routing and the GEMMs.
+//
+// Every wait is bounded: on expiry the role records MOE_ERR_DEVICE_TIMEOUT, raises the CTA's
+// abort flag, and all roles fall through to the common exit, which waits (bounded) for copies
+// still in flight and frees TMEM.
+//
+// Reference arithmetic: megabench/tasks/megamoe.py:146-149 (grouped expert GEMMs),
+// :116-128 (SwiGLU + requantisation), megabench/tasks/frontier.py:180-186 (FP8 linear).
+#include "common.cuh"
+#include "gemm_epilogue.cuh"
+#include "kernels.h"
+
+namespace moe {
+
+constexpr int kThreads = 192;
+constexpr int kAccStages = 2;
+constexpr int kStageBudget = 192 * 1024;
+constexpr int kMaxKBlocks = 112;      // K <= 14336
+
+template <int NT, bool DUAL>
+struct GemmCfg {
+  static constexpr int kABytes = 128 * 128;
+  static constexpr int kBBytes = NT * 128;
+  static constexpr int kStageBytes = (DUAL ? 2 : 1) * kABytes + kBBytes;
+  static constexpr int kStagesRaw = kStageBudget / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kAccCols = (DUAL ? 2 : 1) * NT;
+  static constexpr int kTmemCols = kAccStages * kAccCols < 32 ? 32 : kAccStages * kAccCols;
+  // after the stages: activation scales [kMaxKBlocks][NT], weight scales [2][kMaxKBlocks],
+  // amax scratch [4][NT], barriers, tmem slot, flags
+  static constexpr int kXsBytes = kMaxKBlocks * NT * 4;
+  static constexpr int kWsBytes = 2 * kMaxKBlocks * 4;
+  static constexpr int kAmaxBytes = 4 * NT * 4;
+  static constexpr int kBarBytes = (2 * kStages + 2 * kAccStages) * 8;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kXsBytes + kWsBytes + kAmaxBytes + kBarBytes + 64;
+};
+
+struct GemmDev {
+  const Chunk* chunks;
+  const int32_t* n_chunks;
+  int tiles_m, kblocks, m, n_local;
+  const float* act_scale;
+  const float* w_a_scale;
+  const float* w_b_scale;
+  const float* s_a_scale;
+  const float* s_b_scale;
+  uint8_t* aq;
+  float* as;
+  __nv_bfloat16* out;
+  const int32_t* row_dest;
+  int32_t* status;
+};
+
+template <int NT, bool DUAL>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                    const __grid_constant__ CUtensorMap tm_sa, const __grid_constant__ CUtensorMap tm_sb,
+                    const __grid_constant__ CUtensorMap tm_x, const GemmDev p) {
+  using C = GemmCfg<NT, DUAL>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* stages = base;
+  float* s_xs = reinterpret_cast<float*>(base + C::kStages * C::kStageBytes);
+  float* s_ws = s_xs + kMaxKBlocks * NT;
+  float* s_amax = s_ws + 2 * kMaxKBlocks;
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(s_amax + 4 * NT);
+  uint64_t* bar_empty = bar_full + C::kStages;
+  uint64_t* bar_tfull = bar_empty + C::kStages;
+  uint64_t* bar_tempty = bar_tfull + kAccStages;
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bar_tempty + kAccStages);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  volatile uint32_t* s_issued = reinterpret_cast<volatile uint32_t*>(s_tmem + 2);    // K blocks whose TMA was issued
+  volatile uint32_t* s_consumed = reinterpret_cast<volatile uint32_t*>(s_tmem + 3);  // K blocks whose data arrived
+  volatile uint32_t* s_committed = reinterpret_cast<volatile uint32_t*>(s_tmem + 4); // accumulators committed
+  volatile uint32_t* s_drained = reinterpret_cast<volatile uint32_t*>(s_tmem + 5);   // accumulators read
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) { mbar_init(bar_full + s, 1); mbar_init(bar_empty + s, 1); }
+    for (int s = 0; s < kAccStages; ++s) { mbar_init(bar_tfull + s, 1); mbar_init(bar_tempty + s, 128); }
+    *s_abort = 0; *s_issued = 0; *s_consumed = 0; *s_committed = 0; *s_drained = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tmap(&tm_a); prefetch_tmap(&tm_x);
+    if (DUAL) prefetch_tmap(&tm_b);
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(C::kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+
+  const int n_chunks = *p.n_chunks;
+  const int n_units = n_chunks * p.tiles_m;
+  const int KB = p.kblocks;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      const uint64_t pol_w = policy_evict_first();
+      const uint64_t pol_x = policy_evict_last();
+      uint32_t it = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+        const Chunk ch = p.chunks[u / p.tiles_m];
+        const int mt = u % p.tiles_m;
+        const bool shared_e = ch.expert >= p.n_local;
+        const CUtensorMap* ma = shared_e ? &tm_sa : &tm_a;
+        const CUtensorMap* mb = shared_e ? &tm_sb : &tm_b;
+        const int wrow = (shared_e ? 0 : ch.expert * p.m) + mt * 128;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
+          if (!mbar_wait(bar_empty + s, ph ^ 1u, s_abort)) {
+            if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 1); *s_abort = 1; }
+            ok = false;
+            break;
+          }
+          uint8_t* st = stages + s * C::kStageBytes;
+          mbar_expect_tx(bar_full + s, C::kStageBytes);
+          tma_load_2d(st, ma, kb * 128, wrow, bar_full + s, pol_w);
+          if constexpr (DUAL) tma_load_2d(st + C::kABytes, mb, kb * 128, wrow, bar_full + s, pol_w);
+          tma_load_2d(st + (DUAL ? 2 : 1) * C::kABytes, &tm_x, kb * 128, ch.row0, bar_full + s, pol_x);
+          *s_issued = it + 1;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = idesc_e4m3(128, NT);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
+          const uint32_t as = it % kAccStages, aph = (it / kAccStages) & 1u;
+          if (!mbar_wait(bar_tempty + as, aph ^ 1u, s_abort) || !mbar_wait(bar_full + s, ph, s_abort)) {
+            if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 2); *s_abort = 1; }
+            ok = false;
+            break;
+          }
+          *s_consumed = it + 1;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(stages + s * C::kStageBytes);
+          const uint32_t sb = sa + (DUAL ? 2 : 1) * C::kABytes;
+          const uint32_t d0 = tmem + as * C::kAccCols;
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            const uint64_t bd = smem_desc_sw128(sb + k4 * 32);
+            mma_f8(d0, smem_desc_sw128(sa + k4 * 32), bd, idesc, k4 > 0 ? 1u : 0u);
+            if constexpr (DUAL) mma_f8(d0 + NT, smem_desc_sw128(sa + C::kABytes + k4 * 32), bd, idesc, k4 > 0 ? 1u : 0u);
+          }
+          mma_commit(bar_empty + s);     // the stage may be refilled once these MMAs have read it
+          mma_commit(bar_tfull + as);    // the accumulator is complete
+          *s_committed = it + 1;
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
+    const int m = quarter * 32 + lane;            // output channel inside the tile; also this thread's
+                                                  // index among the 128 epilogue threads
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    uint32_t it = 0;
+    bool failed = false;
+    for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
+      const Chunk ch = p.chunks[u / p.tiles_m];
+      const int mt = u % p.tiles_m;
+      const bool shared_e = ch.expert >= p.n_local;
+      // stage this item's scales: x scales as [kb][n], weight scales as [which][kb]
+      for (int i = m; i < NT * KB; i += 128) {
+        const int n = i / KB, kb = i % KB;
+        s_xs[kb * NT + n] = n < ch.rows ? p.act_scale[static_cast<size_t>(ch.row0 + n) * KB + kb] : 0.f;
+      }
+      {
+        const float* wa = shared_e ? p.s_a_scale : p.w_a_scale + static_cast<size_t>(ch.expert) * p.tiles_m * KB;
+        for (int kb = m; kb < KB; kb += 128) s_ws[kb] = wa[static_cast<size_t>(mt) * KB + kb];
+        if constexpr (DUAL) {
+          const float* wb = shared_e ? p.s_b_scale : p.w_b_scale + static_cast<size_t>(ch.expert) * p.tiles_m * KB;
+          for (int kb = m; kb < KB; kb += 128) s_ws[kMaxKBlocks + kb] = wb[static_cast<size_t>(mt) * KB + kb];
+        }
+      }
+      epilogue_sync();
+
+      float acc_a[NT];
+      float acc_b[NT];
+#pragma unroll
+      for (int n = 0; n < NT; ++n) { acc_a[n] = 0.f; acc_b[n] = 0.f; }
+      for (int kb = 0; kb < KB; ++kb, ++it) {
+        const uint32_t as = it % kAccStages, aph = (it / kAccStages) & 1u;
+        if (!failed && !mbar_wait(bar_tfull + as, aph, s_abort)) {
+          if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 3); *s_abort = 1; }
+          failed = true;
+        }
+        if (failed) continue;   // keep in step with the other epilogue threads up to the item's end
+        tc_fence_after();
+        const float wa = s_ws[kb];
+        const float wb = DUAL ? s_ws[kMaxKBlocks + kb] : 0.f;
+        const float* xs = s_xs + kb * NT;
+        const uint32_t col0 = lane_base + as * C::kAccCols;
+#pragma unroll
+        for (int c = 0; c < NT; c += 16) {
+          float d[16];
+          tmem_ld16(col0 + c, d);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc_a[c + j] = fmaf(d[j], __fmul_rn(wa, xs[c + j]), acc_a[c + j]);
+          if constexpr (DUAL) {
+            tmem_ld16(col0 + NT + c, d);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc_b[c + j] = fmaf(d[j], __fmul_rn(wb, xs[c + j]), acc_b[c + j]);
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(bar_tempty + as);
+        if (m == 0) *s_drained = it + 1;
+      }
+      // One decision for all 128 threads: nobody may be left alone at a later barrier.
+      if (epilogue_any(failed || *s_abort)) break;
+      if constexpr (DUAL) {
+        epilogue_swiglu_requant<NT>(acc_a, acc_b, m, ch.rows, ch.row0, mt, p.m, s_amax, p.aq, p.as);
+      } else {
+        epilogue_store_rows<NT>(acc_a, m, ch.rows, ch.row0, mt, p.m, p.row_dest, p.out);
+        epilogue_sync();   // scales are restaged next
+      }
+    }
+  }
+
+  // ------------------------------ common exit ---------------------------------
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (*s_abort && threadIdx.x == 0) {
+    // Give copies and MMAs that were issued but never consumed a bounded chance to land.
+    for (uint32_t it = *s_consumed; it < *s_issued; ++it)
+      mbar_wait(bar_full + it % C::kStages, (it / C::kStages) & 1u);
+    for (uint32_t it = *s_drained; it < *s_committed; ++it)
+      mbar_wait(bar_tfull + it % kAccStages, (it / kAccStages) & 1u);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kTmemCols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side: tensor maps and launch.
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// 2-D byte matrix [rows, cols], box = [box_rows, 128 bytes], 128-byte swizzle, zero fill outside.
+static int make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -1;
+  if (reinterpret_cast<uintptr_t>(ptr) & 15 || cols % 16) return -2;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+template <int NT, bool DUAL>
+static cudaError_t launch_typed(const GemmArgs& a, const GemmDev& dev, const CUtensorMap* maps, int grid,
+                                cudaStream_t stream) {
+  using C = GemmCfg<NT, DUAL>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<NT, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  grouped_gemm_kernel<NT, DUAL><<<grid, kThreads, C::kSmemBytes, stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], dev);
+  return cudaGetLastError();
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+cudaError_t launch_gemm_tc(const GemmArgs& a, cudaStream_t stream, int* launches, int* driver_error) {
+  if (a.k % 128 || a.m % 128 || a.k / 128 > kMaxKBlocks) return cudaErrorInvalidValue;
+  CUtensorMap maps[5];
+  int rc = 0;
+  const uint64_t wrows = static_cast<uint64_t>(a.n_local) * a.m;
+  // With no routed experts on this rank the routed maps alias the shared ones (never dereferenced).
+  const uint8_t* wa = a.n_local > 0 ? a.w_a : a.s_a;
+  const uint8_t* wb = a.n_local > 0 ? a.w_b : a.s_b;
+  rc |= make_map(&maps[0], wa, a.n_local > 0 ? wrows : a.m, a.k, 128);
+  rc |= make_map(&maps[1], a.dual ? wb : wa, a.n_local > 0 ? wrows : a.m, a.k, 128);
+  const uint8_t* sa = a.s_a ? a.s_a : wa;
+  const uint8_t* sb = a.dual ? (a.s_b ? a.s_b : wb) : sa;
+  rc |= make_map(&maps[2], sa, a.s_a ? a.m : wrows, a.k, 128);
+  rc |= make_map(&maps[3], sb, a.s_a ? a.m : wrows, a.k, 128);
+  rc |= make_map(&maps[4], a.act, a.total_rows, a.k, a.tile);
+  if (rc) {
+    if (driver_error) *driver_error = rc;
+    return cudaErrorUnknown;
+  }
+  GemmDev dev{a.chunks, a.n_chunks, a.m / 128, a.k / 128, a.m, a.n_local, a.act_scale, a.w_a_scale, a.w_b_scale,
+              a.s_a_scale, a.s_b_scale, a.aq, a.as, a.out, a.row_dest, a.status};
+  const int grid = max(1, min(sm_count(), a.max_units));
+  cudaError_t e;
+  if (a.dual) {
+    e = a.tile == 16 ? launch_typed<16, true>(a, dev, maps, grid, stream)
+      : a.tile == 32 ? launch_typed<32, true>(a, dev, maps, grid, stream)
+                     : launch_typed<64, true>(a, dev, maps, grid, stream);
+  } else {
+    e = a.tile == 16 ? launch_typed<16, false>(a, dev, maps, grid, stream)
+      : a.tile == 32 ? launch_typed<32, false>(a, dev, maps, grid, stream)
+                     : launch_typed<64, false>(a, dev, maps, grid, stream);
+  }
+  if (launches) *launches += 1;
+  return e;
+}
+
+}  // namespace moe

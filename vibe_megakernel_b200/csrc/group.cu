@@ -1,0 +1,133 @@
+// Token -> expert permutation: a stable counting sort of the routed rows by expert id.
+//
+// Reference: `torch.sort(ids, stable=True)` + `bincount` (megabench/tasks/megamoe.py:137-138) and
+// the owner-order gather of megabench/tasks/megamoe.py:161-168. The result does not depend on
+// thread timing: a row's position is offset[expert] + (number of earlier rows with the same
+// expert), computed with ballots over the rows in order, never with order-dependent atomics.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace moe {
+
+constexpr int kGroupWarps = 8;
+constexpr int kMaxGroupRows = 32768;   // ids are staged in shared memory as int16
+
+__global__ void __launch_bounds__(kGroupWarps * 32) group_rows_kernel(GroupArgs a) {
+  extern __shared__ int16_t s_ids[];                       // [n]
+  __shared__ int s_count[MOE_MAX_EXPERTS + 1];
+  __shared__ int s_offset[MOE_MAX_EXPERTS + 2];
+  __shared__ int s_chunk0[MOE_MAX_EXPERTS + 2];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int groups = a.n_local + 1;                        // last one is the shared expert
+
+  for (int i = tid; i < groups; i += blockDim.x) s_count[i] = 0;
+  __syncthreads();
+  for (int r = tid; r < a.n; r += blockDim.x) {
+    const long long id = a.ids32 ? static_cast<long long>(a.ids32[r]) : a.ids64[r];
+    const long long local = id - a.id_base;
+    const bool mine = local >= 0 && local < a.n_local;
+    s_ids[r] = mine ? static_cast<int16_t>(local) : static_cast<int16_t>(-1);
+    if (mine) atomicAdd(&s_count[local], 1);
+  }
+  if (tid == 0) s_count[a.n_local] = a.shared_rows;
+  __syncthreads();
+
+  // Exclusive prefix of rows and of chunks per expert, by one warp: each lane owns a run of experts.
+  if (warp == 0) {
+    const int per = (groups + 31) / 32;
+    const int first = lane * per, last = min(first + per, groups);
+    int rows = 0, chunks = 0;
+    for (int e = first; e < last; ++e) {
+      rows += s_count[e];
+      chunks += (s_count[e] + a.tile - 1) / a.tile;
+    }
+    int rows_before = rows, chunks_before = chunks;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int r = __shfl_up_sync(0xffffffffu, rows_before, off);
+      const int c = __shfl_up_sync(0xffffffffu, chunks_before, off);
+      if (lane >= off) { rows_before += r; chunks_before += c; }
+    }
+    rows_before -= rows;
+    chunks_before -= chunks;
+    for (int e = first; e < last; ++e) {
+      s_offset[e] = rows_before;
+      s_chunk0[e] = chunks_before;
+      rows_before += s_count[e];
+      chunks_before += (s_count[e] + a.tile - 1) / a.tile;
+    }
+    if (last == groups && first < groups) {   // the lane holding the final expert closes the prefix
+      s_offset[groups] = rows_before;
+      s_chunk0[groups] = chunks_before;
+    }
+  }
+  __syncthreads();
+
+  // Stable rank: warp w walks the rows in order and places those of its expert.
+  const int e = blockIdx.x * kGroupWarps + warp;
+  if (e < a.n_local && s_count[e] > 0) {
+    int placed = 0;
+    const int base = s_offset[e];
+    for (int r0 = 0; r0 < a.n; r0 += 32) {
+      const int r = r0 + lane;
+      const bool hit = r < a.n && s_ids[r] == e;
+      const unsigned m = __ballot_sync(0xffffffffu, hit);
+      if (hit) {
+        const int pos = base + placed + __popc(m & ((1u << lane) - 1u));
+        if (a.order) a.order[pos] = r;
+        if (a.row_token) a.row_token[pos] = r / a.topk;
+        if (a.row_dest) a.row_dest[pos] = r;
+      }
+      placed += __popc(m);
+    }
+  }
+
+  if (blockIdx.x == 0) {
+    const int kept = s_offset[a.n_local];
+    for (int i = tid; i < groups; i += blockDim.x) {
+      a.counts[i] = s_count[i];
+      const int c = s_count[i];
+      const int nch = (c + a.tile - 1) / a.tile;
+      for (int j = 0; a.chunks && j < nch; ++j) {
+        const int slot = s_chunk0[i] + j;
+        if (slot < a.max_chunks) {
+          Chunk ch;
+          ch.expert = i;
+          ch.row0 = s_offset[i] + j * a.tile;
+          ch.rows = min(a.tile, c - j * a.tile);
+          ch.pad = 0;
+          a.chunks[slot] = ch;
+        }
+      }
+    }
+    if (a.offsets)
+      for (int i = tid; i <= groups; i += blockDim.x) a.offsets[i] = s_offset[i];
+    if (tid == 0 && a.n_chunks) {
+      const int total = s_chunk0[groups];
+      *a.n_chunks = min(total, a.max_chunks);
+      if (total > a.max_chunks && a.status) report(a.status, MOE_ERR_DEVICE_BOUNDS, 100);
+    }
+    // rows of the shared expert follow the routed rows; their output row follows all slot rows
+    for (int t = tid; t < a.shared_rows; t += blockDim.x) {
+      if (a.row_token) a.row_token[kept + t] = t;
+      if (a.row_dest) a.row_dest[kept + t] = a.n + t;
+    }
+    if (a.order)
+      for (int r = kept + tid; r < a.n; r += blockDim.x) a.order[r] = -1;
+  }
+}
+
+cudaError_t launch_group_rows(const GroupArgs& a, cudaStream_t stream, int* launches) {
+  if (a.n > kMaxGroupRows || a.n_local > MOE_MAX_EXPERTS) return cudaErrorInvalidValue;
+  const int blocks = max(1, (a.n_local + kGroupWarps - 1) / kGroupWarps);
+  const size_t smem = static_cast<size_t>(a.n > 0 ? a.n : 1) * sizeof(int16_t);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(group_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    if (e != cudaSuccess) return e;
+  }
+  group_rows_kernel<<<blocks, kGroupWarps * 32, smem, stream>>>(a);
+  if (launches) *launches += 1;
+  return cudaGetLastError();
+}
+
+}  // namespace moe

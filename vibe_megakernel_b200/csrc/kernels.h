@@ -1,0 +1,74 @@
+// Host-callable launchers of the layer's kernels (internal to the library).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/moe_b200.h"
+
+namespace moe {
+
+struct Chunk;
+
+cudaError_t launch_router(const moe_config_t& cfg, const __nv_bfloat16* x, const float* router, const float* bias,
+                          int tokens, float* logits, int32_t* ids32, float* weights, int64_t* ids64,
+                          float* weights_out, cudaStream_t stream, int* launches);
+
+struct GroupArgs {
+  const int32_t* ids32;   // one of ids32 / ids64 is set
+  const int64_t* ids64;
+  int n;                  // routed rows
+  int id_base, n_local;   // ids in [id_base, id_base + n_local) are kept
+  int topk;               // row r belongs to token r / topk
+  int shared_rows;        // rows of the shared expert appended as expert n_local (0 = none)
+  int tile;               // rows per chunk
+  int max_chunks;
+  int32_t* counts;        // [n_local + 1]
+  int32_t* offsets;       // [n_local + 2]
+  int32_t* n_chunks;
+  Chunk* chunks;
+  int32_t* row_token;     // optional
+  int32_t* row_dest;      // optional
+  int64_t* order;         // optional, [n]
+  int32_t* status;        // optional
+};
+cudaError_t launch_group_rows(const GroupArgs& a, cudaStream_t stream, int* launches);
+
+cudaError_t launch_quantize(const void* x, int dtype, int rows, int width, const int32_t* gather, uint8_t* q,
+                            float* scales, cudaStream_t stream, int* launches);
+
+cudaError_t launch_combine(const __nv_bfloat16* slots, const float* weights, int tokens, int topk, int hidden,
+                           int shared, __nv_bfloat16* y, cudaStream_t stream, int* launches);
+
+struct GemmArgs {
+  bool dual;                 // true: gate+up with SwiGLU + requantisation; false: down projection
+  int tile;                  // tokens per MMA tile: 16, 32 or 64
+  int k;                     // contraction length (H for gate/up, I for down)
+  int m;                     // output channels per expert (I for gate/up, H for down)
+  int n_local;               // routed experts held here; chunk.expert == n_local is the shared expert
+  int total_rows;            // rows of the activation buffer
+  int max_units;             // upper bound of chunks * (m / 128)
+  const Chunk* chunks;
+  const int32_t* n_chunks;
+  const uint8_t* act;        // e4m3 [total_rows, k]
+  const float* act_scale;    // [total_rows, k/128]
+  const uint8_t* w_a;        // gate or down, [n_local, m, k]
+  const float* w_a_scale;
+  const uint8_t* w_b;        // up (dual only)
+  const float* w_b_scale;
+  const uint8_t* s_a;        // shared expert counterparts (may be NULL when there is none)
+  const float* s_a_scale;
+  const uint8_t* s_b;
+  const float* s_b_scale;
+  uint8_t* aq;               // dual: e4m3 [total_rows, m]
+  float* as;                 // dual: [total_rows, m/128]
+  __nv_bfloat16* out;        // single: bf16 rows [*, m] addressed through row_dest
+  const int32_t* row_dest;
+  int32_t* status;
+};
+cudaError_t launch_gemm_tc(const GemmArgs& a, cudaStream_t stream, int* launches, int* driver_error);
+cudaError_t launch_gemm_simt(const GemmArgs& a, cudaStream_t stream, int* launches);
+
+}  // namespace moe

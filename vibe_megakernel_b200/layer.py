@@ -1,0 +1,208 @@
+"""Host side of the FP8 MoE decode layer: torch owns memory and streams, the C ABI does the work.
+
+The call signature and tensor names follow the reference's MoE-block tensors
+(megabench/tasks/frontier.py:157-176) and its plugin protocol (megabench/README.md:83-104).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from . import _cabi
+
+
+@dataclass(frozen=True)
+class LayerConfig:
+    hidden: int
+    inter: int
+    experts: int
+    topk: int
+    shared: int = 1
+    scoring: str = "sigmoid"
+    n_group: int = 1
+    topk_group: int = 1
+    scaling: float = 1.0
+    gemm: str = "tcgen05"       # "tcgen05" (product path) or "simt" (check arm)
+
+    @classmethod
+    def from_geometry(cls, geo, **overrides) -> "LayerConfig":
+        base = dict(hidden=geo.hidden, inter=geo.inter, experts=geo.experts, topk=geo.topk, shared=geo.shared,
+                    scoring=geo.scoring, n_group=geo.n_group, topk_group=geo.topk_group, scaling=geo.scaling)
+        base.update(overrides)
+        return cls(**base)
+
+    def c_struct(self, world: int = 1, rank: int = 0) -> _cabi.Config:
+        return _cabi.Config(self.hidden, self.inter, self.experts, self.topk, self.shared,
+                            _cabi.SCORING[self.scoring], self.n_group, self.topk_group, float(self.scaling),
+                            world, rank, _cabi.GEMM_SIMT if self.gemm == "simt" else _cabi.GEMM_TCGEN05)
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _require(t: torch.Tensor, name: str, dtype, shape=None) -> torch.Tensor:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise ValueError(f"{name} must have shape {tuple(shape)}, got {tuple(t.shape)}")
+    return t
+
+
+class MoeLayer:
+    """One GPU holding every expert. ``forward(values)`` takes the reference's tensor dict."""
+
+    def __init__(self, config: LayerConfig, max_tokens: int = 128, device: torch.device | str | None = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("vibe_megakernel_b200 needs a CUDA device; there is no CPU path")
+        self.config = config
+        self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        self.lib = _cabi.load()
+        self.cfg = config.c_struct()
+        self._workspaces: dict[int, tuple[torch.Tensor, _cabi.Layout]] = {}
+        self.max_tokens = max_tokens
+        self.workspace(max_tokens)
+
+    def layout(self, tokens: int) -> _cabi.Layout:
+        lay = _cabi.Layout()
+        _cabi.check("moe_workspace_layout", self.lib.moe_workspace_layout(C.byref(self.cfg), tokens, C.byref(lay)))
+        return lay
+
+    def workspace(self, tokens: int) -> tuple[torch.Tensor, _cabi.Layout]:
+        got = self._workspaces.get(tokens)
+        if got is None:
+            lay = self.layout(tokens)
+            buf = torch.empty(int(lay.total_bytes) + 256, dtype=torch.uint8, device=self.device)
+            skew = (-buf.data_ptr()) % 256
+            got = (buf[skew:skew + int(lay.total_bytes)], lay)
+            self._workspaces[tokens] = got
+        return got
+
+    def weights_struct(self, values: dict[str, torch.Tensor]) -> _cabi.Weights:
+        c = self.config
+        e, h, i = c.experts, c.hidden, c.inter
+        f8, f32 = torch.float8_e4m3fn, torch.float32
+        w = _cabi.Weights()
+        w.router = _require(values["router"], "router", f32, (e, h)).data_ptr()
+        bias = values.get("router_bias")
+        w.router_bias = _ptr(_require(bias, "router_bias", f32, (e,))) if bias is not None else None
+        for name, shape, sshape in (("gate", (e, i, h), (e, i // 128, h // 128)), ("up", (e, i, h), (e, i // 128, h // 128)),
+                                    ("down", (e, h, i), (e, h // 128, i // 128))):
+            setattr(w, name, _require(values[name], name, f8, shape).data_ptr())
+            setattr(w, name + "_scale", _require(values[name + "_scale"], name + "_scale", f32, sshape).data_ptr())
+        if c.shared:
+            for name, shape, sshape in (("shared_gate", (i, h), (i // 128, h // 128)), ("shared_up", (i, h), (i // 128, h // 128)),
+                                        ("shared_down", (h, i), (h // 128, i // 128))):
+                setattr(w, name, _require(values[name], name, f8, shape).data_ptr())
+                setattr(w, name + "_scale", _require(values[name + "_scale"], name + "_scale", f32, sshape).data_ptr())
+        return w
+
+    def forward(self, values: dict[str, torch.Tensor], *, check_status: bool = False) -> dict[str, torch.Tensor]:
+        c = self.config
+        x = _require(values["x"], "x", torch.bfloat16)
+        if x.dim() != 2 or x.shape[1] != c.hidden:
+            raise ValueError(f"x must be [tokens, {c.hidden}]")
+        tokens = x.shape[0]
+        ws, lay = self.workspace(tokens)
+        w = self.weights_struct(values)
+        y = torch.empty_like(x)
+        ids = torch.empty((tokens, c.topk), dtype=torch.int64, device=x.device)
+        tw = torch.empty((tokens, c.topk), dtype=torch.float32, device=x.device)
+        order = torch.empty((tokens * c.topk,), dtype=torch.int64, device=x.device)
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        rc = self.lib.moe_layer_forward(C.byref(self.cfg), C.byref(w), x.data_ptr(), tokens, y.data_ptr(), ids.data_ptr(),
+                                        tw.data_ptr(), order.data_ptr(), ws.data_ptr(), ws.numel(), stream)
+        _cabi.check("moe_layer_forward", rc)
+        if check_status:
+            self.check_device_status(tokens)
+        return {"y": y, "expert_ids": ids, "topk_weights": tw, "order": order}
+
+    __call__ = forward
+
+    def check_device_status(self, tokens: int) -> None:
+        ws, _ = self.workspace(tokens)
+        detail = C.c_int32(0)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self.lib.moe_device_status(ws.data_ptr(), stream, C.byref(detail))
+        if rc != 0:
+            raise _cabi.MoeError("device status", rc, detail.value)
+
+    def launches(self) -> int:
+        return int(self.lib.moe_last_launch_count())
+
+    # ---- stage entry points (unit parity) --------------------------------------------
+    def route(self, x: torch.Tensor, router: torch.Tensor, bias: torch.Tensor | None):
+        c = self.config
+        tokens = x.shape[0]
+        ws, _ = self.workspace(tokens)
+        ids = torch.empty((tokens, c.topk), dtype=torch.int64, device=x.device)
+        tw = torch.empty((tokens, c.topk), dtype=torch.float32, device=x.device)
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        rc = self.lib.moe_route(C.byref(self.cfg), _require(x, "x", torch.bfloat16).data_ptr(),
+                                _require(router, "router", torch.float32).data_ptr(), _ptr(bias), tokens,
+                                ids.data_ptr(), tw.data_ptr(), ws.data_ptr(), ws.numel(), stream)
+        _cabi.check("moe_route", rc)
+        return ids, tw
+
+    def scratch(self, tokens: int, name: str) -> torch.Tensor:
+        """A view of one scratch array of the last call with ``tokens`` rows (tests only)."""
+        ws, lay = self.workspace(tokens)
+        c = self.config
+        rows = lay.rows
+        spec = {
+            "logits": (lay.logits, torch.float32, (tokens, c.experts)),
+            "counts": (lay.counts, torch.int32, (c.experts + 1,)),
+            "offsets": (lay.offsets, torch.int32, (c.experts + 2,)),
+            "n_chunks": (lay.n_chunks, torch.int32, (1,)),
+            "chunks": (lay.chunks, torch.int32, (lay.max_chunks, 4)),
+            "row_token": (lay.row_token, torch.int32, (rows,)),
+            "row_dest": (lay.row_dest, torch.int32, (rows,)),
+            "xq": (lay.xq, torch.uint8, (rows, c.hidden)),
+            "xs": (lay.xs, torch.float32, (rows, c.hidden // 128)),
+            "aq": (lay.aq, torch.uint8, (rows, c.inter)),
+            "as": (lay.as_, torch.float32, (rows, c.inter // 128)),
+            "slots": (lay.slots, torch.bfloat16, (rows, c.hidden)),
+        }[name]
+        off, dtype, shape = spec
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        return ws[off:off + nbytes].view(dtype).view(shape)
+
+
+def quantize_rows(x: torch.Tensor, gather: torch.Tensor | None = None):
+    """e4m3 payload and fp32 scales of ``x`` [rows, width] (bf16 or fp32), per row per 128 channels."""
+    lib = _cabi.load()
+    if x.dtype not in (torch.bfloat16, torch.float32) or not x.is_cuda or not x.is_contiguous() or x.dim() != 2:
+        raise ValueError("x must be a contiguous 2-D CUDA tensor of bf16 or fp32")
+    rows = x.shape[0] if gather is None else gather.numel()
+    width = x.shape[1]
+    q = torch.empty((rows, width), dtype=torch.uint8, device=x.device)
+    s = torch.empty((rows, (width + 127) // 128), dtype=torch.float32, device=x.device)
+    if gather is not None:
+        gather = _require(gather, "gather", torch.int32)
+    rc = lib.moe_quantize_rows(x.data_ptr(), 0 if x.dtype == torch.bfloat16 else 1, rows, width, _ptr(gather),
+                               q.data_ptr(), s.data_ptr(), torch.cuda.current_stream(x.device).cuda_stream)
+    _cabi.check("moe_quantize_rows", rc)
+    return q.view(torch.float8_e4m3fn), s
+
+
+def group_rows(ids: torch.Tensor, n_local: int, id_base: int = 0):
+    """Stable grouping of routed rows by expert: (order int64 [n], counts int32 [n_local])."""
+    lib = _cabi.load()
+    ids = _require(ids.reshape(-1), "ids", torch.int64)
+    n = ids.numel()
+    order = torch.empty((max(n, 1),), dtype=torch.int64, device=ids.device)
+    counts = torch.empty((n_local + 1,), dtype=torch.int32, device=ids.device)
+    rc = lib.moe_group_rows(ids.data_ptr(), n, id_base, n_local, order.data_ptr(), counts.data_ptr(),
+                            torch.cuda.current_stream(ids.device).cuda_stream)
+    _cabi.check("moe_group_rows", rc)
+    return order[:n], counts[:n_local]
