@@ -1,0 +1,78 @@
+"""Shared helpers of the parity tests: geometries, audited seeds, tolerances."""
+
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+
+from oracle import moe_oracle as O
+from vibe_megakernel_b200 import synthetic
+
+# A routing decision is "safe" when every boundary gap, computed from fp64 logits, is far above
+# the noise of an fp32 GEMV (about 1e-6 at these magnitudes).
+MARGIN = 2e-5
+# Layer output tolerance: max-abs 2e-2 where the oracle's output is at most 1 in magnitude, else
+# 2e-2 of the oracle's largest magnitude (one bf16 ulp there), and cosine similarity above 0.999.
+Y_ATOL = 2e-2
+Y_COS = 0.999
+
+
+def spec_of(geo) -> O.LayerSpec:
+    return O.LayerSpec(geo.hidden, geo.inter, geo.experts, geo.topk, geo.shared, geo.scoring,
+                       geo.n_group, geo.topk_group, geo.scaling)
+
+
+def small_geometries():
+    g = synthetic.GEOMETRIES
+    return {
+        "tiny": g["tiny"],
+        "ds_small": dataclasses.replace(g["deepseek_v3"], name="ds_small", hidden=512, inter=256, experts=32, topk=4,
+                                        n_group=4, topk_group=2),
+        "qwen_small": dataclasses.replace(g["qwen3_30b_a3b"], name="qwen_small", hidden=256, inter=128, experts=8,
+                                          topk=2),
+        "kimi_small": dataclasses.replace(g["kimi_k2"], name="kimi_small", hidden=1024, inter=384, experts=48, topk=8,
+                                          router_std=1024 ** -0.5),
+        "mixtral_small": dataclasses.replace(g["mixtral_8x7b"], name="mixtral_small", hidden=512, inter=1792,
+                                             experts=8, topk=2),
+    }
+
+
+def audited_inputs(geo, tokens: int, device="cpu", first_seed: int = 0, max_tries: int = 16):
+    """Seeded inputs whose routing margins pass the audit; returns (values, seed)."""
+    spec = spec_of(geo)
+    for seed in range(first_seed, first_seed + max_tries):
+        values = synthetic.make_inputs(geo, tokens, seed, device)
+        if O.decision_margins(spec, values["x"], values["router"], values.get("router_bias")) >= MARGIN:
+            return values, seed
+    raise AssertionError("no seed passed the routing margin audit")
+
+
+def audited_routing_inputs(geo, tokens: int, device="cpu", first_seed: int = 0, max_tries: int = 16):
+    """Only x, router and bias (cheap at full geometry)."""
+    spec = spec_of(geo)
+    for seed in range(first_seed, first_seed + max_tries):
+        x = synthetic.normal_rows(seed, "x", tokens, geo.hidden, 1.0, device).to(torch.bfloat16)
+        router = synthetic.normal_rows(seed, "router", geo.experts, geo.hidden, geo.router_std, device)
+        bias = synthetic.router_bias(geo, seed, device)
+        if O.decision_margins(spec, x, router, bias) >= MARGIN:
+            return x, router, bias, seed
+    raise AssertionError("no seed passed the routing margin audit")
+
+
+def to_device(values: dict, device) -> dict:
+    return {k: v.to(device) for k, v in values.items()}
+
+
+def y_error(got: torch.Tensor, want: torch.Tensor):
+    g, w = got.double().flatten().cpu(), want.double().flatten().cpu()
+    max_abs = float((g - w).abs().max())
+    cos = float(torch.dot(g, w) / (g.norm() * w.norm() + 1e-300))
+    bound = Y_ATOL * max(1.0, float(w.abs().max()))
+    return max_abs, cos, bound
+
+
+def assert_y_close(got: torch.Tensor, want: torch.Tensor, what: str = "y"):
+    max_abs, cos, bound = y_error(got, want)
+    assert max_abs <= bound and cos > Y_COS, f"{what}: max-abs {max_abs:.4g} (bound {bound:.4g}), cosine {cos:.6f}"
+    return max_abs, cos

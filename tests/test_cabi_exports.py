@@ -1,0 +1,56 @@
+"""CPU checks of the boundary: the library builds, loads and exports what include/moe_b200.h declares."""
+
+import ctypes as C
+import re
+from pathlib import Path
+
+from vibe_megakernel_b200 import _cabi
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def declared_functions():
+    text = (ROOT / "include" / "moe_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\bint\s+(moe_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _cabi.load()
+    names = declared_functions()
+    assert names, "no declarations found"
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared but not exported"
+    assert sorted(_cabi.EXPORTS) == names, "ctypes binding and header disagree"
+
+
+def test_struct_sizes_match_the_header():
+    # 12 four-byte fields; 14 pointers; 16 uint64 + 4 int32
+    assert C.sizeof(_cabi.Config) == 48
+    assert C.sizeof(_cabi.Weights) == 14 * C.sizeof(C.c_void_p)
+    assert C.sizeof(_cabi.Layout) == 16 * 8 + 16
+
+
+def test_workspace_layout_and_argument_checks_need_no_gpu():
+    lib = _cabi.load()
+    cfg = _cabi.Config(7168, 2048, 256, 8, 1, 1, 8, 4, 2.5, 1, 0, 0)
+    lay = _cabi.Layout()
+    assert lib.moe_workspace_layout(C.byref(cfg), 64, C.byref(lay)) == 0
+    assert lay.rows == 64 * 9 and lay.token_tile == 64
+    offsets = [getattr(lay, n) for n in _cabi.LAYOUT_OFFSETS[1:]]
+    assert offsets == sorted(offsets) and all(o % 256 == 0 for o in offsets)
+    assert lay.total_bytes >= lay.slots + 2 * lay.rows * 7168
+    assert lib.moe_workspace_layout(C.byref(cfg), 1, C.byref(lay)) == 0 and lay.token_tile == 16
+    bad = _cabi.Config(7000, 2048, 256, 8, 1, 1, 8, 4, 2.5, 1, 0, 0)
+    assert lib.moe_workspace_layout(C.byref(bad), 64, None) == -2
+    bad = _cabi.Config(7168, 2048, 256, 8, 1, 1, 7, 4, 2.5, 1, 0, 0)      # groups must divide experts
+    assert lib.moe_workspace_layout(C.byref(bad), 64, None) == -1
+    bad = _cabi.Config(7168, 2048, 256, 8, 2, 1, 8, 4, 2.5, 1, 0, 0)      # at most one shared expert
+    assert lib.moe_workspace_layout(C.byref(bad), 64, None) == -2
+    assert lib.moe_workspace_layout(None, 64, None) == -1
+    assert lib.moe_layer_forward(C.byref(cfg), None, None, 64, None, None, None, None, None, 0, None) == -1
+
+
+def test_product_does_not_import_the_oracle():
+    for path in (ROOT / "vibe_megakernel_b200").rglob("*.py"):
+        assert "oracle" not in path.read_text().replace("the oracle", ""), path

@@ -1,0 +1,156 @@
+"""GPU parity of the whole layer (through the C ABI) against the oracle and the golden vectors."""
+
+import dataclasses
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+from tests import helpers as H
+from vibe_megakernel_b200 import synthetic
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def api():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from vibe_megakernel_b200 import layer
+    return layer
+
+
+def run_layer(api, geo, values_cpu, gemm="tcgen05"):
+    tokens = values_cpu["x"].shape[0]
+    layer = api.MoeLayer(api.LayerConfig.from_geometry(geo, gemm=gemm), max_tokens=tokens)
+    values = H.to_device(values_cpu, "cuda")
+    before = {k: v.clone() for k, v in values.items()}
+    out = layer.forward(values, check_status=True)
+    for k, v in values.items():
+        assert torch.equal(v.view(torch.uint8), before[k].view(torch.uint8)), f"input {k} was modified"
+    return layer, out
+
+
+def check_against_oracle(api, geo, values, gemm):
+    want = O.moe_layer(H.spec_of(geo), values, keep_intermediates=True)
+    layer, out = run_layer(api, geo, values, gemm)
+    tokens = values["x"].shape[0]
+    assert torch.equal(out["expert_ids"].cpu(), want["expert_ids"])
+    assert torch.equal(out["order"].cpu(), want["order"])
+    torch.testing.assert_close(out["topk_weights"].cpu(), want["topk_weights"], rtol=2e-5, atol=1e-7)
+    # grouped activation rows: the quantiser is bit-exact
+    routed = tokens * geo.topk
+    src = torch.div(want["order"], geo.topk, rounding_mode="floor")
+    xq = layer.scratch(tokens, "xq").cpu()
+    xs = layer.scratch(tokens, "xs").cpu()
+    assert torch.equal(xq[:routed], want["xq"].view(torch.uint8)[src])
+    assert torch.equal(xs[:routed], want["xs"][src])
+    if geo.shared:
+        assert torch.equal(xq[routed:], want["xq"].view(torch.uint8))
+    # requantised SwiGLU output. The tensor cores multiply the exact e4m3 values, the oracle
+    # multiplies operands rounded to bf16, so gate/up differ by about one bf16 ulp and a share of
+    # the e4m3 codes (3 mantissa bits) lands one step away; the dequantised values stay close.
+    aq = layer.scratch(tokens, "aq").cpu()
+    a_s = layer.scratch(tokens, "as").cpu()
+    start, num, den = 0, 0.0, 0.0
+    for e, n in enumerate(want["counts"].tolist()):
+        if n:
+            ref_q, ref_s = want["requant"][e]
+            ref = O.dequantize_activation(ref_q, ref_s).double()
+            got = O.dequantize_activation(aq[start:start + n].view(torch.float8_e4m3fn), a_s[start:start + n]).double()
+            num += float(((got - ref) ** 2).sum())
+            den += float((ref ** 2).sum())
+            torch.testing.assert_close(a_s[start:start + n], ref_s, rtol=0.04, atol=1e-9)
+            start += n
+    assert num <= (0.05 ** 2) * den, f"requantised SwiGLU output: relative L2 error {(num / max(den, 1e-300)) ** 0.5:.4f}"
+    return H.assert_y_close(out["y"], want["y"])
+
+
+@pytest.mark.parametrize("gemm", ["simt", "tcgen05"])
+@pytest.mark.parametrize("name", ["tiny", "ds_small", "qwen_small", "kimi_small", "mixtral_small"])
+def test_small_layers_match_the_oracle(api, name, gemm):
+    geo = H.small_geometries()[name]
+    for tokens in (1, 4, 19, 40):
+        values, _ = H.audited_inputs(geo, tokens)
+        check_against_oracle(api, geo, values, gemm)
+
+
+def test_tiny_layer_matches_the_reference_vectors(api, golden_dir):
+    g = np.load(golden_dir / "layers.npz")
+    for name in ("tiny", "ds_small", "qwen_small"):
+        geo = H.small_geometries()[name]
+        tokens, seed = int(g[f"{name}_geo"][7]), int(g[f"{name}_geo"][8])
+        values = synthetic.make_inputs(geo, tokens, seed, "cpu")
+        _, out = run_layer(api, geo, values)
+        assert np.array_equal(out["expert_ids"].cpu().numpy(), g[f"{name}_ids"])
+        assert np.array_equal(out["order"].cpu().numpy(), g[f"{name}_order"])
+        want = torch.from_numpy(g[f"{name}_y"].copy()).view(torch.bfloat16)
+        H.assert_y_close(out["y"], want, name)
+
+
+def test_tensor_core_and_check_arm_agree(api):
+    geo = H.small_geometries()["kimi_small"]
+    values, _ = H.audited_inputs(geo, 40)
+    _, a = run_layer(api, geo, values, "tcgen05")
+    _, b = run_layer(api, geo, values, "simt")
+    diff = (a["y"].float() - b["y"].float()).abs().max().item()
+    assert diff <= 2 * 2e-2, diff
+
+
+def test_run_twice_is_bit_identical_and_depends_on_every_input(api):
+    geo = H.small_geometries()["ds_small"]
+    values, _ = H.audited_inputs(geo, 19)
+    layer, first = run_layer(api, geo, values)
+    again = layer.forward(H.to_device(values, "cuda"), check_status=True)
+    for k in first:
+        assert torch.equal(first[k], again[k]), k
+    for name in values:
+        changed = {k: v.clone() for k, v in values.items()}
+        t = changed[name]
+        if t.dtype == torch.float8_e4m3fn:
+            raw = t.view(torch.uint8)
+            raw ^= 0x11                      # as megabench/verify_megamoe.py:112-115
+        elif name == "router_bias":
+            t += torch.linspace(-0.3, 0.3, t.numel())
+        else:
+            t *= 1.5
+        other = layer.forward(H.to_device(changed, "cuda"), check_status=True)
+        assert not torch.equal(first["y"], other["y"]), f"output ignores {name}"
+
+
+def test_experts_with_no_rows_and_one_hot_routing(api):
+    # a bias that sends every token to the same experts leaves all others empty
+    geo = dataclasses.replace(H.small_geometries()["ds_small"], n_group=1, topk_group=1)
+    values, _ = H.audited_inputs(geo, 40)
+    values["router_bias"] = torch.zeros(geo.experts)
+    values["router_bias"][[3, 7, 8, 30]] = torch.tensor([4.0, 3.0, 2.0, 1.0])
+    want = O.moe_layer(H.spec_of(geo), values)
+    assert want["expert_ids"].tolist() == [[3, 7, 8, 30]] * 40
+    _, out = run_layer(api, geo, values)
+    assert torch.equal(out["expert_ids"].cpu(), want["expert_ids"])
+    assert torch.equal(out["order"].cpu(), want["order"])
+    H.assert_y_close(out["y"], want["y"])
+
+
+def test_bad_arguments_are_refused(api):
+    geo = H.small_geometries()["tiny"]
+    values, _ = H.audited_inputs(geo, 4)
+    layer = api.MoeLayer(api.LayerConfig.from_geometry(geo), max_tokens=4)
+    dev = H.to_device(values, "cuda")
+    with pytest.raises(TypeError):
+        layer.forward(dev | {"x": dev["x"].float()})
+    with pytest.raises(ValueError):
+        layer.forward(dev | {"gate": dev["gate"][:, :, :-128].contiguous()})
+    with pytest.raises(ValueError):
+        layer.forward(dev | {"x": values["x"]})
+    from vibe_megakernel_b200 import _cabi
+    with pytest.raises(_cabi.MoeError):
+        api.MoeLayer(api.LayerConfig(hidden=100, inter=128, experts=8, topk=2), max_tokens=1)
+
+
+@pytest.mark.parametrize("name,tokens", [("qwen_small", 300), ("mixtral_small", 257), ("ds_small", 128)])
+def test_experts_with_more_rows_than_one_tile(api, name, tokens):
+    geo = H.small_geometries()[name]
+    values, _ = H.audited_inputs(geo, tokens)
+    check_against_oracle(api, geo, values, "tcgen05")

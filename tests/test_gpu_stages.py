@@ -1,0 +1,112 @@
+"""GPU parity of the single stages (through the C ABI) against the oracle and the golden vectors."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+from tests import helpers as H
+from vibe_megakernel_b200 import synthetic
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def api():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from vibe_megakernel_b200 import layer
+    return layer
+
+
+def bf16(bits):
+    return torch.from_numpy(bits.copy()).view(torch.bfloat16)
+
+
+# ---------------------------------------------------------------- quantiser
+def test_quantiser_matches_reference_vectors(api, golden_dir):
+    g = np.load(golden_dir / "quantizers.npz")
+    for key_in, key_q, key_s, as_bf16 in (("w_in", "wa_q_0", "wa_s_0", True), ("a_in", "a_q_0", "a_s_0", True),
+                                          ("e_in", "ef_q", "ef_s", False), ("f_in", "f_q", "f_s", False)):
+        x = bf16(g[key_in]) if as_bf16 else torch.from_numpy(g[key_in])
+        q, s = api.quantize_rows(x.cuda().contiguous())
+        assert np.array_equal(q.view(torch.uint8).cpu().numpy(), g[key_q]), key_in
+        assert np.array_equal(s.cpu().numpy(), g[key_s]), key_in
+
+
+@pytest.mark.parametrize("rows,width,dtype", [(1, 128, torch.bfloat16), (7, 7168, torch.bfloat16),
+                                              (33, 2048, torch.float32), (5, 259, torch.float32),
+                                              (3, 1, torch.bfloat16), (130, 384, torch.bfloat16)])
+def test_quantiser_matches_oracle(api, rows, width, dtype):
+    gen = torch.Generator().manual_seed(rows * 1000 + width)
+    x = (torch.randn((rows, width), generator=gen) * torch.logspace(-5, 2, rows)[:, None]).to(dtype)
+    x[0, : min(width, 4)] = 0
+    q, s = api.quantize_rows(x.cuda())
+    wq, ws = O.quantize_activation(x)
+    assert torch.equal(q.view(torch.uint8).cpu(), wq.view(torch.uint8))
+    assert torch.equal(s.cpu(), ws)
+
+
+def test_quantiser_gather(api):
+    x = torch.randn((9, 512), generator=torch.Generator().manual_seed(4)).to(torch.bfloat16)
+    idx = torch.tensor([8, 0, 0, 3, 5, 5, 5, 1], dtype=torch.int32)
+    q, s = api.quantize_rows(x.cuda(), idx.cuda())
+    wq, ws = O.quantize_activation(x[idx.long()])
+    assert torch.equal(q.view(torch.uint8).cpu(), wq.view(torch.uint8)) and torch.equal(s.cpu(), ws)
+
+
+# ---------------------------------------------------------------- permutation
+@pytest.mark.parametrize("n,experts,kind", [(32, 16, "random"), (1024, 256, "random"), (8192, 384, "random"),
+                                            (4096, 8, "random"), (64, 16, "one"), (8, 256, "random"),
+                                            (513, 128, "skew"), (1, 4, "random")])
+def test_grouping_is_the_stable_sort(api, n, experts, kind):
+    gen = torch.Generator().manual_seed(n + experts)
+    if kind == "random":
+        ids = torch.randint(0, experts, (n,), generator=gen)
+    elif kind == "one":
+        ids = torch.full((n,), 5, dtype=torch.int64)
+    else:
+        ids = (torch.rand((n,), generator=gen) ** 4 * experts).long().clamp(max=experts - 1)
+    order, counts = api.group_rows(ids.cuda(), experts)
+    want_order, want_counts = O.expert_order(ids, experts)
+    assert torch.equal(order.cpu(), want_order)
+    assert torch.equal(counts.cpu().long(), want_counts)
+
+
+def test_grouping_keeps_only_local_experts(api):
+    gen = torch.Generator().manual_seed(9)
+    ids = torch.randint(0, 64, (500,), generator=gen)
+    order, counts = api.group_rows(ids.cuda(), 16, id_base=32)     # experts 32..47 live here
+    mine = ((ids >= 32) & (ids < 48)).nonzero().flatten()
+    want = mine[torch.sort(ids[mine], stable=True).indices]
+    assert torch.equal(order.cpu()[: want.numel()], want)
+    assert bool((order.cpu()[want.numel():] == -1).all())
+    assert torch.equal(counts.cpu().long(), torch.bincount(ids[mine] - 32, minlength=16))
+
+
+# ---------------------------------------------------------------- router
+@pytest.mark.parametrize("name,tokens", [("tiny", 4), ("deepseek_v3", 1), ("deepseek_v3", 64), ("deepseek_v3", 128),
+                                         ("kimi_k2", 64), ("qwen3_30b_a3b", 37), ("mixtral_8x7b", 16)])
+def test_router_ids_are_bit_exact(api, name, tokens):
+    geo = synthetic.GEOMETRIES[name]
+    x, router, bias, seed = H.audited_routing_inputs(geo, tokens)
+    layer = api.MoeLayer(api.LayerConfig.from_geometry(geo), max_tokens=tokens)
+    ids, w = layer.route(x.cuda(), router.cuda(), None if bias is None else bias.cuda())
+    want_ids, want_w = O.route_tokens(H.spec_of(geo), x, router, bias)
+    assert torch.equal(ids.cpu(), want_ids), f"seed {seed}"
+    torch.testing.assert_close(w.cpu(), want_w, rtol=2e-5, atol=1e-7)
+
+
+def test_router_ties_go_to_the_lower_index(api):
+    # all-zero logits: megabench/tests/test_frontier.py:297-299 expects ids [0, 1], weights 1.25
+    cfg = api.LayerConfig(hidden=128, inter=128, experts=8, topk=2, shared=0, scoring="sigmoid", n_group=2,
+                          topk_group=1, scaling=2.5)
+    layer = api.MoeLayer(cfg, max_tokens=3)
+    x = torch.zeros((3, 128), dtype=torch.bfloat16, device="cuda")
+    router = torch.zeros((8, 128), device="cuda")
+    ids, w = layer.route(x, router, torch.zeros(8, device="cuda"))
+    assert ids.cpu().tolist() == [[0, 1]] * 3
+    assert w.cpu().tolist() == [[1.25, 1.25]] * 3
+    cfg = api.LayerConfig(hidden=128, inter=128, experts=8, topk=3, shared=0, scoring="softmax")
+    ids, w = api.MoeLayer(cfg, max_tokens=3).route(x, router, None)
+    assert ids.cpu().tolist() == [[0, 1, 2]] * 3
