@@ -1,0 +1,353 @@
+"""Benchmark of the FP8 MoE decode layer.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--config deepseek_v3] [--batch 64] [--no-sweep]
+
+A step is one layer call over one batch of seeded synthetic tokens (weights and activations
+follow the benchmark's distributions; there is no dataset). One JSON line is printed by rank 0.
+
+  value        layer latency in microseconds, inputs resident in HBM, CUDA events per step,
+               L2 flushed between steps (max over ranks when N > 1)
+  e2e          the same call through the plugin API with x in pinned host memory: host->device
+               copy of x, layer, device->host copy of y, all inside the timed region
+  roofline     the gate/up grouped GEMM kernel: algorithmic bytes / its event-timed duration
+  cpu_baseline the CPU oracle (a port of the reference's Python) on the host cores, bounded sample
+  sweep        latency / achieved GB/s for the other batch sizes of the configuration
+
+`--impl reference` times the CPU oracle alone (the reference has no implementation of this path
+other than its PyTorch code, which the oracle restates) with all host threads.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+from vibe_megakernel_b200 import synthetic  # noqa: E402
+
+METRIC = "fp8_moe_decode_layer_latency_us"
+L2_FLUSH_BYTES = 512 << 20
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--config", default="deepseek_v3", choices=sorted(synthetic.GEOMETRIES))
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sample-tokens", type=int, default=1, help="tokens per CPU-oracle step")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        d = json.loads(path.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.file = None
+
+    def __enter__(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        if self.proc is None or self.file is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.file.flush()
+        rows = [r.split(",") for r in Path(self.file.name).read_text().splitlines() if r.count(",") >= 6]
+        os.unlink(self.file.name)
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = sorted(float(r[0]) for r in rows)
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].strip() == "Active" for r in rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(rows[0][1]), "samples": len(rows),
+                "power_w_max": max(float(r[2]) for r in rows), "reasons": reasons}
+
+
+def layer_case(geo, tokens: int) -> dict:
+    """The case dict the plugin's build() takes (layout of the reference's Case.to_dict())."""
+    return {"id": f"fp8-moe-layer-{geo.name}-b{tokens}", "family": "fp8_moe_layer", "model": geo.name,
+            "phase": "moe_layer", "gpus": 1, "tp": 1, "ep": 1,
+            "params": {"tokens": tokens, "hidden": geo.hidden, "intermediate": geo.inter, "experts": geo.experts,
+                       "topk": geo.topk, "shared_experts": geo.shared, "router_groups": geo.n_group,
+                       "router_top_groups": geo.topk_group},
+            "moe": {"scoring": geo.scoring, "scaling": geo.scaling}}
+
+
+def timed_steps(fn, steps: int, warmup: int, flush: torch.Tensor, barrier=None) -> list[float]:
+    """Per-step device times in ms: L2 is flushed (a 512 MiB write) before every step, outside its events."""
+    for _ in range(warmup):
+        flush.zero_()
+        fn()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    pairs = []
+    for _ in range(steps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        pairs.append((a, b))
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    return [a.elapsed_time(b) for a, b in pairs]
+
+
+def gate_up_bytes(geo, distinct: int) -> int:
+    """Algorithmic bytes of one gate/up GEMM launch: payload and block scales of gate and up of every
+    expert that is hit (and of the shared expert)."""
+    per_expert = 2 * geo.inter * geo.hidden + 8 * (geo.inter // 128) * (geo.hidden // 128)
+    return (distinct + geo.shared) * per_expert
+
+
+def cpu_oracle_sample(geo, values: dict, sample_tokens: int, distinct_full: int, threads: int, repeats: int = 1):
+    """Time the CPU oracle on the first ``sample_tokens`` tokens; returns (seconds per sample step,
+    scaled microseconds for the full batch, description)."""
+    from oracle import moe_oracle as O
+    torch.set_num_threads(threads)
+    spec = O.LayerSpec(geo.hidden, geo.inter, geo.experts, geo.topk, geo.shared, geo.scoring, geo.n_group,
+                       geo.topk_group, geo.scaling)
+    x = values["x"][:sample_tokens].cpu()
+    router = values["router"].cpu()
+    bias = values["router_bias"].cpu() if "router_bias" in values else None
+    ids, _ = O.route_tokens(spec, x, router, bias)
+    hit = sorted(set(ids.flatten().tolist()))
+    slot = {e: k for k, e in enumerate(hit)}
+    index = torch.tensor(hit, device=values["gate"].device)
+    host = {"x": x, "router": router}
+    if bias is not None:
+        host["router_bias"] = bias
+    for name in ("gate", "up", "down"):
+        host[name] = values[name][index].cpu()
+        host[name + "_scale"] = values[name + "_scale"][index].cpu()
+    for name in values:
+        if name.startswith("shared_"):
+            host[name] = values[name].cpu()
+    O.moe_layer(spec, host, expert_slot=slot)              # warm-up
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        O.moe_layer(spec, host, expert_slot=slot)
+    per_step = (time.perf_counter() - t0) / repeats
+    scale = (distinct_full + geo.shared) / (len(hit) + geo.shared)
+    what = (f"oracle layer pass on the first {sample_tokens} token(s) of the batch ({len(hit)} routed experts + "
+            f"{geo.shared} shared, whole-matrix dequantisation per expert as the reference does), {per_step:.2f} s per "
+            f"pass; scaled x{scale:.2f} by experts hit to the full batch")
+    return per_step, per_step * scale * 1e6, what
+
+
+def measure_batch(geo, values: dict, tokens: int, steps: int, warmup: int, flush, peak: float, *, full: bool):
+    """Latency, stage times and roofline figures of one batch size on this GPU."""
+    from vibe_megakernel_b200 import submission
+    from vibe_megakernel_b200.layer import LayerConfig, MoeLayer
+    inputs = dict(values)
+    inputs["x"] = values["x"][:tokens].contiguous()
+    layer = MoeLayer(LayerConfig.from_geometry(geo), max_tokens=tokens)
+    out = layer.forward(inputs, check_status=True)
+    distinct = int(torch.unique(out["expert_ids"]).numel())
+    launches = layer.launches()
+    ms = timed_steps(lambda: layer.forward(inputs), steps, warmup, flush)
+    layer.check_device_status(tokens)
+    latency_us = 1e3 * sum(ms) / len(ms)
+    # stage times: separate profiled passes, same inputs and flush protocol
+    layer.profile(True)
+    stages = {k: 0.0 for k in MoeLayer.STAGES}
+    reps = max(3, min(steps, 10))
+    for _ in range(reps):
+        flush.zero_()
+        layer.forward(inputs)
+        for k, v in layer.stage_ms().items():
+            stages[k] += v / reps
+    layer.profile(False)
+    total_bytes = synthetic.algorithmic_bytes(geo, tokens, distinct)
+    g_bytes = gate_up_bytes(geo, distinct)
+    g_gbs = g_bytes / (stages["gate_up_gemm"] * 1e-3) / 1e9
+    res = {"batch": tokens, "latency_us": round(latency_us, 2), "min_us": round(1e3 * min(ms), 2),
+           "distinct_experts": distinct, "algorithmic_bytes": total_bytes,
+           "layer_gbs": round(total_bytes / (latency_us * 1e-6) / 1e9, 1),
+           "layer_frac_of_measured_peak": round(total_bytes / (latency_us * 1e-6) / 1e9 / peak, 4),
+           "layer_frac_of_8tbs": round(total_bytes / (latency_us * 1e-6) / 1e9 / 8000.0, 4),
+           "stage_us": {k: round(v * 1e3, 2) for k, v in stages.items()},
+           "gate_up_gbs": round(g_gbs, 1), "launches": launches}
+    if not full:
+        return res, None
+    # end to end through the plugin API: x starts in pinned host memory, y ends there
+    run = submission.build(layer_case(geo, tokens))
+    x_host = inputs["x"].cpu().pin_memory()
+    y_host = torch.empty_like(x_host).pin_memory()
+    x_dev = torch.empty_like(inputs["x"])
+    e2e_inputs = dict(inputs)
+    e2e_inputs["x"] = x_dev
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        y_host.copy_(run(e2e_inputs)["y"], non_blocking=True)
+
+    e2e_ms = timed_steps(e2e_step, steps, warmup, flush)
+    assert torch.equal(y_host, out["y"].cpu()), "plugin path and direct path disagree"
+    extra = {"ms": ms, "e2e_us": 1e3 * sum(e2e_ms) / len(e2e_ms), "io_bytes": x_host.numel() * 2,
+             "gate_up_ms": stages["gate_up_gemm"], "gate_up_bytes": g_bytes, "distinct": distinct,
+             "launches": launches}
+    return res, extra
+
+
+def main_single(args) -> dict:
+    geo = synthetic.GEOMETRIES[args.config]
+    peak, peak_kind = measured_peaks()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    batches = sorted(set(synthetic.BATCHES[args.config]) | {args.batch})
+    t0 = time.time()
+    values = synthetic.make_inputs(geo, max(batches), args.seed, dev)
+    torch.cuda.synchronize()
+    gen_s = time.time() - t0
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    sweep = []
+    with ClockSampler(0) as clocks:      # covers the headline batch and the sweep
+        head, extra = measure_batch(geo, values, args.batch, args.steps, args.warmup, flush, peak, full=True)
+        if not args.no_sweep:
+            for b in batches:
+                if b == args.batch:
+                    sweep.append(head)
+                else:
+                    sweep.append(measure_batch(geo, values, b, max(5, args.steps // 2), 3, flush, peak, full=False)[0])
+    clock_summary = clocks.summary()
+    line = {
+        "metric": METRIC, "value": head["latency_us"], "unit": "us", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(head["latency_us"] / 1e3, 5), "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": f"{geo.name} FP8 MoE decode layer, batch {args.batch}: H={geo.hidden} I={geo.inter} "
+                               f"E={geo.experts}+{geo.shared} top{geo.topk} {geo.scoring}",
+                   "batch": args.batch, "seed": args.seed, "l2": "flushed between steps (512 MiB write)",
+                   "e2e_io": "x bf16 host->device and y bf16 device->host per step; weights resident in HBM",
+                   "input_generation_s": round(gen_s, 1)},
+        "e2e": {"value": round(extra["e2e_us"], 2), "unit": "us", "h2d_bytes_per_step": extra["io_bytes"],
+                "d2h_bytes_per_step": extra["io_bytes"]},
+        "gpu_launches": extra["launches"] * args.steps,
+        "launches_per_step": extra["launches"],
+        "clocks": clock_summary,
+        "roofline": {"bound": "hbm", "kernel": "grouped_gemm_kernel<dual> (gate/up GEMM + SwiGLU + requantisation)",
+                     "achieved": round(extra["gate_up_bytes"] / (extra["gate_up_ms"] * 1e-3) / 1e9, 1), "peak": peak,
+                     "unit": "GB/s", "frac": round(extra["gate_up_bytes"] / (extra["gate_up_ms"] * 1e-3) / 1e9 / peak, 4),
+                     "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "algorithmic_bytes_per_launch": extra["gate_up_bytes"],
+                     "kernel_us": round(extra["gate_up_ms"] * 1e3, 2)},
+        "layer": {k: head[k] for k in ("distinct_experts", "algorithmic_bytes", "layer_gbs",
+                                       "layer_frac_of_measured_peak", "layer_frac_of_8tbs", "stage_us")},
+        "sweep": sweep,
+    }
+    if not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        per_step, scaled_us, what = cpu_oracle_sample(geo, values, args.sample_tokens, extra["distinct"], threads)
+        line["cpu_baseline"] = {"value": round(scaled_us, 1), "unit": "us", "cores": threads, "kind": "port",
+                                "sample": what}
+    return line
+
+
+def main_reference(args) -> dict | None:
+    """The reference's CPU implementation of the path: the oracle port, all host threads, rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return None
+    from oracle import moe_oracle as O
+    geo = synthetic.GEOMETRIES[args.config]
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    spec = O.LayerSpec(geo.hidden, geo.inter, geo.experts, geo.topk, geo.shared, geo.scoring, geo.n_group,
+                       geo.topk_group, geo.scaling)
+    # routing of the full batch decides how many experts a full pass would touch
+    x = synthetic.normal_rows(args.seed, "x", args.batch, geo.hidden, 1.0, "cpu").to(torch.bfloat16)
+    router = synthetic.normal_rows(args.seed, "router", geo.experts, geo.hidden, geo.router_std, "cpu")
+    bias = synthetic.router_bias(geo, args.seed, "cpu")
+    ids, _ = O.route_tokens(spec, x, router, bias)
+    distinct_full = int(torch.unique(ids).numel())
+    hit = sorted(set(ids[:args.sample_tokens].flatten().tolist()))
+    values = synthetic.make_inputs(geo, args.batch, args.seed, "cpu", experts=hit)
+    values["x"] = values["x"][:args.sample_tokens]
+    slot = {e: k for k, e in enumerate(hit)}
+    for _ in range(min(args.warmup, 1)):
+        O.moe_layer(spec, values, expert_slot=slot)
+    times = []
+    budget = time.time() + 150
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        O.moe_layer(spec, values, expert_slot=slot)
+        times.append(time.perf_counter() - t0)
+        if time.time() > budget:
+            break
+    scale = (distinct_full + geo.shared) / (len(hit) + geo.shared)
+    value = sum(times) / len(times) * scale * 1e6
+    what = (f"each step = oracle layer pass on the first {args.sample_tokens} token(s) of the batch ({len(hit)} routed "
+            f"experts + {geo.shared} shared), {sum(times) / len(times):.2f} s; value scaled x{scale:.2f} by experts hit "
+            f"({distinct_full} distinct at batch {args.batch}); {len(times)} of {args.steps} steps ran inside the time bound")
+    return {"impl": "reference", "metric": METRIC, "value": round(value, 1), "unit": "us", "n_gpus": args.gpus,
+            "steps": len(times), "warmup": min(args.warmup, 1), "ms_per_step": round(value / 1e3, 3),
+            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate), CPU",
+            "data": "synthetic",
+            "config": {"workload": f"{geo.name} FP8 MoE decode layer, batch {args.batch}", "batch": args.batch,
+                       "seed": args.seed},
+            "cpu_baseline": {"value": round(value, 1), "unit": "us", "cores": threads, "kind": "port", "sample": what},
+            "e2e": {"value": round(value, 1), "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        line = main_reference(args)
+    elif args.gpus == 1:
+        line = main_single(args)
+    else:
+        from vibe_megakernel_b200 import ep_bench
+        line = ep_bench.run(args)
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

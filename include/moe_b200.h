@@ -143,6 +143,14 @@ int moe_device_status(const void* workspace, void* stream, int32_t* detail);
 /* Number of kernels the last moe_layer_forward call on this thread launched. */
 int moe_last_launch_count(void);
 
+/* Stage timing for measurements (no counterpart in the reference, whose harness times whole calls
+ * with torch.cuda.Event, megabench/harness/benchmark.py:27-38). While enabled, moe_layer_forward
+ * records CUDA events on its stream between stages; moe_profile_read waits for the last call and
+ * returns the six stage durations in milliseconds: router, permutation, quantiser, gate/up GEMM,
+ * down GEMM, combine. Per calling thread. */
+int moe_profile_enable(int32_t on);
+int moe_profile_read(float* stage_ms, int32_t n);
+
 #ifdef __cplusplus
 }
 #endif

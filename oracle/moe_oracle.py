@@ -239,7 +239,8 @@ def expert_mlp(rows_q, rows_s, gate, gate_s, up, up_s, down, down_s, *, compute=
     return back @ wd.T, aq, a_s
 
 
-def moe_layer(spec: LayerSpec, values: dict, *, compute=torch.bfloat16, keep_intermediates: bool = False):
+def moe_layer(spec: LayerSpec, values: dict, *, compute=torch.bfloat16, keep_intermediates: bool = False,
+              expert_slot: dict | None = None):
     """Whole layer on one rank holding every expert.
 
     values: x bf16 [T,H]; router fp32 [E,H]; router_bias fp32 [E] (sigmoid);
@@ -250,6 +251,8 @@ def moe_layer(spec: LayerSpec, values: dict, *, compute=torch.bfloat16, keep_int
     Output keys: y bf16 [T,H]; expert_ids int64 [T,topk] (choice order);
     topk_weights fp32 [T,topk]; order int64 [T*topk] (stable grouping of the
     flattened ids by expert); counts int64 [E].
+    ``expert_slot`` maps an expert id to its index in the weight tensors when only
+    the experts that are hit were materialised (default: identity).
     Combine: fp32 sum over slots in slot order of row*weight, then the shared
     expert's row, one rounding to bf16 (frontier.py:349-354, megamoe.py:176-182).
     """
@@ -269,9 +272,10 @@ def moe_layer(spec: LayerSpec, values: dict, *, compute=torch.bfloat16, keep_int
         sel = order[start:start + n]
         tok = src[start:start + n]
         start += n
-        res, aq, a_s = expert_mlp(xq[tok], xs[tok], values["gate"][e], values["gate_scale"][e],
-                                  values["up"][e], values["up_scale"][e],
-                                  values["down"][e], values["down_scale"][e], compute=compute)
+        k = e if expert_slot is None else expert_slot[e]
+        res, aq, a_s = expert_mlp(xq[tok], xs[tok], values["gate"][k], values["gate_scale"][k],
+                                  values["up"][k], values["up_scale"][k],
+                                  values["down"][k], values["down_scale"][k], compute=compute)
         out_rows[sel] = res
         if keep_intermediates:
             inter[e] = (aq, a_s)

@@ -73,6 +73,33 @@ def y_error(got: torch.Tensor, want: torch.Tensor):
 
 
 def assert_y_close(got: torch.Tensor, want: torch.Tensor, what: str = "y"):
+    """The stated tolerance where outputs are of order one: max-abs 2e-2 and cosine > 0.999."""
     max_abs, cos, bound = y_error(got, want)
     assert max_abs <= bound and cos > Y_COS, f"{what}: max-abs {max_abs:.4g} (bound {bound:.4g}), cosine {cos:.6f}"
     return max_abs, cos
+
+
+# The reference harness' own acceptance band (megabench/harness/correctness.py:64-85 with the
+# defaults of megabench/cases.py:33-38 and the MoE-layer case's atol): the candidate's error
+# against the fp32-widened oracle may reach noise_factor times the bf16 oracle's own error.
+BAND_NOISE_FACTOR = 2.0
+BAND_BF16_RTOL = 0.008
+BAND_ATOL = 0.003
+
+
+def assert_y_in_band(got: torch.Tensor, want: torch.Tensor, exact: torch.Tensor, what: str = "y"):
+    """Tolerance at large output magnitudes (a bf16 ulp of the output alone exceeds 2e-2 there):
+    cosine > 0.999 against the bf16 oracle and the reference harness' band against the fp32 oracle."""
+    g, w, x = got.double().cpu(), want.double().cpu(), exact.double().cpu()
+    err, ref_err = g - x, w - x
+    scale = max(float(x.norm()), 1e-300)
+    rel, ref_rel = float(err.norm()) / scale, float(ref_err.norm()) / scale
+    peak, ref_peak = float(err.abs().max()), float(ref_err.abs().max())
+    cos = float(torch.dot(g.flatten(), w.flatten()) / (g.norm() * w.norm() + 1e-300))
+    ok = (cos > Y_COS and rel <= BAND_NOISE_FACTOR * ref_rel + BAND_BF16_RTOL
+          and peak <= BAND_NOISE_FACTOR * ref_peak + BAND_ATOL + BAND_BF16_RTOL * float(x.abs().max()))
+    detail = (f"{what}: cosine {cos:.6f}, rel-L2 {rel:.5f} (oracle's own {ref_rel:.5f}), max-abs {peak:.4g} "
+              f"(oracle's own {ref_peak:.4g}), max-abs vs bf16 oracle {float((g - w).abs().max()):.4g}, "
+              f"max|y| {float(x.abs().max()):.3g}")
+    assert ok, detail
+    return detail

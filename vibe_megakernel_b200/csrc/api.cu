@@ -9,6 +9,21 @@ namespace {
 
 thread_local int g_last_launches = 0;
 
+// Optional stage timing: events recorded on the launching stream around each stage.
+constexpr int kStages = 6;   // router, permutation, quantiser, gate/up GEMM, down GEMM, combine
+thread_local bool g_profile = false;
+thread_local cudaEvent_t g_events[kStages + 1] = {};
+thread_local bool g_events_ready = false;
+
+void mark(int i, cudaStream_t stream) {
+  if (!g_profile) return;
+  if (!g_events_ready) {
+    for (auto& ev : g_events) cudaEventCreate(&ev);
+    g_events_ready = true;
+  }
+  cudaEventRecord(g_events[i], stream);
+}
+
 inline uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
 
 int check_config(const moe_config_t* c) {
@@ -155,11 +170,13 @@ int moe_layer_forward(const moe_config_t* cfg, const moe_weights_t* w, const voi
   if (e != cudaSuccess) return from_cuda(e);
 
   // 1. router
+  mark(0, stream);
   e = moe::launch_router(*cfg, static_cast<const __nv_bfloat16*>(x_bf16), w->router, w->router_bias, tokens, logits,
                          ids32, tw, expert_ids, topk_weights, stream, &launches);
   if (e != cudaSuccess) return from_cuda(e);
 
   // 2. token -> expert permutation and the work list of the GEMMs
+  mark(1, stream);
   moe::GroupArgs g;
   std::memset(&g, 0, sizeof(g));
   g.ids32 = ids32;
@@ -182,10 +199,12 @@ int moe_layer_forward(const moe_config_t* cfg, const moe_weights_t* w, const voi
   if (e != cudaSuccess) return from_cuda(e);
 
   // 3. activation quantiser, gathering each grouped row from its token
+  mark(2, stream);
   e = moe::launch_quantize(x_bf16, 0, L.rows, cfg->hidden, row_token, xq, xs, stream, &launches);
   if (e != cudaSuccess) return from_cuda(e);
 
   // 4. gate/up GEMM + SwiGLU + requantisation; 5. down GEMM into slot rows
+  mark(3, stream);
   moe::GemmArgs a;
   std::memset(&a, 0, sizeof(a));
   a.tile = L.token_tile;
@@ -213,6 +232,7 @@ int moe_layer_forward(const moe_config_t* cfg, const moe_weights_t* w, const voi
   if (driver_error) return MOE_ERR_DRIVER;
   if (e != cudaSuccess) return from_cuda(e);
 
+  mark(4, stream);
   a.dual = false;
   a.k = cfg->inter;
   a.m = cfg->hidden;
@@ -233,9 +253,24 @@ int moe_layer_forward(const moe_config_t* cfg, const moe_weights_t* w, const voi
   if (e != cudaSuccess) return from_cuda(e);
 
   // 6. weighted combine in slot order, plus the shared expert's row
+  mark(5, stream);
   e = moe::launch_combine(slots, tw, tokens, cfg->topk, cfg->hidden, cfg->n_shared, static_cast<__nv_bfloat16*>(y_bf16),
                           stream, &launches);
+  mark(6, stream);
   g_last_launches = launches;
+  return from_cuda(e);
+}
+
+int moe_profile_enable(int32_t on) {
+  g_profile = on != 0;
+  return MOE_OK;
+}
+
+int moe_profile_read(float* stage_ms, int32_t n) {
+  if (!stage_ms || n < kStages) return MOE_ERR_BAD_ARG;
+  if (!g_events_ready) return MOE_ERR_BAD_ARG;
+  cudaError_t e = cudaEventSynchronize(g_events[kStages]);
+  for (int i = 0; i < kStages && e == cudaSuccess; ++i) e = cudaEventElapsedTime(stage_ms + i, g_events[i], g_events[i + 1]);
   return from_cuda(e);
 }
 

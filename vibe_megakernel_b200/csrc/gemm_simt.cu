@@ -89,9 +89,9 @@ __global__ void __launch_bounds__(128) grouped_gemm_simt_kernel(const SimtDev p)
     }
   }
   if constexpr (DUAL) {
-    epilogue_swiglu_requant<NT>(acc_a, acc_b, m, ch.rows, ch.row0, mt, p.m, s_amax, p.aq, p.as);
+    epilogue_swiglu_requant<NT, 128>(acc_a, acc_b, m, 0, NT, ch.rows, ch.row0, mt, p.m, s_amax, p.aq, p.as);
   } else {
-    epilogue_store_rows<NT>(acc_a, m, ch.rows, ch.row0, mt, p.m, p.row_dest, p.out);
+    epilogue_store_rows<NT>(acc_a, m, 0, ch.rows, ch.row0, mt, p.m, p.row_dest, p.out);
   }
 }
 

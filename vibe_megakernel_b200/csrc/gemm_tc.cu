@@ -1,8 +1,8 @@
 // Persistent grouped FP8 GEMM for the expert MLPs on tcgen05 tensor cores.
 //
 // Orientation: the weights are the MMA's M side (128 output channels per tile) and the tokens
-// of one expert are the N side (16, 32 or 64 per tile), so a decode batch streams every weight
-// byte exactly once through TMA while the token rows stay L2-resident.
+// of one expert are the N side (16 to 64 per tile, in steps of 16), so a decode batch streams
+// every weight byte exactly once through TMA while the token rows stay L2-resident.
 //
 //   D[m, n] = sum_k W[m, k] * X[n, k]       e4m3 x e4m3 -> fp32 in TMEM, kind::f8f6f4
 //
@@ -12,10 +12,13 @@
 // registers as acc += D * (w_scale * x_scale[n]); a second TMEM accumulator stage lets the
 // next K block's MMAs run meanwhile.
 //
-// Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2-5 =
-// epilogue (thread = one TMEM lane = one output channel). Work items (expert, row chunk, channel
-// tile) are taken round-robin by a persistent grid; their list is produced on the device by the
-// permutation kernel, so no host synchronisation is needed between routing and the GEMMs.
+// Roles: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warp 2 = scale loader (stages
+// the next work item's scales in shared memory while the current one is computed), warps 3.. =
+// epilogue (a thread owns one TMEM lane = one output channel, for a run of token columns).
+// Work items (expert, row chunk, channel tile) are taken round-robin by a persistent grid; their
+// list is produced on the device by the permutation kernel, so no host synchronisation is needed
+// between routing and the GEMMs. A chunk with r rows only moves and multiplies ceil(r/16)*16
+// token columns.
 //
 // Every wait is bounded: on expiry the role records MOE_ERR_DEVICE_TIMEOUT, raises the CTA's
 // abort flag, and all roles fall through to the common exit, which waits (bounded) for copies
@@ -29,33 +32,37 @@
 
 namespace moe {
 
-constexpr int kThreads = 192;
 constexpr int kAccStages = 2;
-constexpr int kStageBudget = 192 * 1024;
+constexpr int kMaxStages = 8;
+constexpr int kMaxSmem = 232448;      // 227 KiB per CTA
 constexpr int kMaxKBlocks = 112;      // K <= 14336
 
 template <int NT, bool DUAL>
 struct GemmCfg {
+  static constexpr int kEpiWarps = NT >= 32 ? 8 : 4;
+  static constexpr int kEpiThreads = kEpiWarps * 32;
+  static constexpr int kThreads = 96 + kEpiThreads;
+  static constexpr int kCpt = NT / (kEpiWarps / 4);   // token columns per epilogue thread
   static constexpr int kABytes = 128 * 128;
   static constexpr int kBBytes = NT * 128;
   static constexpr int kStageBytes = (DUAL ? 2 : 1) * kABytes + kBBytes;
-  static constexpr int kStagesRaw = kStageBudget / kStageBytes;
-  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kAccCols = (DUAL ? 2 : 1) * NT;
   static constexpr int kTmemCols = kAccStages * kAccCols < 32 ? 32 : kAccStages * kAccCols;
-  // after the stages: activation scales [kMaxKBlocks][NT], weight scales [2][kMaxKBlocks],
-  // amax scratch [4][NT], barriers, tmem slot, flags
-  static constexpr int kXsBytes = kMaxKBlocks * NT * 4;
-  static constexpr int kWsBytes = 2 * kMaxKBlocks * 4;
-  static constexpr int kAmaxBytes = 4 * NT * 4;
-  static constexpr int kBarBytes = (2 * kStages + 2 * kAccStages) * 8;
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kXsBytes + kWsBytes + kAmaxBytes + kBarBytes + 64;
+  // Shared memory after the stage ring, for a contraction of kb K blocks:
+  //   2 buffers of { x scales [kb][NT], weight scales [2][kb] }, amax scratch [4][NT],
+  //   barriers (2*stages + 4 + 4), 8 words of flags.
+  static constexpr int scale_floats(int kb) { return kb * NT + 2 * kb; }
+  static constexpr int tail_bytes(int kb) { return 2 * scale_floats(kb) * 4 + 4 * NT * 4 + (2 * kMaxStages + 8) * 8 + 64; }
+  static constexpr int stages_for(int kb) {
+    const int s = (kMaxSmem - 1024 - tail_bytes(kb)) / kStageBytes;
+    return s > kMaxStages ? kMaxStages : s;
+  }
 };
 
 struct GemmDev {
   const Chunk* chunks;
   const int32_t* n_chunks;
-  int tiles_m, kblocks, m, n_local;
+  int tiles_m, kblocks, m, n_local, stages;
   const float* act_scale;
   const float* w_a_scale;
   const float* w_b_scale;
@@ -69,22 +76,26 @@ struct GemmDev {
 };
 
 template <int NT, bool DUAL>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(GemmCfg<NT, DUAL>::kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const __grid_constant__ CUtensorMap tm_sa, const __grid_constant__ CUtensorMap tm_sb,
                     const __grid_constant__ CUtensorMap tm_x, const GemmDev p) {
   using C = GemmCfg<NT, DUAL>;
   extern __shared__ uint8_t smem_raw[];
+  const int KB = p.kblocks;
+  const int S = p.stages;
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* stages = base;
-  float* s_xs = reinterpret_cast<float*>(base + C::kStages * C::kStageBytes);
-  float* s_ws = s_xs + kMaxKBlocks * NT;
-  float* s_amax = s_ws + 2 * kMaxKBlocks;
+  float* s_scales = reinterpret_cast<float*>(base + S * C::kStageBytes);     // [2][scale_floats(KB)]
+  const int sf = C::scale_floats(KB);
+  float* s_amax = s_scales + 2 * sf;
   uint64_t* bar_full = reinterpret_cast<uint64_t*>(s_amax + 4 * NT);
-  uint64_t* bar_empty = bar_full + C::kStages;
-  uint64_t* bar_tfull = bar_empty + C::kStages;
+  uint64_t* bar_empty = bar_full + kMaxStages;
+  uint64_t* bar_tfull = bar_empty + kMaxStages;
   uint64_t* bar_tempty = bar_tfull + kAccStages;
-  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bar_tempty + kAccStages);
+  uint64_t* bar_scfull = bar_tempty + kAccStages;
+  uint64_t* bar_scempty = bar_scfull + 2;
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bar_scempty + 2);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   volatile uint32_t* s_issued = reinterpret_cast<volatile uint32_t*>(s_tmem + 2);    // K blocks whose TMA was issued
   volatile uint32_t* s_consumed = reinterpret_cast<volatile uint32_t*>(s_tmem + 3);  // K blocks whose data arrived
@@ -94,8 +105,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::kStages; ++s) { mbar_init(bar_full + s, 1); mbar_init(bar_empty + s, 1); }
-    for (int s = 0; s < kAccStages; ++s) { mbar_init(bar_tfull + s, 1); mbar_init(bar_tempty + s, 128); }
+    for (int s = 0; s < S; ++s) { mbar_init(bar_full + s, 1); mbar_init(bar_empty + s, 1); }
+    for (int s = 0; s < kAccStages; ++s) { mbar_init(bar_tfull + s, 1); mbar_init(bar_tempty + s, C::kEpiThreads); }
+    for (int s = 0; s < 2; ++s) { mbar_init(bar_scfull + s, 32); mbar_init(bar_scempty + s, C::kEpiThreads); }
     *s_abort = 0; *s_issued = 0; *s_consumed = 0; *s_committed = 0; *s_drained = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tmap(&tm_a); prefetch_tmap(&tm_x);
@@ -113,14 +125,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
   const int n_chunks = *p.n_chunks;
   const int n_units = n_chunks * p.tiles_m;
-  const int KB = p.kblocks;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       const uint64_t pol_w = policy_evict_first();
       const uint64_t pol_x = policy_evict_last();
-      uint32_t it = 0;
+      uint32_t it = 0, s = 0, ph = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
         const Chunk ch = p.chunks[u / p.tiles_m];
@@ -129,19 +140,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const CUtensorMap* ma = shared_e ? &tm_sa : &tm_a;
         const CUtensorMap* mb = shared_e ? &tm_sb : &tm_b;
         const int wrow = (shared_e ? 0 : ch.expert * p.m) + mt * 128;
+        const int n16 = (ch.rows + 15) >> 4;
+        const uint32_t bytes = (DUAL ? 2 : 1) * C::kABytes + n16 * 2048;
         for (int kb = 0; kb < KB; ++kb, ++it) {
-          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
           if (!mbar_wait(bar_empty + s, ph ^ 1u, s_abort)) {
             if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 1); *s_abort = 1; }
             ok = false;
             break;
           }
           uint8_t* st = stages + s * C::kStageBytes;
-          mbar_expect_tx(bar_full + s, C::kStageBytes);
+          mbar_expect_tx(bar_full + s, bytes);
           tma_load_2d(st, ma, kb * 128, wrow, bar_full + s, pol_w);
           if constexpr (DUAL) tma_load_2d(st + C::kABytes, mb, kb * 128, wrow, bar_full + s, pol_w);
-          tma_load_2d(st + (DUAL ? 2 : 1) * C::kABytes, &tm_x, kb * 128, ch.row0, bar_full + s, pol_x);
+          uint8_t* sb = st + (DUAL ? 2 : 1) * C::kABytes;
+          for (int j = 0; j < n16; ++j) tma_load_2d(sb + j * 2048, &tm_x, kb * 128, ch.row0 + j * 16, bar_full + s, pol_x);
           *s_issued = it + 1;
+          if (++s == static_cast<uint32_t>(S)) { s = 0; ph ^= 1u; }
         }
       }
     }
@@ -149,12 +163,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
-      const uint32_t idesc = idesc_e4m3(128, NT);
-      uint32_t it = 0;
+      uint32_t it = 0, s = 0, ph = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+        const Chunk ch = p.chunks[u / p.tiles_m];
+        const uint32_t idesc = idesc_e4m3(128, ((ch.rows + 15) >> 4) * 16);
         for (int kb = 0; kb < KB; ++kb, ++it) {
-          const uint32_t s = it % C::kStages, ph = (it / C::kStages) & 1u;
           const uint32_t as = it % kAccStages, aph = (it / kAccStages) & 1u;
           if (!mbar_wait(bar_tempty + as, aph ^ 1u, s_abort) || !mbar_wait(bar_full + s, ph, s_abort)) {
             if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 2); *s_abort = 1; }
@@ -175,41 +189,66 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           mma_commit(bar_empty + s);     // the stage may be refilled once these MMAs have read it
           mma_commit(bar_tfull + as);    // the accumulator is complete
           *s_committed = it + 1;
+          if (++s == static_cast<uint32_t>(S)) { s = 0; ph ^= 1u; }
         }
       }
     }
     __syncwarp();
-  } else {
-    // ------------------------------ epilogue ----------------------------------
-    const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
-    const int m = quarter * 32 + lane;            // output channel inside the tile; also this thread's
-                                                  // index among the 128 epilogue threads
-    const uint32_t lane_base = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
-    uint32_t it = 0;
-    bool failed = false;
-    for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
+  } else if (warp == 2) {
+    // ------------------------------ scale loader ------------------------------
+    // Each lane waits, loads its share and arrives on its own: no warp-level sync, so a lane that
+    // gives up cannot strand the others.
+    uint32_t un = 0;
+    for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++un) {
+      const uint32_t b = un & 1u, ph = (un >> 1) & 1u;
+      if (!mbar_wait(bar_scempty + b, ph ^ 1u, s_abort)) {
+        if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 4); *s_abort = 1; }
+        break;
+      }
       const Chunk ch = p.chunks[u / p.tiles_m];
       const int mt = u % p.tiles_m;
       const bool shared_e = ch.expert >= p.n_local;
-      // stage this item's scales: x scales as [kb][n], weight scales as [which][kb]
-      for (int i = m; i < NT * KB; i += 128) {
-        const int n = i / KB, kb = i % KB;
-        s_xs[kb * NT + n] = n < ch.rows ? p.act_scale[static_cast<size_t>(ch.row0 + n) * KB + kb] : 0.f;
+      float* xs = s_scales + b * sf;            // [kb][NT]
+      float* ws = xs + KB * NT;                 // [2][kb]
+      const int cols = ((ch.rows + 15) >> 4) * 16;
+      for (int i = lane; i < cols * KB; i += 32) {
+        const int n = i / KB, kb = i - n * KB;
+        xs[kb * NT + n] = n < ch.rows ? p.act_scale[static_cast<size_t>(ch.row0 + n) * KB + kb] : 0.f;
       }
-      {
-        const float* wa = shared_e ? p.s_a_scale : p.w_a_scale + static_cast<size_t>(ch.expert) * p.tiles_m * KB;
-        for (int kb = m; kb < KB; kb += 128) s_ws[kb] = wa[static_cast<size_t>(mt) * KB + kb];
-        if constexpr (DUAL) {
-          const float* wb = shared_e ? p.s_b_scale : p.w_b_scale + static_cast<size_t>(ch.expert) * p.tiles_m * KB;
-          for (int kb = m; kb < KB; kb += 128) s_ws[kMaxKBlocks + kb] = wb[static_cast<size_t>(mt) * KB + kb];
-        }
+      const float* wa = (shared_e ? p.s_a_scale : p.w_a_scale + static_cast<size_t>(ch.expert) * p.tiles_m * KB) +
+                        static_cast<size_t>(mt) * KB;
+      for (int kb = lane; kb < KB; kb += 32) ws[kb] = wa[kb];
+      if constexpr (DUAL) {
+        const float* wb = (shared_e ? p.s_b_scale : p.w_b_scale + static_cast<size_t>(ch.expert) * p.tiles_m * KB) +
+                          static_cast<size_t>(mt) * KB;
+        for (int kb = lane; kb < KB; kb += 32) ws[KB + kb] = wb[kb];
       }
-      epilogue_sync();
-
-      float acc_a[NT];
-      float acc_b[NT];
+      mbar_arrive(bar_scfull + b);
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int epi = warp - 3;
+    const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
+    const int m = quarter * 32 + lane;            // output channel inside the tile
+    const int col0 = (epi >> 2) * C::kCpt;        // first token column of this thread
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    uint32_t it = 0, un = 0;
+    bool failed = false;
+    for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++un) {
+      const Chunk ch = p.chunks[u / p.tiles_m];
+      const int mt = u % p.tiles_m;
+      const int cols = ((ch.rows + 15) >> 4) * 16;            // token columns that were multiplied
+      const uint32_t b = un & 1u, sph = (un >> 1) & 1u;
+      const float* xs_all = s_scales + b * sf;
+      const float* ws = xs_all + KB * NT;
+      if (!failed && !mbar_wait(bar_scfull + b, sph, s_abort)) {
+        if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 5); *s_abort = 1; }
+        failed = true;
+      }
+      float acc_a[C::kCpt];
+      float acc_b[C::kCpt];
 #pragma unroll
-      for (int n = 0; n < NT; ++n) { acc_a[n] = 0.f; acc_b[n] = 0.f; }
+      for (int n = 0; n < C::kCpt; ++n) { acc_a[n] = 0.f; acc_b[n] = 0.f; }
       for (int kb = 0; kb < KB; ++kb, ++it) {
         const uint32_t as = it % kAccStages, aph = (it / kAccStages) & 1u;
         if (!failed && !mbar_wait(bar_tfull + as, aph, s_abort)) {
@@ -218,34 +257,45 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
         if (failed) continue;   // keep in step with the other epilogue threads up to the item's end
         tc_fence_after();
-        const float wa = s_ws[kb];
-        const float wb = DUAL ? s_ws[kMaxKBlocks + kb] : 0.f;
-        const float* xs = s_xs + kb * NT;
-        const uint32_t col0 = lane_base + as * C::kAccCols;
+        if (col0 < cols) {      // uniform per warp
+          const float wa = ws[kb];
+          const float wb = DUAL ? ws[KB + kb] : 0.f;
+          const float* xs = xs_all + kb * NT + col0;
+          const uint32_t t0 = lane_base + as * C::kAccCols + col0;
+          uint32_t ra[C::kCpt], rb[DUAL ? C::kCpt : 1];
 #pragma unroll
-        for (int c = 0; c < NT; c += 16) {
-          float d[16];
-          tmem_ld16(col0 + c, d);
+          for (int g = 0; g < C::kCpt; g += 16) {
+            if (col0 + g < cols) {
+              tmem_ld16(t0 + g, ra + g);
+              if constexpr (DUAL) tmem_ld16(t0 + NT + g, rb + g);
+            }
+          }
+          tmem_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) acc_a[c + j] = fmaf(d[j], __fmul_rn(wa, xs[c + j]), acc_a[c + j]);
-          if constexpr (DUAL) {
-            tmem_ld16(col0 + NT + c, d);
+          for (int g = 0; g < C::kCpt; g += 16) {
+            if (col0 + g < cols) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) acc_b[c + j] = fmaf(d[j], __fmul_rn(wb, xs[c + j]), acc_b[c + j]);
+              for (int j = 0; j < 16; ++j) {
+                const float x = xs[g + j];
+                acc_a[g + j] = fmaf(__uint_as_float(ra[g + j]), __fmul_rn(wa, x), acc_a[g + j]);
+                if constexpr (DUAL) acc_b[g + j] = fmaf(__uint_as_float(rb[g + j]), __fmul_rn(wb, x), acc_b[g + j]);
+              }
+            }
           }
         }
         tc_fence_before();
         mbar_arrive(bar_tempty + as);
-        if (m == 0) *s_drained = it + 1;
+        if (m == 0 && epi < 4) *s_drained = it + 1;
       }
-      // One decision for all 128 threads: nobody may be left alone at a later barrier.
-      if (epilogue_any(failed || *s_abort)) break;
+      // One decision for all epilogue threads: nobody may be left alone at a later barrier.
+      if (epilogue_any<C::kEpiThreads>(failed || *s_abort)) break;
       if constexpr (DUAL) {
-        epilogue_swiglu_requant<NT>(acc_a, acc_b, m, ch.rows, ch.row0, mt, p.m, s_amax, p.aq, p.as);
+        epilogue_swiglu_requant<C::kCpt, C::kEpiThreads>(acc_a, acc_b, m, col0, NT, ch.rows, ch.row0, mt, p.m, s_amax,
+                                                         p.aq, p.as);
       } else {
-        epilogue_store_rows<NT>(acc_a, m, ch.rows, ch.row0, mt, p.m, p.row_dest, p.out);
-        epilogue_sync();   // scales are restaged next
+        epilogue_store_rows<C::kCpt>(acc_a, m, col0, ch.rows, ch.row0, mt, p.m, p.row_dest, p.out);
       }
+      mbar_arrive(bar_scempty + b);   // this item's scales are no longer needed
     }
   }
 
@@ -255,10 +305,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   tc_fence_after();
   if (*s_abort && threadIdx.x == 0) {
     // Give copies and MMAs that were issued but never consumed a bounded chance to land.
-    for (uint32_t it = *s_consumed; it < *s_issued; ++it)
-      mbar_wait(bar_full + it % C::kStages, (it / C::kStages) & 1u);
-    for (uint32_t it = *s_drained; it < *s_committed; ++it)
-      mbar_wait(bar_tfull + it % kAccStages, (it / kAccStages) & 1u);
+    for (uint32_t it = *s_consumed; it < *s_issued; ++it) mbar_wait(bar_full + it % S, (it / S) & 1u);
+    for (uint32_t it = *s_drained; it < *s_committed; ++it) mbar_wait(bar_tfull + it % kAccStages, (it / kAccStages) & 1u);
   }
   __syncthreads();
   if (warp == 1) {
@@ -301,17 +349,19 @@ static int make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t c
 }
 
 template <int NT, bool DUAL>
-static cudaError_t launch_typed(const GemmArgs& a, const GemmDev& dev, const CUtensorMap* maps, int grid,
-                                cudaStream_t stream) {
+static cudaError_t launch_typed(GemmDev dev, const CUtensorMap* maps, int grid, cudaStream_t stream) {
   using C = GemmCfg<NT, DUAL>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<NT, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::kSmemBytes);
+                                         kMaxSmem);
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  grouped_gemm_kernel<NT, DUAL><<<grid, kThreads, C::kSmemBytes, stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], dev);
+  dev.stages = C::stages_for(dev.kblocks);
+  if (dev.stages < 2) return cudaErrorInvalidValue;
+  const int smem = 1024 + dev.stages * C::kStageBytes + C::tail_bytes(dev.kblocks);
+  grouped_gemm_kernel<NT, DUAL><<<grid, C::kThreads, smem, stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], dev);
   return cudaGetLastError();
 }
 
@@ -340,23 +390,23 @@ cudaError_t launch_gemm_tc(const GemmArgs& a, cudaStream_t stream, int* launches
   const uint8_t* sb = a.dual ? (a.s_b ? a.s_b : wb) : sa;
   rc |= make_map(&maps[2], sa, a.s_a ? a.m : wrows, a.k, 128);
   rc |= make_map(&maps[3], sb, a.s_a ? a.m : wrows, a.k, 128);
-  rc |= make_map(&maps[4], a.act, a.total_rows, a.k, a.tile);
+  rc |= make_map(&maps[4], a.act, a.total_rows, a.k, 16);      // token rows move in boxes of 16
   if (rc) {
     if (driver_error) *driver_error = rc;
     return cudaErrorUnknown;
   }
-  GemmDev dev{a.chunks, a.n_chunks, a.m / 128, a.k / 128, a.m, a.n_local, a.act_scale, a.w_a_scale, a.w_b_scale,
+  GemmDev dev{a.chunks, a.n_chunks, a.m / 128, a.k / 128, a.m, a.n_local, 0, a.act_scale, a.w_a_scale, a.w_b_scale,
               a.s_a_scale, a.s_b_scale, a.aq, a.as, a.out, a.row_dest, a.status};
   const int grid = max(1, min(sm_count(), a.max_units));
   cudaError_t e;
   if (a.dual) {
-    e = a.tile == 16 ? launch_typed<16, true>(a, dev, maps, grid, stream)
-      : a.tile == 32 ? launch_typed<32, true>(a, dev, maps, grid, stream)
-                     : launch_typed<64, true>(a, dev, maps, grid, stream);
+    e = a.tile == 16 ? launch_typed<16, true>(dev, maps, grid, stream)
+      : a.tile == 32 ? launch_typed<32, true>(dev, maps, grid, stream)
+                     : launch_typed<64, true>(dev, maps, grid, stream);
   } else {
-    e = a.tile == 16 ? launch_typed<16, false>(a, dev, maps, grid, stream)
-      : a.tile == 32 ? launch_typed<32, false>(a, dev, maps, grid, stream)
-                     : launch_typed<64, false>(a, dev, maps, grid, stream);
+    e = a.tile == 16 ? launch_typed<16, false>(dev, maps, grid, stream)
+      : a.tile == 32 ? launch_typed<32, false>(dev, maps, grid, stream)
+                     : launch_typed<64, false>(dev, maps, grid, stream);
   }
   if (launches) *launches += 1;
   return e;

@@ -11,73 +11,140 @@
 
 namespace moe {
 
-constexpr int kLogitExperts = 2;   // experts per block
-constexpr int kLogitTokens = 16;   // tokens per block
+constexpr int kLogitWarps = 8;
+constexpr int kLogitTokens = 8;    // tokens per block
 
 // logits[t][e] = sum_k router[e][k] * x[t][k], products and sums in fp64, one rounding to fp32.
 // fp64 keeps the result within half an fp32 ulp of the exact value whatever the summation
 // order, which is what makes expert ids reproducible against a host fp32 GEMV on inputs whose
 // decision margins are audited.
-__global__ void __launch_bounds__(256) router_logits_kernel(const __nv_bfloat16* __restrict__ x,
-                                                            const float* __restrict__ router, int tokens,
-                                                            int experts, int hidden, float* __restrict__ logits) {
-  const int e0 = blockIdx.x * kLogitExperts;
+//   SPLITK = false: warp w of block b owns expert b*8+w, its lanes sweep the whole row.
+//   SPLITK = true : block b owns expert b, the 128-channel pieces of the row are dealt round-robin
+//                   to the warps (small batches: more blocks in flight for the same bytes).
+template <bool SPLITK>
+__global__ void __launch_bounds__(kLogitWarps * 32) router_logits_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                         const float* __restrict__ router, int tokens,
+                                                                         int experts, int hidden,
+                                                                         float* __restrict__ logits) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int e = SPLITK ? blockIdx.x : blockIdx.x * kLogitWarps + warp;
   const int t0 = blockIdx.y * kLogitTokens;
   const int tcount = min(kLogitTokens, tokens - t0);
-  double acc[kLogitExperts][kLogitTokens];
+  double acc[kLogitTokens];
 #pragma unroll
-  for (int e = 0; e < kLogitExperts; ++e)
+  for (int t = 0; t < kLogitTokens; ++t) acc[t] = 0.0;
+  if (e < experts) {
+    const float* row = router + static_cast<size_t>(e) * hidden;
+    const int pieces = hidden / 128;
+    for (int c = SPLITK ? warp : 0; c < pieces; c += SPLITK ? kLogitWarps : 1) {
+      const int k = c * 128 + lane * 4;
+      const float4 r = *reinterpret_cast<const float4*>(row + k);
+      const double r0 = r.x, r1 = r.y, r2 = r.z, r3 = r.w;
 #pragma unroll
-    for (int t = 0; t < kLogitTokens; ++t) acc[e][t] = 0.0;
-
-  for (int k = threadIdx.x * 4; k < hidden; k += 256 * 4) {
-    float4 r[kLogitExperts];
-#pragma unroll
-    for (int e = 0; e < kLogitExperts; ++e) {
-      r[e] = (e0 + e < experts) ? *reinterpret_cast<const float4*>(router + static_cast<size_t>(e0 + e) * hidden + k)
-                                : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-#pragma unroll
-    for (int t = 0; t < kLogitTokens; ++t) {
-      if (t < tcount) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(x + static_cast<size_t>(t0 + t) * hidden + k);
-        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-        const double x0 = __bfloat162float(lo.x), x1 = __bfloat162float(lo.y);
-        const double x2 = __bfloat162float(hi.x), x3 = __bfloat162float(hi.y);
-#pragma unroll
-        for (int e = 0; e < kLogitExperts; ++e) {
-          double a = acc[e][t];
-          a = fma(static_cast<double>(r[e].x), x0, a);
-          a = fma(static_cast<double>(r[e].y), x1, a);
-          a = fma(static_cast<double>(r[e].z), x2, a);
-          a = fma(static_cast<double>(r[e].w), x3, a);
-          acc[e][t] = a;
+      for (int t = 0; t < kLogitTokens; ++t) {
+        if (t < tcount) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(x + static_cast<size_t>(t0 + t) * hidden + k);
+          const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+          const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+          double a = acc[t];
+          a = fma(r0, static_cast<double>(__bfloat162float(lo.x)), a);
+          a = fma(r1, static_cast<double>(__bfloat162float(lo.y)), a);
+          a = fma(r2, static_cast<double>(__bfloat162float(hi.x)), a);
+          a = fma(r3, static_cast<double>(__bfloat162float(hi.y)), a);
+          acc[t] = a;
         }
       }
     }
   }
-  __shared__ double part[8][kLogitExperts * kLogitTokens];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
-  for (int e = 0; e < kLogitExperts; ++e)
+  for (int t = 0; t < kLogitTokens; ++t) {
+    if (t < tcount) {
 #pragma unroll
-    for (int t = 0; t < kLogitTokens; ++t) {
-      double v = acc[e][t];
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-      if (lane == 0) part[warp][e * kLogitTokens + t] = v;
-    }
-  __syncthreads();
-  if (threadIdx.x < kLogitExperts * kLogitTokens) {
-    const int e = threadIdx.x / kLogitTokens, t = threadIdx.x % kLogitTokens;
-    if (e0 + e < experts && t < tcount) {
-      double v = 0.0;
-#pragma unroll
-      for (int w = 0; w < 8; ++w) v += part[w][threadIdx.x];
-      logits[static_cast<size_t>(t0 + t) * experts + e0 + e] = static_cast<float>(v);
+      for (int off = 16; off > 0; off >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], off);
     }
   }
+  if (SPLITK) {
+    __shared__ double part[kLogitWarps][kLogitTokens];
+    if (lane == 0) {
+#pragma unroll
+      for (int t = 0; t < kLogitTokens; ++t) part[warp][t] = acc[t];
+    }
+    __syncthreads();
+    if (threadIdx.x < tcount && e < experts) {
+      double v = 0.0;
+#pragma unroll
+      for (int w = 0; w < kLogitWarps; ++w) v += part[w][threadIdx.x];
+      logits[static_cast<size_t>(t0 + threadIdx.x) * experts + e] = static_cast<float>(v);
+    }
+  } else if (lane == 0 && e < experts) {
+#pragma unroll
+    for (int t = 0; t < kLogitTokens; ++t)
+      if (t < tcount) logits[static_cast<size_t>(t0 + t) * experts + e] = static_cast<float>(acc[t]);
+  }
+}
+
+// Larger batches: a block keeps 8 token rows in shared memory and streams 16 router rows (two per
+// warp) against them, so x is read from L2 once per block and the inner loop is bound by the
+// fp64 units. Same arithmetic as above: every lane sums its channels in order, lanes are
+// combined by a shuffle tree.
+constexpr int kTiledExpertsPerWarp = 2;
+constexpr int kTiledExperts = kLogitWarps * kTiledExpertsPerWarp;
+
+__global__ void __launch_bounds__(kLogitWarps * 32) router_logits_tiled_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                               const float* __restrict__ router,
+                                                                               int tokens, int experts, int hidden,
+                                                                               float* __restrict__ logits) {
+  extern __shared__ uint2 s_x[];                       // [8][hidden / 4], four bf16 per entry
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int quads = hidden / 4;
+  const int t0 = blockIdx.y * kLogitTokens;
+  const int tcount = min(kLogitTokens, tokens - t0);
+  for (int i = threadIdx.x; i < kLogitTokens * quads; i += blockDim.x) {
+    const int t = i / quads, c = i - t * quads;
+    s_x[i] = t < tcount ? *reinterpret_cast<const uint2*>(x + static_cast<size_t>(t0 + t) * hidden + 4 * c)
+                        : make_uint2(0u, 0u);
+  }
+  __syncthreads();
+  const int e0 = blockIdx.x * kTiledExperts + warp * kTiledExpertsPerWarp;
+  double acc[kTiledExpertsPerWarp][kLogitTokens];
+#pragma unroll
+  for (int j = 0; j < kTiledExpertsPerWarp; ++j)
+#pragma unroll
+    for (int t = 0; t < kLogitTokens; ++t) acc[j][t] = 0.0;
+  for (int q = lane; q < quads; q += 32) {
+    float4 r[kTiledExpertsPerWarp];
+#pragma unroll
+    for (int j = 0; j < kTiledExpertsPerWarp; ++j)
+      r[j] = e0 + j < experts ? *reinterpret_cast<const float4*>(router + static_cast<size_t>(e0 + j) * hidden + 4 * q)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int t = 0; t < kLogitTokens; ++t) {
+      const uint2 raw = s_x[t * quads + q];
+      const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+      const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+      const double x0 = __bfloat162float(lo.x), x1 = __bfloat162float(lo.y);
+      const double x2 = __bfloat162float(hi.x), x3 = __bfloat162float(hi.y);
+#pragma unroll
+      for (int j = 0; j < kTiledExpertsPerWarp; ++j) {
+        double a = acc[j][t];
+        a = fma(static_cast<double>(r[j].x), x0, a);
+        a = fma(static_cast<double>(r[j].y), x1, a);
+        a = fma(static_cast<double>(r[j].z), x2, a);
+        a = fma(static_cast<double>(r[j].w), x3, a);
+        acc[j][t] = a;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kTiledExpertsPerWarp; ++j)
+#pragma unroll
+    for (int t = 0; t < kLogitTokens; ++t) {
+      double v = acc[j][t];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+      if (lane == 0 && t < tcount && e0 + j < experts)
+        logits[static_cast<size_t>(t0 + t) * experts + e0 + j] = static_cast<float>(v);
+    }
 }
 
 struct RouteArgs {
@@ -123,7 +190,9 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_select_kernel(RouteArg
     float score = ninf;
     if (lane < a.n_group) {
       float m1 = ninf, m2 = ninf;
-      for (int j = 0; j < gsz; ++j) {
+      for (int j0 = 0; j0 < gsz; ++j0) {
+        int j = j0 + lane;                  // rotated start: lanes hit different banks
+        if (j >= gsz) j -= gsz * (j / gsz);
         const float v = c[lane * gsz + j];
         if (v > m1) { m2 = m1; m1 = v; } else if (v > m2) { m2 = v; }
       }
@@ -187,8 +256,26 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_select_kernel(RouteArg
 cudaError_t launch_router(const moe_config_t& cfg, const __nv_bfloat16* x, const float* router, const float* bias,
                           int tokens, float* logits, int32_t* ids32, float* weights, int64_t* ids64,
                           float* weights_out, cudaStream_t stream, int* launches) {
-  dim3 grid((cfg.n_experts + kLogitExperts - 1) / kLogitExperts, (tokens + kLogitTokens - 1) / kLogitTokens);
-  router_logits_kernel<<<grid, 256, 0, stream>>>(x, router, tokens, cfg.n_experts, cfg.hidden, logits);
+  const int token_tiles = (tokens + kLogitTokens - 1) / kLogitTokens;
+  const size_t tile_smem = static_cast<size_t>(kLogitTokens) * cfg.hidden * sizeof(__nv_bfloat16);
+  if (token_tiles == 1) {          // up to 8 tokens: one block per expert keeps every SM reading
+    dim3 grid(cfg.n_experts, 1);
+    router_logits_kernel<true><<<grid, kLogitWarps * 32, 0, stream>>>(x, router, tokens, cfg.n_experts, cfg.hidden, logits);
+  } else if (tile_smem <= 200 * 1024) {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(router_logits_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           200 * 1024);
+      if (e != cudaSuccess) return e;
+      configured = true;
+    }
+    dim3 grid((cfg.n_experts + kTiledExperts - 1) / kTiledExperts, token_tiles);
+    router_logits_tiled_kernel<<<grid, kLogitWarps * 32, tile_smem, stream>>>(x, router, tokens, cfg.n_experts,
+                                                                               cfg.hidden, logits);
+  } else {
+    dim3 grid((cfg.n_experts + kLogitWarps - 1) / kLogitWarps, token_tiles);
+    router_logits_kernel<false><<<grid, kLogitWarps * 32, 0, stream>>>(x, router, tokens, cfg.n_experts, cfg.hidden, logits);
+  }
   RouteArgs a{logits, bias, tokens, cfg.n_experts, cfg.topk, cfg.scoring, cfg.n_group, cfg.topk_group,
               cfg.routed_scaling, ids32, weights, ids64, weights_out};
   route_select_kernel<<<(tokens + kRouteWarps - 1) / kRouteWarps, kRouteWarps * 32, 0, stream>>>(a);

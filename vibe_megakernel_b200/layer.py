@@ -137,6 +137,18 @@ class MoeLayer:
     def launches(self) -> int:
         return int(self.lib.moe_last_launch_count())
 
+    STAGES = ("router", "permutation", "quantiser", "gate_up_gemm", "down_gemm", "combine")
+
+    def profile(self, on: bool) -> None:
+        """Record CUDA events between the stages of later ``forward`` calls made by this thread."""
+        self.lib.moe_profile_enable(1 if on else 0)
+
+    def stage_ms(self) -> dict[str, float]:
+        """Durations of the stages of the last profiled ``forward`` call (waits for it)."""
+        buf = (C.c_float * len(self.STAGES))()
+        _cabi.check("moe_profile_read", self.lib.moe_profile_read(buf, len(self.STAGES)))
+        return dict(zip(self.STAGES, (float(v) for v in buf)))
+
     # ---- stage entry points (unit parity) --------------------------------------------
     def route(self, x: torch.Tensor, router: torch.Tensor, bias: torch.Tensor | None):
         c = self.config
