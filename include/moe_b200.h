@@ -110,6 +110,20 @@ int moe_route(const moe_config_t* cfg, const void* x_bf16, const float* router, 
               int32_t tokens, int64_t* expert_ids, float* weights, void* workspace, size_t workspace_bytes,
               void* stream);
 
+/* The router again, for callers that cannot hand over a workspace because they may not allocate
+ * device memory (a plugin given only input and output buffers by a host that forbids cudaMalloc
+ * while serving; an FFI wrapper without an allocator). It has no counterpart in the reference.
+ * Same arguments and results as moe_route without the workspace: the scratch lives in a static
+ * device array inside the library (about 544 KiB held by every GPU that loads the library).
+ * Limits: tokens <= MOE_STATIC_ROUTE_MAX_TOKENS, else MOE_ERR_TOO_LARGE and nothing is launched.
+ * The first call on a device looks up the array's address: make it outside any stream capture.
+ * All calls on a GPU share the array, so calls that can overlap on the GPU race; keep them on
+ * one stream. Calls no cudaMalloc/cudaFree and no allocating library routine. */
+#define MOE_STATIC_ROUTE_MAX_TOKENS 256
+#define MOE_ERR_TOO_LARGE (-7)
+int moe_route_static(const moe_config_t* cfg, const void* x_bf16, const float* router, const float* router_bias,
+                     int32_t tokens, int64_t* expert_ids, float* weights, void* stream);
+
 /* Per-row, per-128-channel e4m3 quantiser: scale = max(amax, 1e-4)/448, q = RNE(x/scale).
  * Replaces pack_fp8_activation(..., scale_format="float") (megabench/tasks/quantization.py:87-109).
  * dtype: 0 = bf16 input, 1 = fp32 input. `width` need not be a multiple of 128 (zero padding).

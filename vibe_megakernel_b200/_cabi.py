@@ -9,7 +9,8 @@ from . import build as _build
 
 OK = 0
 ERRORS = {-1: "bad argument", -2: "unsupported geometry", -3: "workspace too small",
-          -4: "device wait timed out", -5: "tensor-map encode failed", -6: "device index out of range"}
+          -4: "device wait timed out", -5: "tensor-map encode failed", -6: "device index out of range",
+          -7: "request exceeds the static scratch limit"}
 SCORING = {"softmax": 0, "sigmoid": 1}
 GEMM_TCGEN05, GEMM_SIMT = 0, 1
 
@@ -43,6 +44,8 @@ EXPORTS = {
     "moe_workspace_layout": (C.c_int, [C.POINTER(Config), C.c_int32, C.POINTER(Layout)]),
     "moe_route": (C.c_int, [C.POINTER(Config), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p,
                             C.c_void_p, C.c_size_t, C.c_void_p]),
+    "moe_route_static": (C.c_int, [C.POINTER(Config), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
+                                   C.c_void_p, C.c_void_p]),
     "moe_quantize_rows": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
                                     C.c_void_p]),
     "moe_group_rows": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),

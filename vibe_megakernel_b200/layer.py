@@ -190,6 +190,28 @@ class MoeLayer:
         return ws[off:off + nbytes].view(dtype).view(shape)
 
 
+STATIC_ROUTE_MAX_TOKENS = 256
+
+
+def route_static(config: LayerConfig, x: torch.Tensor, router: torch.Tensor, bias: torch.Tensor | None,
+                 ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """Router into caller-owned ``ids`` (int64 [T, topk]) and ``weights`` (fp32 [T, topk]) without
+    any workspace: for hosts that may not allocate device memory. The scratch is a static device
+    array inside the library, shared by every call on the GPU (calls that can overlap on the GPU
+    race; keep them on one stream), and at most ``STATIC_ROUTE_MAX_TOKENS`` tokens are accepted.
+    The first call on a device does a one-time address look-up: make it outside stream capture."""
+    lib = _cabi.load()
+    tokens = x.shape[0]
+    _require(x, "x", torch.bfloat16, (tokens, config.hidden))
+    _require(router, "router", torch.float32, (config.experts, config.hidden))
+    _require(ids, "ids", torch.int64, (tokens, config.topk))
+    _require(weights, "weights", torch.float32, (tokens, config.topk))
+    cfg = config.c_struct()
+    rc = lib.moe_route_static(C.byref(cfg), x.data_ptr(), router.data_ptr(), _ptr(bias), tokens, ids.data_ptr(),
+                              weights.data_ptr(), torch.cuda.current_stream(x.device).cuda_stream)
+    _cabi.check("moe_route_static", rc)
+
+
 def quantize_rows(x: torch.Tensor, gather: torch.Tensor | None = None):
     """e4m3 payload and fp32 scales of ``x`` [rows, width] (bf16 or fp32), per row per 128 channels."""
     lib = _cabi.load()
