@@ -16,6 +16,9 @@ cudaError_t launch_router(const moe_config_t& cfg, const __nv_bfloat16* x, const
                           int tokens, float* logits, int32_t* ids32, float* weights, int64_t* ids64,
                           float* weights_out, cudaStream_t stream, int* launches);
 
+cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* router, int tokens, int experts, int hidden,
+                                 float* logits, cudaStream_t stream);
+
 struct GroupArgs {
   const int32_t* ids32;   // one of ids32 / ids64 is set
   const int64_t* ids64;

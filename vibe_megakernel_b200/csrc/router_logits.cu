@@ -1,0 +1,207 @@
+// Router logits: logits[t][e] = sum_k router[e][k] * x[t][k]  (fp32 router, bf16 tokens).
+// Reference: `router.float() @ x.float()` per token, megabench/tasks/frontier.py:343.
+//
+// Arithmetic: every lane sums its own channels (H/32 of them, in order) with fp32 FMAs; the 32
+// lane partials, and the warp partials where a row is split over warps, are then combined with
+// error-free two-float (hi + lo) sums, so only the short per-lane chains round. At the magnitudes
+// of this layer that is an absolute error of about 1e-7 on a logit, two orders below the decision
+// margin the input audit enforces. The summation order is fixed by the thread layout, so results
+// are bit-reproducible from run to run. (fp64 accumulation would be simpler but runs at a few
+// FMAs per clock per SM on this GPU and made the router the slowest small stage.)
+#include "common.cuh"
+#include "kernels.h"
+
+namespace moe {
+
+constexpr int kLogitWarps = 8;
+constexpr int kLogitTokens = 8;    // tokens per block
+
+struct Sum2 {
+  float hi, lo;
+};
+__device__ __forceinline__ float fma4(const float4& r, const uint2& raw, float acc) {
+  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+  const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  acc = fmaf(r.x, __bfloat162float(lo.x), acc);
+  acc = fmaf(r.y, __bfloat162float(lo.y), acc);
+  acc = fmaf(r.z, __bfloat162float(hi.x), acc);
+  acc = fmaf(r.w, __bfloat162float(hi.y), acc);
+  return acc;
+}
+// a + b in two-float arithmetic; symmetric in its arguments, so a butterfly leaves the same bits
+// in every lane.
+__device__ __forceinline__ Sum2 sum2_merge(const Sum2& a, const Sum2& b) {
+  const float t = __fadd_rn(a.hi, b.hi);
+  const float bb = __fsub_rn(t, a.hi);
+  const float err = __fadd_rn(__fsub_rn(a.hi, __fsub_rn(t, bb)), __fsub_rn(b.hi, bb));
+  return Sum2{t, __fadd_rn(__fadd_rn(a.lo, b.lo), err)};
+}
+__device__ __forceinline__ Sum2 warp_total(float lane_sum) {
+  Sum2 s{lane_sum, 0.f};
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    Sum2 o;
+    o.hi = __shfl_xor_sync(0xffffffffu, s.hi, off);
+    o.lo = __shfl_xor_sync(0xffffffffu, s.lo, off);
+    s = sum2_merge(s, o);
+  }
+  return s;
+}
+
+// Up to 8 tokens: block b owns expert b; the 128-channel pieces of its router row are dealt
+// round-robin to the 8 warps, so every SM has loads in flight even at batch 1.
+template <int TT>
+__global__ void __launch_bounds__(kLogitWarps * 32) router_logits_small_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                               const float* __restrict__ router,
+                                                                               int tokens, int experts, int hidden,
+                                                                               float* __restrict__ logits) {
+  __shared__ Sum2 part[kLogitWarps][TT];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int e = blockIdx.x;
+  const int t0 = blockIdx.y * TT;
+  const int tcount = min(TT, tokens - t0);
+  float acc[TT];
+#pragma unroll
+  for (int t = 0; t < TT; ++t) acc[t] = 0.f;
+  const float* row = router + static_cast<size_t>(e) * hidden;
+  const int pieces = hidden / 128;
+  constexpr int kAhead = 4;      // pieces whose loads are issued together
+  for (int c0 = warp; c0 < pieces; c0 += kLogitWarps * kAhead) {
+    float4 r[kAhead];
+    uint2 xv[kAhead][TT];
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      const int c = c0 + u * kLogitWarps;
+      const int k = c * 128 + lane * 4;
+      r[u] = c < pieces ? *reinterpret_cast<const float4*>(row + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int t = 0; t < TT; ++t)
+        xv[u][t] = (c < pieces && t < tcount)
+                       ? *reinterpret_cast<const uint2*>(x + static_cast<size_t>(t0 + t) * hidden + k)
+                       : make_uint2(0u, 0u);
+    }
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+#pragma unroll
+      for (int t = 0; t < TT; ++t) acc[t] = fma4(r[u], xv[u][t], acc[t]);   // missing pieces/rows are zeros
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < TT; ++t) {
+    if (t < tcount) {
+      const Sum2 v = warp_total(acc[t]);
+      if (lane == 0) part[warp][t] = v;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < tcount) {
+    Sum2 v = part[0][threadIdx.x];
+#pragma unroll
+    for (int w = 1; w < kLogitWarps; ++w) v = sum2_merge(v, part[w][threadIdx.x]);
+    logits[static_cast<size_t>(t0 + threadIdx.x) * experts + e] = __fadd_rn(v.hi, v.lo);
+  }
+}
+
+// Larger batches: a block keeps 8 token rows in shared memory and streams 16 router rows (two per
+// warp) against them, so x is read from L2 once per block.
+constexpr int kTiledExpertsPerWarp = 2;
+constexpr int kTiledExperts = kLogitWarps * kTiledExpertsPerWarp;
+
+__global__ void __launch_bounds__(kLogitWarps * 32) router_logits_tiled_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                               const float* __restrict__ router,
+                                                                               int tokens, int experts, int hidden,
+                                                                               float* __restrict__ logits) {
+  extern __shared__ __align__(128) uint2 s_x[];                   // [8][hidden / 4], four bf16 per entry
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int quads = hidden / 4;
+  const int t0 = blockIdx.y * kLogitTokens;
+  const int tcount = min(kLogitTokens, tokens - t0);
+  // Token rows arrive by bulk async copies (one per row, 16-byte aligned by the launcher's check);
+  // rows past the batch are zero-filled by the threads.
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t row_bytes = static_cast<uint32_t>(hidden) * 2u;
+    mbar_expect_tx(&bar, row_bytes * tcount);
+    for (int t = 0; t < tcount; ++t)
+      bulk_copy_g2s(s_x + static_cast<size_t>(t) * quads, x + static_cast<size_t>(t0 + t) * hidden, row_bytes, &bar);
+  }
+  for (int i = tcount * quads + threadIdx.x; i < kLogitTokens * quads; i += blockDim.x) s_x[i] = make_uint2(0u, 0u);
+  mbar_wait(&bar, 0);           // bounded; a copy that never lands leaves wrong logits, not a hang
+  __syncthreads();
+  const int e0 = blockIdx.x * kTiledExperts + warp * kTiledExpertsPerWarp;
+  float acc[kTiledExpertsPerWarp][kLogitTokens];
+#pragma unroll
+  for (int j = 0; j < kTiledExpertsPerWarp; ++j)
+#pragma unroll
+    for (int t = 0; t < kLogitTokens; ++t) acc[j][t] = 0.f;
+  // Four 128-channel pieces per trip: all router loads of a trip are issued before the first
+  // use, so a warp keeps 4 KB in flight instead of waiting out one L2 round trip per piece.
+  constexpr int kAhead = 4;
+  for (int q0 = lane; q0 < quads; q0 += 32 * kAhead) {
+    float4 r[kAhead][kTiledExpertsPerWarp];
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u)
+#pragma unroll
+      for (int j = 0; j < kTiledExpertsPerWarp; ++j) {
+        const int q = q0 + 32 * u;
+        r[u][j] = (q < quads && e0 + j < experts)
+                      ? *reinterpret_cast<const float4*>(router + static_cast<size_t>(e0 + j) * hidden + 4 * q)
+                      : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      const int q = q0 + 32 * u;
+      if (q < quads) {
+#pragma unroll
+        for (int t = 0; t < kLogitTokens; ++t) {
+          const uint2 raw = s_x[t * quads + q];
+#pragma unroll
+          for (int j = 0; j < kTiledExpertsPerWarp; ++j) acc[j][t] = fma4(r[u][j], raw, acc[j][t]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kTiledExpertsPerWarp; ++j)
+#pragma unroll
+    for (int t = 0; t < kLogitTokens; ++t) {
+      if (t < tcount) {
+        const Sum2 v = warp_total(acc[j][t]);
+        if (lane == 0 && e0 + j < experts)
+          logits[static_cast<size_t>(t0 + t) * experts + e0 + j] = __fadd_rn(v.hi, v.lo);
+      }
+    }
+}
+
+cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* router, int tokens, int experts, int hidden,
+                                 float* logits, cudaStream_t stream) {
+  const int token_tiles = (tokens + kLogitTokens - 1) / kLogitTokens;
+  const size_t tile_smem = static_cast<size_t>(kLogitTokens) * hidden * sizeof(__nv_bfloat16);
+  if (token_tiles == 1 || tile_smem > 200 * 1024 || (reinterpret_cast<uintptr_t>(x) & 15) || hidden % 8) {
+    if (tokens == 1) {
+      router_logits_small_kernel<1><<<dim3(experts, 1), kLogitWarps * 32, 0, stream>>>(x, router, tokens, experts, hidden, logits);
+    } else if (tokens <= 4) {
+      router_logits_small_kernel<4><<<dim3(experts, 1), kLogitWarps * 32, 0, stream>>>(x, router, tokens, experts, hidden, logits);
+    } else {
+      router_logits_small_kernel<kLogitTokens><<<dim3(experts, token_tiles), kLogitWarps * 32, 0, stream>>>(x, router, tokens, experts, hidden, logits);
+    }
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(router_logits_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           200 * 1024);
+      if (e != cudaSuccess) return e;
+      configured = true;
+    }
+    dim3 grid((experts + kTiledExperts - 1) / kTiledExperts, token_tiles);
+    router_logits_tiled_kernel<<<grid, kLogitWarps * 32, tile_smem, stream>>>(x, router, tokens, experts, hidden, logits);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace moe
