@@ -149,6 +149,53 @@ int moe_layer_forward(const moe_config_t* cfg, const moe_weights_t* weights, con
                       void* y_bf16, int64_t* expert_ids, float* topk_weights, int64_t* order, void* workspace,
                       size_t workspace_bytes, void* stream);
 
+/* ---- expert parallelism over the GPUs of one node ------------------------------------------
+ * Rank r owns experts [r*E/world, (r+1)*E/world) and `tokens` rows of the batch; router, bias and
+ * shared expert are replicated (megabench/tasks/megamoe.py:100-105, megabench/tasks/kimi_layer.py:4-6).
+ * Replaces exchange_counts/exchange (megabench/tasks/parallel.py:52-68) and the dispatch/combine
+ * skeleton of megabench/tasks/megamoe.py:153-182: routed rows are quantised and stored straight
+ * into the owning rank's receive buffer by the dispatching kernel (peer stores over NVLink), counts
+ * travel with the data, arrival is signalled by per-source flags that the consumer polls with a
+ * bounded wait; results come back the same way into the source's slot rows. No host
+ * synchronisation and no NCCL call inside a layer call.
+ *
+ * Every rank allocates one exchange buffer of moe_ep_layout().exchange_bytes (zero-filled once)
+ * that its peers can address (moe_ep_buffer_* below, or any other peer-mapped allocation), and
+ * passes the array of all ranks' buffer addresses as seen from this process. */
+typedef struct moe_ep_layout {
+  uint64_t exchange_bytes;   /* peer-visible buffer of every rank */
+  uint64_t local_bytes;      /* private scratch of every rank (256-byte aligned) */
+  uint64_t flags_dispatch;   /* offsets inside the exchange buffer: uint64[world], one per source */
+  uint64_t flags_return;     /* uint64[world], one per owner */
+  uint64_t recv_count;       /* int32[world] rows received from each source */
+  uint64_t recv_expert;      /* int32[world*cap] local expert id of every received row */
+  uint64_t recv_slot;        /* int32[world*cap] slot row (token*topk+slot) at the source */
+  uint64_t recv_q;           /* e4m3 [world*cap, H] */
+  uint64_t recv_s;           /* fp32 [world*cap, H/128] */
+  uint64_t slots;            /* bf16 [cap + max_tokens, H] down-projection rows coming home */
+  int32_t cap;               /* rows one source can send to one owner: max_tokens*topk */
+  int32_t rows;              /* world*cap + max_tokens: rows this rank may have to multiply */
+  int32_t max_chunks;
+  int32_t token_tile;
+} moe_ep_layout_t;
+
+int moe_ep_layout(const moe_config_t* cfg, int32_t max_tokens, moe_ep_layout_t* layout);
+
+/* One layer call of this rank. `exchange` is void*[world]: every rank's exchange buffer (own one at
+ * index ep_rank). `epoch` must increase by one with every call and be the same on all ranks.
+ * x bf16 [tokens, H] -> y bf16 [tokens, H]; expert_ids / topk_weights optional as in moe_layer_forward.
+ * On a bounded wait running out the call still returns; moe_device_status(local, ...) reports it. */
+int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* weights, const void* x_bf16, int32_t tokens,
+                   int32_t max_tokens, void* y_bf16, int64_t* expert_ids, float* topk_weights,
+                   void* const* exchange, void* local, size_t local_bytes, uint64_t epoch, void* stream);
+
+/* Peer-visible device memory for the exchange buffer (cudaMalloc + CUDA IPC): allocate and export
+ * a 64-byte handle, open a peer's handle (enables peer access), close, free. */
+int moe_ep_buffer_alloc(size_t bytes, void** ptr, void* handle64);
+int moe_ep_buffer_open(const void* handle64, void** ptr);
+int moe_ep_buffer_close(void* ptr);
+int moe_ep_buffer_free(void* ptr);
+
 /* Synchronises `stream` and returns the device status word of the workspace: MOE_OK, or
  * MOE_ERR_DEVICE_TIMEOUT / MOE_ERR_DEVICE_BOUNDS when a kernel gave up on a bounded wait or
  * refused an out-of-range index. *detail (may be NULL) receives a code naming the place. */

@@ -1,0 +1,57 @@
+"""Rank program of the multi-GPU expert-parallel test (one process per GPU, launched by
+torch.distributed.run). Every rank also runs the whole problem on its own GPU with the one-GPU
+layer; its expert-parallel rows must equal the matching rows of that result bit for bit, for
+several calls in a row (fresh inputs every call, exchange buffers reused)."""
+
+import json
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+from tests import helpers as H  # noqa: E402
+from vibe_megakernel_b200 import ep, synthetic  # noqa: E402
+from vibe_megakernel_b200.layer import LayerConfig, MoeLayer  # noqa: E402
+
+
+def main(out_path: str) -> None:
+    rank = int(os.environ["RANK"])
+    local_rank = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("gloo")
+    world = dist.get_world_size()
+    dev = torch.device("cuda", local_rank)
+    report = {}
+    for name, tokens_per_rank, calls in (("ds_small", 5, 3), ("kimi_small", 16, 2), ("qwen_small", 40, 2), ("tiny", 2, 2)):
+        geo = H.small_geometries()[name]
+        if geo.experts % world:
+            continue
+        config = LayerConfig.from_geometry(geo)
+        layer = ep.EpMoeLayer(config, max_tokens=tokens_per_rank, device=dev)
+        single = MoeLayer(config, max_tokens=tokens_per_rank * world, device=dev)
+        ok = True
+        for call in range(calls):
+            full = {k: v.to(dev) for k, v in synthetic.make_inputs(geo, tokens_per_rank * world, call, "cpu").items()}
+            mine = ep.shard_inputs(full, geo.experts, world, rank, tokens_per_rank)
+            got = layer.forward(mine, check_status=True)
+            want = single.forward(full, check_status=True)
+            rows = slice(rank * tokens_per_rank, (rank + 1) * tokens_per_rank)
+            ok = ok and torch.equal(got["y"], want["y"][rows]) and torch.equal(got["expert_ids"], want["expert_ids"][rows])
+            ok = ok and torch.equal(got["topk_weights"], want["topk_weights"][rows])
+        flags = [None] * world
+        dist.all_gather_object(flags, bool(ok))
+        report[name] = flags
+        layer.close()
+    if rank == 0:
+        Path(out_path).write_text(json.dumps(report))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main(sys.argv[1])

@@ -40,7 +40,24 @@ class Layout(C.Structure):
         ("rows", C.c_int32), ("max_chunks", C.c_int32), ("token_tile", C.c_int32), ("reserved", C.c_int32)]
 
 
+EP_LAYOUT_OFFSETS = ("exchange_bytes", "local_bytes", "flags_dispatch", "flags_return", "recv_count", "recv_expert",
+                     "recv_slot", "recv_q", "recv_s", "slots")
+
+
+class EpLayout(C.Structure):
+    _fields_ = [(name, C.c_uint64) for name in EP_LAYOUT_OFFSETS] + [
+        ("cap", C.c_int32), ("rows", C.c_int32), ("max_chunks", C.c_int32), ("token_tile", C.c_int32)]
+
+
 EXPORTS = {
+    "moe_ep_layout": (C.c_int, [C.POINTER(Config), C.c_int32, C.POINTER(EpLayout)]),
+    "moe_ep_forward": (C.c_int, [C.POINTER(Config), C.POINTER(Weights), C.c_void_p, C.c_int32, C.c_int32, C.c_void_p,
+                                 C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_void_p, C.c_size_t, C.c_uint64,
+                                 C.c_void_p]),
+    "moe_ep_buffer_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]),
+    "moe_ep_buffer_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "moe_ep_buffer_close": (C.c_int, [C.c_void_p]),
+    "moe_ep_buffer_free": (C.c_int, [C.c_void_p]),
     "moe_workspace_layout": (C.c_int, [C.POINTER(Config), C.c_int32, C.POINTER(Layout)]),
     "moe_route": (C.c_int, [C.POINTER(Config), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p,
                             C.c_void_p, C.c_size_t, C.c_void_p]),

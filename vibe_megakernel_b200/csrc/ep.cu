@@ -1,0 +1,479 @@
+// Expert-parallel layer: dispatch and return of routed rows as peer stores from inside the kernels.
+//
+// Reference: megabench/tasks/megamoe.py:153-182 (owner order, all-to-all dispatch, local experts,
+// all-to-all back, slot-order combine) with megabench/tasks/parallel.py:52-68 as the collective.
+// Here the source rank's quantiser kernel writes each routed row (e4m3 payload, fp32 group scales,
+// local expert id, slot row to return to) directly into the owner's receive buffer at a position
+// that depends only on (source rank, token, slot) order; the last block to finish publishes the
+// row counts and raises one flag per destination. The owner polls the flags of all sources with a
+// bounded wait, groups the arrivals by expert (same stable counting sort as on one GPU), runs the
+// grouped GEMMs, and a return kernel stores every finished row into its source's slot buffer and
+// raises the return flags; the source combines once all owners have reported.
+//
+// A row's result does not depend on the other rows multiplied with it (every token is its own MMA
+// column with a fixed K order), so expert-parallel results equal single-GPU results bit for bit
+// whatever the arrival order.
+//
+// Waits give up after 2 s and report MOE_ERR_DEVICE_TIMEOUT; nothing spins forever.
+#include <algorithm>
+#include <cstring>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace moe {
+
+struct EpLocal {       // offsets inside the private scratch
+  uint64_t status, counters, logits, topk_ids, topk_weights, xq_home, xs_home, counts, offsets, n_chunks, chunks,
+      row_source, xq, xs, aq, as, out, total;
+};
+
+static inline uint64_t up256(uint64_t v) { return (v + 255) / 256 * 256; }
+
+static int ep_token_tile(int rows_per_expert_max) {
+  return rows_per_expert_max <= 16 ? 16 : rows_per_expert_max <= 32 ? 32 : 64;
+}
+
+static void ep_layouts(const moe_config_t& c, int max_tokens, moe_ep_layout_t* L, EpLocal* P) {
+  const int world = c.ep_world;
+  const int n_local = c.n_experts / world;
+  const uint64_t H = c.hidden, I = c.inter;
+  const int cap = max_tokens * c.topk;
+  const int rows = world * cap + max_tokens;
+  const int tile = ep_token_tile(world * max_tokens);
+  const int max_chunks = std::min(world * cap, n_local) + world * cap / tile + (max_tokens + tile - 1) / tile + 1;
+  uint64_t off = 0;
+  auto take = [&](uint64_t bytes) { const uint64_t at = off; off = up256(off + bytes); return at; };
+  std::memset(L, 0, sizeof(*L));
+  L->flags_dispatch = take(8ull * world);
+  L->flags_return = take(8ull * world);
+  L->recv_count = take(4ull * world);
+  L->recv_expert = take(4ull * world * cap);
+  L->recv_slot = take(4ull * world * cap);
+  L->recv_q = take(static_cast<uint64_t>(world) * cap * H);
+  L->recv_s = take(4ull * world * cap * (H / 128));
+  L->slots = take(2ull * (cap + max_tokens) * H);
+  L->exchange_bytes = off;
+  L->cap = cap;
+  L->rows = rows;
+  L->max_chunks = max_chunks;
+  L->token_tile = tile;
+  off = 0;
+  P->status = take(32);
+  P->counters = take(32);
+  P->logits = take(4ull * max_tokens * c.n_experts);
+  P->topk_ids = take(4ull * cap);
+  P->topk_weights = take(4ull * cap);
+  P->xq_home = take(static_cast<uint64_t>(max_tokens) * H);
+  P->xs_home = take(4ull * max_tokens * (H / 128));
+  P->counts = take(4ull * (n_local + 1));
+  P->offsets = take(4ull * (n_local + 2));
+  P->n_chunks = take(4);
+  P->chunks = take(16ull * max_chunks);
+  P->row_source = take(4ull * rows);
+  P->xq = take(static_cast<uint64_t>(rows) * H);
+  P->xs = take(4ull * rows * (H / 128));
+  P->aq = take(static_cast<uint64_t>(rows) * I);
+  P->as = take(4ull * rows * (I / 128));
+  P->out = take(2ull * rows * H);
+  P->total = off;
+  L->local_bytes = off;
+}
+
+__device__ __forceinline__ void store_release_sys(uint64_t* p, uint64_t v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t load_acquire_sys(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+struct Peers {
+  uint8_t* base[8];
+};
+
+// ---- dispatch: quantise each routed row and store it into its owner's receive buffer -----------
+struct DispatchArgs {
+  const __nv_bfloat16* x;
+  const int32_t* ids;        // [tokens*topk] global expert ids, (token, slot) order
+  int tokens, hidden, topk, world, rank, n_local, cap;
+  Peers peers;
+  uint64_t off_count, off_expert, off_slot, off_q, off_s, off_flags;
+  uint8_t* xq_home;          // local copy for the shared expert: [tokens, H]
+  float* xs_home;
+  int32_t* done;
+  uint64_t epoch;
+};
+
+__global__ void __launch_bounds__(256) ep_dispatch_kernel(DispatchArgs a) {
+  __shared__ int s_part[8];
+  __shared__ int s_counts[8];
+  __shared__ int s_last;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int routed = a.tokens * a.topk;
+  const int r = blockIdx.x;
+  const int H = a.hidden, G = H / kGroup;
+  int t;
+  uint8_t* dst_q;
+  float* dst_s;
+  if (r < routed) {
+    t = r / a.topk;
+    const int e = a.ids[r];
+    const int d = e / a.n_local;
+    int before = 0;                      // earlier rows of this rank bound for the same owner
+    for (int q = tid; q < r; q += 256) before += (a.ids[q] / a.n_local == d);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) before += __shfl_xor_sync(0xffffffffu, before, off);
+    if (lane == 0) s_part[warp] = before;
+    __syncthreads();
+    int j = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) j += s_part[w];
+    const size_t row = static_cast<size_t>(a.rank) * a.cap + j;
+    uint8_t* peer = a.peers.base[d];
+    dst_q = peer + a.off_q + row * H;
+    dst_s = reinterpret_cast<float*>(peer + a.off_s) + row * G;
+    if (tid == 0) {
+      reinterpret_cast<int32_t*>(peer + a.off_expert)[row] = e - d * a.n_local;
+      reinterpret_cast<int32_t*>(peer + a.off_slot)[row] = r;
+    }
+  } else {
+    t = r - routed;
+    dst_q = a.xq_home + static_cast<size_t>(t) * H;
+    dst_s = a.xs_home + static_cast<size_t>(t) * G;
+  }
+  // per-row, per-128-channel e4m3 quantiser (megabench/tasks/quantization.py:87-109), one warp per group
+  const __nv_bfloat16* in = a.x + static_cast<size_t>(t) * H;
+  for (int g = warp; g < G; g += 8) {
+    const int k = g * kGroup + lane * 4;
+    const uint2 raw = *reinterpret_cast<const uint2*>(in + k);
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    const float v0 = __bfloat162float(lo.x), v1 = __bfloat162float(lo.y);
+    const float v2 = __bfloat162float(hi.x), v3 = __bfloat162float(hi.y);
+    float amax = fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    const float scale = group_scale(amax);
+    const uint32_t packed = static_cast<uint32_t>(to_e4m3(v0, scale)) | static_cast<uint32_t>(to_e4m3(v1, scale)) << 8 |
+                            static_cast<uint32_t>(to_e4m3(v2, scale)) << 16 |
+                            static_cast<uint32_t>(to_e4m3(v3, scale)) << 24;
+    *reinterpret_cast<uint32_t*>(dst_q + k) = packed;
+    if (lane == 0) dst_s[g] = scale;
+  }
+  // the last block to finish publishes the counts and raises one flag per owner
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) s_last = (atomicAdd(a.done, 1) == static_cast<int>(gridDim.x) - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence_system();
+  if (tid < 8) s_counts[tid] = 0;
+  __syncthreads();
+  for (int q = tid; q < routed; q += 256) atomicAdd(&s_counts[a.ids[q] / a.n_local], 1);
+  __syncthreads();
+  if (tid < a.world) {
+    uint8_t* peer = a.peers.base[tid];
+    reinterpret_cast<int32_t*>(peer + a.off_count)[a.rank] = s_counts[tid];
+    __threadfence_system();
+    store_release_sys(reinterpret_cast<uint64_t*>(peer + a.off_flags) + a.rank, a.epoch);
+  }
+  if (tid == 0) *a.done = 0;
+}
+
+// ---- bounded wait for `world` flags to reach `epoch` --------------------------------------------
+__global__ void ep_wait_kernel(const uint64_t* flags, int world, uint64_t epoch, int32_t* status, int detail) {
+  const int tid = threadIdx.x;
+  if (tid >= world) return;
+  const uint64_t t0 = globaltimer();
+  while (load_acquire_sys(flags + tid) < epoch) {
+    if (globaltimer() - t0 > kWaitNs) {
+      report(status, MOE_ERR_DEVICE_TIMEOUT, detail + tid);
+      break;
+    }
+    __nanosleep(64);
+  }
+}
+
+// ---- owner side: bring arrivals (and the home rows of the shared expert) into expert order ------
+struct GatherArgs {
+  const int32_t* row_source;   // grouped position -> arrival index (routed) or home token (shared)
+  const int32_t* offsets;      // offsets[n_local] = routed rows kept; shared rows follow
+  int n_local, shared_rows, hidden;
+  const uint8_t* recv_q;
+  const float* recv_s;
+  const uint8_t* xq_home;
+  const float* xs_home;
+  uint8_t* xq;
+  float* xs;
+};
+
+__global__ void __launch_bounds__(128) ep_gather_kernel(GatherArgs a) {
+  const int kept = a.offsets[a.n_local];
+  const int pos = blockIdx.x;
+  if (pos >= kept + a.shared_rows) return;
+  const int H = a.hidden, G = H / kGroup;
+  const int src = a.row_source[pos];
+  const uint8_t* q = (pos < kept ? a.recv_q : a.xq_home) + static_cast<size_t>(src) * H;
+  const float* s = (pos < kept ? a.recv_s : a.xs_home) + static_cast<size_t>(src) * G;
+  uint4* dq = reinterpret_cast<uint4*>(a.xq + static_cast<size_t>(pos) * H);
+  for (int i = threadIdx.x; i < H / 16; i += 128) dq[i] = reinterpret_cast<const uint4*>(q)[i];
+  for (int i = threadIdx.x; i < G; i += 128) a.xs[static_cast<size_t>(pos) * G + i] = s[i];
+}
+
+// ---- return: store every finished row into its source's slot buffer, then raise the flags --------
+struct ReturnArgs {
+  const __nv_bfloat16* out;    // [rows, H] grouped order
+  const int32_t* row_source;
+  const int32_t* offsets;
+  const int32_t* recv_slot;
+  int n_local, shared_rows, hidden, cap, world, rank, home_tokens, topk;
+  Peers peers;
+  uint64_t off_slots, off_flags;
+  int32_t* done;
+  uint64_t epoch;
+};
+
+__global__ void __launch_bounds__(128) ep_return_kernel(ReturnArgs a) {
+  __shared__ int s_last;
+  const int kept = a.offsets[a.n_local];
+  const int pos = blockIdx.x;
+  const int H = a.hidden;
+  if (pos < kept + a.shared_rows) {
+    const int src = a.row_source[pos];
+    uint8_t* peer;
+    size_t slot;
+    if (pos < kept) {
+      peer = a.peers.base[src / a.cap];
+      slot = static_cast<size_t>(a.recv_slot[src]);
+    } else {
+      peer = a.peers.base[a.rank];
+      slot = static_cast<size_t>(a.home_tokens) * a.topk + src;
+    }
+    uint4* d = reinterpret_cast<uint4*>(peer + a.off_slots + slot * H * 2);
+    const uint4* s = reinterpret_cast<const uint4*>(a.out + static_cast<size_t>(pos) * H);
+    for (int i = threadIdx.x; i < H / 8; i += 128) d[i] = s[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(a.done, 1) == static_cast<int>(gridDim.x) - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence_system();
+  if (threadIdx.x < a.world)
+    store_release_sys(reinterpret_cast<uint64_t*>(a.peers.base[threadIdx.x] + a.off_flags) + a.rank, a.epoch);
+  if (threadIdx.x == 0) *a.done = 0;
+}
+
+}  // namespace moe
+
+// ---------------------------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+int ep_check(const moe_config_t* c, int max_tokens) {
+  if (!c) return MOE_ERR_BAD_ARG;
+  const int rc = moe_workspace_layout(c, 1, nullptr);      // geometry checks shared with the one-GPU path
+  if (rc != MOE_OK) return rc;
+  if (c->ep_world > 8) return MOE_ERR_UNSUPPORTED;
+  if (max_tokens < 1) return MOE_ERR_BAD_ARG;
+  if (static_cast<int64_t>(c->ep_world) * max_tokens * c->topk > 32768) return MOE_ERR_UNSUPPORTED;
+  return MOE_OK;
+}
+
+inline int cuda_rc(cudaError_t e) { return e == cudaSuccess ? MOE_OK : static_cast<int>(e); }
+
+}  // namespace
+
+extern "C" {
+
+int moe_ep_layout(const moe_config_t* cfg, int32_t max_tokens, moe_ep_layout_t* layout) {
+  const int rc = ep_check(cfg, max_tokens);
+  if (rc) return rc;
+  moe_ep_layout_t L;
+  moe::EpLocal P;
+  moe::ep_layouts(*cfg, max_tokens, &L, &P);
+  if (layout) *layout = L;
+  return MOE_OK;
+}
+
+int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* x_bf16, int32_t tokens,
+                   int32_t max_tokens, void* y_bf16, int64_t* expert_ids, float* topk_weights,
+                   void* const* exchange, void* local, size_t local_bytes, uint64_t epoch, void* stream_) {
+  const int rc = ep_check(cfg, max_tokens);
+  if (rc) return rc;
+  if (!w || !x_bf16 || !y_bf16 || !exchange || !local || tokens < 1 || tokens > max_tokens || epoch == 0)
+    return MOE_ERR_BAD_ARG;
+  if (!w->router || !w->gate || !w->gate_scale || !w->up || !w->up_scale || !w->down || !w->down_scale) return MOE_ERR_BAD_ARG;
+  if (cfg->n_shared && (!w->shared_gate || !w->shared_gate_scale || !w->shared_up || !w->shared_up_scale ||
+                        !w->shared_down || !w->shared_down_scale))
+    return MOE_ERR_BAD_ARG;
+  moe_ep_layout_t L;
+  moe::EpLocal P;
+  moe::ep_layouts(*cfg, max_tokens, &L, &P);
+  if (local_bytes < L.local_bytes) return MOE_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(local) & 255) return MOE_ERR_BAD_ARG;
+  const int world = cfg->ep_world, rank = cfg->ep_rank;
+  moe::Peers peers;
+  for (int i = 0; i < 8; ++i) peers.base[i] = nullptr;
+  for (int i = 0; i < world; ++i) {
+    if (!exchange[i] || (reinterpret_cast<uintptr_t>(exchange[i]) & 255)) return MOE_ERR_BAD_ARG;
+    peers.base[i] = static_cast<uint8_t*>(exchange[i]);
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  uint8_t* ws = static_cast<uint8_t*>(local);
+  uint8_t* mine = peers.base[rank];
+  int32_t* status = reinterpret_cast<int32_t*>(ws + P.status);
+  int32_t* counters = reinterpret_cast<int32_t*>(ws + P.counters);
+  int32_t* ids32 = reinterpret_cast<int32_t*>(ws + P.topk_ids);
+  float* tw = reinterpret_cast<float*>(ws + P.topk_weights);
+  int32_t* offsets = reinterpret_cast<int32_t*>(ws + P.offsets);
+  int32_t* row_source = reinterpret_cast<int32_t*>(ws + P.row_source);
+  const int n_local = cfg->n_experts / world;
+  const int H = cfg->hidden;
+  int launches = 0;
+
+  // counters are only ever left at zero by the kernels; the status word is cleared per call
+  cudaError_t e = cudaMemsetAsync(status, 0, epoch == 1 ? 64 + 256 : 32, stream);
+  if (e != cudaSuccess) return cuda_rc(e);
+
+  // 1. router on the home tokens
+  e = moe::launch_router(*cfg, static_cast<const __nv_bfloat16*>(x_bf16), w->router, w->router_bias, tokens,
+                         reinterpret_cast<float*>(ws + P.logits), ids32, tw, expert_ids, topk_weights, stream, &launches);
+  if (e != cudaSuccess) return cuda_rc(e);
+
+  // 2. quantise + dispatch (peer stores), counts and flags published by the last block
+  moe::DispatchArgs d;
+  d.x = static_cast<const __nv_bfloat16*>(x_bf16);
+  d.ids = ids32;
+  d.tokens = tokens; d.hidden = H; d.topk = cfg->topk; d.world = world; d.rank = rank; d.n_local = n_local; d.cap = L.cap;
+  d.peers = peers;
+  d.off_count = L.recv_count; d.off_expert = L.recv_expert; d.off_slot = L.recv_slot; d.off_q = L.recv_q;
+  d.off_s = L.recv_s; d.off_flags = L.flags_dispatch;
+  d.xq_home = ws + P.xq_home;
+  d.xs_home = reinterpret_cast<float*>(ws + P.xs_home);
+  d.done = counters;
+  d.epoch = epoch;
+  moe::ep_dispatch_kernel<<<tokens * cfg->topk + tokens, 256, 0, stream>>>(d);
+  ++launches;
+
+  // 3. wait for every source, then group the arrivals by expert
+  moe::ep_wait_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<const uint64_t*>(mine + L.flags_dispatch), world, epoch,
+                                            status, 200);
+  ++launches;
+  moe::GroupArgs g;
+  std::memset(&g, 0, sizeof(g));
+  g.ids32 = reinterpret_cast<const int32_t*>(mine + L.recv_expert);
+  g.n = world * L.cap;
+  g.id_base = 0;
+  g.n_local = n_local;
+  g.topk = 1;
+  g.shared_rows = cfg->n_shared ? tokens : 0;
+  g.tile = L.token_tile;
+  g.max_chunks = L.max_chunks;
+  g.counts = reinterpret_cast<int32_t*>(ws + P.counts);
+  g.offsets = offsets;
+  g.n_chunks = reinterpret_cast<int32_t*>(ws + P.n_chunks);
+  g.chunks = reinterpret_cast<moe::Chunk*>(ws + P.chunks);
+  g.row_token = row_source;
+  g.status = status;
+  g.seg_counts = reinterpret_cast<const int32_t*>(mine + L.recv_count);
+  g.seg_cap = L.cap;
+  e = moe::launch_group_rows(g, stream, &launches);
+  if (e != cudaSuccess) return cuda_rc(e);
+
+  moe::GatherArgs ga;
+  ga.row_source = row_source; ga.offsets = offsets; ga.n_local = n_local; ga.shared_rows = g.shared_rows; ga.hidden = H;
+  ga.recv_q = mine + L.recv_q;
+  ga.recv_s = reinterpret_cast<const float*>(mine + L.recv_s);
+  ga.xq_home = ws + P.xq_home;
+  ga.xs_home = reinterpret_cast<const float*>(ws + P.xs_home);
+  ga.xq = ws + P.xq;
+  ga.xs = reinterpret_cast<float*>(ws + P.xs);
+  const int row_blocks = world * L.cap + g.shared_rows;
+  moe::ep_gather_kernel<<<row_blocks, 128, 0, stream>>>(ga);
+  ++launches;
+
+  // 4. grouped GEMMs on the local experts (and the shared expert for the home tokens)
+  moe::GemmArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.tile = L.token_tile;
+  a.n_local = n_local;
+  a.total_rows = L.rows;
+  a.chunks = g.chunks;
+  a.n_chunks = g.n_chunks;
+  a.status = status;
+  int driver_error = 0;
+  a.dual = true;
+  a.k = H; a.m = cfg->inter;
+  a.max_units = L.max_chunks * (cfg->inter / 128);
+  a.act = ws + P.xq; a.act_scale = reinterpret_cast<const float*>(ws + P.xs);
+  a.w_a = w->gate; a.w_a_scale = w->gate_scale; a.w_b = w->up; a.w_b_scale = w->up_scale;
+  a.s_a = w->shared_gate; a.s_a_scale = w->shared_gate_scale; a.s_b = w->shared_up; a.s_b_scale = w->shared_up_scale;
+  a.aq = ws + P.aq; a.as = reinterpret_cast<float*>(ws + P.as);
+  e = cfg->gemm_impl == MOE_GEMM_TCGEN05 ? moe::launch_gemm_tc(a, stream, &launches, &driver_error)
+                                         : moe::launch_gemm_simt(a, stream, &launches);
+  if (driver_error) return MOE_ERR_DRIVER;
+  if (e != cudaSuccess) return cuda_rc(e);
+  a.dual = false;
+  a.k = cfg->inter; a.m = H;
+  a.max_units = L.max_chunks * (H / 128);
+  a.act = ws + P.aq; a.act_scale = reinterpret_cast<const float*>(ws + P.as);
+  a.w_a = w->down; a.w_a_scale = w->down_scale; a.w_b = nullptr; a.w_b_scale = nullptr;
+  a.s_a = w->shared_down; a.s_a_scale = w->shared_down_scale; a.s_b = nullptr; a.s_b_scale = nullptr;
+  a.aq = nullptr; a.as = nullptr;
+  a.out = reinterpret_cast<__nv_bfloat16*>(ws + P.out);
+  a.row_dest = nullptr;
+  e = cfg->gemm_impl == MOE_GEMM_TCGEN05 ? moe::launch_gemm_tc(a, stream, &launches, &driver_error)
+                                         : moe::launch_gemm_simt(a, stream, &launches);
+  if (driver_error) return MOE_ERR_DRIVER;
+  if (e != cudaSuccess) return cuda_rc(e);
+
+  // 5. rows go home (peer stores), flags raised by the last block; 6. wait for all owners, combine
+  moe::ReturnArgs r;
+  r.out = a.out; r.row_source = row_source; r.offsets = offsets;
+  r.recv_slot = reinterpret_cast<const int32_t*>(mine + L.recv_slot);
+  r.n_local = n_local; r.shared_rows = g.shared_rows; r.hidden = H; r.cap = L.cap; r.world = world; r.rank = rank;
+  r.home_tokens = tokens; r.topk = cfg->topk;
+  r.peers = peers;
+  r.off_slots = L.slots; r.off_flags = L.flags_return;
+  r.done = counters + 1;
+  r.epoch = epoch;
+  moe::ep_return_kernel<<<row_blocks, 128, 0, stream>>>(r);
+  ++launches;
+  moe::ep_wait_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<const uint64_t*>(mine + L.flags_return), world, epoch,
+                                            status, 300);
+  ++launches;
+  e = moe::launch_combine(reinterpret_cast<const __nv_bfloat16*>(mine + L.slots), tw, tokens, cfg->topk, H, cfg->n_shared,
+                          static_cast<__nv_bfloat16*>(y_bf16), stream, &launches);
+  return cuda_rc(e);
+}
+
+int moe_ep_buffer_alloc(size_t bytes, void** ptr, void* handle64) {
+  if (!ptr || !handle64 || bytes == 0) return MOE_ERR_BAD_ARG;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaError_t e = cudaMalloc(ptr, bytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaMemset(*ptr, 0, bytes);
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle64), *ptr);
+  if (e != cudaSuccess) {
+    cudaFree(*ptr);
+    *ptr = nullptr;
+  }
+  return cuda_rc(e);
+}
+
+int moe_ep_buffer_open(const void* handle64, void** ptr) {
+  if (!handle64 || !ptr) return MOE_ERR_BAD_ARG;
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle64, sizeof(h));
+  return cuda_rc(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+}
+
+int moe_ep_buffer_close(void* ptr) { return ptr ? cuda_rc(cudaIpcCloseMemHandle(ptr)) : MOE_ERR_BAD_ARG; }
+
+int moe_ep_buffer_free(void* ptr) { return ptr ? cuda_rc(cudaFree(ptr)) : MOE_ERR_BAD_ARG; }
+
+}  // extern "C"

@@ -73,7 +73,7 @@ __device__ __forceinline__ void epilogue_store_rows(const float (&acc)[CPT], int
   for (int n = 0; n < CPT; ++n) {
     const int c = col0 + n;
     if (c < rows) {
-      const size_t dest = static_cast<size_t>(row_dest[row0 + c]);
+      const size_t dest = static_cast<size_t>(row_dest ? row_dest[row0 + c] : row0 + c);   // null = in place
       out[dest * hidden + tile_m * kGroup + m] = __float2bfloat16_rn(acc[n]);
     }
   }

@@ -25,7 +25,10 @@ __global__ void __launch_bounds__(kGroupWarps * 32) group_rows_kernel(GroupArgs 
   for (int r = tid; r < a.n; r += blockDim.x) {
     const long long id = a.ids32 ? static_cast<long long>(a.ids32[r]) : a.ids64[r];
     const long long local = id - a.id_base;
-    const bool mine = local >= 0 && local < a.n_local;
+    // segmented input (expert-parallel arrivals): row r of segment r / seg_cap exists only below
+    // that segment's count
+    const bool present = !a.seg_counts || (r % a.seg_cap) < a.seg_counts[r / a.seg_cap];
+    const bool mine = present && local >= 0 && local < a.n_local;
     s_ids[r] = mine ? static_cast<int16_t>(local) : static_cast<int16_t>(-1);
     if (mine) atomicAdd(&s_count[local], 1);
   }

@@ -36,6 +36,8 @@ struct GroupArgs {
   int32_t* row_dest;      // optional
   int64_t* order;         // optional, [n]
   int32_t* status;        // optional
+  const int32_t* seg_counts;  // optional: rows come in segments of seg_cap, segment s holds seg_counts[s] rows
+  int seg_cap;
 };
 cudaError_t launch_group_rows(const GroupArgs& a, cudaStream_t stream, int* launches);
 

@@ -56,6 +56,26 @@ def _require(t: torch.Tensor, name: str, dtype, shape=None) -> torch.Tensor:
     return t
 
 
+def weights_struct(c: LayerConfig, values: dict[str, torch.Tensor], n_local: int) -> _cabi.Weights:
+    """Checked device pointers of the weight tensors; ``n_local`` experts are held by this rank."""
+    e, h, i = n_local, c.hidden, c.inter
+    f8, f32 = torch.float8_e4m3fn, torch.float32
+    w = _cabi.Weights()
+    w.router = _require(values["router"], "router", f32, (c.experts, h)).data_ptr()
+    bias = values.get("router_bias")
+    w.router_bias = _ptr(_require(bias, "router_bias", f32, (c.experts,))) if bias is not None else None
+    for name, shape, sshape in (("gate", (e, i, h), (e, i // 128, h // 128)), ("up", (e, i, h), (e, i // 128, h // 128)),
+                                ("down", (e, h, i), (e, h // 128, i // 128))):
+        setattr(w, name, _require(values[name], name, f8, shape).data_ptr())
+        setattr(w, name + "_scale", _require(values[name + "_scale"], name + "_scale", f32, sshape).data_ptr())
+    if c.shared:
+        for name, shape, sshape in (("shared_gate", (i, h), (i // 128, h // 128)), ("shared_up", (i, h), (i // 128, h // 128)),
+                                    ("shared_down", (h, i), (h // 128, i // 128))):
+            setattr(w, name, _require(values[name], name, f8, shape).data_ptr())
+            setattr(w, name + "_scale", _require(values[name + "_scale"], name + "_scale", f32, sshape).data_ptr())
+    return w
+
+
 class MoeLayer:
     """One GPU holding every expert. ``forward(values)`` takes the reference's tensor dict."""
 
@@ -86,23 +106,7 @@ class MoeLayer:
         return got
 
     def weights_struct(self, values: dict[str, torch.Tensor]) -> _cabi.Weights:
-        c = self.config
-        e, h, i = c.experts, c.hidden, c.inter
-        f8, f32 = torch.float8_e4m3fn, torch.float32
-        w = _cabi.Weights()
-        w.router = _require(values["router"], "router", f32, (e, h)).data_ptr()
-        bias = values.get("router_bias")
-        w.router_bias = _ptr(_require(bias, "router_bias", f32, (e,))) if bias is not None else None
-        for name, shape, sshape in (("gate", (e, i, h), (e, i // 128, h // 128)), ("up", (e, i, h), (e, i // 128, h // 128)),
-                                    ("down", (e, h, i), (e, h // 128, i // 128))):
-            setattr(w, name, _require(values[name], name, f8, shape).data_ptr())
-            setattr(w, name + "_scale", _require(values[name + "_scale"], name + "_scale", f32, sshape).data_ptr())
-        if c.shared:
-            for name, shape, sshape in (("shared_gate", (i, h), (i // 128, h // 128)), ("shared_up", (i, h), (i // 128, h // 128)),
-                                        ("shared_down", (h, i), (h // 128, i // 128))):
-                setattr(w, name, _require(values[name], name, f8, shape).data_ptr())
-                setattr(w, name + "_scale", _require(values[name + "_scale"], name + "_scale", f32, sshape).data_ptr())
-        return w
+        return weights_struct(self.config, values, self.config.experts)
 
     def forward(self, values: dict[str, torch.Tensor], *, check_status: bool = False) -> dict[str, torch.Tensor]:
         c = self.config
