@@ -51,8 +51,17 @@ def parse_args():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--experts", type=int, default=0, help="shrink the routed expert count (profiling captures only)")
     ap.add_argument("--sample-tokens", type=int, default=1, help="tokens per CPU-oracle step")
     return ap.parse_args()
+
+
+def geometry_of(args):
+    geo = synthetic.GEOMETRIES[args.config]
+    if args.experts:
+        import dataclasses
+        geo = dataclasses.replace(geo, name=f"{geo.name}-e{args.experts}", experts=args.experts)
+    return geo
 
 
 def measured_peaks():
@@ -238,7 +247,7 @@ def measure_batch(geo, values: dict, tokens: int, steps: int, warmup: int, flush
 
 
 def main_single(args) -> dict:
-    geo = synthetic.GEOMETRIES[args.config]
+    geo = geometry_of(args)
     peak, peak_kind = measured_peaks()
     torch.cuda.set_device(0)
     dev = torch.device("cuda:0")
@@ -295,7 +304,7 @@ def main_reference(args) -> dict | None:
     if int(os.environ.get("RANK", "0")) != 0:
         return None
     from oracle import moe_oracle as O
-    geo = synthetic.GEOMETRIES[args.config]
+    geo = geometry_of(args)
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
     spec = O.LayerSpec(geo.hidden, geo.inter, geo.experts, geo.topk, geo.shared, geo.scoring, geo.n_group,
@@ -344,7 +353,8 @@ def main():
         line = main_single(args)
     else:
         from vibe_megakernel_b200 import ep_bench
-        line = ep_bench.run(args)
+        peak, peak_kind = measured_peaks()
+        line = ep_bench.run(args, geometry_of(args), METRIC, peak, peak_kind, ClockSampler)
     if line is not None:
         print(json.dumps(line), flush=True)
 

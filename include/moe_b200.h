@@ -139,6 +139,17 @@ int moe_quantize_rows(const void* x, int32_t dtype, int32_t rows, int32_t width,
 int moe_group_rows(const int64_t* ids, int32_t n, int32_t id_base, int32_t n_local, int64_t* order,
                    int32_t* counts, void* stream);
 
+/* The experts held by this rank applied to rows that are already quantised: gate/up GEMM, SwiGLU,
+ * requantisation, down GEMM; result rows bf16 [n_rows, H] in the order of the input rows.
+ * Replaces `experts(...)` of megabench/tasks/megamoe.py:131-150 for the FP8 block-scaled format
+ * (rows e4m3 [n_rows, H] + fp32 scales [n_rows, H/128]; local_ids int32 [n_rows] in
+ * [0, n_experts/ep_world), or NULL to send every row through the shared expert).
+ * moe_experts_workspace gives the scratch size for n_rows. */
+int moe_experts_workspace(const moe_config_t* cfg, int32_t n_rows, uint64_t* bytes);
+int moe_experts_forward(const moe_config_t* cfg, const moe_weights_t* weights, const uint8_t* rows_q,
+                        const float* rows_scale, const int32_t* local_ids, int32_t n_rows, void* out_bf16,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
 /* Whole layer on one GPU (ep_world == 1): router, permutation, activation quantiser, grouped
  * gate/up GEMM with SwiGLU + requantisation, grouped down GEMM, shared expert, weighted combine.
  * Replaces the MoE block of megabench/tasks/frontier.py:343-353 batched over tokens with the

@@ -16,6 +16,7 @@ sys.path.insert(0, str(ROOT))
 
 from tests import helpers as H  # noqa: E402
 from vibe_megakernel_b200 import ep, synthetic  # noqa: E402
+from vibe_megakernel_b200.ep_collective import EpCollectiveLayer  # noqa: E402
 from vibe_megakernel_b200.layer import LayerConfig, MoeLayer  # noqa: E402
 
 
@@ -23,7 +24,7 @@ def main(out_path: str) -> None:
     rank = int(os.environ["RANK"])
     local_rank = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local_rank)
-    dist.init_process_group("gloo")
+    dist.init_process_group("cpu:gloo,cuda:nccl")
     world = dist.get_world_size()
     dev = torch.device("cuda", local_rank)
     report = {}
@@ -34,6 +35,7 @@ def main(out_path: str) -> None:
         config = LayerConfig.from_geometry(geo)
         layer = ep.EpMoeLayer(config, max_tokens=tokens_per_rank, device=dev)
         single = MoeLayer(config, max_tokens=tokens_per_rank * world, device=dev)
+        collective = EpCollectiveLayer(config, max_tokens=tokens_per_rank, device=dev)   # NCCL all-to-all arm
         ok = True
         for call in range(calls):
             full = {k: v.to(dev) for k, v in synthetic.make_inputs(geo, tokens_per_rank * world, call, "cpu").items()}
@@ -43,6 +45,8 @@ def main(out_path: str) -> None:
             rows = slice(rank * tokens_per_rank, (rank + 1) * tokens_per_rank)
             ok = ok and torch.equal(got["y"], want["y"][rows]) and torch.equal(got["expert_ids"], want["expert_ids"][rows])
             ok = ok and torch.equal(got["topk_weights"], want["topk_weights"][rows])
+            alt = collective.forward(mine)
+            ok = ok and torch.equal(alt["y"], got["y"]) and torch.equal(alt["expert_ids"], got["expert_ids"])
         flags = [None] * world
         dist.all_gather_object(flags, bool(ok))
         report[name] = flags

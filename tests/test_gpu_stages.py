@@ -110,3 +110,32 @@ def test_router_ties_go_to_the_lower_index(api):
     cfg = api.LayerConfig(hidden=128, inter=128, experts=8, topk=3, shared=0, scoring="softmax")
     ids, w = api.MoeLayer(cfg, max_tokens=3).route(x, router, None)
     assert ids.cpu().tolist() == [[0, 1, 2]] * 3
+
+
+# ---------------------------------------------------------------- experts over quantised rows
+@pytest.mark.parametrize("name,n", [("ds_small", 23), ("kimi_small", 150), ("mixtral_small", 70)])
+def test_experts_entry_point_matches_the_oracle_and_the_layer(api, name, n):
+    geo = H.small_geometries()[name]
+    values = synthetic.make_inputs(geo, 8, 3, "cpu")
+    gen = torch.Generator().manual_seed(n)
+    rows = torch.randn((n, geo.hidden), generator=gen).to(torch.bfloat16)
+    ids = torch.randint(0, geo.experts, (n,), generator=gen)
+    ids[: min(n, 70)] = 1                                     # one expert with more rows than a tile
+    q, s = O.quantize_activation(rows)
+    want = torch.empty((n, geo.hidden), dtype=torch.bfloat16)
+    for e in ids.unique().tolist():
+        sel = (ids == e).nonzero().flatten()
+        want[sel], _, _ = O.expert_mlp(q[sel], s[sel], values["gate"][e], values["gate_scale"][e], values["up"][e],
+                                       values["up_scale"][e], values["down"][e], values["down_scale"][e])
+    dev = H.to_device(values, "cuda")
+    config = api.LayerConfig.from_geometry(geo)
+    got = api.experts_forward(config, dev, q.cuda(), s.cuda(), ids.to(torch.int32).cuda())
+    H.assert_y_close(got, want, "expert rows")
+    # a row's result does not depend on its neighbours or its position: any permutation gives the same bits
+    perm = torch.randperm(n, generator=gen)
+    again = api.experts_forward(config, dev, q[perm].cuda(), s[perm].cuda(), ids[perm].to(torch.int32).cuda())
+    assert torch.equal(again.cpu(), got.cpu()[perm])
+    if geo.shared:
+        want_sh, _, _ = O.expert_mlp(q, s, values["shared_gate"], values["shared_gate_scale"], values["shared_up"],
+                                     values["shared_up_scale"], values["shared_down"], values["shared_down_scale"])
+        H.assert_y_close(api.experts_forward(config, dev, q.cuda(), s.cuda(), None), want_sh, "shared expert rows")

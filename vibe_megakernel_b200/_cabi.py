@@ -50,6 +50,9 @@ class EpLayout(C.Structure):
 
 
 EXPORTS = {
+    "moe_experts_workspace": (C.c_int, [C.POINTER(Config), C.c_int32, C.POINTER(C.c_uint64)]),
+    "moe_experts_forward": (C.c_int, [C.POINTER(Config), C.POINTER(Weights), C.c_void_p, C.c_void_p, C.c_void_p,
+                                      C.c_int32, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "moe_ep_layout": (C.c_int, [C.POINTER(Config), C.c_int32, C.POINTER(EpLayout)]),
     "moe_ep_forward": (C.c_int, [C.POINTER(Config), C.POINTER(Weights), C.c_void_p, C.c_int32, C.c_int32, C.c_void_p,
                                  C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_void_p, C.c_size_t, C.c_uint64,

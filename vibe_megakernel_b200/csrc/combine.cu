@@ -13,6 +13,7 @@ namespace moe {
 __global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __restrict__ slots,
                                                       const float* __restrict__ weights, int tokens, int topk,
                                                       int hidden, int shared, __nv_bfloat16* __restrict__ y) {
+  dependent_wait();
   const int t = blockIdx.y;
   const int c = (blockIdx.x * 256 + threadIdx.x) * 8;
   if (c >= hidden) return;
@@ -44,7 +45,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __res
 cudaError_t launch_combine(const __nv_bfloat16* slots, const float* weights, int tokens, int topk, int hidden,
                            int shared, __nv_bfloat16* y, cudaStream_t stream, int* launches) {
   dim3 grid((hidden / 8 + 255) / 256, tokens);
-  combine_kernel<<<grid, 256, 0, stream>>>(slots, weights, tokens, topk, hidden, shared, y);
+  launch_dependent(combine_kernel, grid, dim3(256), 0, stream, slots, weights, tokens, topk, hidden, shared, y);
   if (launches) *launches += 1;
   return cudaGetLastError();
 }

@@ -197,18 +197,6 @@ __global__ void ep_wait_kernel(const uint64_t* flags, int world, uint64_t epoch,
 }
 
 // ---- owner side: bring arrivals (and the home rows of the shared expert) into expert order ------
-struct GatherArgs {
-  const int32_t* row_source;   // grouped position -> arrival index (routed) or home token (shared)
-  const int32_t* offsets;      // offsets[n_local] = routed rows kept; shared rows follow
-  int n_local, shared_rows, hidden;
-  const uint8_t* recv_q;
-  const float* recv_s;
-  const uint8_t* xq_home;
-  const float* xs_home;
-  uint8_t* xq;
-  float* xs;
-};
-
 __global__ void __launch_bounds__(128) ep_gather_kernel(GatherArgs a) {
   const int kept = a.offsets[a.n_local];
   const int pos = blockIdx.x;
@@ -220,6 +208,12 @@ __global__ void __launch_bounds__(128) ep_gather_kernel(GatherArgs a) {
   uint4* dq = reinterpret_cast<uint4*>(a.xq + static_cast<size_t>(pos) * H);
   for (int i = threadIdx.x; i < H / 16; i += 128) dq[i] = reinterpret_cast<const uint4*>(q)[i];
   for (int i = threadIdx.x; i < G; i += 128) a.xs[static_cast<size_t>(pos) * G + i] = s[i];
+}
+
+cudaError_t launch_gather_rows(const GatherArgs& a, int row_blocks, cudaStream_t stream, int* launches) {
+  ep_gather_kernel<<<row_blocks > 0 ? row_blocks : 1, 128, 0, stream>>>(a);
+  if (launches) *launches += 1;
+  return cudaGetLastError();
 }
 
 // ---- return: store every finished row into its source's slot buffer, then raise the flags --------
@@ -393,8 +387,8 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* 
   ga.xq = ws + P.xq;
   ga.xs = reinterpret_cast<float*>(ws + P.xs);
   const int row_blocks = world * L.cap + g.shared_rows;
-  moe::ep_gather_kernel<<<row_blocks, 128, 0, stream>>>(ga);
-  ++launches;
+  e = moe::launch_gather_rows(ga, row_blocks, stream, &launches);
+  if (e != cudaSuccess) return cuda_rc(e);
 
   // 4. grouped GEMMs on the local experts (and the shared expert for the home tokens)
   moe::GemmArgs a;

@@ -32,8 +32,8 @@
 
 namespace moe {
 
-constexpr int kAccStages = 2;
-constexpr int kMaxStages = 8;
+constexpr int kAccStages = 4;         // TMEM accumulators in flight: the MMAs run up to 4 K blocks ahead
+constexpr int kMaxStages = 12;
 constexpr int kMaxSmem = 232448;      // 227 KiB per CTA
 constexpr int kMaxKBlocks = 112;      // K <= 14336
 
@@ -51,13 +51,23 @@ struct GemmCfg {
   // Shared memory after the stage ring, for a contraction of kb K blocks:
   //   2 buffers of { x scales [kb][NT], weight scales [2][kb] }, amax scratch [4][NT],
   //   barriers (2*stages + 4 + 4), 8 words of flags.
-  static constexpr int scale_floats(int kb) { return kb * NT + 2 * kb; }
+  static constexpr int scale_floats(int kb) { return kb * NT + 2 * kb + NT; }   // + destination rows [NT]
   static constexpr int tail_bytes(int kb) { return 2 * scale_floats(kb) * 4 + 4 * NT * 4 + (2 * kMaxStages + 8) * 8 + 64; }
   static constexpr int stages_for(int kb) {
     const int s = (kMaxSmem - 1024 - tail_bytes(kb)) / kStageBytes;
     return s > kMaxStages ? kMaxStages : s;
   }
 };
+
+// Work item u of this CTA's walk, or an empty one past the end (16-byte load).
+__device__ __forceinline__ Chunk load_chunk(const Chunk* chunks, int u, int n_units, int tiles_m) {
+  Chunk c{0, 0, 0, 0};
+  if (u < n_units) {
+    const int4 v = *reinterpret_cast<const int4*>(chunks + u / tiles_m);
+    c.expert = v.x; c.row0 = v.y; c.rows = v.z; c.pad = v.w;
+  }
+  return c;
+}
 
 struct GemmDev {
   const Chunk* chunks;
@@ -123,6 +133,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
 
+  // Everything above touched only shared memory, TMEM and kernel parameters: under a dependent
+  // launch it overlaps the tail of the previous kernel. From here on its results are needed.
+  dependent_wait();
+  dependents_may_launch();
   const int n_chunks = *p.n_chunks;
   const int n_units = n_chunks * p.tiles_m;
 
@@ -133,8 +147,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const uint64_t pol_x = policy_evict_last();
       uint32_t it = 0, s = 0, ph = 0;
       bool ok = true;
+      Chunk next = load_chunk(p.chunks, blockIdx.x, n_units, p.tiles_m);
       for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-        const Chunk ch = p.chunks[u / p.tiles_m];
+        const Chunk ch = next;
+        next = load_chunk(p.chunks, u + gridDim.x, n_units, p.tiles_m);   // in flight during this item
         const int mt = u % p.tiles_m;
         const bool shared_e = ch.expert >= p.n_local;
         const CUtensorMap* ma = shared_e ? &tm_sa : &tm_a;
@@ -165,8 +181,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     if (lane == 0) {
       uint32_t it = 0, s = 0, ph = 0;
       bool ok = true;
+      Chunk next = load_chunk(p.chunks, blockIdx.x, n_units, p.tiles_m);
       for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-        const Chunk ch = p.chunks[u / p.tiles_m];
+        const Chunk ch = next;
+        next = load_chunk(p.chunks, u + gridDim.x, n_units, p.tiles_m);
         const uint32_t idesc = idesc_e4m3(128, ((ch.rows + 15) >> 4) * 16);
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t as = it % kAccStages, aph = (it / kAccStages) & 1u;
@@ -199,18 +217,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     // Each lane waits, loads its share and arrives on its own: no warp-level sync, so a lane that
     // gives up cannot strand the others.
     uint32_t un = 0;
+    Chunk next = load_chunk(p.chunks, blockIdx.x, n_units, p.tiles_m);
     for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++un) {
       const uint32_t b = un & 1u, ph = (un >> 1) & 1u;
+      const Chunk ch = next;
+      next = load_chunk(p.chunks, u + gridDim.x, n_units, p.tiles_m);
       if (!mbar_wait(bar_scempty + b, ph ^ 1u, s_abort)) {
         if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 4); *s_abort = 1; }
         break;
       }
-      const Chunk ch = p.chunks[u / p.tiles_m];
       const int mt = u % p.tiles_m;
       const bool shared_e = ch.expert >= p.n_local;
       float* xs = s_scales + b * sf;            // [kb][NT]
       float* ws = xs + KB * NT;                 // [2][kb]
+      int* sd = reinterpret_cast<int*>(ws + 2 * KB);   // [NT] destination row of every token column
       const int cols = ((ch.rows + 15) >> 4) * 16;
+      if constexpr (!DUAL) {
+        for (int n = lane; n < NT; n += 32)
+          sd[n] = n < ch.rows ? (p.row_dest ? p.row_dest[ch.row0 + n] : ch.row0 + n) : 0;
+      }
       for (int i = lane; i < cols * KB; i += 32) {
         const int n = i / KB, kb = i - n * KB;
         xs[kb * NT + n] = n < ch.rows ? p.act_scale[static_cast<size_t>(ch.row0 + n) * KB + kb] : 0.f;
@@ -234,16 +259,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const uint32_t lane_base = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
     uint32_t it = 0, un = 0;
     bool failed = false;
+    Chunk next = load_chunk(p.chunks, blockIdx.x, n_units, p.tiles_m);
     for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++un) {
-      const Chunk ch = p.chunks[u / p.tiles_m];
+      const Chunk ch = next;
+      next = load_chunk(p.chunks, u + gridDim.x, n_units, p.tiles_m);
       const int mt = u % p.tiles_m;
       const int cols = ((ch.rows + 15) >> 4) * 16;            // token columns that were multiplied
       const uint32_t b = un & 1u, sph = (un >> 1) & 1u;
       const float* xs_all = s_scales + b * sf;
       const float* ws = xs_all + KB * NT;
+      const int* sd = reinterpret_cast<const int*>(ws + 2 * KB);
       if (!failed && !mbar_wait(bar_scfull + b, sph, s_abort)) {
         if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 5); *s_abort = 1; }
         failed = true;
+      }
+      // destination rows were staged by the scale loader together with the scales
+      int dest[DUAL ? 1 : C::kCpt];
+      if constexpr (!DUAL) {
+#pragma unroll
+        for (int n = 0; n < C::kCpt; ++n) dest[n] = sd[col0 + n];
       }
       float acc_a[C::kCpt];
       float acc_b[C::kCpt];
@@ -293,7 +327,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         epilogue_swiglu_requant<C::kCpt, C::kEpiThreads>(acc_a, acc_b, m, col0, NT, ch.rows, ch.row0, mt, p.m, s_amax,
                                                          p.aq, p.as);
       } else {
-        epilogue_store_rows<C::kCpt>(acc_a, m, col0, ch.rows, ch.row0, mt, p.m, p.row_dest, p.out);
+#pragma unroll
+        for (int n = 0; n < C::kCpt; ++n) {
+          if (col0 + n < ch.rows)   // one bf16 rounding of the fp32 sum (megabench/tasks/megamoe.py:149)
+            p.out[static_cast<size_t>(dest[n]) * p.m + mt * kGroup + m] = __float2bfloat16_rn(acc_a[n]);
+        }
       }
       mbar_arrive(bar_scempty + b);   // this item's scales are no longer needed
     }
@@ -361,8 +399,8 @@ static cudaError_t launch_typed(GemmDev dev, const CUtensorMap* maps, int grid, 
   dev.stages = C::stages_for(dev.kblocks);
   if (dev.stages < 2) return cudaErrorInvalidValue;
   const int smem = 1024 + dev.stages * C::kStageBytes + C::tail_bytes(dev.kblocks);
-  grouped_gemm_kernel<NT, DUAL><<<grid, C::kThreads, smem, stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], dev);
-  return cudaGetLastError();
+  return launch_dependent(grouped_gemm_kernel<NT, DUAL>, dim3(grid), dim3(C::kThreads), smem, stream, maps[0], maps[1],
+                          maps[2], maps[3], maps[4], dev);
 }
 
 static int sm_count() {

@@ -19,6 +19,8 @@ __global__ void __launch_bounds__(kGroupWarps * 32) group_rows_kernel(GroupArgs 
   __shared__ int s_chunk0[MOE_MAX_EXPERTS + 2];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int groups = a.n_local + 1;                        // last one is the shared expert
+  dependent_wait();
+  dependents_may_launch();
 
   for (int i = tid; i < groups; i += blockDim.x) s_count[i] = 0;
   __syncthreads();
@@ -128,7 +130,7 @@ cudaError_t launch_group_rows(const GroupArgs& a, cudaStream_t stream, int* laun
     cudaError_t e = cudaFuncSetAttribute(group_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
     if (e != cudaSuccess) return e;
   }
-  group_rows_kernel<<<blocks, kGroupWarps * 32, smem, stream>>>(a);
+  launch_dependent(group_rows_kernel, dim3(blocks), dim3(kGroupWarps * 32), smem, stream, a);
   if (launches) *launches += 1;
   return cudaGetLastError();
 }

@@ -8,9 +8,29 @@
 
 #include "../../include/moe_b200.h"
 
+#include <utility>
+
 namespace moe {
 
 struct Chunk;
+
+// Launch with programmatic stream serialization: the kernel may start while the previous kernel of
+// the stream drains; it must call dependent_wait() before reading what that kernel wrote.
+template <typename... Params, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 cudaError_t launch_router(const moe_config_t& cfg, const __nv_bfloat16* x, const float* router, const float* bias,
                           int tokens, float* logits, int32_t* ids32, float* weights, int64_t* ids64,
@@ -46,6 +66,20 @@ cudaError_t launch_quantize(const void* x, int dtype, int rows, int width, const
 
 cudaError_t launch_combine(const __nv_bfloat16* slots, const float* weights, int tokens, int topk, int hidden,
                            int shared, __nv_bfloat16* y, cudaStream_t stream, int* launches);
+
+// Copy rows that arrived in any order (and the home rows of the shared expert) into expert order.
+struct GatherArgs {
+  const int32_t* row_source;   // grouped position -> arrival index (routed) or home token (shared)
+  const int32_t* offsets;      // offsets[n_local] = routed rows kept; shared rows follow
+  int n_local, shared_rows, hidden;
+  const uint8_t* recv_q;       // arrivals: e4m3 [*, H] and fp32 scales [*, H/128]
+  const float* recv_s;
+  const uint8_t* xq_home;      // rows of the shared expert
+  const float* xs_home;
+  uint8_t* xq;                 // grouped output
+  float* xs;
+};
+cudaError_t launch_gather_rows(const GatherArgs& a, int row_blocks, cudaStream_t stream, int* launches);
 
 struct GemmArgs {
   bool dual;                 // true: gate+up with SwiGLU + requantisation; false: down projection

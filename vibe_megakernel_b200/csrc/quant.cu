@@ -20,6 +20,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) quantize_rows_kernel(const T* __restrict__ x, int rows, int width,
                                                             const int32_t* __restrict__ gather,
                                                             uint8_t* __restrict__ q, float* __restrict__ scales) {
+  dependent_wait();
+  dependents_may_launch();
   const int groups = (width + kGroup - 1) / kGroup;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = static_cast<long long>(blockIdx.x) * 8 + warp;   // (row, group) pair
@@ -55,11 +57,11 @@ cudaError_t launch_quantize(const void* x, int dtype, int rows, int width, const
   const long long items = static_cast<long long>(rows) * ((width + kGroup - 1) / kGroup);
   const unsigned blocks = static_cast<unsigned>((items + 7) / 8);
   if (dtype == 0)
-    quantize_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows, width,
-                                                                    gather, q, scales);
+    launch_dependent(quantize_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
+                     static_cast<const __nv_bfloat16*>(x), rows, width, gather, q, scales);
   else
-    quantize_rows_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(x), rows, width, gather, q,
-                                                            scales);
+    launch_dependent(quantize_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, static_cast<const float*>(x),
+                     rows, width, gather, q, scales);
   if (launches) *launches += 1;
   return cudaGetLastError();
 }

@@ -30,6 +30,8 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_select_kernel(RouteArg
   __shared__ int s_pick[kRouteWarps][MOE_MAX_TOPK];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * kRouteWarps + warp;
+  dependent_wait();
+  dependents_may_launch();
   if (t >= a.tokens) return;
   float* c = s_choice[warp];
   float* p = s_prob[warp];
@@ -125,23 +127,29 @@ template <int EPL>
 __global__ void __launch_bounds__(kRouteWarps * 32) route_select_regs_kernel(RouteArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * kRouteWarps + warp;
+  dependent_wait();
+  dependents_may_launch();
   if (t >= a.tokens) return;
   const int E = a.experts;
   const float ninf = __int_as_float(0xff800000);
   const bool sigmoid = a.scoring == MOE_SCORING_SIGMOID;
   const int e0 = lane * EPL;
-  float p[EPL], c[EPL];
+  float p[EPL], c[EPL], s[EPL], b[EPL];
+  // E == 32 * EPL here, so every lane's run is in range: plain loads, all issued before first use
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) s[i] = __ldg(a.logits + static_cast<size_t>(t) * E + e0 + i);
+  const bool biased = sigmoid && a.bias != nullptr;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) b[i] = biased ? __ldg(a.bias + e0 + i) : 0.f;
 #pragma unroll
   for (int i = 0; i < EPL; ++i) {
-    const int e = e0 + i;
-    const float s = e < E ? a.logits[static_cast<size_t>(t) * E + e] : ninf;
     if (sigmoid) {
-      const float pr = __fdiv_rn(1.f, __fadd_rn(1.f, expf(-s)));
+      const float pr = __fdiv_rn(1.f, __fadd_rn(1.f, expf(-s[i])));
       p[i] = pr;
-      c[i] = e < E ? __fadd_rn(pr, a.bias ? a.bias[e] : 0.f) : ninf;
+      c[i] = __fadd_rn(pr, b[i]);
     } else {
-      p[i] = s;
-      c[i] = s;
+      p[i] = s[i];
+      c[i] = s[i];
     }
   }
   if (sigmoid && a.n_group > 1) {
@@ -239,13 +247,14 @@ cudaError_t launch_router(const moe_config_t& cfg, const __nv_bfloat16* x, const
               cfg.routed_scaling, ids32, weights, ids64, weights_out};
   const int blocks = (tokens + kRouteWarps - 1) / kRouteWarps;
   const int threads = kRouteWarps * 32;
-  if (regs_variant_fits(cfg, 1)) route_select_regs_kernel<1><<<blocks, threads, 0, stream>>>(a);
-  else if (regs_variant_fits(cfg, 2)) route_select_regs_kernel<2><<<blocks, threads, 0, stream>>>(a);
-  else if (regs_variant_fits(cfg, 4)) route_select_regs_kernel<4><<<blocks, threads, 0, stream>>>(a);
-  else if (regs_variant_fits(cfg, 8)) route_select_regs_kernel<8><<<blocks, threads, 0, stream>>>(a);
-  else if (regs_variant_fits(cfg, 12)) route_select_regs_kernel<12><<<blocks, threads, 0, stream>>>(a);
-  else if (regs_variant_fits(cfg, 16)) route_select_regs_kernel<16><<<blocks, threads, 0, stream>>>(a);
-  else route_select_kernel<<<blocks, threads, 0, stream>>>(a);
+  void (*kernel)(RouteArgs) = route_select_kernel;
+  if (regs_variant_fits(cfg, 1)) kernel = route_select_regs_kernel<1>;
+  else if (regs_variant_fits(cfg, 2)) kernel = route_select_regs_kernel<2>;
+  else if (regs_variant_fits(cfg, 4)) kernel = route_select_regs_kernel<4>;
+  else if (regs_variant_fits(cfg, 8)) kernel = route_select_regs_kernel<8>;
+  else if (regs_variant_fits(cfg, 12)) kernel = route_select_regs_kernel<12>;
+  else if (regs_variant_fits(cfg, 16)) kernel = route_select_regs_kernel<16>;
+  launch_dependent(kernel, dim3(blocks), dim3(threads), 0, stream, a);
   if (launches) *launches += 2;
   return cudaGetLastError();
 }

@@ -1,20 +1,19 @@
 // Router logits: logits[t][e] = sum_k router[e][k] * x[t][k]  (fp32 router, bf16 tokens).
 // Reference: `router.float() @ x.float()` per token, megabench/tasks/frontier.py:343.
 //
-// Arithmetic: every lane sums its own channels (H/32 of them, in order) with fp32 FMAs; the 32
-// lane partials, and the warp partials where a row is split over warps, are then combined with
-// error-free two-float (hi + lo) sums, so only the short per-lane chains round. At the magnitudes
-// of this layer that is an absolute error of about 1e-7 on a logit, two orders below the decision
-// margin the input audit enforces. The summation order is fixed by the thread layout, so results
-// are bit-reproducible from run to run. (fp64 accumulation would be simpler but runs at a few
-// FMAs per clock per SM on this GPU and made the router the slowest small stage.)
+// Arithmetic, the same in both kernels so that a token's logits do not depend on the batch it
+// came in: one warp owns one (expert, token) sum; lane l adds channels 4q..4q+3 for
+// q = l, l+32, l+64, ... in that order with fp32 FMAs; the 32 lane partials are combined by a
+// butterfly of error-free two-float (hi + lo) sums and rounded once. Only the short per-lane
+// chains round: an absolute error of about 1e-7 on a logit at the magnitudes of this layer, two
+// orders below the decision margin the input audit enforces. (fp64 accumulation would be simpler
+// but runs at a few FMAs per clock per SM on this GPU and made the router the slowest small stage.)
 #include "common.cuh"
 #include "kernels.h"
 
 namespace moe {
 
-constexpr int kLogitWarps = 8;
-constexpr int kLogitTokens = 8;    // tokens per block
+constexpr int kLogitTokens = 8;    // tokens per block of the tiled kernel
 
 struct Sum2 {
   float hi, lo;
@@ -36,7 +35,7 @@ __device__ __forceinline__ Sum2 sum2_merge(const Sum2& a, const Sum2& b) {
   const float err = __fadd_rn(__fsub_rn(a.hi, __fsub_rn(t, bb)), __fsub_rn(b.hi, bb));
   return Sum2{t, __fadd_rn(__fadd_rn(a.lo, b.lo), err)};
 }
-__device__ __forceinline__ Sum2 warp_total(float lane_sum) {
+__device__ __forceinline__ float warp_total(float lane_sum) {
   Sum2 s{lane_sum, 0.f};
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) {
@@ -45,73 +44,73 @@ __device__ __forceinline__ Sum2 warp_total(float lane_sum) {
     o.lo = __shfl_xor_sync(0xffffffffu, s.lo, off);
     s = sum2_merge(s, o);
   }
-  return s;
+  return __fadd_rn(s.hi, s.lo);
 }
 
-// Up to 8 tokens: block b owns expert b; the 128-channel pieces of its router row are dealt
-// round-robin to the 8 warps, so every SM has loads in flight even at batch 1.
+// Small batches (TT tokens at most): two warps per block, one expert row per warp, so that a
+// 256-expert router still spreads over 128 blocks; each trip issues the loads of 8 pieces of 128
+// channels (4 KB of the router row per warp) before the first use.
+constexpr int kRowsWarps = 2;
+constexpr int kRowsAhead = 8;
+
 template <int TT>
-__global__ void __launch_bounds__(kLogitWarps * 32) router_logits_small_kernel(const __nv_bfloat16* __restrict__ x,
-                                                                               const float* __restrict__ router,
-                                                                               int tokens, int experts, int hidden,
-                                                                               float* __restrict__ logits) {
-  __shared__ Sum2 part[kLogitWarps][TT];
+__global__ void __launch_bounds__(kRowsWarps * 32) router_logits_rows_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                              const float* __restrict__ router,
+                                                                              int tokens, int experts, int hidden,
+                                                                              float* __restrict__ logits) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int e = blockIdx.x;
+  const int e = blockIdx.x * kRowsWarps + warp;
   const int t0 = blockIdx.y * TT;
   const int tcount = min(TT, tokens - t0);
+  dependent_wait();
+  dependents_may_launch();
+  if (e >= experts) return;
   float acc[TT];
 #pragma unroll
   for (int t = 0; t < TT; ++t) acc[t] = 0.f;
   const float* row = router + static_cast<size_t>(e) * hidden;
-  const int pieces = hidden / 128;
-  constexpr int kAhead = 4;      // pieces whose loads are issued together
-  for (int c0 = warp; c0 < pieces; c0 += kLogitWarps * kAhead) {
-    float4 r[kAhead];
-    uint2 xv[kAhead][TT];
+  const int quads = hidden / 4;
+  for (int q0 = lane; q0 < quads; q0 += 32 * kRowsAhead) {
+    float4 r[kRowsAhead];
+    uint2 xv[kRowsAhead][TT];
 #pragma unroll
-    for (int u = 0; u < kAhead; ++u) {
-      const int c = c0 + u * kLogitWarps;
-      const int k = c * 128 + lane * 4;
-      r[u] = c < pieces ? *reinterpret_cast<const float4*>(row + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int u = 0; u < kRowsAhead; ++u) {
+      // unconditional loads from clamped addresses: the compiler can then issue all of a trip's
+      // loads back to back (values loaded past the row or the batch are never used)
+      const int q = min(q0 + 32 * u, quads - 1);
+      r[u] = __ldg(reinterpret_cast<const float4*>(row + 4 * q));
 #pragma unroll
       for (int t = 0; t < TT; ++t)
-        xv[u][t] = (c < pieces && t < tcount)
-                       ? *reinterpret_cast<const uint2*>(x + static_cast<size_t>(t0 + t) * hidden + k)
-                       : make_uint2(0u, 0u);
+        xv[u][t] = __ldg(reinterpret_cast<const uint2*>(x + static_cast<size_t>(t0 + min(t, tcount - 1)) * hidden + 4 * q));
     }
 #pragma unroll
-    for (int u = 0; u < kAhead; ++u) {
+    for (int u = 0; u < kRowsAhead; ++u) {
+      if (q0 + 32 * u < quads) {
 #pragma unroll
-      for (int t = 0; t < TT; ++t) acc[t] = fma4(r[u], xv[u][t], acc[t]);   // missing pieces/rows are zeros
+        for (int t = 0; t < TT; ++t) acc[t] = fma4(r[u], xv[u][t], acc[t]);
+      }
     }
   }
 #pragma unroll
   for (int t = 0; t < TT; ++t) {
     if (t < tcount) {
-      const Sum2 v = warp_total(acc[t]);
-      if (lane == 0) part[warp][t] = v;
+      const float v = warp_total(acc[t]);
+      if (lane == 0) logits[static_cast<size_t>(t0 + t) * experts + e] = v;
     }
-  }
-  __syncthreads();
-  if (threadIdx.x < tcount) {
-    Sum2 v = part[0][threadIdx.x];
-#pragma unroll
-    for (int w = 1; w < kLogitWarps; ++w) v = sum2_merge(v, part[w][threadIdx.x]);
-    logits[static_cast<size_t>(t0 + threadIdx.x) * experts + e] = __fadd_rn(v.hi, v.lo);
   }
 }
 
 // Larger batches: a block keeps 8 token rows in shared memory and streams 16 router rows (two per
 // warp) against them, so x is read from L2 once per block.
+constexpr int kTiledWarps = 8;
 constexpr int kTiledExpertsPerWarp = 2;
-constexpr int kTiledExperts = kLogitWarps * kTiledExpertsPerWarp;
+constexpr int kTiledExperts = kTiledWarps * kTiledExpertsPerWarp;
 
-__global__ void __launch_bounds__(kLogitWarps * 32) router_logits_tiled_kernel(const __nv_bfloat16* __restrict__ x,
+__global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(const __nv_bfloat16* __restrict__ x,
                                                                                const float* __restrict__ router,
                                                                                int tokens, int experts, int hidden,
                                                                                float* __restrict__ logits) {
-  extern __shared__ __align__(128) uint2 s_x[];                   // [8][hidden / 4], four bf16 per entry
+  extern __shared__ __align__(128) uint2 s_x[];        // [8][hidden / 4], four bf16 per entry
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int quads = hidden / 4;
   const int t0 = blockIdx.y * kLogitTokens;
@@ -124,6 +123,8 @@ __global__ void __launch_bounds__(kLogitWarps * 32) router_logits_tiled_kernel(c
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  dependent_wait();
+  dependents_may_launch();
   if (threadIdx.x == 0) {
     const uint32_t row_bytes = static_cast<uint32_t>(hidden) * 2u;
     mbar_expect_tx(&bar, row_bytes * tcount);
@@ -139,8 +140,8 @@ __global__ void __launch_bounds__(kLogitWarps * 32) router_logits_tiled_kernel(c
   for (int j = 0; j < kTiledExpertsPerWarp; ++j)
 #pragma unroll
     for (int t = 0; t < kLogitTokens; ++t) acc[j][t] = 0.f;
-  // Four 128-channel pieces per trip: all router loads of a trip are issued before the first
-  // use, so a warp keeps 4 KB in flight instead of waiting out one L2 round trip per piece.
+  // Four pieces per trip: all router loads of a trip are issued before the first use, so a warp
+  // keeps 4 KB in flight instead of waiting out one L2 round trip per piece.
   constexpr int kAhead = 4;
   for (int q0 = lane; q0 < quads; q0 += 32 * kAhead) {
     float4 r[kAhead][kTiledExpertsPerWarp];
@@ -148,10 +149,9 @@ __global__ void __launch_bounds__(kLogitWarps * 32) router_logits_tiled_kernel(c
     for (int u = 0; u < kAhead; ++u)
 #pragma unroll
       for (int j = 0; j < kTiledExpertsPerWarp; ++j) {
-        const int q = q0 + 32 * u;
-        r[u][j] = (q < quads && e0 + j < experts)
-                      ? *reinterpret_cast<const float4*>(router + static_cast<size_t>(e0 + j) * hidden + 4 * q)
-                      : make_float4(0.f, 0.f, 0.f, 0.f);
+        const int q = min(q0 + 32 * u, quads - 1);       // clamped, unconditional (see the rows kernel)
+        const int e = min(e0 + j, experts - 1);
+        r[u][j] = __ldg(reinterpret_cast<const float4*>(router + static_cast<size_t>(e) * hidden + 4 * q));
       }
 #pragma unroll
     for (int u = 0; u < kAhead; ++u) {
@@ -171,25 +171,27 @@ __global__ void __launch_bounds__(kLogitWarps * 32) router_logits_tiled_kernel(c
 #pragma unroll
     for (int t = 0; t < kLogitTokens; ++t) {
       if (t < tcount) {
-        const Sum2 v = warp_total(acc[j][t]);
-        if (lane == 0 && e0 + j < experts)
-          logits[static_cast<size_t>(t0 + t) * experts + e0 + j] = __fadd_rn(v.hi, v.lo);
+        const float v = warp_total(acc[j][t]);
+        if (lane == 0 && e0 + j < experts) logits[static_cast<size_t>(t0 + t) * experts + e0 + j] = v;
       }
     }
 }
 
 cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* router, int tokens, int experts, int hidden,
                                  float* logits, cudaStream_t stream) {
-  const int token_tiles = (tokens + kLogitTokens - 1) / kLogitTokens;
   const size_t tile_smem = static_cast<size_t>(kLogitTokens) * hidden * sizeof(__nv_bfloat16);
-  if (token_tiles == 1 || tile_smem > 200 * 1024 || (reinterpret_cast<uintptr_t>(x) & 15) || hidden % 8) {
-    if (tokens == 1) {
-      router_logits_small_kernel<1><<<dim3(experts, 1), kLogitWarps * 32, 0, stream>>>(x, router, tokens, experts, hidden, logits);
-    } else if (tokens <= 4) {
-      router_logits_small_kernel<4><<<dim3(experts, 1), kLogitWarps * 32, 0, stream>>>(x, router, tokens, experts, hidden, logits);
-    } else {
-      router_logits_small_kernel<kLogitTokens><<<dim3(experts, token_tiles), kLogitWarps * 32, 0, stream>>>(x, router, tokens, experts, hidden, logits);
-    }
+  const int row_blocks = (experts + kRowsWarps - 1) / kRowsWarps;
+  const bool tiled_ok = tile_smem <= 200 * 1024 && !(reinterpret_cast<uintptr_t>(x) & 15) && hidden % 8 == 0;
+  const dim3 rows_block(kRowsWarps * 32);
+  if (tokens == 1) {
+    launch_dependent(router_logits_rows_kernel<1>, dim3(row_blocks, 1), rows_block, 0, stream, x, router, tokens, experts,
+                     hidden, logits);
+  } else if (tokens <= 4) {
+    launch_dependent(router_logits_rows_kernel<4>, dim3(row_blocks, 1), rows_block, 0, stream, x, router, tokens, experts,
+                     hidden, logits);
+  } else if (tokens <= 8 || !tiled_ok) {
+    launch_dependent(router_logits_rows_kernel<8>, dim3(row_blocks, (tokens + 7) / 8), rows_block, 0, stream, x, router,
+                     tokens, experts, hidden, logits);
   } else {
     static bool configured = false;
     if (!configured) {
@@ -198,8 +200,9 @@ cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* router, in
       if (e != cudaSuccess) return e;
       configured = true;
     }
-    dim3 grid((experts + kTiledExperts - 1) / kTiledExperts, token_tiles);
-    router_logits_tiled_kernel<<<grid, kLogitWarps * 32, tile_smem, stream>>>(x, router, tokens, experts, hidden, logits);
+    dim3 grid((experts + kTiledExperts - 1) / kTiledExperts, (tokens + kLogitTokens - 1) / kLogitTokens);
+    launch_dependent(router_logits_tiled_kernel, grid, dim3(kTiledWarps * 32), tile_smem, stream, x, router, tokens,
+                     experts, hidden, logits);
   }
   return cudaGetLastError();
 }

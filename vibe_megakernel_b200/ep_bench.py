@@ -1,0 +1,156 @@
+"""Benchmark arm for N > 1 GPUs: the same layer, experts sharded over the ranks, the batch split evenly.
+
+Launched by ``python -m torch.distributed.run --nproc-per-node N bench.py --gpus N ...``: one process
+per GPU. Total work is fixed as N grows (strong scaling): every rank holds E/N experts and batch/N
+tokens. Timing: barrier + synchronize, K steps each bracketed by CUDA events on the rank's stream with
+an L2 flush before it, synchronize + barrier; a rank's time is the mean of its step times and the
+reported latency is the maximum over ranks.
+
+Two exchanges are timed on the same inputs: the product path (rows stored into the owner's memory by
+the dispatching kernel, bounded flag waits, no collective call) and the reference's host-driven
+NCCL all-to-all around the same kernels (``ep_collective``), at the headline batch and over the
+configuration's batch sweep.
+"""
+
+from __future__ import annotations
+
+import os
+import time
+
+import torch
+import torch.distributed as dist
+
+from . import synthetic
+from .ep import EpMoeLayer
+from .ep_collective import EpCollectiveLayer
+from .layer import LayerConfig
+
+L2_FLUSH_BYTES = 512 << 20
+LAUNCHES_PER_CALL = 11   # router 2, dispatch, wait, group, gather, 2 GEMMs, return, wait, combine
+
+
+def _reduce(value: float, op) -> float:
+    t = torch.tensor([value], dtype=torch.float64)
+    dist.all_reduce(t, op=op)       # CPU tensor: carried by Gloo
+    return float(t[0])
+
+
+def _timed(fn, steps: int, warmup: int, flush: torch.Tensor) -> float:
+    """Mean step time in ms, maximum over ranks."""
+    for _ in range(warmup):
+        flush.zero_()
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    pairs = []
+    for _ in range(steps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        pairs.append((a, b))
+    torch.cuda.synchronize()
+    dist.barrier()
+    mine = sum(a.elapsed_time(b) for a, b in pairs) / steps
+    return _reduce(mine, dist.ReduceOp.MAX)
+
+
+def run(args, geo, metric: str, peak: float, peak_kind: str, clock_sampler) -> dict | None:
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (torch.distributed.run), got WORLD_SIZE={world}")
+    if args.batch % world or geo.experts % world:
+        raise SystemExit("batch and experts must divide the number of GPUs")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    # Gloo carries set-up objects and the max-over-ranks; NCCL is only used by the comparison arm.
+    dist.init_process_group("cpu:gloo,cuda:nccl", device_id=dev)
+    config = LayerConfig.from_geometry(geo)
+    batches = [args.batch] if args.no_sweep else sorted(
+        {b for b in synthetic.BATCHES[args.config] if b % world == 0 and b >= world} | {args.batch})
+    t0 = time.time()
+    values = synthetic.make_inputs(geo, max(batches) // world, args.seed, dev, rank=rank, world=world)
+    torch.cuda.synchronize()
+    gen_s = time.time() - t0
+    x_all = values["x"]
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+    local = geo.experts // world
+
+    def measure(batch: int, steps: int, warmup: int, full: bool):
+        tokens = batch // world
+        inputs = dict(values)
+        inputs["x"] = x_all[:tokens].contiguous()
+        layer = EpMoeLayer(config, max_tokens=tokens, device=dev)
+        out = layer.forward(inputs, check_status=True)
+        ids_all = [None] * world
+        dist.all_gather_object(ids_all, out["expert_ids"].cpu())
+        ids_all = torch.cat(ids_all)
+        mine_hit = int(torch.unique(ids_all[(ids_all >= rank * local) & (ids_all < (rank + 1) * local)]).numel())
+        rank_bytes = (mine_hit + geo.shared) * geo.expert_bytes() + 4 * geo.experts * geo.hidden + 4 * tokens * geo.hidden
+        busiest = _reduce(float(rank_bytes), dist.ReduceOp.MAX)
+        ms = _timed(lambda: layer.forward(inputs), steps, warmup, flush)
+        layer.check_device_status()
+        res = {"batch": batch, "tokens_per_gpu": tokens, "peer_store_us": round(ms * 1e3, 2),
+               "distinct_experts": int(torch.unique(ids_all).numel()), "busiest_rank_bytes": int(busiest),
+               "busiest_rank_gbs": round(busiest / (ms * 1e-3) / 1e9, 1)}
+        extra = None
+        if full:
+            x_host = inputs["x"].cpu().pin_memory()
+            y_host = torch.empty_like(x_host).pin_memory()
+            x_dev = torch.empty_like(inputs["x"])
+            e2e_inputs = dict(inputs)
+            e2e_inputs["x"] = x_dev
+
+            def e2e_step():
+                x_dev.copy_(x_host, non_blocking=True)
+                y_host.copy_(layer.forward(e2e_inputs)["y"], non_blocking=True)
+
+            e2e_ms = _timed(e2e_step, steps, warmup, flush)
+            same = bool(torch.equal(y_host, out["y"].cpu()))
+            extra = {"e2e_us": e2e_ms * 1e3, "io_bytes": _reduce(float(x_host.numel() * 2), dist.ReduceOp.SUM),
+                     "agree": _reduce(1.0 if same else 0.0, dist.ReduceOp.SUM) == world, "busiest": busiest, "ms": ms}
+        layer.close()
+        collective = EpCollectiveLayer(config, max_tokens=tokens, device=dev)
+        alt = collective.forward(inputs)
+        res["collective_equals_peer_store"] = _reduce(1.0 if torch.equal(alt["y"], out["y"]) else 0.0,
+                                                      dist.ReduceOp.SUM) == world
+        res["nccl_all_to_all_us"] = round(_timed(lambda: collective.forward(inputs), steps, warmup, flush) * 1e3, 2)
+        return res, extra
+
+    sweep = []
+    with clock_sampler(local_rank) as clocks:
+        head, extra = measure(args.batch, args.steps, args.warmup, True)
+        for b in batches:
+            sweep.append(head if b == args.batch else measure(b, max(5, args.steps // 2), 3, False)[0])
+    line = None
+    if rank == 0:
+        latency_us = extra["ms"] * 1e3
+        achieved = extra["busiest"] / (latency_us * 1e-6) / 1e9
+        line = {
+            "metric": metric, "value": round(latency_us, 2), "unit": "us", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(extra["ms"], 5), "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": f"{geo.name} FP8 MoE decode layer, batch {args.batch} over {world} GPUs (expert parallel): "
+                                   f"H={geo.hidden} I={geo.inter} E={geo.experts}+{geo.shared} top{geo.topk} {geo.scoring}",
+                       "batch": args.batch, "tokens_per_gpu": args.batch // world, "experts_per_gpu": local,
+                       "seed": args.seed,
+                       "exchange": "in-kernel peer stores over NVLink, bounded flag waits, no NCCL call per layer",
+                       "l2": "flushed between steps (512 MiB write)",
+                       "e2e_io": "x bf16 host->device and y bf16 device->host per step on every rank; weights resident in HBM",
+                       "input_generation_s": round(gen_s, 1)},
+            "e2e": {"value": round(extra["e2e_us"], 2), "unit": "us", "h2d_bytes_per_step": int(extra["io_bytes"]),
+                    "d2h_bytes_per_step": int(extra["io_bytes"]), "plugin_path_equals_direct_path": extra["agree"]},
+            "gpu_launches": LAUNCHES_PER_CALL * args.steps * world, "launches_per_step_per_gpu": LAUNCHES_PER_CALL,
+            "clocks": clocks.summary(),
+            "roofline": {"bound": "hbm", "kernel": "whole layer on the busiest rank (weights of the experts it is hit on)",
+                         "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                         "peak_kind": f"of {peak_kind}", "traffic": None,
+                         "algorithmic_bytes_per_launch": int(extra["busiest"])},
+            "exchange_comparison": sweep,
+        }
+    dist.barrier()
+    dist.destroy_process_group()
+    return line

@@ -194,6 +194,47 @@ class MoeLayer:
         return ws[off:off + nbytes].view(dtype).view(shape)
 
 
+_experts_scratch: dict = {}
+
+
+def experts_forward(config: LayerConfig, values: dict[str, torch.Tensor], rows_q: torch.Tensor, rows_scale: torch.Tensor,
+                    local_ids: torch.Tensor | None, *, world: int = 1, rank: int = 0) -> torch.Tensor:
+    """Local experts over quantised rows (the reference's ``experts()``, megabench/tasks/megamoe.py:131-150):
+    bf16 rows [n, H] in input order. ``local_ids`` int32 [n], or None for the shared expert."""
+    lib = _cabi.load()
+    n = rows_q.shape[0]
+    h = config.hidden
+    rows_q = _require(rows_q.view(torch.uint8), "rows_q", torch.uint8, (n, h))
+    rows_scale = _require(rows_scale, "rows_scale", torch.float32, (n, h // 128))
+    if local_ids is not None:
+        local_ids = _require(local_ids, "local_ids", torch.int32, (n,))
+    out = torch.empty((n, h), dtype=torch.bfloat16, device=rows_q.device)
+    if n == 0:
+        return out
+    cfg = config.c_struct(world, rank)
+    need = C.c_uint64(0)
+    _cabi.check("moe_experts_workspace", lib.moe_experts_workspace(C.byref(cfg), n, C.byref(need)))
+    key = (rows_q.device, int(need.value))
+    ws = _experts_scratch.get(key)
+    if ws is None:
+        buf = torch.empty(int(need.value) + 256, dtype=torch.uint8, device=rows_q.device)
+        skew = (-buf.data_ptr()) % 256
+        ws = _experts_scratch[key] = buf[skew:skew + int(need.value)]
+    n_local = config.experts // world
+    w = _cabi.Weights()
+    f8, f32 = torch.float8_e4m3fn, torch.float32
+    i = config.inter
+    names = (("shared_gate", (i, h)), ("shared_up", (i, h)), ("shared_down", (h, i))) if local_ids is None else (
+        ("gate", (n_local, i, h)), ("up", (n_local, i, h)), ("down", (n_local, h, i)))
+    for name, shape in names:
+        setattr(w, name, _require(values[name], name, f8, shape).data_ptr())
+        setattr(w, name + "_scale", _require(values[name + "_scale"], name + "_scale", f32).data_ptr())
+    rc = lib.moe_experts_forward(C.byref(cfg), C.byref(w), rows_q.data_ptr(), rows_scale.data_ptr(), _ptr(local_ids), n,
+                                 out.data_ptr(), ws.data_ptr(), ws.numel(), torch.cuda.current_stream(rows_q.device).cuda_stream)
+    _cabi.check("moe_experts_forward", rc)
+    return out
+
+
 STATIC_ROUTE_MAX_TOKENS = 256
 
 
