@@ -52,7 +52,7 @@ def parse_args():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--experts", type=int, default=0, help="shrink the routed expert count (profiling captures only)")
-    ap.add_argument("--sample-tokens", type=int, default=1, help="tokens per CPU-oracle step")
+    ap.add_argument("--sample-tokens", type=int, default=8, help="tokens per CPU-oracle step")
     return ap.parse_args()
 
 

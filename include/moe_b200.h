@@ -1,8 +1,8 @@
 /*
  * C ABI of the B200 FP8 mixture-of-experts decode layer.
  *
- * Every entry point takes plain device pointers and sizes; none allocates device memory: the
- * caller owns inputs, outputs and the scratch workspace. All work is enqueued on `stream`
+ * Every entry point takes plain device pointers and sizes. Except moe_ep_buffer_alloc, none
+ * allocates device memory: the caller owns inputs, outputs and the scratch workspace. All work is enqueued on `stream`
  * (a cudaStream_t passed as void*). Return value: 0 = ok, > 0 = a cudaError_t, < 0 = one of
  * the MOE_ERR_* codes below. Kernels never trap: a bounded on-device wait that runs out is
  * reported through moe_device_status().

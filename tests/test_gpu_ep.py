@@ -76,7 +76,7 @@ def test_deepseek_shape_single_rank_exchange(single_rank_group):
 def test_ranks_on_several_gpus_equal_the_one_gpu_layer(tmp_path):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs at least two GPUs")
-    world = 2 if torch.cuda.device_count() < 4 else 4
+    world = max(n for n in (2, 4, 8) if n <= torch.cuda.device_count())
     out = tmp_path / "report.json"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1",
            "--nproc-per-node", str(world), str(ROOT / "tests" / "ep_gpu_worker.py"), str(out)]
