@@ -142,7 +142,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
+    {   // warp-uniform loop, one elected lane issues the copies (see the MMA role below)
       const uint64_t pol_w = policy_evict_first();
       const uint64_t pol_x = policy_evict_last();
       uint32_t it = 0, s = 0, ph = 0;
@@ -159,18 +159,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const int n16 = (ch.rows + 15) >> 4;
         const uint32_t bytes = (DUAL ? 2 : 1) * C::kABytes + n16 * 2048;
         for (int kb = 0; kb < KB; ++kb, ++it) {
-          if (!mbar_wait(bar_empty + s, ph ^ 1u, s_abort)) {
-            if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 1); *s_abort = 1; }
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + s, ph ^ 1u, s_abort))) {
+            if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 1); *s_abort = 1; }
             ok = false;
             break;
           }
           uint8_t* st = stages + s * C::kStageBytes;
-          mbar_expect_tx(bar_full + s, bytes);
-          tma_load_2d(st, ma, kb * 128, wrow, bar_full + s, pol_w);
-          if constexpr (DUAL) tma_load_2d(st + C::kABytes, mb, kb * 128, wrow, bar_full + s, pol_w);
-          uint8_t* sb = st + (DUAL ? 2 : 1) * C::kABytes;
-          for (int j = 0; j < n16; ++j) tma_load_2d(sb + j * 2048, &tm_x, kb * 128, ch.row0 + j * 16, bar_full + s, pol_x);
-          *s_issued = it + 1;
+          if (elect_one()) {
+            mbar_expect_tx(bar_full + s, bytes);
+            tma_load_2d(st, ma, kb * 128, wrow, bar_full + s, pol_w);
+            if constexpr (DUAL) tma_load_2d(st + C::kABytes, mb, kb * 128, wrow, bar_full + s, pol_w);
+            uint8_t* sb = st + (DUAL ? 2 : 1) * C::kABytes;
+            for (int j = 0; j < n16; ++j) tma_load_2d(sb + j * 2048, &tm_x, kb * 128, ch.row0 + j * 16, bar_full + s, pol_x);
+            *s_issued = it + 1;
+          }
+          __syncwarp();
           if (++s == static_cast<uint32_t>(S)) { s = 0; ph ^= 1u; }
         }
       }
@@ -178,7 +181,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
+    // The whole warp runs the loop with warp-uniform values (work item, stage, descriptors) and
+    // one elected lane issues: operands of tcgen05.mma live in uniform registers, and a loop run
+    // by a single diverged lane had to move every descriptor there per instruction, which made
+    // the issue path, not HBM, set the pace of the down GEMM.
+    {
       uint32_t it = 0, s = 0, ph = 0;
       bool ok = true;
       Chunk next = load_chunk(p.chunks, blockIdx.x, n_units, p.tiles_m);
@@ -188,25 +195,29 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const uint32_t idesc = idesc_e4m3(128, ((ch.rows + 15) >> 4) * 16);
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t as = it % kAccStages, aph = (it / kAccStages) & 1u;
-          if (!mbar_wait(bar_tempty + as, aph ^ 1u, s_abort) || !mbar_wait(bar_full + s, ph, s_abort)) {
-            if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 2); *s_abort = 1; }
+          const bool got = mbar_wait(bar_tempty + as, aph ^ 1u, s_abort) && mbar_wait(bar_full + s, ph, s_abort);
+          if (!__all_sync(0xffffffffu, got)) {      // one decision for the warp
+            if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 2); *s_abort = 1; }
             ok = false;
             break;
           }
-          *s_consumed = it + 1;
           tc_fence_after();
           const uint32_t sa = smem_u32(stages + s * C::kStageBytes);
           const uint32_t sb = sa + (DUAL ? 2 : 1) * C::kABytes;
           const uint32_t d0 = tmem + as * C::kAccCols;
+          if (elect_one()) {
+            *s_consumed = it + 1;
 #pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4) {
-            const uint64_t bd = smem_desc_sw128(sb + k4 * 32);
-            mma_f8(d0, smem_desc_sw128(sa + k4 * 32), bd, idesc, k4 > 0 ? 1u : 0u);
-            if constexpr (DUAL) mma_f8(d0 + NT, smem_desc_sw128(sa + C::kABytes + k4 * 32), bd, idesc, k4 > 0 ? 1u : 0u);
+            for (int k4 = 0; k4 < 4; ++k4) {
+              const uint64_t bd = smem_desc_sw128(sb + k4 * 32);
+              mma_f8(d0, smem_desc_sw128(sa + k4 * 32), bd, idesc, k4 > 0 ? 1u : 0u);
+              if constexpr (DUAL) mma_f8(d0 + NT, smem_desc_sw128(sa + C::kABytes + k4 * 32), bd, idesc, k4 > 0 ? 1u : 0u);
+            }
+            mma_commit(bar_empty + s);     // the stage may be refilled once these MMAs have read it
+            mma_commit(bar_tfull + as);    // the accumulator is complete
+            *s_committed = it + 1;
           }
-          mma_commit(bar_empty + s);     // the stage may be refilled once these MMAs have read it
-          mma_commit(bar_tfull + as);    // the accumulator is complete
-          *s_committed = it + 1;
+          __syncwarp();
           if (++s == static_cast<uint32_t>(S)) { s = 0; ph ^= 1u; }
         }
       }
