@@ -200,6 +200,15 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* weights, const 
                    int32_t max_tokens, void* y_bf16, int64_t* expert_ids, float* topk_weights,
                    void* const* exchange, void* local, size_t local_bytes, uint64_t epoch, void* stream);
 
+/* The bounded wait the expert-parallel layer uses for its arrival and return flags, on its own:
+ * waits until flags[0..world) >= epoch or `timeout_ns` (at most 2 s) has passed; on expiry it writes
+ * MOE_ERR_DEVICE_TIMEOUT and 200 + the index of a late flag into status_words (int32[2], as read by
+ * moe_device_status) and returns normally. It is how failure detection is exercised without
+ * faulting a GPU: a flag that nothing raises makes the wait run out. The reference's counterpart
+ * is the process-group timeout of its host-driven collectives (megabench/verify_megamoe.py:149). */
+int moe_ep_wait_flags(const uint64_t* flags, int32_t world, uint64_t epoch, uint64_t timeout_ns, void* status_words,
+                      void* stream);
+
 /* Peer-visible device memory for the exchange buffer (cudaMalloc + CUDA IPC): allocate and export
  * a 64-byte handle, open a peer's handle (enables peer access), close, free. */
 int moe_ep_buffer_alloc(size_t bytes, void** ptr, void* handle64);

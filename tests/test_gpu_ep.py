@@ -73,6 +73,30 @@ def test_deepseek_shape_single_rank_exchange(single_rank_group):
         layer.close()
 
 
+def test_a_flag_nobody_raises_times_out_with_a_status_not_a_hang():
+    """Failure detection without a GPU fault: the wait gives up after its (here 1 ms) limit, the kernel
+    returns normally, the status word names the late peer, and the context stays usable."""
+    import ctypes as C
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from vibe_megakernel_b200 import _cabi
+    lib = _cabi.load()
+    flags = torch.zeros(8, dtype=torch.int64, device="cuda")
+    flags[:2] = 5                                       # peers 0 and 1 reported epoch 5, peer 2 never did
+    status = torch.zeros(8, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.moe_ep_wait_flags(flags.data_ptr(), 3, 5, 1_000_000, status.data_ptr(), stream) == 0
+    detail = C.c_int32(0)
+    assert lib.moe_device_status(status.data_ptr(), stream, C.byref(detail)) == -4        # MOE_ERR_DEVICE_TIMEOUT
+    assert detail.value == 202
+    status.zero_()
+    flags[2] = 5
+    assert lib.moe_ep_wait_flags(flags.data_ptr(), 3, 5, 1_000_000, status.data_ptr(), stream) == 0
+    assert lib.moe_device_status(status.data_ptr(), stream, C.byref(detail)) == 0
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0                                   # context still fine
+    assert lib.moe_ep_wait_flags(flags.data_ptr(), 3, 5, 3_000_000_000, status.data_ptr(), stream) == -1   # limit is 2 s
+
+
 def test_ranks_on_several_gpus_equal_the_one_gpu_layer(tmp_path):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs at least two GPUs")

@@ -70,7 +70,8 @@ def test_rerun_is_bit_identical_and_rows_do_not_depend_on_their_neighbours(api, 
     assert torch.equal(c["y"][0], a["y"][5])
 
 
-@pytest.mark.parametrize("name,tokens", [("qwen3_30b_a3b", 512), ("kimi_k2", 64)])
+@pytest.mark.parametrize("name,tokens", [("qwen3_30b_a3b", 512), ("kimi_k2", 64), ("mixtral_8x7b", 16),
+                                         ("mixtral_8x7b", 300)])
 def test_other_full_geometries(api, name, tokens):
     geo = synthetic.GEOMETRIES[name]
     spec = H.spec_of(geo)

@@ -57,6 +57,7 @@ EXPORTS = {
     "moe_ep_forward": (C.c_int, [C.POINTER(Config), C.POINTER(Weights), C.c_void_p, C.c_int32, C.c_int32, C.c_void_p,
                                  C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_void_p, C.c_size_t, C.c_uint64,
                                  C.c_void_p]),
+    "moe_ep_wait_flags": (C.c_int, [C.c_void_p, C.c_int32, C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p]),
     "moe_ep_buffer_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]),
     "moe_ep_buffer_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
     "moe_ep_buffer_close": (C.c_int, [C.c_void_p]),

@@ -183,12 +183,13 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(DispatchArgs a) {
 }
 
 // ---- bounded wait for `world` flags to reach `epoch` --------------------------------------------
-__global__ void ep_wait_kernel(const uint64_t* flags, int world, uint64_t epoch, int32_t* status, int detail) {
+__global__ void ep_wait_kernel(const uint64_t* flags, int world, uint64_t epoch, int32_t* status, int detail,
+                               uint64_t timeout_ns) {
   const int tid = threadIdx.x;
   if (tid >= world) return;
   const uint64_t t0 = globaltimer();
   while (load_acquire_sys(flags + tid) < epoch) {
-    if (globaltimer() - t0 > kWaitNs) {
+    if (globaltimer() - t0 > timeout_ns) {
       report(status, MOE_ERR_DEVICE_TIMEOUT, detail + tid);
       break;
     }
@@ -355,7 +356,7 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* 
 
   // 3. wait for every source, then group the arrivals by expert
   moe::ep_wait_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<const uint64_t*>(mine + L.flags_dispatch), world, epoch,
-                                            status, 200);
+                                            status, 200, moe::kWaitNs);
   ++launches;
   moe::GroupArgs g;
   std::memset(&g, 0, sizeof(g));
@@ -438,11 +439,20 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* 
   moe::ep_return_kernel<<<row_blocks, 128, 0, stream>>>(r);
   ++launches;
   moe::ep_wait_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<const uint64_t*>(mine + L.flags_return), world, epoch,
-                                            status, 300);
+                                            status, 300, moe::kWaitNs);
   ++launches;
   e = moe::launch_combine(reinterpret_cast<const __nv_bfloat16*>(mine + L.slots), tw, tokens, cfg->topk, H, cfg->n_shared,
                           static_cast<__nv_bfloat16*>(y_bf16), stream, &launches);
   return cuda_rc(e);
+}
+
+int moe_ep_wait_flags(const uint64_t* flags, int32_t world, uint64_t epoch, uint64_t timeout_ns, void* status_words,
+                      void* stream) {
+  if (!flags || !status_words || world < 1 || world > 8 || timeout_ns == 0 || timeout_ns > moe::kWaitNs)
+    return MOE_ERR_BAD_ARG;
+  moe::ep_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, world, epoch,
+                                                                      static_cast<int32_t*>(status_words), 200, timeout_ns);
+  return cuda_rc(cudaGetLastError());
 }
 
 int moe_ep_buffer_alloc(size_t bytes, void** ptr, void* handle64) {

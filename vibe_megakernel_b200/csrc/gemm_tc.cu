@@ -9,8 +9,8 @@
 // Block scales: W has one fp32 scale per 128x128 block, X one per token per 128 channels
 // (megabench/tasks/quantization.py:87-131). They are not powers of two, so each 128-deep K block
 // is accumulated into a fresh TMEM accumulator and the epilogue warps fold it into fp32
-// registers as acc += D * (w_scale * x_scale[n]); a second TMEM accumulator stage lets the
-// next K block's MMAs run meanwhile.
+// registers as acc += D * (w_scale * x_scale[n]); four TMEM accumulator stages let the MMAs of
+// the next K blocks run meanwhile.
 //
 // Roles: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warp 2 = scale loader (stages
 // the next work item's scales in shared memory while the current one is computed), warps 3.. =
