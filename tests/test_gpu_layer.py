@@ -119,6 +119,27 @@ def test_run_twice_is_bit_identical_and_depends_on_every_input(api):
         assert not torch.equal(first["y"], other["y"]), f"output ignores {name}"
 
 
+@pytest.mark.parametrize("name,tokens", [("ds_small", 40), ("kimi_small", 7), ("mixtral_small", 130)])
+def test_gemm_handover_and_separate_kernels_agree(api, name, tokens):
+    # Stage timing runs the two GEMMs strictly one after the other; a plain call lets the down
+    # GEMM start on finished chunks of the gate/up GEMM. Both orders give the same bits.
+    geo = H.small_geometries()[name]
+    values, _ = H.audited_inputs(geo, tokens)
+    layer, plain = run_layer(api, geo, values)
+    dev = H.to_device(values, "cuda")
+    layer.profile(True)
+    try:
+        timed = layer.forward(dev, check_status=True)
+        stages = layer.stage_ms()
+    finally:
+        layer.profile(False)
+    assert set(stages) == set(layer.STAGES) and all(v >= 0 for v in stages.values())
+    for _ in range(3):
+        again = layer.forward(dev, check_status=True)
+        for k in plain:
+            assert torch.equal(plain[k], timed[k]) and torch.equal(plain[k], again[k]), k
+
+
 def test_experts_with_no_rows_and_one_hot_routing(api):
     # a bias that sends every token to the same experts leaves all others empty
     geo = dataclasses.replace(H.small_geometries()["ds_small"], n_group=1, topk_group=1)

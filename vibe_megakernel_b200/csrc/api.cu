@@ -64,7 +64,7 @@ int layout_of(const moe_config_t* c, int tokens, moe_workspace_layout_t* L) {
   l.counts = take(4ull * (n_local + 1));
   l.offsets = take(4ull * (n_local + 2));
   l.n_chunks = take(4);
-  l.chunks = take(16ull * max_chunks);
+  l.chunks = take(16ull * max_chunks + 4ull * (max_chunks + 4));   // work items, then their progress counters
   l.row_token = take(4ull * rows);
   l.row_dest = take(4ull * rows);
   l.xq = take(static_cast<uint64_t>(rows) * H);
@@ -195,6 +195,7 @@ int moe_layer_forward(const moe_config_t* cfg, const moe_weights_t* w, const voi
   g.row_dest = row_dest;
   g.order = order;
   g.status = status;
+  g.progress = reinterpret_cast<int32_t*>(chunks + L.max_chunks);
   e = moe::launch_group_rows(g, stream, &launches);
   if (e != cudaSuccess) return from_cuda(e);
 
@@ -213,6 +214,9 @@ int moe_layer_forward(const moe_config_t* cfg, const moe_weights_t* w, const voi
   a.chunks = chunks;
   a.n_chunks = n_chunks;
   a.status = status;
+  a.progress = g_profile ? nullptr : g.progress;   // per-stage timing wants the two GEMMs apart
+  a.max_chunks = L.max_chunks;
+  a.tiles_before = cfg->inter / 128;
   int driver_error = 0;
 
   a.dual = true;

@@ -69,7 +69,7 @@ static void ep_layouts(const moe_config_t& c, int max_tokens, moe_ep_layout_t* L
   P->counts = take(4ull * (n_local + 1));
   P->offsets = take(4ull * (n_local + 2));
   P->n_chunks = take(4);
-  P->chunks = take(16ull * max_chunks);
+  P->chunks = take(16ull * max_chunks + 4ull * (max_chunks + 4));   // work items, then their progress counters
   P->row_source = take(4ull * rows);
   P->xq = take(static_cast<uint64_t>(rows) * H);
   P->xs = take(4ull * rows * (H / 128));
@@ -376,6 +376,7 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* 
   g.status = status;
   g.seg_counts = reinterpret_cast<const int32_t*>(mine + L.recv_count);
   g.seg_cap = L.cap;
+  g.progress = reinterpret_cast<int32_t*>(g.chunks + L.max_chunks);
   e = moe::launch_group_rows(g, stream, &launches);
   if (e != cudaSuccess) return cuda_rc(e);
 
@@ -400,6 +401,9 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* 
   a.chunks = g.chunks;
   a.n_chunks = g.n_chunks;
   a.status = status;
+  a.progress = g.progress;
+  a.max_chunks = L.max_chunks;
+  a.tiles_before = cfg->inter / 128;
   int driver_error = 0;
   a.dual = true;
   a.k = H; a.m = cfg->inter;

@@ -36,7 +36,7 @@ int experts_layout(const moe_config_t* c, int n_rows, ExpertsLayout* L) {
   L->counts = take(4ull * (n_local + 1));
   L->offsets = take(4ull * (n_local + 2));
   L->n_chunks = take(4);
-  L->chunks = take(16ull * max_chunks);
+  L->chunks = take(16ull * max_chunks + 4ull * (max_chunks + 4));   // work items, then their progress counters
   L->row_source = take(4ull * n_rows);
   L->row_dest = take(4ull * n_rows);
   L->xq = take(static_cast<uint64_t>(n_rows) * H);
@@ -102,6 +102,7 @@ int moe_experts_forward(const moe_config_t* cfg, const moe_weights_t* w, const u
   g.row_token = reinterpret_cast<int32_t*>(ws + L.row_source);
   g.row_dest = reinterpret_cast<int32_t*>(ws + L.row_dest);
   g.status = status;
+  g.progress = reinterpret_cast<int32_t*>(g.chunks + L.max_chunks);
   e = moe::launch_group_rows(g, stream, &launches);
   if (e != cudaSuccess) return cuda_rc(e);
 
@@ -126,6 +127,9 @@ int moe_experts_forward(const moe_config_t* cfg, const moe_weights_t* w, const u
   a.chunks = g.chunks;
   a.n_chunks = g.n_chunks;
   a.status = status;
+  a.progress = g.progress;
+  a.max_chunks = L.max_chunks;
+  a.tiles_before = cfg->inter / 128;
   int driver_error = 0;
   a.dual = true;
   a.k = cfg->hidden; a.m = cfg->inter;

@@ -60,6 +60,10 @@ __device__ __forceinline__ void epilogue_swiglu_requant(float (&gate)[CPT], cons
       if (m == 0) as[row * groups + tile_m] = scale;
     }
   }
+  // The stores above are made visible device-wide (to plain loads and to TMA reads) before the
+  // barrier, so one thread may announce the tile right after it.
+  __threadfence();
+  fence_async_global();
   epilogue_sync<THREADS>();   // s_amax may be reused by the next work item
 }
 

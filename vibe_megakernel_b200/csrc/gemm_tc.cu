@@ -15,10 +15,19 @@
 // Roles: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warp 2 = scale loader (stages
 // the next work item's scales in shared memory while the current one is computed), warps 3.. =
 // epilogue (a thread owns one TMEM lane = one output channel, for a run of token columns).
-// Work items (expert, row chunk, channel tile) are taken round-robin by a persistent grid; their
-// list is produced on the device by the permutation kernel, so no host synchronisation is needed
-// between routing and the GEMMs. A chunk with r rows only moves and multiplies ceil(r/16)*16
-// token columns.
+// Work items (expert, row chunk, channel tile) are walked by a persistent grid; their list is
+// produced on the device by the permutation kernel, so no host synchronisation is needed between
+// routing and the GEMMs. A chunk with r rows only moves and multiplies ceil(r/16)*16 token
+// columns. The producer warp decides the CTA's next item and passes it to the other roles through
+// a small queue in shared memory.
+//
+// Hand-over between the two GEMMs of a layer: the gate/up GEMM counts finished tiles per chunk in
+// global memory; the down GEMM does not wait for the gate/up kernel as a whole but, per item, for
+// that chunk's counter, and takes its items from a global dispenser instead of a fixed stride.
+// Its CTAs therefore start on SMs the gate/up GEMM has already left and stream down-projection
+// weights while the last gate/up tiles finish elsewhere. All gate/up CTAs are resident before the
+// first down CTA can be scheduled (the grid is at most one CTA per SM and the dependent launch is
+// released only after every gate/up CTA has started), so the waits cannot starve their producers.
 //
 // Every wait is bounded: on expiry the role records MOE_ERR_DEVICE_TIMEOUT, raises the CTA's
 // abort flag, and all roles fall through to the common exit, which waits (bounded) for copies
@@ -36,6 +45,7 @@ constexpr int kAccStages = 4;         // TMEM accumulators in flight: the MMAs r
 constexpr int kMaxStages = 12;
 constexpr int kMaxSmem = 232448;      // 227 KiB per CTA
 constexpr int kMaxKBlocks = 112;      // K <= 14336
+constexpr int kQueue = 4;             // work items the producer may run ahead of the slowest role
 
 template <int NT, bool DUAL>
 struct GemmCfg {
@@ -50,23 +60,37 @@ struct GemmCfg {
   static constexpr int kTmemCols = kAccStages * kAccCols < 32 ? 32 : kAccStages * kAccCols;
   // Shared memory after the stage ring, for a contraction of kb K blocks:
   //   2 buffers of { x scales [kb][NT], weight scales [2][kb] }, amax scratch [4][NT],
-  //   barriers (2*stages + 4 + 4), 8 words of flags.
+  //   barriers (2*kMaxStages + 4 + 4 + 2 + 2 + 2*kQueue), the item queue, 8 words of flags.
   static constexpr int scale_floats(int kb) { return kb * NT + 2 * kb + NT; }   // + destination rows [NT]
-  static constexpr int tail_bytes(int kb) { return 2 * scale_floats(kb) * 4 + 4 * NT * 4 + (2 * kMaxStages + 8) * 8 + 64; }
+  static constexpr int tail_bytes(int kb) {
+    return 2 * scale_floats(kb) * 4 + 4 * NT * 4 + (2 * kMaxStages + 12 + 2 * kQueue) * 8 + kQueue * 16 + 64;
+  }
   static constexpr int stages_for(int kb) {
     const int s = (kMaxSmem - 1024 - tail_bytes(kb)) / kStageBytes;
     return s > kMaxStages ? kMaxStages : s;
   }
 };
 
-// Work item u of this CTA's walk, or an empty one past the end (16-byte load).
-__device__ __forceinline__ Chunk load_chunk(const Chunk* chunks, int u, int n_units, int tiles_m) {
+// The chunk of work item u, or an empty one for u < 0 (16-byte load).
+__device__ __forceinline__ Chunk load_chunk(const Chunk* chunks, int u, int tiles_m) {
   Chunk c{0, 0, 0, 0};
-  if (u < n_units) {
+  if (u >= 0) {
     const int4 v = *reinterpret_cast<const int4*>(chunks + u / tiles_m);
     c.expert = v.x; c.row0 = v.y; c.rows = v.z; c.pad = v.w;
   }
   return c;
+}
+
+// The CTA's i-th work item as published by the producer warp: {u, expert, row0, rows}, u < 0 after
+// the last one. Every consumer thread takes every item and arrives on the slot's empty barrier.
+__device__ __forceinline__ bool take_item(const int4* queue, uint64_t* bar_qfull, uint64_t* bar_qempty, uint32_t i,
+                                          const volatile int* abort, int& u, Chunk& ch) {
+  const uint32_t q = i % kQueue;
+  if (!mbar_wait(bar_qfull + q, (i / kQueue) & 1u, abort)) return false;
+  const int4 v = queue[q];
+  u = v.x; ch.expert = v.y; ch.row0 = v.z; ch.rows = v.w; ch.pad = 0;
+  mbar_arrive(bar_qempty + q);
+  return true;
 }
 
 struct GemmDev {
@@ -83,6 +107,8 @@ struct GemmDev {
   __nv_bfloat16* out;
   const int32_t* row_dest;
   int32_t* status;
+  int32_t* progress;       // see GemmArgs; NULL = kernel-boundary ordering, fixed-stride walk
+  int max_chunks, tiles_before;
 };
 
 template <int NT, bool DUAL>
@@ -105,7 +131,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   uint64_t* bar_tempty = bar_tfull + kAccStages;
   uint64_t* bar_scfull = bar_tempty + kAccStages;
   uint64_t* bar_scempty = bar_scfull + 2;
-  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bar_scempty + 2);
+  uint64_t* bar_qfull = bar_scempty + 2;
+  uint64_t* bar_qempty = bar_qfull + kQueue;
+  int4* s_queue = reinterpret_cast<int4*>(bar_qempty + kQueue);     // 16-byte aligned: all parts above are
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_queue + kQueue);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   volatile uint32_t* s_issued = reinterpret_cast<volatile uint32_t*>(s_tmem + 2);    // K blocks whose TMA was issued
   volatile uint32_t* s_consumed = reinterpret_cast<volatile uint32_t*>(s_tmem + 3);  // K blocks whose data arrived
@@ -118,6 +147,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     for (int s = 0; s < S; ++s) { mbar_init(bar_full + s, 1); mbar_init(bar_empty + s, 1); }
     for (int s = 0; s < kAccStages; ++s) { mbar_init(bar_tfull + s, 1); mbar_init(bar_tempty + s, C::kEpiThreads); }
     for (int s = 0; s < 2; ++s) { mbar_init(bar_scfull + s, 32); mbar_init(bar_scempty + s, C::kEpiThreads); }
+    for (int s = 0; s < kQueue; ++s) { mbar_init(bar_qfull + s, 1); mbar_init(bar_qempty + s, 64 + C::kEpiThreads); }
     *s_abort = 0; *s_issued = 0; *s_consumed = 0; *s_committed = 0; *s_drained = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tmap(&tm_a); prefetch_tmap(&tm_x);
@@ -135,7 +165,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
   // Everything above touched only shared memory, TMEM and kernel parameters: under a dependent
   // launch it overlaps the tail of the previous kernel. From here on its results are needed.
-  dependent_wait();
+  // The down GEMM in hand-over mode is the exception: what it reads was written either before the
+  // gate/up kernel started (complete by the time this kernel can be scheduled) or by gate/up tiles
+  // it waits for one by one.
+  const bool handover = !DUAL && p.progress != nullptr;
+  if (!handover) dependent_wait();
   dependents_may_launch();
   const int n_chunks = *p.n_chunks;
   const int n_units = n_chunks * p.tiles_m;
@@ -145,12 +179,50 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     {   // warp-uniform loop, one elected lane issues the copies (see the MMA role below)
       const uint64_t pol_w = policy_evict_first();
       const uint64_t pol_x = policy_evict_last();
-      uint32_t it = 0, s = 0, ph = 0;
+      uint32_t it = 0, s = 0, ph = 0, item = 0;
+      int ready_chunk = -1;
       bool ok = true;
-      Chunk next = load_chunk(p.chunks, blockIdx.x, n_units, p.tiles_m);
-      for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+      // The CTA's next item: a fixed stride over the list, or the next free one of the dispenser.
+      auto next_unit = [&](uint32_t ordinal) -> int {
+        int u;
+        if (handover) {
+          int v = 0;
+          if (lane == 0) v = atomicAdd(p.progress + p.max_chunks, 1);
+          u = __shfl_sync(0xffffffffu, v, 0);
+        } else {
+          u = blockIdx.x + ordinal * gridDim.x;
+        }
+        return u < n_units ? u : -1;
+      };
+      int u_next = next_unit(0);
+      Chunk next = load_chunk(p.chunks, u_next, p.tiles_m);
+      for (; ok; ++item) {
+        const int u = u_next;
         const Chunk ch = next;
-        next = load_chunk(p.chunks, u + gridDim.x, n_units, p.tiles_m);   // in flight during this item
+        {   // publish the item (or the end mark) to the other roles
+          const uint32_t q = item % kQueue;
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_qempty + q, ((item / kQueue) & 1u) ^ 1u, s_abort))) {
+            if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 6); *s_abort = 1; }
+            break;
+          }
+          if (lane == 0) {
+            s_queue[q] = make_int4(u, ch.expert, ch.row0, ch.rows);
+            mbar_arrive(bar_qfull + q);
+          }
+          __syncwarp();
+        }
+        if (u < 0) break;
+        u_next = next_unit(item + 1);                          // both in flight during this item
+        next = load_chunk(p.chunks, u_next, p.tiles_m);
+        if (handover && u / p.tiles_m != ready_chunk) {
+          // the chunk's rows of the intermediate activation must be complete before TMA reads them
+          if (!__all_sync(0xffffffffu, wait_counter(p.progress + u / p.tiles_m, p.tiles_before, s_abort))) {
+            if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 7); *s_abort = 1; }
+            break;
+          }
+          fence_async_global();
+          ready_chunk = u / p.tiles_m;
+        }
         const int mt = u % p.tiles_m;
         const bool shared_e = ch.expert >= p.n_local;
         const CUtensorMap* ma = shared_e ? &tm_sa : &tm_a;
@@ -188,10 +260,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     {
       uint32_t it = 0, s = 0, ph = 0;
       bool ok = true;
-      Chunk next = load_chunk(p.chunks, blockIdx.x, n_units, p.tiles_m);
-      for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-        const Chunk ch = next;
-        next = load_chunk(p.chunks, u + gridDim.x, n_units, p.tiles_m);
+      for (uint32_t item = 0; ok; ++item) {
+        int u = -1;
+        Chunk ch;
+        if (!__all_sync(0xffffffffu, take_item(s_queue, bar_qfull, bar_qempty, item, s_abort, u, ch))) {
+          if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 8); *s_abort = 1; }
+          break;
+        }
+        if (u < 0) break;
         const uint32_t idesc = idesc_e4m3(128, ((ch.rows + 15) >> 4) * 16);
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t as = it % kAccStages, aph = (it / kAccStages) & 1u;
@@ -227,16 +303,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     // ------------------------------ scale loader ------------------------------
     // Each lane waits, loads its share and arrives on its own: no warp-level sync, so a lane that
     // gives up cannot strand the others.
-    uint32_t un = 0;
-    Chunk next = load_chunk(p.chunks, blockIdx.x, n_units, p.tiles_m);
-    for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++un) {
+    for (uint32_t un = 0;; ++un) {
       const uint32_t b = un & 1u, ph = (un >> 1) & 1u;
-      const Chunk ch = next;
-      next = load_chunk(p.chunks, u + gridDim.x, n_units, p.tiles_m);
-      if (!mbar_wait(bar_scempty + b, ph ^ 1u, s_abort)) {
+      int u = -1;
+      Chunk ch;
+      if (!take_item(s_queue, bar_qfull, bar_qempty, un, s_abort, u, ch) ||
+          (u >= 0 && !mbar_wait(bar_scempty + b, ph ^ 1u, s_abort)) ||
+          // the previous GEMM's scales of this chunk must be complete (this lane's own acquire)
+          (u >= 0 && handover && !wait_counter(p.progress + u / p.tiles_m, p.tiles_before, s_abort))) {
         if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 4); *s_abort = 1; }
         break;
       }
+      if (u < 0) break;
       const int mt = u % p.tiles_m;
       const bool shared_e = ch.expert >= p.n_local;
       float* xs = s_scales + b * sf;            // [kb][NT]
@@ -249,7 +327,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
       for (int i = lane; i < cols * KB; i += 32) {
         const int n = i / KB, kb = i - n * KB;
-        xs[kb * NT + n] = n < ch.rows ? p.act_scale[static_cast<size_t>(ch.row0 + n) * KB + kb] : 0.f;
+        // read at L2: a line shared with a neighbouring chunk may have been fetched before that
+        // chunk's scales were written
+        xs[kb * NT + n] = n < ch.rows ? __ldcg(p.act_scale + static_cast<size_t>(ch.row0 + n) * KB + kb) : 0.f;
       }
       const float* wa = (shared_e ? p.s_a_scale : p.w_a_scale + static_cast<size_t>(ch.expert) * p.tiles_m * KB) +
                         static_cast<size_t>(mt) * KB;
@@ -268,12 +348,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const int m = quarter * 32 + lane;            // output channel inside the tile
     const int col0 = (epi >> 2) * C::kCpt;        // first token column of this thread
     const uint32_t lane_base = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
-    uint32_t it = 0, un = 0;
+    uint32_t it = 0;
     bool failed = false;
-    Chunk next = load_chunk(p.chunks, blockIdx.x, n_units, p.tiles_m);
-    for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++un) {
-      const Chunk ch = next;
-      next = load_chunk(p.chunks, u + gridDim.x, n_units, p.tiles_m);
+    for (uint32_t un = 0;; ++un) {
+      int u = -1;
+      Chunk ch;
+      if (!take_item(s_queue, bar_qfull, bar_qempty, un, s_abort, u, ch)) {
+        if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 9); *s_abort = 1; }
+        failed = true;
+      }
+      // one decision for all epilogue threads (the item is the same for all of them unless one failed)
+      if (epilogue_any<C::kEpiThreads>(failed) || u < 0) break;
       const int mt = u % p.tiles_m;
       const int cols = ((ch.rows + 15) >> 4) * 16;            // token columns that were multiplied
       const uint32_t b = un & 1u, sph = (un >> 1) & 1u;
@@ -337,6 +422,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if constexpr (DUAL) {
         epilogue_swiglu_requant<C::kCpt, C::kEpiThreads>(acc_a, acc_b, m, col0, NT, ch.rows, ch.row0, mt, p.m, s_amax,
                                                          p.aq, p.as);
+        // every thread's stores were fenced before the epilogue's closing barrier: announce the tile
+        if (p.progress && epi == 0 && lane == 0) {
+          __threadfence();
+          atomicAdd(p.progress + u / p.tiles_m, 1);
+        }
       } else {
 #pragma unroll
         for (int n = 0; n < C::kCpt; ++n) {
@@ -361,6 +451,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kTmemCols) : "memory");
   }
+  // Keep the stream's ordering for whatever follows: this grid does not complete before the
+  // gate/up grid has (a CTA that found the dispenser empty idles here until that grid's last
+  // tiles are done; one that did work finds it finished).
+  if (handover && threadIdx.x == 0) dependent_wait();
 }
 
 // ---------------------------------------------------------------------------------------
@@ -445,7 +539,8 @@ cudaError_t launch_gemm_tc(const GemmArgs& a, cudaStream_t stream, int* launches
     return cudaErrorUnknown;
   }
   GemmDev dev{a.chunks, a.n_chunks, a.m / 128, a.k / 128, a.m, a.n_local, 0, a.act_scale, a.w_a_scale, a.w_b_scale,
-              a.s_a_scale, a.s_b_scale, a.aq, a.as, a.out, a.row_dest, a.status};
+              a.s_a_scale, a.s_b_scale, a.aq, a.as, a.out, a.row_dest, a.status, a.progress, a.max_chunks,
+              a.tiles_before};
   const int grid = max(1, min(sm_count(), a.max_units));
   cudaError_t e;
   if (a.dual) {

@@ -88,6 +88,8 @@ __global__ void __launch_bounds__(kGroupWarps * 32) group_rows_kernel(GroupArgs 
   }
 
   if (blockIdx.x == 0) {
+    if (a.progress)
+      for (int i = tid; i < a.max_chunks + 4; i += blockDim.x) a.progress[i] = 0;
     const int kept = s_offset[a.n_local];
     for (int i = tid; i < groups; i += blockDim.x) {
       a.counts[i] = s_count[i];

@@ -58,6 +58,7 @@ struct GroupArgs {
   int32_t* status;        // optional
   const int32_t* seg_counts;  // optional: rows come in segments of seg_cap, segment s holds seg_counts[s] rows
   int seg_cap;
+  int32_t* progress;          // optional: [max_chunks + 4] counters of the GEMMs, zeroed here (see GemmArgs)
 };
 cudaError_t launch_group_rows(const GroupArgs& a, cudaStream_t stream, int* launches);
 
@@ -106,6 +107,14 @@ struct GemmArgs {
   __nv_bfloat16* out;        // single: bf16 rows [*, m] addressed through row_dest
   const int32_t* row_dest;
   int32_t* status;
+  // Hand-over between the two GEMMs of a layer call without a kernel boundary: progress[c] counts
+  // the gate/up tiles of work item c that are finished and visible; progress[max_chunks] is the
+  // down GEMM's work-item dispenser. The gate/up GEMM increments, the down GEMM (which may be
+  // scheduled on SMs the gate/up GEMM has already left) waits per work item and takes items
+  // dynamically. NULL = plain kernel-boundary ordering and a static walk.
+  int32_t* progress;
+  int max_chunks;
+  int tiles_before;          // down GEMM: gate/up tiles per work item that must be finished
 };
 cudaError_t launch_gemm_tc(const GemmArgs& a, cudaStream_t stream, int* launches, int* driver_error);
 cudaError_t launch_gemm_simt(const GemmArgs& a, cudaStream_t stream, int* launches);
