@@ -35,6 +35,8 @@ def small_geometries():
                                           router_std=1024 ** -0.5),
         "mixtral_small": dataclasses.replace(g["mixtral_8x7b"], name="mixtral_small", hidden=512, inter=1792,
                                              experts=8, topk=2),
+        # 66 K blocks in the down projection: the contraction is cut in three parts
+        "long_k": dataclasses.replace(g["mixtral_8x7b"], name="long_k", hidden=256, inter=8448, experts=4, topk=2),
     }
 
 

@@ -36,11 +36,18 @@ def test_workspace_layout_and_argument_checks_need_no_gpu():
     cfg = _cabi.Config(7168, 2048, 256, 8, 1, 1, 8, 4, 2.5, 1, 0, 0)
     lay = _cabi.Layout()
     assert lib.moe_workspace_layout(C.byref(cfg), 64, C.byref(lay)) == 0
-    assert lay.rows == 64 * 9 and lay.token_tile == 64
+    assert lay.rows == 64 * 9 and lay.token_tile == 16          # 512 routed rows over 256 experts: narrow tiles
     offsets = [getattr(lay, n) for n in _cabi.LAYOUT_OFFSETS[1:]]
     assert offsets == sorted(offsets) and all(o % 256 == 0 for o in offsets)
     assert lay.total_bytes >= lay.slots + 2 * lay.rows * 7168
     assert lib.moe_workspace_layout(C.byref(cfg), 1, C.byref(lay)) == 0 and lay.token_tile == 16
+    assert lib.moe_workspace_layout(C.byref(cfg), 1024, C.byref(lay)) == 0 and lay.token_tile == 64   # 32 rows per expert
+    dense = _cabi.Config(4096, 14336, 8, 2, 0, 0, 1, 1, 1.0, 1, 0, 0)     # long down contraction: room for partial tiles
+    small = _cabi.Config(4096, 8192, 8, 2, 0, 0, 1, 1, 1.0, 1, 0, 0)
+    big, ref = _cabi.Layout(), _cabi.Layout()
+    assert lib.moe_workspace_layout(C.byref(dense), 16, C.byref(big)) == 0
+    assert lib.moe_workspace_layout(C.byref(small), 16, C.byref(ref)) == 0
+    assert big.row_token - big.chunks > ref.row_token - ref.chunks + 4 * 32 * 4 * 16 * 128
     bad = _cabi.Config(7000, 2048, 256, 8, 1, 1, 8, 4, 2.5, 1, 0, 0)
     assert lib.moe_workspace_layout(C.byref(bad), 64, None) == -2
     bad = _cabi.Config(7168, 2048, 256, 8, 1, 1, 7, 4, 2.5, 1, 0, 0)      # groups must divide experts

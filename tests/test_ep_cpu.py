@@ -39,7 +39,8 @@ def test_exchange_layout_through_the_c_abi():
     cfg = _cabi.Config(7168, 2048, 256, 8, 1, 1, 8, 4, 2.5, 8, 3, 0)
     lay = _cabi.EpLayout()
     assert lib.moe_ep_layout(C.byref(cfg), 16, C.byref(lay)) == 0
-    assert lay.cap == 16 * 8 and lay.rows == 8 * lay.cap + 16 and lay.token_tile == 64
+    # 8 ranks x 16 tokens x top-8 = 1024 routed rows over 256 experts: 4 per expert, narrow tiles
+    assert lay.cap == 16 * 8 and lay.rows == 8 * lay.cap + 16 and lay.token_tile == 16
     offsets = [getattr(lay, n) for n in _cabi.EP_LAYOUT_OFFSETS[2:]]
     assert offsets == sorted(offsets) and all(o % 256 == 0 for o in offsets)
     assert lay.exchange_bytes >= lay.slots + 2 * (lay.cap + 16) * 7168

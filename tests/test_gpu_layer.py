@@ -68,7 +68,7 @@ def check_against_oracle(api, geo, values, gemm):
 
 
 @pytest.mark.parametrize("gemm", ["simt", "tcgen05"])
-@pytest.mark.parametrize("name", ["tiny", "ds_small", "qwen_small", "kimi_small", "mixtral_small"])
+@pytest.mark.parametrize("name", ["tiny", "ds_small", "qwen_small", "kimi_small", "mixtral_small", "long_k"])
 def test_small_layers_match_the_oracle(api, name, gemm):
     geo = H.small_geometries()[name]
     for tokens in (1, 4, 19, 40):
@@ -119,7 +119,7 @@ def test_run_twice_is_bit_identical_and_depends_on_every_input(api):
         assert not torch.equal(first["y"], other["y"]), f"output ignores {name}"
 
 
-@pytest.mark.parametrize("name,tokens", [("ds_small", 40), ("kimi_small", 7), ("mixtral_small", 130)])
+@pytest.mark.parametrize("name,tokens", [("ds_small", 40), ("kimi_small", 7), ("mixtral_small", 130), ("long_k", 21)])
 def test_gemm_handover_and_separate_kernels_agree(api, name, tokens):
     # Stage timing runs the two GEMMs strictly one after the other; a plain call lets the down
     # GEMM start on finished chunks of the gate/up GEMM. Both orders give the same bits.

@@ -41,7 +41,6 @@ int check_config(const moe_config_t* c) {
   return MOE_OK;
 }
 
-int token_tile(int tokens) { return tokens <= 16 ? 16 : tokens <= 32 ? 32 : 64; }
 
 int layout_of(const moe_config_t* c, int tokens, moe_workspace_layout_t* L) {
   const int rc = check_config(c);
@@ -50,7 +49,7 @@ int layout_of(const moe_config_t* c, int tokens, moe_workspace_layout_t* L) {
   const int n_local = c->n_experts / c->ep_world;
   const int routed = tokens * c->topk;
   const int rows = routed + tokens * c->n_shared;
-  const int tile = token_tile(tokens);
+  const int tile = moe::pick_token_tile(routed, n_local);
   const int max_chunks = std::min(routed, n_local) + routed / tile + (tokens + tile - 1) / tile + 1;
   const uint64_t H = c->hidden, I = c->inter;
   uint64_t off = 0;
@@ -64,7 +63,7 @@ int layout_of(const moe_config_t* c, int tokens, moe_workspace_layout_t* L) {
   l.counts = take(4ull * (n_local + 1));
   l.offsets = take(4ull * (n_local + 2));
   l.n_chunks = take(4);
-  l.chunks = take(16ull * max_chunks + 4ull * (max_chunks + 4));   // work items, then their progress counters
+  l.chunks = take(moe::work_list_layout(max_chunks, c->hidden, c->inter, tile).bytes);   // work items, counters, partial tiles
   l.row_token = take(4ull * rows);
   l.row_dest = take(4ull * rows);
   l.xq = take(static_cast<uint64_t>(rows) * H);
@@ -169,14 +168,6 @@ int moe_layer_forward(const moe_config_t* cfg, const moe_weights_t* w, const voi
   cudaError_t e = cudaMemsetAsync(status, 0, 32, stream);
   if (e != cudaSuccess) return from_cuda(e);
 
-  // 1. router
-  mark(0, stream);
-  e = moe::launch_router(*cfg, static_cast<const __nv_bfloat16*>(x_bf16), w->router, w->router_bias, tokens, logits,
-                         ids32, tw, expert_ids, topk_weights, stream, &launches);
-  if (e != cudaSuccess) return from_cuda(e);
-
-  // 2. token -> expert permutation and the work list of the GEMMs
-  mark(1, stream);
   moe::GroupArgs g;
   std::memset(&g, 0, sizeof(g));
   g.ids32 = ids32;
@@ -195,14 +186,42 @@ int moe_layer_forward(const moe_config_t* cfg, const moe_weights_t* w, const voi
   g.row_dest = row_dest;
   g.order = order;
   g.status = status;
-  g.progress = reinterpret_cast<int32_t*>(chunks + L.max_chunks);
-  e = moe::launch_group_rows(g, stream, &launches);
-  if (e != cudaSuccess) return from_cuda(e);
+  const moe::WorkListLayout W = moe::work_list_layout(L.max_chunks, cfg->hidden, cfg->inter, L.token_tile);
+  g.progress = reinterpret_cast<int32_t*>(ws + L.chunks + W.counters);
+  g.progress_len = W.counters_len;
 
-  // 3. activation quantiser, gathering each grouped row from its token
-  mark(2, stream);
-  e = moe::launch_quantize(x_bf16, 0, L.rows, cfg->hidden, row_token, xq, xs, stream, &launches);
-  if (e != cudaSuccess) return from_cuda(e);
+  // The shared expert's weights are needed whatever the router decides: the logits kernel asks
+  // the L2 for them while HBM has little else to do.
+  moe::L2Warm warm = {};
+  if (cfg->n_shared) {
+    const uint64_t bytes = static_cast<uint64_t>(cfg->inter) * cfg->hidden;
+    warm.ptr[0] = w->shared_gate; warm.bytes[0] = bytes;
+    warm.ptr[1] = w->shared_up; warm.bytes[1] = bytes;
+    warm.ptr[2] = w->shared_down; warm.bytes[2] = bytes;
+  }
+
+  mark(0, stream);
+  if (!g_profile && moe::fused_route_fits(*cfg, tokens)) {
+    // small batch: logits, then selection + permutation + quantiser in one launch (steps 1-3 below)
+    e = moe::launch_router_fused(*cfg, static_cast<const __nv_bfloat16*>(x_bf16), w->router, w->router_bias, tokens,
+                                 logits, ids32, tw, expert_ids, topk_weights, g, xq, xs, stream, &launches, &warm);
+    if (e != cudaSuccess) return from_cuda(e);
+  } else {
+    // 1. router
+    e = moe::launch_router(*cfg, static_cast<const __nv_bfloat16*>(x_bf16), w->router, w->router_bias, tokens, logits,
+                           ids32, tw, expert_ids, topk_weights, stream, &launches, g_profile ? nullptr : &warm);
+    if (e != cudaSuccess) return from_cuda(e);
+
+    // 2. token -> expert permutation and the work list of the GEMMs
+    mark(1, stream);
+    e = moe::launch_group_rows(g, stream, &launches);
+    if (e != cudaSuccess) return from_cuda(e);
+
+    // 3. activation quantiser, gathering each grouped row from its token
+    mark(2, stream);
+    e = moe::launch_quantize(x_bf16, 0, L.rows, cfg->hidden, row_token, xq, xs, stream, &launches);
+    if (e != cudaSuccess) return from_cuda(e);
+  }
 
   // 4. gate/up GEMM + SwiGLU + requantisation; 5. down GEMM into slot rows
   mark(3, stream);
@@ -241,6 +260,9 @@ int moe_layer_forward(const moe_config_t* cfg, const moe_weights_t* w, const voi
   a.k = cfg->inter;
   a.m = cfg->hidden;
   a.max_units = L.max_chunks * (cfg->hidden / 128);
+  a.ksplit = moe::down_ksplit(cfg->inter);
+  a.partial = reinterpret_cast<float*>(ws + L.chunks + W.partial);
+  a.parts_done = reinterpret_cast<int32_t*>(ws + L.chunks + W.parts_done);
   a.act = aq;
   a.act_scale = as;
   a.w_a = w->down; a.w_a_scale = w->down_scale;

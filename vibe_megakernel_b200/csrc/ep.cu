@@ -30,17 +30,13 @@ struct EpLocal {       // offsets inside the private scratch
 
 static inline uint64_t up256(uint64_t v) { return (v + 255) / 256 * 256; }
 
-static int ep_token_tile(int rows_per_expert_max) {
-  return rows_per_expert_max <= 16 ? 16 : rows_per_expert_max <= 32 ? 32 : 64;
-}
-
 static void ep_layouts(const moe_config_t& c, int max_tokens, moe_ep_layout_t* L, EpLocal* P) {
   const int world = c.ep_world;
   const int n_local = c.n_experts / world;
   const uint64_t H = c.hidden, I = c.inter;
   const int cap = max_tokens * c.topk;
   const int rows = world * cap + max_tokens;
-  const int tile = ep_token_tile(world * max_tokens);
+  const int tile = moe::pick_token_tile(static_cast<long long>(world) * cap, c.n_experts);
   const int max_chunks = std::min(world * cap, n_local) + world * cap / tile + (max_tokens + tile - 1) / tile + 1;
   uint64_t off = 0;
   auto take = [&](uint64_t bytes) { const uint64_t at = off; off = up256(off + bytes); return at; };
@@ -69,7 +65,7 @@ static void ep_layouts(const moe_config_t& c, int max_tokens, moe_ep_layout_t* L
   P->counts = take(4ull * (n_local + 1));
   P->offsets = take(4ull * (n_local + 2));
   P->n_chunks = take(4);
-  P->chunks = take(16ull * max_chunks + 4ull * (max_chunks + 4));   // work items, then their progress counters
+  P->chunks = take(moe::work_list_layout(max_chunks, c.hidden, c.inter, tile).bytes);   // work items, counters, partial tiles
   P->row_source = take(4ull * rows);
   P->xq = take(static_cast<uint64_t>(rows) * H);
   P->xs = take(4ull * rows * (H / 128));
@@ -376,7 +372,9 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* 
   g.status = status;
   g.seg_counts = reinterpret_cast<const int32_t*>(mine + L.recv_count);
   g.seg_cap = L.cap;
-  g.progress = reinterpret_cast<int32_t*>(g.chunks + L.max_chunks);
+  const moe::WorkListLayout W = moe::work_list_layout(L.max_chunks, cfg->hidden, cfg->inter, L.token_tile);
+  g.progress = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(g.chunks) + W.counters);
+  g.progress_len = W.counters_len;
   e = moe::launch_group_rows(g, stream, &launches);
   if (e != cudaSuccess) return cuda_rc(e);
 
@@ -419,6 +417,9 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* 
   a.dual = false;
   a.k = cfg->inter; a.m = H;
   a.max_units = L.max_chunks * (H / 128);
+  a.ksplit = moe::down_ksplit(cfg->inter);
+  a.partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(g.chunks) + W.partial);
+  a.parts_done = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(g.chunks) + W.parts_done);
   a.act = ws + P.aq; a.act_scale = reinterpret_cast<const float*>(ws + P.as);
   a.w_a = w->down; a.w_a_scale = w->down_scale; a.w_b = nullptr; a.w_b_scale = nullptr;
   a.s_a = w->shared_down; a.s_a_scale = w->shared_down_scale; a.s_b = nullptr; a.s_b_scale = nullptr;

@@ -28,15 +28,16 @@ int experts_layout(const moe_config_t* c, int n_rows, ExpertsLayout* L) {
   if (n_rows < 1 || n_rows > 32768) return MOE_ERR_UNSUPPORTED;
   const int n_local = c->n_experts / c->ep_world;
   const uint64_t H = c->hidden, I = c->inter;
-  const int tile = n_rows <= 16 ? 16 : n_rows <= 32 ? 32 : 64;
-  const int max_chunks = std::min(n_rows, n_local) + n_rows / tile + (n_rows + tile - 1) / tile + 1;
+  const int tile = moe::pick_token_tile(n_rows, n_local);
+  // sized for the narrowest tile: a call for the shared expert alone picks its own (all rows are one expert's)
+  const int max_chunks = std::min(n_rows, n_local) + n_rows / 16 + (n_rows + 15) / 16 + 1;
   uint64_t off = 0;
   auto take = [&](uint64_t bytes) { const uint64_t at = off; off = up256(off + bytes); return at; };
   L->status = take(32);
   L->counts = take(4ull * (n_local + 1));
   L->offsets = take(4ull * (n_local + 2));
   L->n_chunks = take(4);
-  L->chunks = take(16ull * max_chunks + 4ull * (max_chunks + 4));   // work items, then their progress counters
+  L->chunks = take(moe::work_list_layout(max_chunks, c->hidden, c->inter, 64).bytes);   // work items, counters, partial tiles
   L->row_source = take(4ull * n_rows);
   L->row_dest = take(4ull * n_rows);
   L->xq = take(static_cast<uint64_t>(n_rows) * H);
@@ -93,7 +94,8 @@ int moe_experts_forward(const moe_config_t* cfg, const moe_weights_t* w, const u
   g.n_local = n_local;
   g.topk = 1;
   g.shared_rows = shared ? n_rows : 0;
-  g.tile = L.tile;
+  const int tile = shared ? moe::pick_token_tile(n_rows, 1) : L.tile;
+  g.tile = tile;
   g.max_chunks = L.max_chunks;
   g.counts = reinterpret_cast<int32_t*>(ws + L.counts);
   g.offsets = reinterpret_cast<int32_t*>(ws + L.offsets);
@@ -102,7 +104,9 @@ int moe_experts_forward(const moe_config_t* cfg, const moe_weights_t* w, const u
   g.row_token = reinterpret_cast<int32_t*>(ws + L.row_source);
   g.row_dest = reinterpret_cast<int32_t*>(ws + L.row_dest);
   g.status = status;
-  g.progress = reinterpret_cast<int32_t*>(g.chunks + L.max_chunks);
+  const moe::WorkListLayout W = moe::work_list_layout(L.max_chunks, cfg->hidden, cfg->inter, 64);
+  g.progress = reinterpret_cast<int32_t*>(ws + L.chunks + W.counters);
+  g.progress_len = W.counters_len;
   e = moe::launch_group_rows(g, stream, &launches);
   if (e != cudaSuccess) return cuda_rc(e);
 
@@ -121,7 +125,7 @@ int moe_experts_forward(const moe_config_t* cfg, const moe_weights_t* w, const u
 
   moe::GemmArgs a;
   std::memset(&a, 0, sizeof(a));
-  a.tile = L.tile;
+  a.tile = tile;
   a.n_local = n_local;
   a.total_rows = n_rows;
   a.chunks = g.chunks;
@@ -146,6 +150,9 @@ int moe_experts_forward(const moe_config_t* cfg, const moe_weights_t* w, const u
   a.dual = false;
   a.k = cfg->inter; a.m = cfg->hidden;
   a.max_units = L.max_chunks * (cfg->hidden / 128);
+  a.ksplit = moe::down_ksplit(cfg->inter);
+  a.partial = reinterpret_cast<float*>(ws + L.chunks + W.partial);
+  a.parts_done = reinterpret_cast<int32_t*>(ws + L.chunks + W.parts_done);
   a.act = ws + L.aq; a.act_scale = reinterpret_cast<const float*>(ws + L.as);
   a.w_a = shared ? nullptr : w->down; a.w_a_scale = w->down_scale; a.w_b = nullptr; a.w_b_scale = nullptr;
   a.s_a = w->shared_down; a.s_a_scale = w->shared_down_scale; a.s_b = nullptr; a.s_b_scale = nullptr;

@@ -9,8 +9,8 @@
 // Block scales: W has one fp32 scale per 128x128 block, X one per token per 128 channels
 // (megabench/tasks/quantization.py:87-131). They are not powers of two, so each 128-deep K block
 // is accumulated into a fresh TMEM accumulator and the epilogue warps fold it into fp32
-// registers as acc += D * (w_scale * x_scale[n]); four TMEM accumulator stages let the MMAs of
-// the next K blocks run meanwhile.
+// registers as acc += D * (w_scale * x_scale[n]); four to eight TMEM accumulators let the MMAs
+// of the next K blocks run meanwhile.
 //
 // Roles: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warp 2 = scale loader (stages
 // the next work item's scales in shared memory while the current one is computed), warps 3.. =
@@ -41,7 +41,30 @@
 
 namespace moe {
 
-constexpr int kAccStages = 4;         // TMEM accumulators in flight: the MMAs run up to 4 K blocks ahead
+// Optional probe (compile with -DMOE_GEMM_PROBE): cycles each role spends waiting, summed over the
+// CTAs into the spare status words in units of 256 cycles: [2] producer for a free stage, [3] MMA
+// for a free accumulator, [4] MMA for data, [5] epilogue for an accumulator, [6] epilogue for
+// scales, [7] lifetime of the CTA. MOE_GEMM_PROBE=1 records the gate/up GEMM, =2 the down GEMM.
+// Off by default: the words stay zero.
+#ifdef MOE_GEMM_PROBE
+#define PROBE_DECL(name) long long name = 0
+#define PROBE_START(t) const long long t = clock64()
+#define PROBE_ADD(name, t) name += clock64() - t
+#define PROBE_FLUSH(status, slot, name) \
+  if (DUAL == (MOE_GEMM_PROBE == 1)) atomicAdd((status) + (slot), static_cast<int>((name) >> 8))
+#else
+#define PROBE_DECL(name)
+#define PROBE_START(t)
+#define PROBE_ADD(name, t)
+#define PROBE_FLUSH(status, slot, name)
+#endif
+
+// TMEM accumulators in flight (per configuration: as many as fit in the 512 columns, at most 8).
+// One K block's round trip MMA -> commit -> epilogue wake-up -> tcgen05.ld -> release -> MMA takes
+// about a microsecond, so the number of accumulators bounds the K blocks a CTA retires per
+// microsecond: 4 of them capped a down-projection CTA (16 KB of weights per K block) near
+// 40 GB/s, which showed wherever fewer CTAs than SMs had work.
+constexpr int kMaxAccStages = 8;
 constexpr int kMaxStages = 12;
 constexpr int kMaxSmem = 232448;      // 227 KiB per CTA
 constexpr int kMaxKBlocks = 112;      // K <= 14336
@@ -57,13 +80,14 @@ struct GemmCfg {
   static constexpr int kBBytes = NT * 128;
   static constexpr int kStageBytes = (DUAL ? 2 : 1) * kABytes + kBBytes;
   static constexpr int kAccCols = (DUAL ? 2 : 1) * NT;
-  static constexpr int kTmemCols = kAccStages * kAccCols < 32 ? 32 : kAccStages * kAccCols;
+  static constexpr int kAcc = 512 / kAccCols < kMaxAccStages ? 512 / kAccCols : kMaxAccStages;
+  static constexpr int kTmemCols = kAcc * kAccCols < 32 ? 32 : kAcc * kAccCols;   // a power of two
   // Shared memory after the stage ring, for a contraction of kb K blocks:
   //   2 buffers of { x scales [kb][NT], weight scales [2][kb] }, amax scratch [4][NT],
-  //   barriers (2*kMaxStages + 4 + 4 + 2 + 2 + 2*kQueue), the item queue, 8 words of flags.
+  //   barriers (2*kMaxStages + 2*kMaxAccStages + 2 + 2 + 2*kQueue), the item queue, 8 words of flags.
   static constexpr int scale_floats(int kb) { return kb * NT + 2 * kb + NT; }   // + destination rows [NT]
   static constexpr int tail_bytes(int kb) {
-    return 2 * scale_floats(kb) * 4 + 4 * NT * 4 + (2 * kMaxStages + 12 + 2 * kQueue) * 8 + kQueue * 16 + 64;
+    return 2 * scale_floats(kb) * 4 + 4 * NT * 4 + (2 * kMaxStages + 2 * kMaxAccStages + 4 + 2 * kQueue) * 8 + kQueue * 16 + 64;
   }
   static constexpr int stages_for(int kb) {
     const int s = (kMaxSmem - 1024 - tail_bytes(kb)) / kStageBytes;
@@ -71,11 +95,24 @@ struct GemmCfg {
   }
 };
 
-// The chunk of work item u, or an empty one for u < 0 (16-byte load).
-__device__ __forceinline__ Chunk load_chunk(const Chunk* chunks, int u, int tiles_m) {
+// Position u of the walk -> work item. The walk goes expert by expert; inside an expert with
+// several row chunks it goes channel tile by channel tile with the chunks innermost, so that the
+// CTAs running at the same time read the same weight tile (once from HBM, then from L2) instead
+// of returning to it one pass over the expert's weights later. Returns the chunk and rewrites u
+// to chunk_index * tiles_m + channel_tile; u < 0 gives an empty chunk.
+__device__ __forceinline__ Chunk load_chunk(const Chunk* chunks, int& u, int tiles_m) {
   Chunk c{0, 0, 0, 0};
   if (u >= 0) {
-    const int4 v = *reinterpret_cast<const int4*>(chunks + u / tiles_m);
+    const int at = u / tiles_m;
+    int4 v = __ldg(reinterpret_cast<const int4*>(chunks + at));
+    const int nc = v.w >> 16;
+    if (nc > 1) {
+      const int first = at - (v.w & 0xffff);
+      const int local = u - first * tiles_m;
+      const int mt = local / nc, which = first + local % nc;
+      v = __ldg(reinterpret_cast<const int4*>(chunks + which));
+      u = which * tiles_m + mt;
+    }
     c.expert = v.x; c.row0 = v.y; c.rows = v.z; c.pad = v.w;
   }
   return c;
@@ -88,9 +125,16 @@ __device__ __forceinline__ bool take_item(const int4* queue, uint64_t* bar_qfull
   const uint32_t q = i % kQueue;
   if (!mbar_wait(bar_qfull + q, (i / kQueue) & 1u, abort)) return false;
   const int4 v = queue[q];
-  u = v.x; ch.expert = v.y; ch.row0 = v.z; ch.rows = v.w; ch.pad = 0;
+  u = v.x; ch.expert = v.y; ch.row0 = v.z; ch.rows = v.w & 0xff; ch.pad = v.w >> 8;   // pad: part of a split contraction
   mbar_arrive(bar_qempty + q);
   return true;
+}
+
+// K blocks [lo, hi) of part `part` when the contraction of `kblocks` blocks is cut in `parts`.
+__device__ __forceinline__ void k_range(int kblocks, int parts, int part, int& lo, int& hi) {
+  const int per = (kblocks + parts - 1) / parts;
+  lo = part * per;
+  hi = min(kblocks, lo + per);
 }
 
 struct GemmDev {
@@ -109,6 +153,9 @@ struct GemmDev {
   int32_t* status;
   int32_t* progress;       // see GemmArgs; NULL = kernel-boundary ordering, fixed-stride walk
   int max_chunks, tiles_before;
+  int ksplit;              // down GEMM: parts the contraction is cut in (1 = whole)
+  float* partial;          // ksplit > 1: fp32 [tile index][part][NT columns][128 channels]
+  int32_t* parts_done;     // ksplit > 1: per (chunk, channel tile) count of finished parts, zero on entry
 };
 
 template <int NT, bool DUAL>
@@ -128,8 +175,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   uint64_t* bar_full = reinterpret_cast<uint64_t*>(s_amax + 4 * NT);
   uint64_t* bar_empty = bar_full + kMaxStages;
   uint64_t* bar_tfull = bar_empty + kMaxStages;
-  uint64_t* bar_tempty = bar_tfull + kAccStages;
-  uint64_t* bar_scfull = bar_tempty + kAccStages;
+  uint64_t* bar_tempty = bar_tfull + kMaxAccStages;
+  uint64_t* bar_scfull = bar_tempty + kMaxAccStages;
   uint64_t* bar_scempty = bar_scfull + 2;
   uint64_t* bar_qfull = bar_scempty + 2;
   uint64_t* bar_qempty = bar_qfull + kQueue;
@@ -140,12 +187,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   volatile uint32_t* s_consumed = reinterpret_cast<volatile uint32_t*>(s_tmem + 3);  // K blocks whose data arrived
   volatile uint32_t* s_committed = reinterpret_cast<volatile uint32_t*>(s_tmem + 4); // accumulators committed
   volatile uint32_t* s_drained = reinterpret_cast<volatile uint32_t*>(s_tmem + 5);   // accumulators read
+  volatile int* s_last_part = reinterpret_cast<volatile int*>(s_tmem + 6);           // split contraction: this CTA closes the tile
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) { mbar_init(bar_full + s, 1); mbar_init(bar_empty + s, 1); }
-    for (int s = 0; s < kAccStages; ++s) { mbar_init(bar_tfull + s, 1); mbar_init(bar_tempty + s, C::kEpiThreads); }
+    for (int s = 0; s < C::kAcc; ++s) { mbar_init(bar_tfull + s, 1); mbar_init(bar_tempty + s, C::kEpiThreads); }
     for (int s = 0; s < 2; ++s) { mbar_init(bar_scfull + s, 32); mbar_init(bar_scempty + s, C::kEpiThreads); }
     for (int s = 0; s < kQueue; ++s) { mbar_init(bar_qfull + s, 1); mbar_init(bar_qempty + s, 64 + C::kEpiThreads); }
     *s_abort = 0; *s_issued = 0; *s_consumed = 0; *s_committed = 0; *s_drained = 0;
@@ -171,8 +219,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const bool handover = !DUAL && p.progress != nullptr;
   if (!handover) dependent_wait();
   dependents_may_launch();
+  PROBE_START(t_cta);
   const int n_chunks = *p.n_chunks;
-  const int n_units = n_chunks * p.tiles_m;
+  // A long contraction of the down GEMM is summed in `ksplit` parts, each from zero, added in part
+  // order: that is the arithmetic whatever the batch. When the tiles are too few to occupy the
+  // SMs, the parts become work items of their own (neighbours in the walk, so they run at the same
+  // time) and the last one to finish adds them up; otherwise one CTA runs all parts of a tile.
+  const int ksplit = DUAL ? 1 : p.ksplit;
+  const bool spread = ksplit > 1 && n_chunks * p.tiles_m < 2 * static_cast<int>(gridDim.x);
+  const int n_units = n_chunks * p.tiles_m * (spread ? ksplit : 1);
+  // K blocks of a work item: one part when spread, else the whole contraction
+  auto item_range = [&](int part, int& lo, int& hi) {
+    if (spread) k_range(KB, ksplit, part, lo, hi);
+    else { lo = 0; hi = KB; }
+  };
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -182,6 +242,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       uint32_t it = 0, s = 0, ph = 0, item = 0;
       int ready_chunk = -1;
       bool ok = true;
+      PROBE_DECL(probe_stage);
       // The CTA's next item: a fixed stride over the list, or the next free one of the dispenser.
       auto next_unit = [&](uint32_t ordinal) -> int {
         int u;
@@ -194,10 +255,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
         return u < n_units ? u : -1;
       };
-      int u_next = next_unit(0);
-      Chunk next = load_chunk(p.chunks, u_next, p.tiles_m);
+      // position of the walk -> (tile position, part), then tile position -> work item
+      auto resolve = [&](int& u, int& part) -> Chunk {
+        part = 0;
+        if (u >= 0 && spread) { part = u % ksplit; u /= ksplit; }
+        return load_chunk(p.chunks, u, p.tiles_m);
+      };
+      int u_next = next_unit(0), part_next = 0;
+      Chunk next = resolve(u_next, part_next);
       for (; ok; ++item) {
-        const int u = u_next;
+        const int u = u_next, part = part_next;
         const Chunk ch = next;
         {   // publish the item (or the end mark) to the other roles
           const uint32_t q = item % kQueue;
@@ -206,14 +273,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             break;
           }
           if (lane == 0) {
-            s_queue[q] = make_int4(u, ch.expert, ch.row0, ch.rows);
+            s_queue[q] = make_int4(u, ch.expert, ch.row0, ch.rows | (part << 8));
             mbar_arrive(bar_qfull + q);
           }
           __syncwarp();
         }
-        if (u < 0) break;
+        if (u < 0) {
+          if (lane == 0) { PROBE_FLUSH(p.status, 2, probe_stage); }
+          break;
+        }
         u_next = next_unit(item + 1);                          // both in flight during this item
-        next = load_chunk(p.chunks, u_next, p.tiles_m);
+        next = resolve(u_next, part_next);
         if (handover && u / p.tiles_m != ready_chunk) {
           // the chunk's rows of the intermediate activation must be complete before TMA reads them
           if (!__all_sync(0xffffffffu, wait_counter(p.progress + u / p.tiles_m, p.tiles_before, s_abort))) {
@@ -230,12 +300,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const int wrow = (shared_e ? 0 : ch.expert * p.m) + mt * 128;
         const int n16 = (ch.rows + 15) >> 4;
         const uint32_t bytes = (DUAL ? 2 : 1) * C::kABytes + n16 * 2048;
-        for (int kb = 0; kb < KB; ++kb, ++it) {
+        int kb_lo, kb_hi;
+        item_range(part, kb_lo, kb_hi);
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
+          PROBE_START(t_stage);
           if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + s, ph ^ 1u, s_abort))) {
             if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 1); *s_abort = 1; }
             ok = false;
             break;
           }
+          PROBE_ADD(probe_stage, t_stage);
           uint8_t* st = stages + s * C::kStageBytes;
           if (elect_one()) {
             mbar_expect_tx(bar_full + s, bytes);
@@ -260,6 +334,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     {
       uint32_t it = 0, s = 0, ph = 0;
       bool ok = true;
+      PROBE_DECL(probe_acc);
+      PROBE_DECL(probe_data);
       for (uint32_t item = 0; ok; ++item) {
         int u = -1;
         Chunk ch;
@@ -267,11 +343,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 8); *s_abort = 1; }
           break;
         }
-        if (u < 0) break;
+        if (u < 0) {
+          if (lane == 0) { PROBE_FLUSH(p.status, 3, probe_acc); PROBE_FLUSH(p.status, 4, probe_data); }
+          break;
+        }
         const uint32_t idesc = idesc_e4m3(128, ((ch.rows + 15) >> 4) * 16);
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const uint32_t as = it % kAccStages, aph = (it / kAccStages) & 1u;
-          const bool got = mbar_wait(bar_tempty + as, aph ^ 1u, s_abort) && mbar_wait(bar_full + s, ph, s_abort);
+        int kb_lo, kb_hi;
+        item_range(ch.pad, kb_lo, kb_hi);
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
+          const uint32_t as = it % C::kAcc, aph = (it / C::kAcc) & 1u;
+          PROBE_START(t_acc);
+          bool got = mbar_wait(bar_tempty + as, aph ^ 1u, s_abort);
+          PROBE_ADD(probe_acc, t_acc);
+          PROBE_START(t_data);
+          got = got && mbar_wait(bar_full + s, ph, s_abort);
+          PROBE_ADD(probe_data, t_data);
           if (!__all_sync(0xffffffffu, got)) {      // one decision for the warp
             if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 2); *s_abort = 1; }
             ok = false;
@@ -325,19 +411,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         for (int n = lane; n < NT; n += 32)
           sd[n] = n < ch.rows ? (p.row_dest ? p.row_dest[ch.row0 + n] : ch.row0 + n) : 0;
       }
-      for (int i = lane; i < cols * KB; i += 32) {
-        const int n = i / KB, kb = i - n * KB;
+      int kb_lo, kb_hi;
+      item_range(ch.pad, kb_lo, kb_hi);
+      const int nk = kb_hi - kb_lo;
+      for (int i = lane; i < cols * nk; i += 32) {
+        const int n = i / nk, kb = kb_lo + i - n * nk;
         // read at L2: a line shared with a neighbouring chunk may have been fetched before that
         // chunk's scales were written
         xs[kb * NT + n] = n < ch.rows ? __ldcg(p.act_scale + static_cast<size_t>(ch.row0 + n) * KB + kb) : 0.f;
       }
       const float* wa = (shared_e ? p.s_a_scale : p.w_a_scale + static_cast<size_t>(ch.expert) * p.tiles_m * KB) +
                         static_cast<size_t>(mt) * KB;
-      for (int kb = lane; kb < KB; kb += 32) ws[kb] = wa[kb];
+      for (int kb = kb_lo + lane; kb < kb_hi; kb += 32) ws[kb] = wa[kb];
       if constexpr (DUAL) {
         const float* wb = (shared_e ? p.s_b_scale : p.w_b_scale + static_cast<size_t>(ch.expert) * p.tiles_m * KB) +
                           static_cast<size_t>(mt) * KB;
-        for (int kb = lane; kb < KB; kb += 32) ws[KB + kb] = wb[kb];
+        for (int kb = kb_lo + lane; kb < kb_hi; kb += 32) ws[KB + kb] = wb[kb];
       }
       mbar_arrive(bar_scfull + b);
     }
@@ -350,6 +439,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const uint32_t lane_base = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
     uint32_t it = 0;
     bool failed = false;
+    PROBE_DECL(probe_tfull);
+    PROBE_DECL(probe_scales);
     for (uint32_t un = 0;; ++un) {
       int u = -1;
       Chunk ch;
@@ -358,41 +449,46 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         failed = true;
       }
       // one decision for all epilogue threads (the item is the same for all of them unless one failed)
-      if (epilogue_any<C::kEpiThreads>(failed) || u < 0) break;
+      if (epilogue_any<C::kEpiThreads>(failed) || u < 0) {
+        if (threadIdx.x == 96) { PROBE_FLUSH(p.status, 5, probe_tfull); PROBE_FLUSH(p.status, 6, probe_scales); }
+        break;
+      }
       const int mt = u % p.tiles_m;
       const int cols = ((ch.rows + 15) >> 4) * 16;            // token columns that were multiplied
       const uint32_t b = un & 1u, sph = (un >> 1) & 1u;
       const float* xs_all = s_scales + b * sf;
       const float* ws = xs_all + KB * NT;
       const int* sd = reinterpret_cast<const int*>(ws + 2 * KB);
+      PROBE_START(t_scales);
       if (!failed && !mbar_wait(bar_scfull + b, sph, s_abort)) {
         if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 5); *s_abort = 1; }
         failed = true;
       }
-      // destination rows were staged by the scale loader together with the scales
-      int dest[DUAL ? 1 : C::kCpt];
-      if constexpr (!DUAL) {
-#pragma unroll
-        for (int n = 0; n < C::kCpt; ++n) dest[n] = sd[col0 + n];
-      }
+      PROBE_ADD(probe_scales, t_scales);
       float acc_a[C::kCpt];
       float acc_b[C::kCpt];
 #pragma unroll
       for (int n = 0; n < C::kCpt; ++n) { acc_a[n] = 0.f; acc_b[n] = 0.f; }
-      for (int kb = 0; kb < KB; ++kb, ++it) {
-        const uint32_t as = it % kAccStages, aph = (it / kAccStages) & 1u;
+      int kb_lo, kb_hi;
+      item_range(ch.pad, kb_lo, kb_hi);
+      // one CTA runs every part of a split contraction: acc_a restarts at each part's first K
+      // block and acc_b (unused by the down GEMM otherwise) keeps the sum of the finished parts
+      const bool parts_here = !DUAL && ksplit > 1 && !spread;
+      const int part_len = (KB + ksplit - 1) / ksplit;
+      for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
+        const uint32_t as = it % C::kAcc, aph = (it / C::kAcc) & 1u;
+        PROBE_START(t_tfull);
         if (!failed && !mbar_wait(bar_tfull + as, aph, s_abort)) {
           if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 3); *s_abort = 1; }
           failed = true;
         }
+        PROBE_ADD(probe_tfull, t_tfull);
         if (failed) continue;   // keep in step with the other epilogue threads up to the item's end
         tc_fence_after();
-        if (col0 < cols) {      // uniform per warp
-          const float wa = ws[kb];
-          const float wb = DUAL ? ws[KB + kb] : 0.f;
-          const float* xs = xs_all + kb * NT + col0;
+        const bool active = col0 < cols;      // uniform per warp
+        uint32_t ra[C::kCpt], rb[DUAL ? C::kCpt : 1];
+        if (active) {
           const uint32_t t0 = lane_base + as * C::kAccCols + col0;
-          uint32_t ra[C::kCpt], rb[DUAL ? C::kCpt : 1];
 #pragma unroll
           for (int g = 0; g < C::kCpt; g += 16) {
             if (col0 + g < cols) {
@@ -401,6 +497,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
           }
           tmem_wait_ld();
+        }
+        // The values are in registers: hand the accumulator back before folding them, which
+        // shortens the round trip that bounds the K blocks per microsecond.
+        tc_fence_before();
+        mbar_arrive(bar_tempty + as);
+        if (m == 0 && epi < 4) *s_drained = it + 1;
+        if (active) {
+          const float wa = ws[kb];
+          const float wb = DUAL ? ws[KB + kb] : 0.f;
+          const float* xs = xs_all + kb * NT + col0;
 #pragma unroll
           for (int g = 0; g < C::kCpt; g += 16) {
             if (col0 + g < cols) {
@@ -412,10 +518,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               }
             }
           }
+          if constexpr (!DUAL) {
+            if (parts_here && ((kb + 1) % part_len == 0 || kb + 1 == KB)) {   // a part ends here
+#pragma unroll
+              for (int n = 0; n < C::kCpt; ++n) {
+                acc_b[n] = __fadd_rn(acc_b[n], acc_a[n]);
+                acc_a[n] = 0.f;
+              }
+            }
+          }
         }
-        tc_fence_before();
-        mbar_arrive(bar_tempty + as);
-        if (m == 0 && epi < 4) *s_drained = it + 1;
       }
       // One decision for all epilogue threads: nobody may be left alone at a later barrier.
       if (epilogue_any<C::kEpiThreads>(failed || *s_abort)) break;
@@ -427,11 +539,45 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           __threadfence();
           atomicAdd(p.progress + u / p.tiles_m, 1);
         }
+      } else if (spread) {
+        // This part's fp32 sums go to global memory; the CTA that finishes a tile's last part adds
+        // all parts in part order (so the result does not depend on which one that is) and rounds.
+        // destination rows were staged by the scale loader together with the scales
+        int dest[C::kCpt];
+#pragma unroll
+        for (int n = 0; n < C::kCpt; ++n) dest[n] = sd[col0 + n];
+        const size_t tile_floats = static_cast<size_t>(NT) * 128;
+        float* parts = p.partial + static_cast<size_t>(u) * ksplit * tile_floats;
+#pragma unroll
+        for (int n = 0; n < C::kCpt; ++n)
+          if (col0 + n < ch.rows) __stcg(parts + ch.pad * tile_floats + (col0 + n) * 128 + m, acc_a[n]);
+        __threadfence();
+        epilogue_sync<C::kEpiThreads>();
+        if (epi == 0 && lane == 0) {
+          __threadfence();
+          const int before = atomicAdd(p.parts_done + u, 1);
+          __threadfence();
+          *s_last_part = before == ksplit - 1 ? 1 : 0;
+        }
+        epilogue_sync<C::kEpiThreads>();
+        if (*s_last_part) {
+#pragma unroll
+          for (int n = 0; n < C::kCpt; ++n) {
+            if (col0 + n < ch.rows) {
+              float sum = 0.f;
+              for (int part = 0; part < ksplit; ++part)
+                sum = __fadd_rn(sum, __ldcg(parts + part * tile_floats + (col0 + n) * 128 + m));
+              p.out[static_cast<size_t>(dest[n]) * p.m + mt * kGroup + m] = __float2bfloat16_rn(sum);
+            }
+          }
+        }
       } else {
 #pragma unroll
         for (int n = 0; n < C::kCpt; ++n) {
-          if (col0 + n < ch.rows)   // one bf16 rounding of the fp32 sum (megabench/tasks/megamoe.py:149)
-            p.out[static_cast<size_t>(dest[n]) * p.m + mt * kGroup + m] = __float2bfloat16_rn(acc_a[n]);
+          if (col0 + n < ch.rows) {   // one bf16 rounding of the fp32 sum (megabench/tasks/megamoe.py:149)
+            const float sum = parts_here ? acc_b[n] : acc_a[n];
+            p.out[static_cast<size_t>(sd[col0 + n]) * p.m + mt * kGroup + m] = __float2bfloat16_rn(sum);
+          }
         }
       }
       mbar_arrive(bar_scempty + b);   // this item's scales are no longer needed
@@ -442,10 +588,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (threadIdx.x == 0) {
+    PROBE_DECL(probe_cta);
+    PROBE_ADD(probe_cta, t_cta);
+    PROBE_FLUSH(p.status, 7, probe_cta);
+  }
   if (*s_abort && threadIdx.x == 0) {
     // Give copies and MMAs that were issued but never consumed a bounded chance to land.
     for (uint32_t it = *s_consumed; it < *s_issued; ++it) mbar_wait(bar_full + it % S, (it / S) & 1u);
-    for (uint32_t it = *s_drained; it < *s_committed; ++it) mbar_wait(bar_tfull + it % kAccStages, (it / kAccStages) & 1u);
+    for (uint32_t it = *s_drained; it < *s_committed; ++it) mbar_wait(bar_tfull + it % C::kAcc, (it / C::kAcc) & 1u);
   }
   __syncthreads();
   if (warp == 1) {
@@ -540,8 +691,16 @@ cudaError_t launch_gemm_tc(const GemmArgs& a, cudaStream_t stream, int* launches
   }
   GemmDev dev{a.chunks, a.n_chunks, a.m / 128, a.k / 128, a.m, a.n_local, 0, a.act_scale, a.w_a_scale, a.w_b_scale,
               a.s_a_scale, a.s_b_scale, a.aq, a.as, a.out, a.row_dest, a.status, a.progress, a.max_chunks,
-              a.tiles_before};
-  const int grid = max(1, min(sm_count(), a.max_units));
+              a.tiles_before, 1, nullptr, nullptr};
+  if (!a.dual && a.ksplit > 1) {
+    const int per = (a.k / 128 + a.ksplit - 1) / a.ksplit;
+    if (!a.partial || !a.parts_done || (a.ksplit - 1) * per >= a.k / 128 || a.ksplit > 255) return cudaErrorInvalidValue;
+    dev.ksplit = a.ksplit;
+    dev.partial = a.partial;
+    dev.parts_done = a.parts_done;
+  }
+  const long long units = static_cast<long long>(a.max_units) * dev.ksplit;
+  const int grid = static_cast<int>(max(1ll, min(static_cast<long long>(sm_count()), units)));
   cudaError_t e;
   if (a.dual) {
     e = a.tile == 16 ? launch_typed<16, true>(dev, maps, grid, stream)

@@ -5,6 +5,7 @@
 // thread timing: a row's position is offset[expert] + (number of earlier rows with the same
 // expert), computed with ballots over the rows in order, never with order-dependent atomics.
 #include "common.cuh"
+#include "group_tables.cuh"
 #include "kernels.h"
 
 namespace moe {
@@ -37,35 +38,7 @@ __global__ void __launch_bounds__(kGroupWarps * 32) group_rows_kernel(GroupArgs 
   if (tid == 0) s_count[a.n_local] = a.shared_rows;
   __syncthreads();
 
-  // Exclusive prefix of rows and of chunks per expert, by one warp: each lane owns a run of experts.
-  if (warp == 0) {
-    const int per = (groups + 31) / 32;
-    const int first = lane * per, last = min(first + per, groups);
-    int rows = 0, chunks = 0;
-    for (int e = first; e < last; ++e) {
-      rows += s_count[e];
-      chunks += (s_count[e] + a.tile - 1) / a.tile;
-    }
-    int rows_before = rows, chunks_before = chunks;
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      const int r = __shfl_up_sync(0xffffffffu, rows_before, off);
-      const int c = __shfl_up_sync(0xffffffffu, chunks_before, off);
-      if (lane >= off) { rows_before += r; chunks_before += c; }
-    }
-    rows_before -= rows;
-    chunks_before -= chunks;
-    for (int e = first; e < last; ++e) {
-      s_offset[e] = rows_before;
-      s_chunk0[e] = chunks_before;
-      rows_before += s_count[e];
-      chunks_before += (s_count[e] + a.tile - 1) / a.tile;
-    }
-    if (last == groups && first < groups) {   // the lane holding the final expert closes the prefix
-      s_offset[groups] = rows_before;
-      s_chunk0[groups] = chunks_before;
-    }
-  }
+  if (warp == 0) group_prefix(s_count, s_offset, s_chunk0, groups, a.tile, lane);
   __syncthreads();
 
   // Stable rank: warp w walks the rows in order and places those of its expert.
@@ -87,41 +60,7 @@ __global__ void __launch_bounds__(kGroupWarps * 32) group_rows_kernel(GroupArgs 
     }
   }
 
-  if (blockIdx.x == 0) {
-    if (a.progress)
-      for (int i = tid; i < a.max_chunks + 4; i += blockDim.x) a.progress[i] = 0;
-    const int kept = s_offset[a.n_local];
-    for (int i = tid; i < groups; i += blockDim.x) {
-      a.counts[i] = s_count[i];
-      const int c = s_count[i];
-      const int nch = (c + a.tile - 1) / a.tile;
-      for (int j = 0; a.chunks && j < nch; ++j) {
-        const int slot = s_chunk0[i] + j;
-        if (slot < a.max_chunks) {
-          Chunk ch;
-          ch.expert = i;
-          ch.row0 = s_offset[i] + j * a.tile;
-          ch.rows = min(a.tile, c - j * a.tile);
-          ch.pad = 0;
-          a.chunks[slot] = ch;
-        }
-      }
-    }
-    if (a.offsets)
-      for (int i = tid; i <= groups; i += blockDim.x) a.offsets[i] = s_offset[i];
-    if (tid == 0 && a.n_chunks) {
-      const int total = s_chunk0[groups];
-      *a.n_chunks = min(total, a.max_chunks);
-      if (total > a.max_chunks && a.status) report(a.status, MOE_ERR_DEVICE_BOUNDS, 100);
-    }
-    // rows of the shared expert follow the routed rows; their output row follows all slot rows
-    for (int t = tid; t < a.shared_rows; t += blockDim.x) {
-      if (a.row_token) a.row_token[kept + t] = t;
-      if (a.row_dest) a.row_dest[kept + t] = a.n + t;
-    }
-    if (a.order)
-      for (int r = kept + tid; r < a.n; r += blockDim.x) a.order[r] = -1;
-  }
+  if (blockIdx.x == 0) group_publish(a, s_count, s_offset, s_chunk0, tid, blockDim.x);
 }
 
 cudaError_t launch_group_rows(const GroupArgs& a, cudaStream_t stream, int* launches) {

@@ -32,12 +32,20 @@ inline cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 b
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
+// Byte ranges the logits kernel asks the L2 to fetch while it runs (extra blocks, fire and forget):
+// the shared expert's weights do not depend on the routing, so they can be on their way while HBM
+// is otherwise nearly idle. Addresses and sizes are multiples of 16.
+struct L2Warm {
+  const uint8_t* ptr[3];
+  uint64_t bytes[3];
+};
+
 cudaError_t launch_router(const moe_config_t& cfg, const __nv_bfloat16* x, const float* router, const float* bias,
                           int tokens, float* logits, int32_t* ids32, float* weights, int64_t* ids64,
-                          float* weights_out, cudaStream_t stream, int* launches);
+                          float* weights_out, cudaStream_t stream, int* launches, const L2Warm* warm = nullptr);
 
 cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* router, int tokens, int experts, int hidden,
-                                 float* logits, cudaStream_t stream);
+                                 float* logits, cudaStream_t stream, const L2Warm* warm = nullptr);
 
 struct GroupArgs {
   const int32_t* ids32;   // one of ids32 / ids64 is set
@@ -58,9 +66,18 @@ struct GroupArgs {
   int32_t* status;        // optional
   const int32_t* seg_counts;  // optional: rows come in segments of seg_cap, segment s holds seg_counts[s] rows
   int seg_cap;
-  int32_t* progress;          // optional: [max_chunks + 4] counters of the GEMMs, zeroed here (see GemmArgs)
+  int32_t* progress;          // optional: counters of the GEMMs, zeroed here (see GemmArgs, WorkListLayout)
+  int progress_len;
 };
 cudaError_t launch_group_rows(const GroupArgs& a, cudaStream_t stream, int* launches);
+
+// Small batches: logits, then ONE kernel for selection + permutation + work list + quantiser of the
+// grouped rows (bf16 tokens, every expert local). `fused_route_fits` says whether the shape allows it.
+bool fused_route_fits(const moe_config_t& cfg, int tokens);
+cudaError_t launch_router_fused(const moe_config_t& cfg, const __nv_bfloat16* x, const float* router, const float* bias,
+                                int tokens, float* logits, int32_t* ids32, float* weights, int64_t* ids64,
+                                float* weights_out, const GroupArgs& g, uint8_t* xq, float* xs, cudaStream_t stream,
+                                int* launches, const L2Warm* warm = nullptr);
 
 cudaError_t launch_quantize(const void* x, int dtype, int rows, int width, const int32_t* gather, uint8_t* q,
                             float* scales, cudaStream_t stream, int* launches);
@@ -81,6 +98,45 @@ struct GatherArgs {
   float* xs;
 };
 cudaError_t launch_gather_rows(const GatherArgs& a, int row_blocks, cudaStream_t stream, int* launches);
+
+// Tokens per MMA tile (the N extent: 16, 32 or 64), from the rows a routed expert can expect.
+// A tile wider than the chunks it meets costs shared memory per pipeline stage and epilogue
+// registers for columns that are never used; a narrower one only splits the few large chunks
+// (the shared expert, hot experts), whose weight tiles are then re-read from the L2.
+inline int pick_token_tile(long long routed_rows, int experts) {
+  const long long expected = (routed_rows + experts - 1) / (experts > 0 ? experts : 1);
+  return expected <= 8 ? 16 : expected <= 16 ? 32 : 64;
+}
+
+// Parts the down projection's contraction is cut in, from the geometry alone (never from the
+// batch, so that a token's result does not depend on what else is in flight): contractions
+// longer than 64 K blocks are cut in parts of at most 32.
+inline int down_ksplit(int inter) {
+  const int kblocks = inter / 128;
+  return kblocks > 64 ? (kblocks + 31) / 32 : 1;
+}
+
+// The work list's region of a workspace: the chunks, then the int32 counters the permutation
+// kernel zeroes (per-chunk gate/up progress, 4 spare words of which the first is the down GEMM's
+// dispenser, and with a split contraction one counter per down tile), then the fp32 partial tiles.
+struct WorkListLayout {
+  uint64_t counters, parts_done, partial, bytes;   // byte offsets from the first chunk
+  int counters_len;
+};
+inline WorkListLayout work_list_layout(int max_chunks, int hidden, int inter, int tile) {
+  const int ksplit = down_ksplit(inter);
+  const int tiles_down = hidden / 128;
+  WorkListLayout w;
+  w.counters = 16ull * max_chunks;
+  w.counters_len = max_chunks + 4 + (ksplit > 1 ? max_chunks * tiles_down : 0);
+  w.parts_done = w.counters + 4ull * (max_chunks + 4);
+  uint64_t off = w.counters + 4ull * w.counters_len;
+  off = (off + 255) / 256 * 256;
+  w.partial = off;
+  if (ksplit > 1) off += 4ull * max_chunks * tiles_down * ksplit * tile * 128;
+  w.bytes = off;
+  return w;
+}
 
 struct GemmArgs {
   bool dual;                 // true: gate+up with SwiGLU + requantisation; false: down projection
@@ -115,6 +171,11 @@ struct GemmArgs {
   int32_t* progress;
   int max_chunks;
   int tiles_before;          // down GEMM: gate/up tiles per work item that must be finished
+  // Down GEMM with a long contraction: cut in `ksplit` parts (work items of their own); fp32
+  // partial tiles [chunk * tiles + tile][part][token column][128] and one zeroed counter per tile.
+  int ksplit;
+  float* partial;
+  int32_t* parts_done;
 };
 cudaError_t launch_gemm_tc(const GemmArgs& a, cudaStream_t stream, int* launches, int* driver_error);
 cudaError_t launch_gemm_simt(const GemmArgs& a, cudaStream_t stream, int* launches);

@@ -6,15 +6,9 @@
 // padded with zeros for the amax and the padding is not stored.
 #include "common.cuh"
 #include "kernels.h"
+#include "quant_group.cuh"
 
 namespace moe {
-
-template <typename T>
-__device__ __forceinline__ float load_as_float(const T* p);
-template <>
-__device__ __forceinline__ float load_as_float<float>(const float* p) { return *p; }
-template <>
-__device__ __forceinline__ float load_as_float<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 
 template <typename T>
 __global__ void __launch_bounds__(256) quantize_rows_kernel(const T* __restrict__ x, int rows, int width,
@@ -28,26 +22,8 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const T* __restrict_
   if (item >= static_cast<long long>(rows) * groups) return;
   const int row = static_cast<int>(item / groups), g = static_cast<int>(item % groups);
   const int src = gather ? gather[row] : row;
-  const T* in = x + static_cast<size_t>(src) * width;
-  const int k0 = g * kGroup + lane * 4;
-  float v[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) v[j] = (k0 + j < width) ? load_as_float<T>(in + k0 + j) : 0.f;
-  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-  const float scale = group_scale(amax);
-  uint8_t* out = q + static_cast<size_t>(row) * width;
-  if (k0 + 3 < width && (width & 3) == 0) {
-    uint32_t packed = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) packed |= static_cast<uint32_t>(to_e4m3(v[j], scale)) << (8 * j);
-    *reinterpret_cast<uint32_t*>(out + k0) = packed;
-  } else {
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (k0 + j < width) out[k0 + j] = to_e4m3(v[j], scale);
-  }
+  const float scale = quantize_group<T>(x + static_cast<size_t>(src) * width, q + static_cast<size_t>(row) * width, g,
+                                        width, lane);
   if (lane == 0) scales[static_cast<size_t>(row) * groups + g] = scale;
 }
 

@@ -7,7 +7,9 @@
 //            stable descending sort of c; w = p[ids] / (sum + 1e-20) * scaling.
 //   softmax: ids = first topk of a stable descending sort of s; w = softmax(s[ids]).
 #include "common.cuh"
+#include "group_tables.cuh"
 #include "kernels.h"
+#include "quant_group.cuh"
 
 namespace moe {
 
@@ -123,13 +125,9 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_select_kernel(RouteArg
 // E/32 values, loaded as one contiguous run), a router group is a whole number of lanes, and every
 // step is shuffles over registers instead of shared-memory sweeps. Same rules, same tie order
 // (larger value first, lower expert index on equal values).
+// One warp selects for token t; lane j < topk returns choice j and its weight.
 template <int EPL>
-__global__ void __launch_bounds__(kRouteWarps * 32) route_select_regs_kernel(RouteArgs a) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * kRouteWarps + warp;
-  dependent_wait();
-  dependents_may_launch();
-  if (t >= a.tokens) return;
+__device__ __forceinline__ void select_in_registers(const RouteArgs& a, int t, int lane, int& pick, float& weight) {
   const int E = a.experts;
   const float ninf = __int_as_float(0xff800000);
   const bool sigmoid = a.scoring == MOE_SCORING_SIGMOID;
@@ -216,12 +214,126 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_select_regs_kernel(Rou
     for (int j = 0; j < a.topk; ++j) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, ex, j));
     w = __fdiv_rn(ex, sum);
   }
+  pick = my_pick;
+  weight = w;
+}
+
+template <int EPL>
+__global__ void __launch_bounds__(kRouteWarps * 32) route_select_regs_kernel(RouteArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kRouteWarps + warp;
+  dependent_wait();
+  dependents_may_launch();
+  if (t >= a.tokens) return;
+  int pick;
+  float w;
+  select_in_registers<EPL>(a, t, lane, pick, w);
   if (lane < a.topk) {
     const size_t o = static_cast<size_t>(t) * a.topk + lane;
-    a.ids32[o] = my_pick;
+    a.ids32[o] = pick;
     a.weights[o] = w;
-    if (a.ids64) a.ids64[o] = my_pick;
+    if (a.ids64) a.ids64[o] = pick;
     if (a.weights_out) a.weights_out[o] = w;
+  }
+}
+
+// Small batches, one launch for everything between the logits and the expert GEMMs: every block
+// repeats the selection of all tokens (a warp per token) and the stable grouping of the
+// tokens * topk rows (a few hundred comparisons per thread), then quantises the one grouped row
+// it is responsible for; block 0 also publishes ids, weights, permutation and the work list. The
+// three separate kernels cost more in launch hand-overs than in work at these sizes. Same device
+// functions as the separate kernels, so the bytes are the same.
+constexpr int kFusedMaxRows = 512;     // tokens * topk
+constexpr int kFusedMaxTokens = 32;
+
+struct FusedArgs {
+  RouteArgs r;
+  GroupArgs g;               // ids32 / n / topk / id_base = 0 / n_local = experts as for the permutation kernel
+  const __nv_bfloat16* x;    // [tokens, hidden]
+  int hidden;
+  uint8_t* xq;               // grouped rows, then the shared expert's rows
+  float* xs;
+};
+
+template <int EPL, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) route_group_quant_kernel(FusedArgs a) {
+  __shared__ int16_t s_id[kFusedMaxRows];
+  __shared__ int16_t s_pos[kFusedMaxRows];
+  __shared__ float s_w[kFusedMaxRows];
+  __shared__ int s_count[MOE_MAX_EXPERTS + 1];
+  __shared__ int s_offset[MOE_MAX_EXPERTS + 2];
+  __shared__ int s_chunk0[MOE_MAX_EXPERTS + 2];
+  __shared__ int s_src;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int T = a.r.tokens, K = a.r.topk, R = T * K, E = a.r.experts;
+  const bool publisher = blockIdx.x == 0;
+  dependent_wait();
+  dependents_may_launch();
+
+  if (warp < T) {
+    int pick;
+    float w;
+    select_in_registers<EPL>(a.r, warp, lane, pick, w);
+    if (lane < K) {
+      s_id[warp * K + lane] = static_cast<int16_t>(pick);
+      s_w[warp * K + lane] = w;
+    }
+  }
+  for (int i = tid; i <= E; i += WARPS * 32) s_count[i] = 0;
+  if (tid == 0) s_src = 0;
+  __syncthreads();
+
+  // Stable position of every row: rows of lower experts first, then earlier rows of the same one.
+  for (int r = tid; r < R; r += WARPS * 32) {
+    const int e = s_id[r];
+    int pos = 0;
+    for (int o = 0; o < R; ++o) {
+      const int eo = s_id[o];
+      pos += (eo < e || (eo == e && o < r)) ? 1 : 0;
+    }
+    s_pos[r] = static_cast<int16_t>(pos);
+    if (pos == static_cast<int>(blockIdx.x)) s_src = r / K;
+    if (publisher) atomicAdd(&s_count[e], 1);
+  }
+  if (static_cast<int>(blockIdx.x) >= R && tid == 0) s_src = blockIdx.x - R;   // a row of the shared expert
+  if (publisher && tid == 0) s_count[E] = a.g.shared_rows;
+  __syncthreads();
+
+  {   // this block's row
+    const int groups = (a.hidden + kGroup - 1) / kGroup;
+    const __nv_bfloat16* in = a.x + static_cast<size_t>(s_src) * a.hidden;
+    uint8_t* out = a.xq + static_cast<size_t>(blockIdx.x) * a.hidden;
+    constexpr int kAhead = 4;     // groups whose loads a warp issues before it uses the first
+    for (int g0 = warp; g0 < groups; g0 += WARPS * kAhead) {
+      float v[kAhead][4];
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u) load_group<__nv_bfloat16>(in, min(g0 + u * WARPS, groups - 1), a.hidden, lane, v[u]);
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u) {
+        const int g = g0 + u * WARPS;
+        if (g < groups) {
+          const float scale = quantize_loaded(v[u], out, g, a.hidden, lane);
+          if (lane == 0) a.xs[static_cast<size_t>(blockIdx.x) * groups + g] = scale;
+        }
+      }
+    }
+  }
+
+  if (publisher) {
+    if (warp == 0) group_prefix(s_count, s_offset, s_chunk0, E + 1, a.g.tile, lane);
+    for (int r = tid; r < R; r += WARPS * 32) {
+      const int pos = s_pos[r], id = s_id[r];
+      const float w = s_w[r];
+      a.r.ids32[r] = id;
+      a.r.weights[r] = w;
+      if (a.r.ids64) a.r.ids64[r] = id;
+      if (a.r.weights_out) a.r.weights_out[r] = w;
+      if (a.g.order) a.g.order[pos] = r;
+      if (a.g.row_token) a.g.row_token[pos] = r / K;
+      if (a.g.row_dest) a.g.row_dest[pos] = r;
+    }
+    __syncthreads();
+    group_publish(a.g, s_count, s_offset, s_chunk0, tid, WARPS * 32);
   }
 }
 
@@ -238,10 +350,57 @@ static bool regs_variant_fits(const moe_config_t& cfg, int epl) {
   return true;
 }
 
+static int regs_variant_of(const moe_config_t& cfg) {
+  for (int epl : {1, 2, 4, 8, 12, 16})
+    if (regs_variant_fits(cfg, epl)) return epl;
+  return 0;
+}
+
+bool fused_route_fits(const moe_config_t& cfg, int tokens) {
+  return tokens >= 1 && tokens <= kFusedMaxTokens && tokens * cfg.topk <= kFusedMaxRows && regs_variant_of(cfg) != 0;
+}
+
+template <int EPL>
+static void launch_fused_typed(const FusedArgs& a, int blocks, cudaStream_t stream) {
+  if (a.r.tokens <= 16)
+    launch_dependent(route_group_quant_kernel<EPL, 16>, dim3(blocks), dim3(16 * 32), 0, stream, a);
+  else
+    launch_dependent(route_group_quant_kernel<EPL, 32>, dim3(blocks), dim3(32 * 32), 0, stream, a);
+}
+
+cudaError_t launch_router_fused(const moe_config_t& cfg, const __nv_bfloat16* x, const float* router, const float* bias,
+                                int tokens, float* logits, int32_t* ids32, float* weights, int64_t* ids64,
+                                float* weights_out, const GroupArgs& g, uint8_t* xq, float* xs, cudaStream_t stream,
+                                int* launches, const L2Warm* warm) {
+  if (!fused_route_fits(cfg, tokens) || g.n_local != cfg.n_experts || g.id_base != 0 || g.n != tokens * cfg.topk)
+    return cudaErrorInvalidValue;
+  cudaError_t e = launch_router_logits(x, router, tokens, cfg.n_experts, cfg.hidden, logits, stream, warm);
+  if (e != cudaSuccess) return e;
+  FusedArgs a;
+  a.r = RouteArgs{logits, bias, tokens, cfg.n_experts, cfg.topk, cfg.scoring, cfg.n_group, cfg.topk_group,
+                  cfg.routed_scaling, ids32, weights, ids64, weights_out};
+  a.g = g;
+  a.x = x;
+  a.hidden = cfg.hidden;
+  a.xq = xq;
+  a.xs = xs;
+  const int blocks = g.n + g.shared_rows;
+  switch (regs_variant_of(cfg)) {
+    case 1: launch_fused_typed<1>(a, blocks, stream); break;
+    case 2: launch_fused_typed<2>(a, blocks, stream); break;
+    case 4: launch_fused_typed<4>(a, blocks, stream); break;
+    case 8: launch_fused_typed<8>(a, blocks, stream); break;
+    case 12: launch_fused_typed<12>(a, blocks, stream); break;
+    default: launch_fused_typed<16>(a, blocks, stream); break;
+  }
+  if (launches) *launches += 2;
+  return cudaGetLastError();
+}
+
 cudaError_t launch_router(const moe_config_t& cfg, const __nv_bfloat16* x, const float* router, const float* bias,
                           int tokens, float* logits, int32_t* ids32, float* weights, int64_t* ids64,
-                          float* weights_out, cudaStream_t stream, int* launches) {
-  cudaError_t e = launch_router_logits(x, router, tokens, cfg.n_experts, cfg.hidden, logits, stream);
+                          float* weights_out, cudaStream_t stream, int* launches, const L2Warm* warm) {
+  cudaError_t e = launch_router_logits(x, router, tokens, cfg.n_experts, cfg.hidden, logits, stream, warm);
   if (e != cudaSuccess) return e;
   RouteArgs a{logits, bias, tokens, cfg.n_experts, cfg.topk, cfg.scoring, cfg.n_group, cfg.topk_group,
               cfg.routed_scaling, ids32, weights, ids64, weights_out};

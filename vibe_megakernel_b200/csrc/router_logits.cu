@@ -47,17 +47,41 @@ __device__ __forceinline__ float warp_total(float lane_sum) {
   return __fadd_rn(s.hi, s.lo);
 }
 
+// Blocks past the logits grid (index `block` of `blocks`) ask the L2 to fetch the given ranges,
+// 4 KB per request, and return without waiting for the data.
+constexpr int kWarmBlocks = 32;
+constexpr uint32_t kWarmPiece = 4096;
+__device__ __forceinline__ void warm_l2(const L2Warm& w, int block, int blocks) {
+  const uint64_t first = static_cast<uint64_t>(block) * blockDim.x + threadIdx.x;
+  const uint64_t stride = static_cast<uint64_t>(blocks) * blockDim.x;
+#pragma unroll
+  for (int r = 0; r < 3; ++r) {
+    const uint64_t pieces = w.bytes[r] / kWarmPiece;     // a ragged tail is left to the GEMM's own loads
+    for (uint64_t i = first; i < pieces; i += stride)
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(w.ptr[r] + i * kWarmPiece), "r"(kWarmPiece) : "memory");
+  }
+}
+
 // Small batches (TT tokens at most): two warps per block, one expert row per warp, so that a
-// 256-expert router still spreads over 128 blocks; each trip issues the loads of 8 pieces of 128
-// channels (4 KB of the router row per warp) before the first use.
+// 256-expert router still spreads over 128 blocks; each trip issues the loads of kRowsAhead pieces
+// of 128 channels before the first use (14 KB of the router row per warp for a single token: with
+// two warps per SM the kernel is bound by memory round trips, so fewer and larger trips win).
 constexpr int kRowsWarps = 2;
-constexpr int kRowsAhead = 8;
+template <int TT>
+struct RowsAhead {
+  static constexpr int value = TT == 1 ? 28 : TT <= 4 ? 14 : 8;
+};
 
 template <int TT>
 __global__ void __launch_bounds__(kRowsWarps * 32) router_logits_rows_kernel(const __nv_bfloat16* __restrict__ x,
                                                                               const float* __restrict__ router,
                                                                               int tokens, int experts, int hidden,
-                                                                              float* __restrict__ logits) {
+                                                                              float* __restrict__ logits,
+                                                                              const L2Warm warm, int logit_blocks) {
+  if (static_cast<int>(blockIdx.x) >= logit_blocks) {   // weights do not change: no need to wait for anything
+    if (blockIdx.y == 0) warm_l2(warm, blockIdx.x - logit_blocks, gridDim.x - logit_blocks);
+    return;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int e = blockIdx.x * kRowsWarps + warp;
   const int t0 = blockIdx.y * TT;
@@ -70,6 +94,7 @@ __global__ void __launch_bounds__(kRowsWarps * 32) router_logits_rows_kernel(con
   for (int t = 0; t < TT; ++t) acc[t] = 0.f;
   const float* row = router + static_cast<size_t>(e) * hidden;
   const int quads = hidden / 4;
+  constexpr int kRowsAhead = RowsAhead<TT>::value;
   for (int q0 = lane; q0 < quads; q0 += 32 * kRowsAhead) {
     float4 r[kRowsAhead];
     uint2 xv[kRowsAhead][TT];
@@ -109,8 +134,13 @@ constexpr int kTiledExperts = kTiledWarps * kTiledExpertsPerWarp;
 __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(const __nv_bfloat16* __restrict__ x,
                                                                                const float* __restrict__ router,
                                                                                int tokens, int experts, int hidden,
-                                                                               float* __restrict__ logits) {
+                                                                               float* __restrict__ logits,
+                                                                               const L2Warm warm, int logit_blocks) {
   extern __shared__ __align__(128) uint2 s_x[];        // [8][hidden / 4], four bf16 per entry
+  if (static_cast<int>(blockIdx.x) >= logit_blocks) {
+    if (blockIdx.y == 0) warm_l2(warm, blockIdx.x - logit_blocks, gridDim.x - logit_blocks);
+    return;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int quads = hidden / 4;
   const int t0 = blockIdx.y * kLogitTokens;
@@ -178,20 +208,31 @@ __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(c
 }
 
 cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* router, int tokens, int experts, int hidden,
-                                 float* logits, cudaStream_t stream) {
+                                 float* logits, cudaStream_t stream, const L2Warm* warm_request) {
   const size_t tile_smem = static_cast<size_t>(kLogitTokens) * hidden * sizeof(__nv_bfloat16);
   const int row_blocks = (experts + kRowsWarps - 1) / kRowsWarps;
   const bool tiled_ok = tile_smem <= 200 * 1024 && !(reinterpret_cast<uintptr_t>(x) & 15) && hidden % 8 == 0;
   const dim3 rows_block(kRowsWarps * 32);
+  L2Warm warm = {};
+  int extra = 0;
+  if (warm_request) {
+    for (int r = 0; r < 3; ++r) {
+      if (warm_request->ptr[r] && !(reinterpret_cast<uintptr_t>(warm_request->ptr[r]) & 15)) {
+        warm.ptr[r] = warm_request->ptr[r];
+        warm.bytes[r] = warm_request->bytes[r];
+        extra = kWarmBlocks;
+      }
+    }
+  }
   if (tokens == 1) {
-    launch_dependent(router_logits_rows_kernel<1>, dim3(row_blocks, 1), rows_block, 0, stream, x, router, tokens, experts,
-                     hidden, logits);
+    launch_dependent(router_logits_rows_kernel<1>, dim3(row_blocks + extra, 1), rows_block, 0, stream, x, router, tokens,
+                     experts, hidden, logits, warm, row_blocks);
   } else if (tokens <= 4) {
-    launch_dependent(router_logits_rows_kernel<4>, dim3(row_blocks, 1), rows_block, 0, stream, x, router, tokens, experts,
-                     hidden, logits);
+    launch_dependent(router_logits_rows_kernel<4>, dim3(row_blocks + extra, 1), rows_block, 0, stream, x, router, tokens,
+                     experts, hidden, logits, warm, row_blocks);
   } else if (tokens <= 8 || !tiled_ok) {
-    launch_dependent(router_logits_rows_kernel<8>, dim3(row_blocks, (tokens + 7) / 8), rows_block, 0, stream, x, router,
-                     tokens, experts, hidden, logits);
+    launch_dependent(router_logits_rows_kernel<8>, dim3(row_blocks + extra, (tokens + 7) / 8), rows_block, 0, stream, x,
+                     router, tokens, experts, hidden, logits, warm, row_blocks);
   } else {
     static bool configured = false;
     if (!configured) {
@@ -200,9 +241,10 @@ cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* router, in
       if (e != cudaSuccess) return e;
       configured = true;
     }
-    dim3 grid((experts + kTiledExperts - 1) / kTiledExperts, (tokens + kLogitTokens - 1) / kLogitTokens);
+    const int tiled_blocks = (experts + kTiledExperts - 1) / kTiledExperts;
+    dim3 grid(tiled_blocks + extra, (tokens + kLogitTokens - 1) / kLogitTokens);
     launch_dependent(router_logits_tiled_kernel, grid, dim3(kTiledWarps * 32), tile_smem, stream, x, router, tokens,
-                     experts, hidden, logits);
+                     experts, hidden, logits, warm, tiled_blocks);
   }
   return cudaGetLastError();
 }
