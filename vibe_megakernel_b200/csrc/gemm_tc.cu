@@ -85,7 +85,9 @@ struct GemmCfg {
   // Shared memory after the stage ring, for a contraction of kb K blocks:
   //   2 buffers of { x scales [kb][NT], weight scales [2][kb] }, amax scratch [4][NT],
   //   barriers (2*kMaxStages + 2*kMaxAccStages + 2 + 2 + 2*kQueue), the item queue, 8 words of flags.
-  static constexpr int scale_floats(int kb) { return kb * NT + 2 * kb + NT; }   // + destination rows [NT]
+  // (every part a multiple of four floats, so the token scales can be read 16 bytes at a time)
+  static constexpr int weight_scale_floats(int kb) { return (2 * kb + 3) & ~3; }
+  static constexpr int scale_floats(int kb) { return kb * NT + weight_scale_floats(kb) + NT; }   // + destination rows [NT]
   static constexpr int tail_bytes(int kb) {
     return 2 * scale_floats(kb) * 4 + 4 * NT * 4 + (2 * kMaxStages + 2 * kMaxAccStages + 4 + 2 * kQueue) * 8 + kQueue * 16 + 64;
   }
@@ -405,7 +407,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const bool shared_e = ch.expert >= p.n_local;
       float* xs = s_scales + b * sf;            // [kb][NT]
       float* ws = xs + KB * NT;                 // [2][kb]
-      int* sd = reinterpret_cast<int*>(ws + 2 * KB);   // [NT] destination row of every token column
+      int* sd = reinterpret_cast<int*>(ws + C::weight_scale_floats(KB));   // [NT] destination row of every token column
       const int cols = ((ch.rows + 15) >> 4) * 16;
       if constexpr (!DUAL) {
         for (int n = lane; n < NT; n += 32)
@@ -414,11 +416,37 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       int kb_lo, kb_hi;
       item_range(ch.pad, kb_lo, kb_hi);
       const int nk = kb_hi - kb_lo;
-      for (int i = lane; i < cols * nk; i += 32) {
-        const int n = i / nk, kb = kb_lo + i - n * nk;
-        // read at L2: a line shared with a neighbouring chunk may have been fetched before that
-        // chunk's scales were written
-        xs[kb * NT + n] = n < ch.rows ? __ldcg(p.act_scale + static_cast<size_t>(ch.row0 + n) * KB + kb) : 0.f;
+      // Token scales, transposed to [K block][column]. Read at L2: a line shared with a
+      // neighbouring chunk may have been fetched before that chunk's scales were written.
+      if (((KB | kb_lo | nk) & 3) == 0) {
+        // a lane takes a row (the transposed stores then fall in different banks), four K blocks
+        // per load, eight loads in flight
+        const int quads = nk >> 2;
+        for (int n = lane; n < cols; n += 32) {
+          const bool live = n < ch.rows;
+          const float4* src =
+              reinterpret_cast<const float4*>(p.act_scale + static_cast<size_t>(ch.row0 + (live ? n : 0)) * KB + kb_lo);
+          for (int q0 = 0; q0 < quads; q0 += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __ldcg(src + min(q0 + j, quads - 1));
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (q0 + j < quads) {
+                float* dst = xs + (kb_lo + 4 * (q0 + j)) * NT + n;
+                dst[0] = live ? v[j].x : 0.f;
+                dst[NT] = live ? v[j].y : 0.f;
+                dst[2 * NT] = live ? v[j].z : 0.f;
+                dst[3 * NT] = live ? v[j].w : 0.f;
+              }
+            }
+          }
+        }
+      } else {
+        for (int i = lane; i < cols * nk; i += 32) {
+          const int n = i / nk, kb = kb_lo + i - n * nk;
+          xs[kb * NT + n] = n < ch.rows ? __ldcg(p.act_scale + static_cast<size_t>(ch.row0 + n) * KB + kb) : 0.f;
+        }
       }
       const float* wa = (shared_e ? p.s_a_scale : p.w_a_scale + static_cast<size_t>(ch.expert) * p.tiles_m * KB) +
                         static_cast<size_t>(mt) * KB;
@@ -458,7 +486,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const uint32_t b = un & 1u, sph = (un >> 1) & 1u;
       const float* xs_all = s_scales + b * sf;
       const float* ws = xs_all + KB * NT;
-      const int* sd = reinterpret_cast<const int*>(ws + 2 * KB);
+      const int* sd = reinterpret_cast<const int*>(ws + C::weight_scale_floats(KB));
       PROBE_START(t_scales);
       if (!failed && !mbar_wait(bar_scfull + b, sph, s_abort)) {
         if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 5); *s_abort = 1; }
@@ -510,9 +538,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
           for (int g = 0; g < C::kCpt; g += 16) {
             if (col0 + g < cols) {
+              // 16 token scales as four 16-byte loads (col0 and NT are multiples of 16)
+              float x16[16];
+#pragma unroll
+              for (int j = 0; j < 16; j += 4)
+                *reinterpret_cast<float4*>(x16 + j) = *reinterpret_cast<const float4*>(xs + g + j);
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
-                const float x = xs[g + j];
+                const float x = x16[j];
                 acc_a[g + j] = fmaf(__uint_as_float(ra[g + j]), __fmul_rn(wa, x), acc_a[g + j]);
                 if constexpr (DUAL) acc_b[g + j] = fmaf(__uint_as_float(rb[g + j]), __fmul_rn(wb, x), acc_b[g + j]);
               }
