@@ -191,15 +191,18 @@ __device__ __forceinline__ void select_in_registers(const RouteArgs& a, int t, i
       const int e = e0 + i;
       if (e < E && !((taken >> i) & 1u) && (be < 0 || c[i] > bv)) { bv = c[i]; be = e; bp = p[i]; }
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
-      const int oe = __shfl_xor_sync(0xffffffffu, be, off);
-      const float op = __shfl_xor_sync(0xffffffffu, bp, off);
-      if (oe >= 0 && (be < 0 || ov > bv || (ov == bv && oe < be))) { bv = ov; be = oe; bp = op; }
-    }
-    if (be >= 0 && be / EPL == lane) taken |= 1u << (be - e0);
-    if (lane == j) { my_pick = be; my_prob = bp; }      // lane j keeps pick j
+    // Across the warp with two integer reductions: the largest value (floats mapped to unsigned
+    // keys of the same order; -0 counts as +0 as in a float comparison), then the lowest expert
+    // index among the lanes holding it.
+    const unsigned bits = __float_as_uint(bv + 0.f);
+    const unsigned key = be < 0 ? 0u : ((bits & 0x80000000u) ? ~bits : (bits | 0x80000000u));
+    const unsigned top = __reduce_max_sync(0xffffffffu, key);
+    const unsigned lowest =
+        __reduce_min_sync(0xffffffffu, (be >= 0 && key == top) ? static_cast<unsigned>(be) : 0xffffffffu);
+    const int chosen = static_cast<int>(lowest);            // -1 when nothing was left
+    const float chosen_p = __shfl_sync(0xffffffffu, bp, max(chosen, 0) / EPL);
+    if (chosen >= 0 && chosen / EPL == lane) taken |= 1u << (chosen - e0);
+    if (lane == j) { my_pick = chosen; my_prob = chosen_p; }      // lane j keeps pick j
   }
   // weights: slot-order sum as the scalar reference code, then one division per slot
   float w = 0.f;
@@ -240,7 +243,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_select_regs_kernel(Rou
 // Small batches, one launch for everything between the logits and the expert GEMMs: every block
 // repeats the selection of all tokens (a warp per token) and the stable grouping of the
 // tokens * topk rows (a few hundred comparisons per thread), then quantises the one grouped row
-// it is responsible for; block 0 also publishes ids, weights, permutation and the work list. The
+// it is responsible for; block 0 instead publishes ids, weights, permutation and the work list. The
 // three separate kernels cost more in launch hand-overs than in work at these sizes. Same device
 // functions as the separate kernels, so the bytes are the same.
 constexpr int kFusedMaxRows = 512;     // tokens * topk
@@ -266,7 +269,8 @@ __global__ void __launch_bounds__(WARPS * 32) route_group_quant_kernel(FusedArgs
   __shared__ int s_src;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int T = a.r.tokens, K = a.r.topk, R = T * K, E = a.r.experts;
-  const bool publisher = blockIdx.x == 0;
+  const bool publisher = blockIdx.x == 0;      // block 0 publishes the tables, block 1 + i quantises grouped row i
+  const int my_row = static_cast<int>(blockIdx.x) - 1;
   dependent_wait();
   dependents_may_launch();
 
@@ -292,17 +296,17 @@ __global__ void __launch_bounds__(WARPS * 32) route_group_quant_kernel(FusedArgs
       pos += (eo < e || (eo == e && o < r)) ? 1 : 0;
     }
     s_pos[r] = static_cast<int16_t>(pos);
-    if (pos == static_cast<int>(blockIdx.x)) s_src = r / K;
+    if (pos == my_row) s_src = r / K;
     if (publisher) atomicAdd(&s_count[e], 1);
   }
-  if (static_cast<int>(blockIdx.x) >= R && tid == 0) s_src = blockIdx.x - R;   // a row of the shared expert
+  if (my_row >= R && tid == 0) s_src = my_row - R;   // a row of the shared expert
   if (publisher && tid == 0) s_count[E] = a.g.shared_rows;
   __syncthreads();
 
-  {   // this block's row
+  if (!publisher) {   // this block's row
     const int groups = (a.hidden + kGroup - 1) / kGroup;
     const __nv_bfloat16* in = a.x + static_cast<size_t>(s_src) * a.hidden;
-    uint8_t* out = a.xq + static_cast<size_t>(blockIdx.x) * a.hidden;
+    uint8_t* out = a.xq + static_cast<size_t>(my_row) * a.hidden;
     constexpr int kAhead = 4;     // groups whose loads a warp issues before it uses the first
     for (int g0 = warp; g0 < groups; g0 += WARPS * kAhead) {
       float v[kAhead][4];
@@ -313,13 +317,11 @@ __global__ void __launch_bounds__(WARPS * 32) route_group_quant_kernel(FusedArgs
         const int g = g0 + u * WARPS;
         if (g < groups) {
           const float scale = quantize_loaded(v[u], out, g, a.hidden, lane);
-          if (lane == 0) a.xs[static_cast<size_t>(blockIdx.x) * groups + g] = scale;
+          if (lane == 0) a.xs[static_cast<size_t>(my_row) * groups + g] = scale;
         }
       }
     }
-  }
-
-  if (publisher) {
+  } else {
     if (warp == 0) group_prefix(s_count, s_offset, s_chunk0, E + 1, a.g.tile, lane);
     for (int r = tid; r < R; r += WARPS * 32) {
       const int pos = s_pos[r], id = s_id[r];
@@ -384,7 +386,7 @@ cudaError_t launch_router_fused(const moe_config_t& cfg, const __nv_bfloat16* x,
   a.hidden = cfg.hidden;
   a.xq = xq;
   a.xs = xs;
-  const int blocks = g.n + g.shared_rows;
+  const int blocks = 1 + g.n + g.shared_rows;
   switch (regs_variant_of(cfg)) {
     case 1: launch_fused_typed<1>(a, blocks, stream); break;
     case 2: launch_fused_typed<2>(a, blocks, stream); break;

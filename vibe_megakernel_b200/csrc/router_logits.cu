@@ -63,14 +63,11 @@ __device__ __forceinline__ void warm_l2(const L2Warm& w, int block, int blocks) 
 }
 
 // Small batches (TT tokens at most): two warps per block, one expert row per warp, so that a
-// 256-expert router still spreads over 128 blocks; each trip issues the loads of kRowsAhead pieces
-// of 128 channels before the first use (14 KB of the router row per warp for a single token: with
-// two warps per SM the kernel is bound by memory round trips, so fewer and larger trips win).
+// 256-expert router still spreads over 128 blocks. The router rows (weights: requested before the
+// wait on the previous kernel) and the token rows arrive in shared memory by bulk async copies, one
+// request per row: everything a block needs is in flight at once, which loads through registers
+// did not achieve (the compiler kept a handful in flight and the kernel was bound by round trips).
 constexpr int kRowsWarps = 2;
-template <int TT>
-struct RowsAhead {
-  static constexpr int value = TT == 1 ? 28 : TT <= 4 ? 14 : 8;
-};
 
 template <int TT>
 __global__ void __launch_bounds__(kRowsWarps * 32) router_logits_rows_kernel(const __nv_bfloat16* __restrict__ x,
@@ -78,43 +75,48 @@ __global__ void __launch_bounds__(kRowsWarps * 32) router_logits_rows_kernel(con
                                                                               int tokens, int experts, int hidden,
                                                                               float* __restrict__ logits,
                                                                               const L2Warm warm, int logit_blocks) {
+  extern __shared__ __align__(128) uint8_t s_rows_raw[];
   if (static_cast<int>(blockIdx.x) >= logit_blocks) {   // weights do not change: no need to wait for anything
     if (blockIdx.y == 0) warm_l2(warm, blockIdx.x - logit_blocks, gridDim.x - logit_blocks);
     return;
   }
+  __shared__ uint64_t bar;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int e = blockIdx.x * kRowsWarps + warp;
+  const int e_first = blockIdx.x * kRowsWarps;
   const int t0 = blockIdx.y * TT;
   const int tcount = min(TT, tokens - t0);
+  const int quads = hidden / 4;
+  float4* s_router = reinterpret_cast<float4*>(s_rows_raw);                       // [kRowsWarps][quads]
+  uint2* s_x = reinterpret_cast<uint2*>(s_router + kRowsWarps * quads);           // [TT][quads], four bf16 per entry
+  const int rows_here = min(kRowsWarps, experts - e_first);
+  const uint32_t router_bytes = static_cast<uint32_t>(hidden) * 4u, x_bytes = static_cast<uint32_t>(hidden) * 2u;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_expect_tx(&bar, router_bytes * rows_here + x_bytes * tcount);
+    for (int w = 0; w < rows_here; ++w)
+      bulk_copy_g2s(s_router + static_cast<size_t>(w) * quads, router + static_cast<size_t>(e_first + w) * hidden,
+                    router_bytes, &bar);
+  }
   dependent_wait();
   dependents_may_launch();
+  if (threadIdx.x == 0) {
+    for (int t = 0; t < tcount; ++t)
+      bulk_copy_g2s(s_x + static_cast<size_t>(t) * quads, x + static_cast<size_t>(t0 + t) * hidden, x_bytes, &bar);
+  }
+  __syncthreads();              // the barrier is initialised before anyone polls it
+  mbar_wait(&bar, 0);           // bounded; a copy that never lands leaves wrong logits, not a hang
   if (e >= experts) return;
   float acc[TT];
 #pragma unroll
   for (int t = 0; t < TT; ++t) acc[t] = 0.f;
-  const float* row = router + static_cast<size_t>(e) * hidden;
-  const int quads = hidden / 4;
-  constexpr int kRowsAhead = RowsAhead<TT>::value;
-  for (int q0 = lane; q0 < quads; q0 += 32 * kRowsAhead) {
-    float4 r[kRowsAhead];
-    uint2 xv[kRowsAhead][TT];
+  const float4* row = s_router + static_cast<size_t>(warp) * quads;
+  for (int q = lane; q < quads; q += 32) {
+    const float4 r = row[q];
 #pragma unroll
-    for (int u = 0; u < kRowsAhead; ++u) {
-      // unconditional loads from clamped addresses: the compiler can then issue all of a trip's
-      // loads back to back (values loaded past the row or the batch are never used)
-      const int q = min(q0 + 32 * u, quads - 1);
-      r[u] = __ldg(reinterpret_cast<const float4*>(row + 4 * q));
-#pragma unroll
-      for (int t = 0; t < TT; ++t)
-        xv[u][t] = __ldg(reinterpret_cast<const uint2*>(x + static_cast<size_t>(t0 + min(t, tcount - 1)) * hidden + 4 * q));
-    }
-#pragma unroll
-    for (int u = 0; u < kRowsAhead; ++u) {
-      if (q0 + 32 * u < quads) {
-#pragma unroll
-        for (int t = 0; t < TT; ++t) acc[t] = fma4(r[u], xv[u][t], acc[t]);
-      }
-    }
+    for (int t = 0; t < TT; ++t)
+      if (t < tcount) acc[t] = fma4(r, s_x[static_cast<size_t>(t) * quads + q], acc[t]);
   }
 #pragma unroll
   for (int t = 0; t < TT; ++t) {
@@ -224,15 +226,27 @@ cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* router, in
       }
     }
   }
-  if (tokens == 1) {
-    launch_dependent(router_logits_rows_kernel<1>, dim3(row_blocks + extra, 1), rows_block, 0, stream, x, router, tokens,
-                     experts, hidden, logits, warm, row_blocks);
-  } else if (tokens <= 4) {
-    launch_dependent(router_logits_rows_kernel<4>, dim3(row_blocks + extra, 1), rows_block, 0, stream, x, router, tokens,
-                     experts, hidden, logits, warm, row_blocks);
+  // bulk copies need 16-byte aligned rows (hidden is a multiple of 128, so only the bases matter)
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(router)) & 15) return cudaErrorMisalignedAddress;
+  const size_t router_smem = static_cast<size_t>(kRowsWarps) * hidden * sizeof(float);
+  auto rows_smem = [&](int tt) { return router_smem + static_cast<size_t>(tt) * hidden * sizeof(__nv_bfloat16); };
+  auto launch_rows = [&](auto kernel, int tt) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+    return launch_dependent(kernel, dim3(row_blocks + extra, (tokens + tt - 1) / tt), rows_block, rows_smem(tt), stream, x,
+                            router, tokens, experts, hidden, logits, warm, row_blocks);
+  };
+  const size_t smem_limit = 200 * 1024;
+  if (rows_smem(1) > smem_limit) return cudaErrorInvalidValue;
+  if (tokens == 1 || rows_smem(4) > smem_limit) {
+    cudaError_t e = launch_rows(router_logits_rows_kernel<1>, 1);
+    if (e != cudaSuccess) return e;
+  } else if (tokens <= 4 || rows_smem(8) > smem_limit) {
+    cudaError_t e = launch_rows(router_logits_rows_kernel<4>, 4);
+    if (e != cudaSuccess) return e;
   } else if (tokens <= 8 || !tiled_ok) {
-    launch_dependent(router_logits_rows_kernel<8>, dim3(row_blocks + extra, (tokens + 7) / 8), rows_block, 0, stream, x,
-                     router, tokens, experts, hidden, logits, warm, row_blocks);
+    cudaError_t e = launch_rows(router_logits_rows_kernel<8>, 8);
+    if (e != cudaSuccess) return e;
   } else {
     static bool configured = false;
     if (!configured) {
