@@ -156,6 +156,18 @@ def gate_up_bytes(geo, distinct: int) -> int:
     return (distinct + geo.shared) * per_expert
 
 
+# DRAM traffic of one gate/up GEMM launch per unit (one expert hit by the batch), from an ncu capture
+# (--set full) of this kernel on a small case of the DeepSeek-V3 geometry (64 routed experts, batch 8):
+# dram__bytes_read.sum + dram__bytes_write.sum = 1,322,132,000 + 3,483,392 B for 45 units. Traffic
+# grows in proportion to the experts hit, every weight byte being read once.
+NCU_GATE_UP_TRAFFIC_PER_UNIT = {(7168, 2048): (1_322_132_000 + 3_483_392) / 45}
+
+
+def gate_up_traffic(geo, distinct: int):
+    per_unit = NCU_GATE_UP_TRAFFIC_PER_UNIT.get((geo.hidden, geo.inter))
+    return None if per_unit is None else int(round((distinct + geo.shared) * per_unit))
+
+
 def cpu_oracle_sample(geo, values: dict, sample_tokens: int, distinct_full: int, threads: int, repeats: int = 1):
     """Time the CPU oracle on the first ``sample_tokens`` tokens; returns (seconds per sample step,
     scaled microseconds for the full batch, description)."""
@@ -284,7 +296,8 @@ def main_single(args) -> dict:
         "roofline": {"bound": "hbm", "kernel": "grouped_gemm_kernel<dual> (gate/up GEMM + SwiGLU + requantisation)",
                      "achieved": round(extra["gate_up_bytes"] / (extra["gate_up_ms"] * 1e-3) / 1e9, 1), "peak": peak,
                      "unit": "GB/s", "frac": round(extra["gate_up_bytes"] / (extra["gate_up_ms"] * 1e-3) / 1e9 / peak, 4),
-                     "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "peak_kind": f"of {peak_kind}", "traffic": gate_up_traffic(geo, extra["distinct"]),
+                     "traffic_source": "ncu dram bytes of a smaller case of the same kernel, scaled by experts hit",
                      "algorithmic_bytes_per_launch": extra["gate_up_bytes"],
                      "kernel_us": round(extra["gate_up_ms"] * 1e3, 2)},
         "layer": {k: head[k] for k in ("distinct_experts", "algorithmic_bytes", "layer_gbs",

@@ -31,6 +31,12 @@ extern "C" {
 
 #define MOE_SCORING_SOFTMAX 0 /* stable top-k of the logits, softmax over the selection */
 #define MOE_SCORING_SIGMOID 1 /* sigmoid + selection bias, group-limited, normalised, scaled */
+/* p = sqrt(softplus(logit)); selection on p + bias (the same group limit applies when n_group > 1);
+ * weights p[ids] / (sum + 1e-20) * routed_scaling: megabench/tasks/dsv41.py:622-626. */
+#define MOE_SCORING_SQRT_SOFTPLUS 2
+/* The bias is the router's linear-layer bias: scores = logit + bias decide the stable top-k AND
+ * enter the softmax over the selection: megabench/tasks/gptoss.py:106-109. */
+#define MOE_SCORING_SOFTMAX_BIASED 3
 
 #define MOE_GEMM_TCGEN05 0 /* tcgen05 FP8 MMA, TMEM accumulators, TMA-fed (the product path) */
 #define MOE_GEMM_SIMT 1    /* plain CUDA-core check arm used by the tests to localise faults */
@@ -138,6 +144,15 @@ int moe_quantize_rows(const void* x, int32_t dtype, int32_t rows, int32_t width,
  * (rows per expert; the last entry is reserved and written as 0). */
 int moe_group_rows(const int64_t* ids, int32_t n, int32_t id_base, int32_t n_local, int64_t* order,
                    int32_t* counts, void* stream);
+
+/* Weighted combine / un-permute of down-projection rows stored in slot order:
+ * y[t] = bf16( sum over slot = 0..topk-1, in that order, of fp32(rows[t*topk + slot]) * weights[t*topk + slot],
+ * then + fp32(rows[tokens*topk + t]) when `shared` is non-zero ), every product and sum rounded to fp32.
+ * Replaces the fp32 slot-order sum with one bf16 rounding of megabench/tasks/megamoe.py:176-182 in
+ * its weighted form, megabench/tasks/frontier.py:349-354. rows bf16 [tokens*topk (+ tokens), hidden],
+ * weights fp32 [tokens*topk], y bf16 [tokens, hidden]; hidden a multiple of 8, pointers 16-byte aligned. */
+int moe_combine(const void* rows_bf16, const float* weights, int32_t tokens, int32_t topk, int32_t hidden,
+                int32_t shared, void* y_bf16, void* stream);
 
 /* The experts held by this rank applied to rows that are already quantised: gate/up GEMM, SwiGLU,
  * requantisation, down GEMM; result rows bf16 [n_rows, H] in the order of the input rows.

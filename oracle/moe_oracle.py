@@ -157,6 +157,27 @@ def route_softmax(scores: torch.Tensor, topk: int):
     return ids, torch.softmax(scores[ids], dim=-1)
 
 
+def route_sqrt_softplus(scores: torch.Tensor, bias: torch.Tensor | None, topk: int, scaling: float):
+    """One token. p = sqrt(softplus(s)); ids = first ``topk`` of a stable
+    descending sort of p + bias; weights = p[ids] / (sum + 1e-20) * scaling.
+    megabench/tasks/dsv41.py:622-626 (``descending`` is the stable argsort of
+    megabench/tasks/dsv41.py:278-280)."""
+    p = torch.nn.functional.softplus(scores.to(torch.float32)).sqrt()
+    c = p if bias is None else p + bias
+    ids = torch.argsort(c, descending=True, stable=True)[:topk]
+    w = p[ids]
+    return ids, w / (w.sum() + 1e-20) * scaling
+
+
+def route_softmax_biased(scores: torch.Tensor, bias: torch.Tensor | None, topk: int):
+    """One token. The bias is the router's linear-layer bias: s = logits + bias,
+    ids = first ``topk`` of a stable descending sort of s, weights =
+    softmax(s[ids]). megabench/tasks/gptoss.py:106-109."""
+    s = scores if bias is None else scores + bias
+    ids = torch.argsort(s, descending=True, stable=True)[:topk]
+    return ids, torch.softmax(s[ids], dim=-1)
+
+
 # --------------------------------------------------------------------------
 # Layer
 # --------------------------------------------------------------------------
@@ -190,6 +211,10 @@ def route_tokens(spec: LayerSpec, x: torch.Tensor, router: torch.Tensor, bias: t
             i, w = route_sigmoid_grouped(s, bias, spec.topk, spec.n_group, spec.topk_group, spec.scaling)
         elif spec.scoring == "softmax":
             i, w = route_softmax(s, spec.topk)
+        elif spec.scoring == "sqrt_softplus":
+            i, w = route_sqrt_softplus(s, bias, spec.topk, spec.scaling)
+        elif spec.scoring == "softmax_biased":
+            i, w = route_softmax_biased(s, bias, spec.topk)
         else:
             raise ValueError(spec.scoring)
         ids.append(i)
@@ -320,6 +345,10 @@ def decision_margins(spec: LayerSpec, x: torch.Tensor, router: torch.Tensor, bia
                 alive = torch.zeros(spec.n_group, dtype=torch.bool, device=x.device)
                 alive[keep] = True
                 c = torch.where(alive[:, None], g, torch.full_like(g, -math.inf)).reshape(-1)
+        elif spec.scoring == "sqrt_softplus":
+            c = torch.nn.functional.softplus(s).sqrt() + (bias.to(torch.float64) if bias is not None else 0)
+        elif spec.scoring == "softmax_biased":
+            c = s + (bias.to(torch.float64) if bias is not None else 0)
         else:
             c = s
         top = torch.sort(c, descending=True).values[:spec.topk + 1]

@@ -121,6 +121,33 @@ def router_vectors():
         for t in range(12):
             ids[t], ws[t] = softmax_route(scores[t], topk)
         out[f"{name}_scores"], out[f"{name}_ids"], out[f"{name}_w"] = scores.numpy(), ids.numpy(), ws.numpy()
+    # sqrt-softplus scores with a selection bias: the expressions of tasks/dsv41.py:623-626
+    from megabench.tasks import dsv41
+    for name, e, topk in (("sp256", 256, 6), ("sp32", 32, 4)):
+        scores = torch.randn((12, e), generator=gen) * 3
+        scores[2, 0] = 25.0                                   # beyond softplus's threshold
+        scores[5, 3] = scores[5, 9]                           # an exact tie
+        bias = torch.randn((e,), generator=gen) * 0.05
+        p = torch.nn.functional.softplus(scores.float()).sqrt()
+        ids = dsv41.descending(p + bias, topk)
+        ws = p.gather(-1, ids)
+        ws = ws / (ws.sum(-1, keepdim=True) + 1e-20) * dsv41.ROUTE_SCALE
+        out[f"{name}_scores"], out[f"{name}_bias"] = scores.numpy(), bias.numpy()
+        out[f"{name}_ids"], out[f"{name}_w"] = ids.numpy(), ws.numpy()
+    out["sp_scaling"] = np.array([dsv41.ROUTE_SCALE], dtype=np.float64)
+    # router with a linear-layer bias, stable top-k, softmax over the selection: tasks/gptoss.py:106-109
+    for name, e, topk in (("go32", 32, 4), ("go128", 128, 4)):
+        x = torch.randn((12, 64), generator=gen)
+        router = torch.randn((e, 64), generator=gen) * 0.2
+        bias = torch.randn((e,), generator=gen) * 0.3
+        ids = torch.empty((12, topk), dtype=torch.int64)
+        ws = torch.empty((12, topk))
+        for t in range(12):
+            scores = torch.nn.functional.linear(x[t], router, bias)
+            selected = torch.argsort(scores, descending=True, stable=True)[:topk]
+            ids[t], ws[t] = selected, scores[selected].softmax(-1)
+        out[f"{name}_logits"] = (x @ router.T).numpy()        # without the bias: the kernels add it themselves
+        out[f"{name}_bias"], out[f"{name}_ids"], out[f"{name}_w"] = bias.numpy(), ids.numpy(), ws.numpy()
     np.savez_compressed(HERE / "routers.npz", **out)
 
 

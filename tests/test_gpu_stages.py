@@ -1,5 +1,7 @@
 """GPU parity of the single stages (through the C ABI) against the oracle and the golden vectors."""
 
+import dataclasses
+
 import numpy as np
 import pytest
 import torch
@@ -97,6 +99,37 @@ def test_router_ids_are_bit_exact(api, name, tokens):
     torch.testing.assert_close(w.cpu(), want_w, rtol=2e-5, atol=1e-7)
 
 
+@pytest.mark.parametrize("scoring,experts,topk,tokens", [("sqrt_softplus", 256, 6, 1), ("sqrt_softplus", 256, 6, 40),
+                                                          ("sqrt_softplus", 48, 8, 19), ("softmax_biased", 128, 4, 1),
+                                                          ("softmax_biased", 32, 4, 33), ("softmax_biased", 40, 4, 70)])
+def test_other_router_scorings(api, scoring, experts, topk, tokens):
+    # sqrt-softplus scores with a selection bias (megabench/tasks/dsv41.py:622-626) and the softmax
+    # router with a linear bias (megabench/tasks/gptoss.py:106-109): ids bit-exact, weights to 2e-5
+    geo = dataclasses.replace(synthetic.GEOMETRIES["qwen3_30b_a3b"], name=scoring, hidden=512, inter=128,
+                              experts=experts, topk=topk, scoring=scoring, scaling=1.5, bias_kind="normal",
+                              bias_std=0.05 if scoring == "sqrt_softplus" else 0.3, router_std=0.05)
+    x, router, bias, seed = H.audited_routing_inputs(geo, tokens)
+    layer = api.MoeLayer(api.LayerConfig.from_geometry(geo), max_tokens=tokens)
+    ids, w = layer.route(x.cuda(), router.cuda(), bias.cuda())
+    want_ids, want_w = O.route_tokens(H.spec_of(geo), x, router, bias)
+    assert torch.equal(ids.cpu(), want_ids), f"seed {seed}"
+    torch.testing.assert_close(w.cpu(), want_w, rtol=2e-5, atol=1e-7)
+
+
+def test_other_router_scorings_through_the_layer(api):
+    for scoring in ("sqrt_softplus", "softmax_biased"):
+        geo = dataclasses.replace(H.small_geometries()["kimi_small"], name=scoring, scoring=scoring, scaling=1.5,
+                                  bias_kind="normal", bias_std=0.05)
+        for tokens in (3, 40):
+            values, _ = H.audited_inputs(geo, tokens)
+            want = O.moe_layer(H.spec_of(geo), values)
+            layer = api.MoeLayer(api.LayerConfig.from_geometry(geo), max_tokens=tokens)
+            out = layer.forward(H.to_device(values, "cuda"), check_status=True)
+            assert torch.equal(out["expert_ids"].cpu(), want["expert_ids"])
+            assert torch.equal(out["order"].cpu(), want["order"])
+            H.assert_y_close(out["y"], want["y"], scoring)
+
+
 def test_router_ties_go_to_the_lower_index(api):
     # all-zero logits: megabench/tests/test_frontier.py:297-299 expects ids [0, 1], weights 1.25
     cfg = api.LayerConfig(hidden=128, inter=128, experts=8, topk=2, shared=0, scoring="sigmoid", n_group=2,
@@ -139,3 +172,21 @@ def test_experts_entry_point_matches_the_oracle_and_the_layer(api, name, n):
         want_sh, _, _ = O.expert_mlp(q, s, values["shared_gate"], values["shared_gate_scale"], values["shared_up"],
                                      values["shared_up_scale"], values["shared_down"], values["shared_down_scale"])
         H.assert_y_close(api.experts_forward(config, dev, q.cuda(), s.cuda(), None), want_sh, "shared expert rows")
+
+
+# ---------------------------------------------------------------- combine
+@pytest.mark.parametrize("tokens,topk,hidden,shared", [(1, 8, 7168, True), (19, 4, 512, False), (64, 2, 4096, True)])
+def test_combine_is_the_slot_order_fp32_sum(api, tokens, topk, hidden, shared):
+    # megabench/tasks/megamoe.py:176-182 (fp32 accumulator, slots in order, one bf16 rounding) with the
+    # weights of megabench/tasks/frontier.py:352: bit-exact, the order of the additions is fixed
+    gen = torch.Generator().manual_seed(tokens * 31 + topk)
+    rows = torch.randn((tokens * topk + (tokens if shared else 0), hidden), generator=gen).to(torch.bfloat16)
+    w = torch.rand((tokens, topk), generator=gen) * 2.5
+    acc = torch.zeros((tokens, hidden), dtype=torch.float32)
+    slots = rows[: tokens * topk].reshape(tokens, topk, hidden)
+    for s in range(topk):
+        acc = acc + slots[:, s].to(torch.float32) * w[:, s:s + 1]
+    if shared:
+        acc = acc + rows[tokens * topk:].to(torch.float32)
+    got = api.combine(rows.cuda(), w.cuda(), tokens, shared)
+    assert torch.equal(got.cpu().view(torch.int16), acc.to(torch.bfloat16).view(torch.int16))

@@ -82,6 +82,29 @@ def test_softmax_router(golden_dir):
             assert np.array_equal(w.numpy(), g[f"{name}_w"][t])
 
 
+def test_sqrt_softplus_router(golden_dir):
+    # vectors made with the expressions of megabench/tasks/dsv41.py:623-626
+    g = np.load(golden_dir / "routers.npz")
+    scaling = float(g["sp_scaling"][0])
+    for name, k in (("sp256", 6), ("sp32", 4)):
+        scores, bias = torch.from_numpy(g[f"{name}_scores"]), torch.from_numpy(g[f"{name}_bias"])
+        for t in range(scores.shape[0]):
+            ids, w = O.route_sqrt_softplus(scores[t], bias, k, scaling)
+            assert np.array_equal(ids.numpy(), g[f"{name}_ids"][t])
+            np.testing.assert_allclose(w.numpy(), g[f"{name}_w"][t], rtol=1e-6, atol=0)
+
+
+def test_biased_softmax_router(golden_dir):
+    # vectors made with the expressions of megabench/tasks/gptoss.py:106-109
+    g = np.load(golden_dir / "routers.npz")
+    for name, k in (("go32", 4), ("go128", 4)):
+        logits, bias = torch.from_numpy(g[f"{name}_logits"]), torch.from_numpy(g[f"{name}_bias"])
+        for t in range(logits.shape[0]):
+            ids, w = O.route_softmax_biased(logits[t], bias, k)
+            assert np.array_equal(ids.numpy(), g[f"{name}_ids"][t])
+            np.testing.assert_allclose(w.numpy(), g[f"{name}_w"][t], rtol=1e-5, atol=1e-7)
+
+
 def small_layers():
     return {
         "tiny": synthetic.GEOMETRIES["tiny"],

@@ -11,7 +11,7 @@ OK = 0
 ERRORS = {-1: "bad argument", -2: "unsupported geometry", -3: "workspace too small",
           -4: "device wait timed out", -5: "tensor-map encode failed", -6: "device index out of range",
           -7: "request exceeds the static scratch limit"}
-SCORING = {"softmax": 0, "sigmoid": 1}
+SCORING = {"softmax": 0, "sigmoid": 1, "sqrt_softplus": 2, "softmax_biased": 3}
 GEMM_TCGEN05, GEMM_SIMT = 0, 1
 
 
@@ -70,6 +70,8 @@ EXPORTS = {
     "moe_quantize_rows": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
                                     C.c_void_p]),
     "moe_group_rows": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "moe_combine": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                              C.c_void_p]),
     "moe_layer_forward": (C.c_int, [C.POINTER(Config), C.POINTER(Weights), C.c_void_p, C.c_int32, C.c_void_p,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "moe_device_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]),

@@ -32,7 +32,7 @@ int check_config(const moe_config_t* c) {
   if (c->hidden % 128 || c->inter % 128) return MOE_ERR_UNSUPPORTED;
   if (c->n_experts > MOE_MAX_EXPERTS || c->topk > MOE_MAX_TOPK || c->topk > c->n_experts) return MOE_ERR_UNSUPPORTED;
   if (c->n_shared < 0 || c->n_shared > 1) return MOE_ERR_UNSUPPORTED;
-  if (c->scoring != MOE_SCORING_SOFTMAX && c->scoring != MOE_SCORING_SIGMOID) return MOE_ERR_BAD_ARG;
+  if (c->scoring < MOE_SCORING_SOFTMAX || c->scoring > MOE_SCORING_SOFTMAX_BIASED) return MOE_ERR_BAD_ARG;
   if (c->n_group < 1 || c->n_group > 32 || c->n_experts % c->n_group) return MOE_ERR_BAD_ARG;
   if (c->topk_group < 1 || c->topk_group > c->n_group) return MOE_ERR_BAD_ARG;
   if (c->ep_world < 1 || c->ep_rank < 0 || c->ep_rank >= c->ep_world || c->n_experts % c->ep_world) return MOE_ERR_BAD_ARG;
@@ -129,6 +129,16 @@ int moe_group_rows(const int64_t* ids, int32_t n, int32_t id_base, int32_t n_loc
   a.order = order;
   int launches = 0;
   return from_cuda(moe::launch_group_rows(a, static_cast<cudaStream_t>(stream), &launches));
+}
+
+int moe_combine(const void* rows_bf16, const float* weights, int32_t tokens, int32_t topk, int32_t hidden, int32_t shared,
+                void* y_bf16, void* stream) {
+  if (!rows_bf16 || !weights || !y_bf16 || tokens < 1 || topk < 1 || hidden < 8 || hidden % 8) return MOE_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(rows_bf16) | reinterpret_cast<uintptr_t>(y_bf16)) & 15) return MOE_ERR_BAD_ARG;
+  int launches = 0;
+  return from_cuda(moe::launch_combine(static_cast<const __nv_bfloat16*>(rows_bf16), weights, tokens, topk, hidden,
+                                       shared ? 1 : 0, static_cast<__nv_bfloat16*>(y_bf16),
+                                       static_cast<cudaStream_t>(stream), &launches));
 }
 
 int moe_layer_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* x_bf16, int32_t tokens,

@@ -6,6 +6,9 @@
 //            topk_group best groups (ties to the lower group), others -> -inf; ids = first topk of a
 //            stable descending sort of c; w = p[ids] / (sum + 1e-20) * scaling.
 //   softmax: ids = first topk of a stable descending sort of s; w = softmax(s[ids]).
+// Two more scorings ride on the same two shapes (see score_of): sqrt-softplus scores with the
+// sigmoid rule's selection bias and normalisation (megabench/tasks/dsv41.py:622-626), and a softmax
+// over logits that carry the router's linear bias (megabench/tasks/gptoss.py:106-109).
 #include "common.cuh"
 #include "group_tables.cuh"
 #include "kernels.h"
@@ -26,6 +29,33 @@ struct RouteArgs {
 
 constexpr int kRouteWarps = 4;
 
+// Score p (what the weights are made of) and selection value c of one logit.
+//   sigmoid:        p = sigmoid(s), c = p + bias                (megabench/tasks/frontier.py:229-231)
+//   sqrt-softplus:  p = sqrt(softplus(s)), c = p + bias         (megabench/tasks/dsv41.py:623-624; softplus with
+//                   torch's threshold: s itself above 20)
+//   softmax:        p = c = s
+//   biased softmax: p = c = s + bias                            (megabench/tasks/gptoss.py:106)
+__device__ __forceinline__ void score_of(int scoring, float s, float bias, float& p, float& c) {
+  if (scoring == MOE_SCORING_SIGMOID) {
+    p = __fdiv_rn(1.f, __fadd_rn(1.f, expf(-s)));
+    c = __fadd_rn(p, bias);
+  } else if (scoring == MOE_SCORING_SQRT_SOFTPLUS) {
+    p = __fsqrt_rn(s > 20.f ? s : log1pf(expf(s)));
+    c = __fadd_rn(p, bias);
+  } else if (scoring == MOE_SCORING_SOFTMAX_BIASED) {
+    p = __fadd_rn(s, bias);
+    c = p;
+  } else {
+    p = s;
+    c = s;
+  }
+}
+// The rules whose weights are p / (sum of the picked p) * scaling and which know router groups;
+// the others take a softmax over the picked values.
+__device__ __forceinline__ bool normalised_scoring(int scoring) {
+  return scoring == MOE_SCORING_SIGMOID || scoring == MOE_SCORING_SQRT_SOFTPLUS;
+}
+
 __global__ void __launch_bounds__(kRouteWarps * 32) route_select_kernel(RouteArgs a) {
   __shared__ float s_choice[kRouteWarps][MOE_MAX_EXPERTS];
   __shared__ float s_prob[kRouteWarps][MOE_MAX_EXPERTS];
@@ -40,20 +70,12 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_select_kernel(RouteArg
   const int E = a.experts;
   const float ninf = __int_as_float(0xff800000);
 
-  for (int e = lane; e < E; e += 32) {
-    const float s = a.logits[static_cast<size_t>(t) * E + e];
-    if (a.scoring == MOE_SCORING_SIGMOID) {
-      const float pr = __fdiv_rn(1.f, __fadd_rn(1.f, expf(-s)));
-      p[e] = pr;
-      c[e] = __fadd_rn(pr, a.bias ? a.bias[e] : 0.f);
-    } else {
-      p[e] = s;
-      c[e] = s;
-    }
-  }
+  const bool normalised = normalised_scoring(a.scoring);
+  for (int e = lane; e < E; e += 32)
+    score_of(a.scoring, a.logits[static_cast<size_t>(t) * E + e], a.bias ? a.bias[e] : 0.f, p[e], c[e]);
   __syncwarp();
 
-  if (a.scoring == MOE_SCORING_SIGMOID && a.n_group > 1) {
+  if (normalised && a.n_group > 1) {
     const int gsz = E / a.n_group;
     float score = ninf;
     if (lane < a.n_group) {
@@ -100,7 +122,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_select_kernel(RouteArg
 
   if (lane == 0) {
     float w[MOE_MAX_TOPK];
-    if (a.scoring == MOE_SCORING_SIGMOID) {
+    if (normalised) {
       float sum = 0.f;
       for (int j = 0; j < a.topk; ++j) { w[j] = p[s_pick[warp][j]]; sum = __fadd_rn(sum, w[j]); }
       const float den = __fadd_rn(sum, 1e-20f);
@@ -130,26 +152,17 @@ template <int EPL>
 __device__ __forceinline__ void select_in_registers(const RouteArgs& a, int t, int lane, int& pick, float& weight) {
   const int E = a.experts;
   const float ninf = __int_as_float(0xff800000);
-  const bool sigmoid = a.scoring == MOE_SCORING_SIGMOID;
+  const bool sigmoid = normalised_scoring(a.scoring);    // sigmoid-like: grouped, normalised weights
   const int e0 = lane * EPL;
   float p[EPL], c[EPL], s[EPL], b[EPL];
   // E == 32 * EPL here, so every lane's run is in range: plain loads, all issued before first use
 #pragma unroll
   for (int i = 0; i < EPL; ++i) s[i] = __ldg(a.logits + static_cast<size_t>(t) * E + e0 + i);
-  const bool biased = sigmoid && a.bias != nullptr;
+  const bool biased = a.scoring != MOE_SCORING_SOFTMAX && a.bias != nullptr;
 #pragma unroll
   for (int i = 0; i < EPL; ++i) b[i] = biased ? __ldg(a.bias + e0 + i) : 0.f;
 #pragma unroll
-  for (int i = 0; i < EPL; ++i) {
-    if (sigmoid) {
-      const float pr = __fdiv_rn(1.f, __fadd_rn(1.f, expf(-s[i])));
-      p[i] = pr;
-      c[i] = __fadd_rn(pr, b[i]);
-    } else {
-      p[i] = s[i];
-      c[i] = s[i];
-    }
-  }
+  for (int i = 0; i < EPL; ++i) score_of(a.scoring, s[i], b[i], p[i], c[i]);
   if (sigmoid && a.n_group > 1) {
     const int gsz = E / a.n_group;
     const int lanes_per_group = gsz / EPL;             // power of two (checked by the launcher)
@@ -343,7 +356,7 @@ __global__ void __launch_bounds__(WARPS * 32) route_group_quant_kernel(FusedArgs
 // runs of lanes.
 static bool regs_variant_fits(const moe_config_t& cfg, int epl) {
   if (cfg.n_experts != 32 * epl || cfg.topk > 32) return false;
-  if (cfg.scoring == MOE_SCORING_SIGMOID && cfg.n_group > 1) {
+  if ((cfg.scoring == MOE_SCORING_SIGMOID || cfg.scoring == MOE_SCORING_SQRT_SOFTPLUS) && cfg.n_group > 1) {
     const int gsz = cfg.n_experts / cfg.n_group;
     if (gsz % epl) return false;
     const int lpg = gsz / epl;

@@ -285,3 +285,20 @@ def group_rows(ids: torch.Tensor, n_local: int, id_base: int = 0):
                             torch.cuda.current_stream(ids.device).cuda_stream)
     _cabi.check("moe_group_rows", rc)
     return order[:n], counts[:n_local]
+
+
+def combine(rows: torch.Tensor, weights: torch.Tensor, tokens: int, shared: bool) -> torch.Tensor:
+    """Slot-order weighted sum of down-projection rows (plus the shared expert's row): bf16 [tokens, H].
+
+    ``rows`` bf16 [tokens*topk (+ tokens), H] in slot order, ``weights`` fp32 [tokens, topk]."""
+    lib = _cabi.load()
+    rows = _require(rows, "rows", torch.bfloat16)
+    weights = _require(weights, "weights", torch.float32)
+    topk = weights.numel() // tokens
+    if rows.dim() != 2 or rows.shape[0] != tokens * topk + (tokens if shared else 0):
+        raise ValueError("rows must be [tokens*topk (+ tokens), H]")
+    y = torch.empty((tokens, rows.shape[1]), dtype=torch.bfloat16, device=rows.device)
+    rc = lib.moe_combine(rows.data_ptr(), weights.data_ptr(), tokens, topk, rows.shape[1], 1 if shared else 0,
+                         y.data_ptr(), torch.cuda.current_stream(rows.device).cuda_stream)
+    _cabi.check("moe_combine", rc)
+    return y

@@ -31,7 +31,7 @@ class MoeGeometry:
     experts: int
     topk: int
     shared: int            # shared experts (0 or 1)
-    scoring: str           # "sigmoid" | "softmax"
+    scoring: str           # "sigmoid" | "softmax" | "sqrt_softplus" | "softmax_biased"
     n_group: int
     topk_group: int
     scaling: float
@@ -112,7 +112,7 @@ def fp8_matrix(seed: int, name: str, rows: int, cols: int, std: float, device):
 
 def router_bias(geo: MoeGeometry, seed: int, device) -> torch.Tensor | None:
     if geo.bias_kind == "none":
-        return torch.zeros(geo.experts, device=device, dtype=torch.float32) if geo.scoring == "sigmoid" else None
+        return torch.zeros(geo.experts, device=device, dtype=torch.float32) if geo.scoring != "softmax" else None
     if geo.bias_kind == "normal":
         return _normal(seed, "router_bias", (geo.experts,), geo.bias_std, device)
     if geo.bias_kind == "zipf":
