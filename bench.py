@@ -252,9 +252,14 @@ def measure_batch(geo, values: dict, tokens: int, steps: int, warmup: int, flush
 
     e2e_ms = timed_steps(e2e_step, steps, warmup, flush)
     assert torch.equal(y_host, out["y"].cpu()), "plugin path and direct path disagree"
+    # the layer with the step either side of it (RMSNorm in front, residual add behind): one more launch
+    gamma = torch.ones(geo.hidden, dtype=torch.bfloat16, device=inputs["x"].device)
+    block_ms = timed_steps(lambda: layer.block_forward(inputs, gamma, 1e-6, weight_in_fp32=True),
+                           max(3, steps // 2), 3, flush)
+    layer.check_device_status(tokens)
     extra = {"ms": ms, "e2e_us": 1e3 * sum(e2e_ms) / len(e2e_ms), "io_bytes": x_host.numel() * 2,
              "gate_up_ms": stages["gate_up_gemm"], "gate_up_bytes": g_bytes, "distinct": distinct,
-             "launches": launches}
+             "launches": launches, "block_us": 1e3 * sum(block_ms) / len(block_ms)}
     return res, extra
 
 
@@ -302,6 +307,7 @@ def main_single(args) -> dict:
                      "kernel_us": round(extra["gate_up_ms"] * 1e3, 2)},
         "layer": {k: head[k] for k in ("distinct_experts", "algorithmic_bytes", "layer_gbs",
                                        "layer_frac_of_measured_peak", "layer_frac_of_8tbs", "stage_us")},
+        "block_with_norm_and_residual_us": round(extra["block_us"], 2),
         "sweep": sweep,
     }
     if not args.no_cpu_baseline:

@@ -175,6 +175,20 @@ int moe_layer_forward(const moe_config_t* cfg, const moe_weights_t* weights, con
                       void* y_bf16, int64_t* expert_ids, float* topk_weights, int64_t* order, void* workspace,
                       size_t workspace_bytes, void* stream);
 
+/* The layer with the step either side of it: RMSNorm of the residual stream in front, residual add
+ * behind. Replaces megabench/tasks/frontier.py:335 (`normalized = norm(x, ln2)`, `rms` of
+ * megabench/tasks/common.py:13-21) ... :354 (`x = x + output.to(x.dtype)`):
+ *   n = bf16 RMSNorm(x) with weight norm_weight_bf16 [H] and eps; weight_in_fp32 != 0 rounds once,
+ *   after the fp32 product with the weight (DeepSeek family), 0 rounds the normalised value to bf16
+ *   first and multiplies in bf16 (Llama/Qwen/GLM);
+ *   x_out = bf16(x + bf16(layer(n))).
+ * x_out may be x itself (the stream is then updated in place); the other arguments are those of
+ * moe_layer_forward and the same workspace serves both. */
+int moe_block_forward(const moe_config_t* cfg, const moe_weights_t* weights, const void* x_bf16,
+                      const void* norm_weight_bf16, float eps, int32_t weight_in_fp32, int32_t tokens,
+                      void* x_out_bf16, int64_t* expert_ids, float* topk_weights, int64_t* order, void* workspace,
+                      size_t workspace_bytes, void* stream);
+
 /* ---- expert parallelism over the GPUs of one node ------------------------------------------
  * Rank r owns experts [r*E/world, (r+1)*E/world) and `tokens` rows of the batch; router, bias and
  * shared expert are replicated (megabench/tasks/megamoe.py:100-105, megabench/tasks/kimi_layer.py:4-6).

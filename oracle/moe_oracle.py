@@ -322,6 +322,33 @@ def moe_layer(spec: LayerSpec, values: dict, *, compute=torch.bfloat16, keep_int
     return out
 
 
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, *, weight_in_fp32: bool = False) -> torch.Tensor:
+    """RMSNorm in front of the MoE block. n = x.float() * rsqrt(mean(x.float()^2)
+    + eps); ``weight_in_fp32`` (DeepSeek family): (n * weight.float()) rounded
+    once to x's dtype; otherwise n is rounded to x's dtype and multiplied by
+    the weight in that dtype. megabench/tasks/common.py:13-21 (without the
+    Gemma offset), called at megabench/tasks/frontier.py:260,335."""
+    xf = x.to(torch.float32)
+    n = xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)
+    if weight_in_fp32:
+        return (n * weight.to(torch.float32)).to(x.dtype)
+    return n.to(x.dtype) * weight.to(x.dtype)
+
+
+def moe_block(spec: LayerSpec, values: dict, norm_weight: torch.Tensor, eps: float = 1e-6, *,
+              weight_in_fp32: bool = False, **kwargs) -> dict:
+    """The layer with the step either side: ``x + layer(rms(x))`` where the
+    layer's output is rounded to x's dtype before the add and the sum is
+    rounded again (megabench/tasks/frontier.py:335 ... 354). Returns the
+    layer's outputs with ``x`` (the new residual stream) and ``normalized``."""
+    x = values["x"]
+    normalized = rms_norm(x, norm_weight, eps, weight_in_fp32=weight_in_fp32)
+    out = moe_layer(spec, {**values, "x": normalized}, **kwargs)
+    out["normalized"] = normalized
+    out["x"] = x + out["y"].to(x.dtype)
+    return out
+
+
 def decision_margins(spec: LayerSpec, x: torch.Tensor, router: torch.Tensor, bias: torch.Tensor | None) -> float:
     """Smallest gap at any routing decision boundary, from fp64 logits.
 

@@ -230,9 +230,37 @@ def layer_vectors():
     np.savez_compressed(HERE / "layers.npz", **out)
 
 
+def block_vectors():
+    """RMSNorm -> layer -> residual add, as megabench/tasks/frontier.py:335-354 strings them together."""
+    import dataclasses
+    from megabench.tasks.common import rms
+    out = {}
+    specs = {
+        "ds_small": (dataclasses.replace(synthetic.GEOMETRIES["deepseek_v3"], name="ds_small", hidden=512, inter=256,
+                                         experts=32, topk=4, n_group=4, topk_group=2), 6, 1, True),
+        "qwen_small": (dataclasses.replace(synthetic.GEOMETRIES["qwen3_30b_a3b"], name="qwen_small", hidden=256,
+                                           inter=128, experts=8, topk=2), 5, 1, False),
+    }
+    for name, (geo, tokens, seed, fp32_weight) in specs.items():
+        values = synthetic.make_inputs(geo, tokens, seed, "cpu")
+        gen = torch.Generator().manual_seed(77 + tokens)
+        stream = (torch.randn((tokens, geo.hidden), generator=gen) * 3).to(torch.bfloat16)
+        gamma = (torch.randn((geo.hidden,), generator=gen) / 100 + 1).to(torch.bfloat16)      # as frontier.py:87
+        normalized = rms(stream, gamma, eps=1e-6, weight_in_fp32=fp32_weight)                   # frontier.py:260,335
+        got = reference_layer(geo, {**values, "x": normalized})
+        new_stream = stream + got["y"].to(stream.dtype)                                        # frontier.py:354
+        out[f"{name}_x"], out[f"{name}_gamma"] = bf16_bits(stream), bf16_bits(gamma)
+        out[f"{name}_normalized"], out[f"{name}_x_out"] = bf16_bits(normalized), bf16_bits(new_stream)
+        out[f"{name}_ids"], out[f"{name}_order"] = got["expert_ids"].numpy(), got["order"].numpy()
+        out[f"{name}_geo"] = np.array([geo.hidden, geo.inter, geo.experts, geo.topk, geo.shared, geo.n_group,
+                                       geo.topk_group, tokens, seed, int(fp32_weight)], dtype=np.int64)
+    np.savez_compressed(HERE / "blocks.npz", **out)
+
+
 if __name__ == "__main__":
     quantizer_vectors()
     router_vectors()
     layer_vectors()
+    block_vectors()
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size)

@@ -140,6 +140,50 @@ def test_gemm_handover_and_separate_kernels_agree(api, name, tokens):
             assert torch.equal(plain[k], timed[k]) and torch.equal(plain[k], again[k]), k
 
 
+@pytest.mark.parametrize("name,tokens,fp32_weight", [("ds_small", 6, True), ("ds_small", 40, True), ("qwen_small", 5, False),
+                                                     ("kimi_small", 33, True), ("mixtral_small", 1, False)])
+def test_block_with_norm_and_residual(api, golden_dir, name, tokens, fp32_weight):
+    # megabench/tasks/frontier.py:335-354: RMSNorm, the layer, the residual add
+    geo = H.small_geometries()[name]
+    gen = torch.Generator().manual_seed(77 + tokens)
+    values = None
+    for seed in range(1, 17):            # the router sees the normalised rows: audit those
+        candidate = synthetic.make_inputs(geo, tokens, seed, "cpu")
+        candidate["x"] = (torch.randn((tokens, geo.hidden), generator=gen) * 3).to(torch.bfloat16)
+        gamma = (torch.randn((geo.hidden,), generator=gen) / 100 + 1).to(torch.bfloat16)
+        normalized = O.rms_norm(candidate["x"], gamma, 1e-6, weight_in_fp32=fp32_weight)
+        if O.decision_margins(H.spec_of(geo), normalized, candidate["router"], candidate.get("router_bias")) >= H.MARGIN:
+            values = candidate
+            break
+    assert values is not None, "no seed passed the routing margin audit"
+    want = O.moe_block(H.spec_of(geo), values, gamma, 1e-6, weight_in_fp32=fp32_weight)
+    layer = api.MoeLayer(api.LayerConfig.from_geometry(geo), max_tokens=tokens)
+    dev = H.to_device(values, "cuda")
+    before = dev["x"].clone()
+    out = layer.block_forward(dev, gamma.cuda(), 1e-6, weight_in_fp32=fp32_weight, check_status=True)
+    assert torch.equal(dev["x"], before), "the residual stream was modified"
+    assert torch.equal(out["expert_ids"].cpu(), want["expert_ids"])
+    assert torch.equal(out["order"].cpu(), want["order"])
+    # The layer's own tolerance (max-abs 2e-2 where max|y| <= 1) plus one bf16 step of the stream,
+    # whose rounding after the add may fall the other way.
+    def close(got_x, want_x, want_y, x_in):
+        tol = 2e-2 * max(1.0, float(want_y.float().abs().max())) + float(x_in.float().abs().max()) * 2.0 ** -7
+        assert float((got_x.float() - want_x.float()).abs().max()) <= tol
+    close(out["x"].cpu(), want["x"], want["y"], values["x"])
+    # golden vectors of the reference's own composition, where this case has them
+    g = np.load(golden_dir / "blocks.npz")
+    if f"{name}_geo" in g.files and int(g[f"{name}_geo"][7]) == tokens:
+        pinned = synthetic.make_inputs(geo, tokens, int(g[f"{name}_geo"][8]), "cpu")
+        pinned["x"] = torch.from_numpy(g[f"{name}_x"].copy()).view(torch.bfloat16)
+        gamma_g = torch.from_numpy(g[f"{name}_gamma"].copy()).view(torch.bfloat16)
+        got = layer.block_forward(H.to_device(pinned, "cuda"), gamma_g.cuda(), 1e-6, weight_in_fp32=fp32_weight,
+                                  check_status=True)
+        assert np.array_equal(got["expert_ids"].cpu().numpy(), g[f"{name}_ids"])
+        assert np.array_equal(got["order"].cpu().numpy(), g[f"{name}_order"])
+        want_x = torch.from_numpy(g[f"{name}_x_out"].copy()).view(torch.bfloat16)
+        close(got["x"].cpu(), want_x, (want_x.float() - pinned["x"].float()), pinned["x"])
+
+
 def test_experts_with_no_rows_and_one_hot_routing(api):
     # a bias that sends every token to the same experts leaves all others empty
     geo = dataclasses.replace(H.small_geometries()["ds_small"], n_group=1, topk_group=1)

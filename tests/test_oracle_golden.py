@@ -137,6 +137,22 @@ def test_layer_matches_reference_composition(golden_dir):
         assert np.array_equal(wide["y_fp32"].numpy(), g[f"{name}_y_fp32"])
 
 
+def test_block_matches_reference_composition(golden_dir):
+    # RMSNorm (megabench/tasks/common.py:13-21) -> layer -> residual add (megabench/tasks/frontier.py:335-354)
+    g = np.load(golden_dir / "blocks.npz")
+    for name in ("ds_small", "qwen_small"):
+        geo = small_layers()[name]
+        tokens, seed, fp32_weight = (int(v) for v in g[f"{name}_geo"][7:10])
+        values = synthetic.make_inputs(geo, tokens, seed, "cpu")
+        values["x"] = torch.from_numpy(g[f"{name}_x"].copy()).view(torch.bfloat16)
+        gamma = torch.from_numpy(g[f"{name}_gamma"].copy()).view(torch.bfloat16)
+        got = O.moe_block(spec_of(geo), values, gamma, 1e-6, weight_in_fp32=bool(fp32_weight))
+        assert np.array_equal(got["normalized"].view(torch.int16).numpy(), g[f"{name}_normalized"])
+        assert np.array_equal(got["expert_ids"].numpy(), g[f"{name}_ids"])
+        assert np.array_equal(got["order"].numpy(), g[f"{name}_order"])
+        assert np.array_equal(got["x"].view(torch.int16).numpy(), g[f"{name}_x_out"])
+
+
 def test_weight_generator_uses_the_reference_block_format():
     w = torch.randn((256, 384), generator=torch.Generator().manual_seed(2)) * 0.02
     q, s = synthetic.block_quantize_weight(w)

@@ -71,12 +71,18 @@ int layout_of(const moe_config_t* c, int tokens, moe_workspace_layout_t* L) {
   l.aq = take(static_cast<uint64_t>(rows) * I);
   l.as = take(4ull * rows * (I / 128));
   l.slots = take(2ull * rows * H);
+  take(2ull * tokens * H);               // normalised token rows of moe_block_forward (see norm_offset)
   l.total_bytes = off;
   l.rows = rows;
   l.max_chunks = max_chunks;
   l.token_tile = tile;
   if (L) *L = l;
   return MOE_OK;
+}
+
+// bf16 [T, H] behind the slot rows: the RMSNorm output when the call covers the whole block
+inline uint64_t norm_offset(const moe_workspace_layout_t& L, int hidden) {
+  return align_up(L.slots + 2ull * L.rows * hidden, 256);
 }
 
 inline int from_cuda(cudaError_t e) { return e == cudaSuccess ? MOE_OK : static_cast<int>(e); }
@@ -141,13 +147,16 @@ int moe_combine(const void* rows_bf16, const float* weights, int32_t tokens, int
                                        static_cast<cudaStream_t>(stream), &launches));
 }
 
-int moe_layer_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* x_bf16, int32_t tokens,
-                      void* y_bf16, int64_t* expert_ids, float* topk_weights, int64_t* order, void* workspace,
-                      size_t workspace_bytes, void* stream_) {
+// One layer call; with `norm_weight` the whole block: RMSNorm in front, residual add behind.
+static int layer_forward_impl(const moe_config_t* cfg, const moe_weights_t* w, const void* x_in, int32_t tokens,
+                              void* y_bf16, int64_t* expert_ids, float* topk_weights, int64_t* order, void* workspace,
+                              size_t workspace_bytes, void* stream_, const void* norm_weight, float eps,
+                              int weight_in_fp32) {
   moe_workspace_layout_t L;
   const int rc = layout_of(cfg, tokens, &L);
   if (rc) return rc;
   if (cfg->ep_world != 1) return MOE_ERR_UNSUPPORTED;
+  const void* x_bf16 = x_in;
   if (!w || !x_bf16 || !y_bf16 || !workspace) return MOE_ERR_BAD_ARG;
   if (!w->router || !w->gate || !w->gate_scale || !w->up || !w->up_scale || !w->down || !w->down_scale) return MOE_ERR_BAD_ARG;
   if (cfg->n_shared && (!w->shared_gate || !w->shared_gate_scale || !w->shared_up || !w->shared_up_scale ||
@@ -177,6 +186,17 @@ int moe_layer_forward(const moe_config_t* cfg, const moe_weights_t* w, const voi
   int launches = 0;
   cudaError_t e = cudaMemsetAsync(status, 0, 32, stream);
   if (e != cudaSuccess) return from_cuda(e);
+
+  const __nv_bfloat16* residual = nullptr;
+  if (norm_weight) {
+    // the normalised rows live behind the last scratch array of the layout (counted in total_bytes)
+    __nv_bfloat16* normalised = reinterpret_cast<__nv_bfloat16*>(ws + norm_offset(L, cfg->hidden));
+    e = moe::launch_rmsnorm(static_cast<const __nv_bfloat16*>(x_in), static_cast<const __nv_bfloat16*>(norm_weight), eps,
+                            weight_in_fp32, tokens, cfg->hidden, normalised, stream, &launches);
+    if (e != cudaSuccess) return from_cuda(e);
+    residual = static_cast<const __nv_bfloat16*>(x_in);
+    x_bf16 = normalised;
+  }
 
   moe::GroupArgs g;
   std::memset(&g, 0, sizeof(g));
@@ -291,10 +311,25 @@ int moe_layer_forward(const moe_config_t* cfg, const moe_weights_t* w, const voi
   // 6. weighted combine in slot order, plus the shared expert's row
   mark(5, stream);
   e = moe::launch_combine(slots, tw, tokens, cfg->topk, cfg->hidden, cfg->n_shared, static_cast<__nv_bfloat16*>(y_bf16),
-                          stream, &launches);
+                          stream, &launches, residual);
   mark(6, stream);
   g_last_launches = launches;
   return from_cuda(e);
+}
+
+int moe_layer_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* x_bf16, int32_t tokens,
+                      void* y_bf16, int64_t* expert_ids, float* topk_weights, int64_t* order, void* workspace,
+                      size_t workspace_bytes, void* stream) {
+  return layer_forward_impl(cfg, w, x_bf16, tokens, y_bf16, expert_ids, topk_weights, order, workspace, workspace_bytes,
+                            stream, nullptr, 0.f, 0);
+}
+
+int moe_block_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* x_bf16, const void* norm_weight_bf16,
+                      float eps, int32_t weight_in_fp32, int32_t tokens, void* x_out_bf16, int64_t* expert_ids,
+                      float* topk_weights, int64_t* order, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!norm_weight_bf16 || !(eps >= 0.f)) return MOE_ERR_BAD_ARG;
+  return layer_forward_impl(cfg, w, x_bf16, tokens, x_out_bf16, expert_ids, topk_weights, order, workspace,
+                            workspace_bytes, stream, norm_weight_bf16, eps, weight_in_fp32 ? 1 : 0);
 }
 
 int moe_profile_enable(int32_t on) {

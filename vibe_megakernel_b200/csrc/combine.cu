@@ -5,6 +5,8 @@
 // shared expert) and the slot-order fp32 sum with one bf16 rounding of
 // megabench/tasks/megamoe.py:176-182. The down-projection rows are already stored in slot order
 // (row token*topk+slot), which is the reference's `slots[order] = output` un-permutation.
+// With a residual stream the block's output is x + bf16(sum), itself rounded to bf16
+// (`x = x + output.to(x.dtype)`, megabench/tasks/frontier.py:354).
 #include "common.cuh"
 #include "kernels.h"
 
@@ -12,7 +14,8 @@ namespace moe {
 
 __global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __restrict__ slots,
                                                       const float* __restrict__ weights, int tokens, int topk,
-                                                      int hidden, int shared, __nv_bfloat16* __restrict__ y) {
+                                                      int hidden, int shared, __nv_bfloat16* __restrict__ y,
+                                                      const __nv_bfloat16* __restrict__ residual) {
   dependent_wait();
   const int t = blockIdx.y;
   const int c = (blockIdx.x * 256 + threadIdx.x) * 8;
@@ -39,13 +42,21 @@ __global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __res
   __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&packed);
 #pragma unroll
   for (int i = 0; i < 8; ++i) o[i] = __float2bfloat16_rn(acc[i]);
+  if (residual) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(residual + static_cast<size_t>(t) * hidden + c);
+    const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = __float2bfloat16_rn(__fadd_rn(__bfloat162float(v[i]), __bfloat162float(o[i])));
+  }
   *reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * hidden + c) = packed;
 }
 
 cudaError_t launch_combine(const __nv_bfloat16* slots, const float* weights, int tokens, int topk, int hidden,
-                           int shared, __nv_bfloat16* y, cudaStream_t stream, int* launches) {
+                           int shared, __nv_bfloat16* y, cudaStream_t stream, int* launches,
+                           const __nv_bfloat16* residual) {
   dim3 grid((hidden / 8 + 255) / 256, tokens);
-  launch_dependent(combine_kernel, grid, dim3(256), 0, stream, slots, weights, tokens, topk, hidden, shared, y);
+  launch_dependent(combine_kernel, grid, dim3(256), 0, stream, slots, weights, tokens, topk, hidden, shared, y,
+                   residual);
   if (launches) *launches += 1;
   return cudaGetLastError();
 }

@@ -82,8 +82,14 @@ cudaError_t launch_router_fused(const moe_config_t& cfg, const __nv_bfloat16* x,
 cudaError_t launch_quantize(const void* x, int dtype, int rows, int width, const int32_t* gather, uint8_t* q,
                             float* scales, cudaStream_t stream, int* launches);
 
+// residual (optional, bf16 [tokens, hidden]): y = bf16(residual + bf16(sum)) instead of bf16(sum)
 cudaError_t launch_combine(const __nv_bfloat16* slots, const float* weights, int tokens, int topk, int hidden,
-                           int shared, __nv_bfloat16* y, cudaStream_t stream, int* launches);
+                           int shared, __nv_bfloat16* y, cudaStream_t stream, int* launches,
+                           const __nv_bfloat16* residual = nullptr);
+
+// RMSNorm of bf16 rows with a bf16 weight (megabench/tasks/common.py:13-21), both roundings of the reference.
+cudaError_t launch_rmsnorm(const __nv_bfloat16* x, const __nv_bfloat16* weight, float eps, int weight_in_fp32, int tokens,
+                           int hidden, __nv_bfloat16* out, cudaStream_t stream, int* launches);
 
 // Copy rows that arrived in any order (and the home rows of the shared expert) into expert order.
 struct GatherArgs {

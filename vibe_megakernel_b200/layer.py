@@ -130,6 +130,31 @@ class MoeLayer:
 
     __call__ = forward
 
+    def block_forward(self, values: dict[str, torch.Tensor], norm_weight: torch.Tensor, eps: float = 1e-6, *,
+                      weight_in_fp32: bool = False, check_status: bool = False) -> dict[str, torch.Tensor]:
+        """The layer between the RMSNorm of the residual stream ``values["x"]`` and the residual add:
+        ``x_out = x + layer(rms(x, norm_weight, eps))`` (megabench/tasks/frontier.py:335-354)."""
+        c = self.config
+        x = _require(values["x"], "x", torch.bfloat16)
+        if x.dim() != 2 or x.shape[1] != c.hidden:
+            raise ValueError(f"x must be [tokens, {c.hidden}]")
+        gamma = _require(norm_weight, "norm_weight", torch.bfloat16, (c.hidden,))
+        tokens = x.shape[0]
+        ws, lay = self.workspace(tokens)
+        w = self.weights_struct(values)
+        out = torch.empty_like(x)
+        ids = torch.empty((tokens, c.topk), dtype=torch.int64, device=x.device)
+        tw = torch.empty((tokens, c.topk), dtype=torch.float32, device=x.device)
+        order = torch.empty((tokens * c.topk,), dtype=torch.int64, device=x.device)
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        rc = self.lib.moe_block_forward(C.byref(self.cfg), C.byref(w), x.data_ptr(), gamma.data_ptr(), float(eps),
+                                        1 if weight_in_fp32 else 0, tokens, out.data_ptr(), ids.data_ptr(),
+                                        tw.data_ptr(), order.data_ptr(), ws.data_ptr(), ws.numel(), stream)
+        _cabi.check("moe_block_forward", rc)
+        if check_status:
+            self.check_device_status(tokens)
+        return {"x": out, "expert_ids": ids, "topk_weights": tw, "order": order}
+
     def check_device_status(self, tokens: int) -> None:
         ws, _ = self.workspace(tokens)
         detail = C.c_int32(0)
