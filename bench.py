@@ -128,16 +128,18 @@ def layer_case(geo, tokens: int) -> dict:
 
 
 def timed_steps(fn, steps: int, warmup: int, flush: torch.Tensor, barrier=None) -> list[float]:
-    """Per-step device times in ms: L2 is flushed (a 512 MiB write) before every step, outside its events."""
+    """Per-step device times in ms: L2 is flushed (a 512 MiB write, then read back) before every step,
+    outside its events."""
+    from vibe_megakernel_b200.ep_bench import flush_l2
     for _ in range(warmup):
-        flush.zero_()
+        flush_l2(flush)
         fn()
     torch.cuda.synchronize()
     if barrier:
         barrier()
     pairs = []
     for _ in range(steps):
-        flush.zero_()
+        flush_l2(flush)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         fn()
@@ -220,8 +222,9 @@ def measure_batch(geo, values: dict, tokens: int, steps: int, warmup: int, flush
     layer.profile(True)
     stages = {k: 0.0 for k in MoeLayer.STAGES}
     reps = max(3, min(steps, 10))
+    from vibe_megakernel_b200.ep_bench import flush_l2
     for _ in range(reps):
-        flush.zero_()
+        flush_l2(flush)
         layer.forward(inputs)
         for k, v in layer.stage_ms().items():
             stages[k] += v / reps
@@ -290,7 +293,7 @@ def main_single(args) -> dict:
         "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
         "config": {"workload": f"{geo.name} FP8 MoE decode layer, batch {args.batch}: H={geo.hidden} I={geo.inter} "
                                f"E={geo.experts}+{geo.shared} top{geo.topk} {geo.scoring}",
-                   "batch": args.batch, "seed": args.seed, "l2": "flushed between steps (512 MiB write)",
+                   "batch": args.batch, "seed": args.seed, "l2": "flushed between steps (512 MiB write, then read back: no dirty lines left)",
                    "e2e_io": "x bf16 host->device and y bf16 device->host per step; weights resident in HBM",
                    "input_generation_s": round(gen_s, 1)},
         "e2e": {"value": round(extra["e2e_us"], 2), "unit": "us", "h2d_bytes_per_step": extra["io_bytes"],

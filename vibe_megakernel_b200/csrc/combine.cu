@@ -15,8 +15,9 @@ namespace moe {
 __global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __restrict__ slots,
                                                       const float* __restrict__ weights, int tokens, int topk,
                                                       int hidden, int shared, __nv_bfloat16* __restrict__ y,
-                                                      const __nv_bfloat16* __restrict__ residual) {
+                                                      const __nv_bfloat16* __restrict__ residual, const FlagWait wait) {
   dependent_wait();
+  wait_for_peers(wait);         // expert parallel: the slot rows come from the experts' owners
   const int t = blockIdx.y;
   const int c = (blockIdx.x * 256 + threadIdx.x) * 8;
   if (c >= hidden) return;
@@ -53,10 +54,10 @@ __global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __res
 
 cudaError_t launch_combine(const __nv_bfloat16* slots, const float* weights, int tokens, int topk, int hidden,
                            int shared, __nv_bfloat16* y, cudaStream_t stream, int* launches,
-                           const __nv_bfloat16* residual) {
+                           const __nv_bfloat16* residual, const FlagWait* wait) {
   dim3 grid((hidden / 8 + 255) / 256, tokens);
   launch_dependent(combine_kernel, grid, dim3(256), 0, stream, slots, weights, tokens, topk, hidden, shared, y,
-                   residual);
+                   residual, wait ? *wait : FlagWait{});
   if (launches) *launches += 1;
   return cudaGetLastError();
 }

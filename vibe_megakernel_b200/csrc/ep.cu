@@ -76,15 +76,6 @@ static void ep_layouts(const moe_config_t& c, int max_tokens, moe_ep_layout_t* L
   L->local_bytes = off;
 }
 
-__device__ __forceinline__ void store_release_sys(uint64_t* p, uint64_t v) {
-  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ uint64_t load_acquire_sys(const uint64_t* p) {
-  uint64_t v;
-  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-
 struct Peers {
   uint8_t* base[8];
 };
@@ -110,6 +101,8 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(DispatchArgs a) {
   const int routed = a.tokens * a.topk;
   const int r = blockIdx.x;
   const int H = a.hidden, G = H / kGroup;
+  dependent_wait();             // the picks come from the kernel before
+  dependents_may_launch();
   int t;
   uint8_t* dst_q;
   float* dst_s;
@@ -182,6 +175,8 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(DispatchArgs a) {
 __global__ void ep_wait_kernel(const uint64_t* flags, int world, uint64_t epoch, int32_t* status, int detail,
                                uint64_t timeout_ns) {
   const int tid = threadIdx.x;
+  dependent_wait();             // under a dependent launch: polling starts when the predecessor is done
+  dependents_may_launch();
   if (tid >= world) return;
   const uint64_t t0 = globaltimer();
   while (load_acquire_sys(flags + tid) < epoch) {
@@ -195,6 +190,8 @@ __global__ void ep_wait_kernel(const uint64_t* flags, int world, uint64_t epoch,
 
 // ---- owner side: bring arrivals (and the home rows of the shared expert) into expert order ------
 __global__ void __launch_bounds__(128) ep_gather_kernel(GatherArgs a) {
+  dependent_wait();
+  dependents_may_launch();
   const int kept = a.offsets[a.n_local];
   const int pos = blockIdx.x;
   if (pos >= kept + a.shared_rows) return;
@@ -208,7 +205,7 @@ __global__ void __launch_bounds__(128) ep_gather_kernel(GatherArgs a) {
 }
 
 cudaError_t launch_gather_rows(const GatherArgs& a, int row_blocks, cudaStream_t stream, int* launches) {
-  ep_gather_kernel<<<row_blocks > 0 ? row_blocks : 1, 128, 0, stream>>>(a);
+  launch_dependent(ep_gather_kernel, dim3(row_blocks > 0 ? row_blocks : 1), dim3(128), 0, stream, a);
   if (launches) *launches += 1;
   return cudaGetLastError();
 }
@@ -228,6 +225,8 @@ struct ReturnArgs {
 
 __global__ void __launch_bounds__(128) ep_return_kernel(ReturnArgs a) {
   __shared__ int s_last;
+  dependent_wait();
+  dependents_may_launch();
   const int kept = a.offsets[a.n_local];
   const int pos = blockIdx.x;
   const int H = a.hidden;
@@ -331,8 +330,16 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* 
   if (e != cudaSuccess) return cuda_rc(e);
 
   // 1. router on the home tokens
+  moe::L2Warm warm = {};      // the shared expert's weights are needed whatever the router decides
+  if (cfg->n_shared) {
+    const uint64_t bytes = static_cast<uint64_t>(cfg->inter) * cfg->hidden;
+    warm.ptr[0] = w->shared_gate; warm.bytes[0] = bytes;
+    warm.ptr[1] = w->shared_up; warm.bytes[1] = bytes;
+    warm.ptr[2] = w->shared_down; warm.bytes[2] = bytes;
+  }
   e = moe::launch_router(*cfg, static_cast<const __nv_bfloat16*>(x_bf16), w->router, w->router_bias, tokens,
-                         reinterpret_cast<float*>(ws + P.logits), ids32, tw, expert_ids, topk_weights, stream, &launches);
+                         reinterpret_cast<float*>(ws + P.logits), ids32, tw, expert_ids, topk_weights, stream, &launches,
+                         &warm);
   if (e != cudaSuccess) return cuda_rc(e);
 
   // 2. quantise + dispatch (peer stores), counts and flags published by the last block
@@ -347,15 +354,13 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* 
   d.xs_home = reinterpret_cast<float*>(ws + P.xs_home);
   d.done = counters;
   d.epoch = epoch;
-  moe::ep_dispatch_kernel<<<tokens * cfg->topk + tokens, 256, 0, stream>>>(d);
+  moe::launch_dependent(moe::ep_dispatch_kernel, dim3(tokens * cfg->topk + tokens), dim3(256), 0, stream, d);
   ++launches;
 
-  // 3. wait for every source, then group the arrivals by expert
-  moe::ep_wait_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<const uint64_t*>(mine + L.flags_dispatch), world, epoch,
-                                            status, 200, moe::kWaitNs);
-  ++launches;
+  // 3. the grouping kernel waits for every source (bounded), then groups the arrivals by expert
   moe::GroupArgs g;
   std::memset(&g, 0, sizeof(g));
+  g.wait = moe::FlagWait{reinterpret_cast<const uint64_t*>(mine + L.flags_dispatch), world, epoch, moe::kWaitNs, status, 200};
   g.ids32 = reinterpret_cast<const int32_t*>(mine + L.recv_expert);
   g.n = world * L.cap;
   g.id_base = 0;
@@ -441,13 +446,11 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* 
   r.off_slots = L.slots; r.off_flags = L.flags_return;
   r.done = counters + 1;
   r.epoch = epoch;
-  moe::ep_return_kernel<<<row_blocks, 128, 0, stream>>>(r);
+  moe::launch_dependent(moe::ep_return_kernel, dim3(row_blocks), dim3(128), 0, stream, r);
   ++launches;
-  moe::ep_wait_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<const uint64_t*>(mine + L.flags_return), world, epoch,
-                                            status, 300, moe::kWaitNs);
-  ++launches;
+  const moe::FlagWait home{reinterpret_cast<const uint64_t*>(mine + L.flags_return), world, epoch, moe::kWaitNs, status, 300};
   e = moe::launch_combine(reinterpret_cast<const __nv_bfloat16*>(mine + L.slots), tw, tokens, cfg->topk, H, cfg->n_shared,
-                          static_cast<__nv_bfloat16*>(y_bf16), stream, &launches);
+                          static_cast<__nv_bfloat16*>(y_bf16), stream, &launches, nullptr, &home);
   return cuda_rc(e);
 }
 

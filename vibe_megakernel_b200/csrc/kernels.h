@@ -10,9 +10,9 @@
 
 #include <utility>
 
-namespace moe {
+#include "common.cuh"
 
-struct Chunk;
+namespace moe {
 
 // Launch with programmatic stream serialization: the kernel may start while the previous kernel of
 // the stream drains; it must call dependent_wait() before reading what that kernel wrote.
@@ -68,6 +68,7 @@ struct GroupArgs {
   int seg_cap;
   int32_t* progress;          // optional: counters of the GEMMs, zeroed here (see GemmArgs, WorkListLayout)
   int progress_len;
+  FlagWait wait;              // expert parallel: the rows and ids were stored by peers; wait for their flags first
 };
 cudaError_t launch_group_rows(const GroupArgs& a, cudaStream_t stream, int* launches);
 
@@ -85,7 +86,7 @@ cudaError_t launch_quantize(const void* x, int dtype, int rows, int width, const
 // residual (optional, bf16 [tokens, hidden]): y = bf16(residual + bf16(sum)) instead of bf16(sum)
 cudaError_t launch_combine(const __nv_bfloat16* slots, const float* weights, int tokens, int topk, int hidden,
                            int shared, __nv_bfloat16* y, cudaStream_t stream, int* launches,
-                           const __nv_bfloat16* residual = nullptr);
+                           const __nv_bfloat16* residual = nullptr, const FlagWait* wait = nullptr);
 
 // RMSNorm of bf16 rows with a bf16 weight (megabench/tasks/common.py:13-21), both roundings of the reference.
 cudaError_t launch_rmsnorm(const __nv_bfloat16* x, const __nv_bfloat16* weight, float eps, int weight_in_fp32, int tokens,
