@@ -184,8 +184,7 @@ static int layer_forward_impl(const moe_config_t* cfg, const moe_weights_t* w, c
   const int n_local = cfg->n_experts;
   const int routed = tokens * cfg->topk;
   int launches = 0;
-  cudaError_t e = cudaMemsetAsync(status, 0, 32, stream);
-  if (e != cudaSuccess) return from_cuda(e);
+  cudaError_t e = cudaSuccess;      // the status words are cleared by the permutation kernel (see zero_status)
 
   const __nv_bfloat16* residual = nullptr;
   if (norm_weight) {
@@ -216,6 +215,7 @@ static int layer_forward_impl(const moe_config_t* cfg, const moe_weights_t* w, c
   g.row_dest = row_dest;
   g.order = order;
   g.status = status;
+  g.zero_status = 1;       // no kernel before the permutation reports, so no memset node in front of the call
   const moe::WorkListLayout W = moe::work_list_layout(L.max_chunks, cfg->hidden, cfg->inter, L.token_tile);
   g.progress = reinterpret_cast<int32_t*>(ws + L.chunks + W.counters);
   g.progress_len = W.counters_len;

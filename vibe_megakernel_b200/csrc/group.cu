@@ -22,6 +22,7 @@ __global__ void __launch_bounds__(kGroupWarps * 32) group_rows_kernel(GroupArgs 
   const int groups = a.n_local + 1;                        // last one is the shared expert
   dependent_wait();
   dependents_may_launch();
+  if (a.zero_status && a.status && blockIdx.x == 0 && tid < 8) a.status[tid] = 0;   // only block 0 reports, later
   wait_for_peers(a.wait);
 
   for (int i = tid; i < groups; i += blockDim.x) s_count[i] = 0;

@@ -64,6 +64,7 @@ struct GroupArgs {
   int32_t* row_dest;      // optional
   int64_t* order;         // optional, [n]
   int32_t* status;        // optional
+  int zero_status;        // the kernel clears the 8 status words itself (it is the call's first that may report)
   const int32_t* seg_counts;  // optional: rows come in segments of seg_cap, segment s holds seg_counts[s] rows
   int seg_cap;
   int32_t* progress;          // optional: counters of the GEMMs, zeroed here (see GemmArgs, WorkListLayout)

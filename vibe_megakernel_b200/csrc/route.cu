@@ -286,6 +286,7 @@ __global__ void __launch_bounds__(WARPS * 32) route_group_quant_kernel(FusedArgs
   const int my_row = static_cast<int>(blockIdx.x) - 1;
   dependent_wait();
   dependents_may_launch();
+  if (a.g.zero_status && a.g.status && publisher && tid < 8) a.g.status[tid] = 0;
 
   if (warp < T) {
     int pick;
