@@ -245,13 +245,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       int ready_chunk = -1;
       bool ok = true;
       PROBE_DECL(probe_stage);
-      // The CTA's next item: a fixed stride over the list, or the next free one of the dispenser.
+      // The CTA's next item: a fixed stride over the list, or the next free ones of the dispenser.
+      // Short items are taken a few at a time (about 16 K blocks' worth), and the claim for the
+      // batch after the current one is already in flight: the atomic's round trip (about a
+      // microsecond, half the life of a 6-K-block item) is never waited for.
+      const int grab = max(1, min(8, 16 / (spread ? (KB + ksplit - 1) / ksplit : KB)));
+      int batch_next = 0, batch_end = 0, pending = 0;
+      auto claim = [&]() -> int { return lane == 0 ? atomicAdd(p.progress + p.max_chunks, grab) : 0; };
+      if (handover) pending = claim();
       auto next_unit = [&](uint32_t ordinal) -> int {
         int u;
         if (handover) {
-          int v = 0;
-          if (lane == 0) v = atomicAdd(p.progress + p.max_chunks, 1);
-          u = __shfl_sync(0xffffffffu, v, 0);
+          if (batch_next == batch_end) {
+            batch_next = __shfl_sync(0xffffffffu, pending, 0);
+            batch_end = batch_next + grab;
+            pending = claim();
+          }
+          u = batch_next++;
         } else {
           u = blockIdx.x + ordinal * gridDim.x;
         }
@@ -391,6 +401,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     // ------------------------------ scale loader ------------------------------
     // Each lane waits, loads its share and arrives on its own: no warp-level sync, so a lane that
     // gives up cannot strand the others.
+    int ready_chunk = -1;      // the chunk this lane has already seen complete
     for (uint32_t un = 0;; ++un) {
       const uint32_t b = un & 1u, ph = (un >> 1) & 1u;
       int u = -1;
@@ -398,11 +409,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if (!take_item(s_queue, bar_qfull, bar_qempty, un, s_abort, u, ch) ||
           (u >= 0 && !mbar_wait(bar_scempty + b, ph ^ 1u, s_abort)) ||
           // the previous GEMM's scales of this chunk must be complete (this lane's own acquire)
-          (u >= 0 && handover && !wait_counter(p.progress + u / p.tiles_m, p.tiles_before, s_abort))) {
+          (u >= 0 && handover && u / p.tiles_m != ready_chunk &&
+           !wait_counter(p.progress + u / p.tiles_m, p.tiles_before, s_abort))) {
         if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 4); *s_abort = 1; }
         break;
       }
       if (u < 0) break;
+      ready_chunk = u / p.tiles_m;
       const int mt = u % p.tiles_m;
       const bool shared_e = ch.expert >= p.n_local;
       float* xs = s_scales + b * sf;            // [kb][NT]
@@ -543,11 +556,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
               for (int j = 0; j < 16; j += 4)
                 *reinterpret_cast<float4*>(x16 + j) = *reinterpret_cast<const float4*>(xs + g + j);
+              // two columns per instruction: acc += D * (w_scale * x_scale), every step rounded as before
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const float x = x16[j];
-                acc_a[g + j] = fmaf(__uint_as_float(ra[g + j]), __fmul_rn(wa, x), acc_a[g + j]);
-                if constexpr (DUAL) acc_b[g + j] = fmaf(__uint_as_float(rb[g + j]), __fmul_rn(wb, x), acc_b[g + j]);
+              for (int j = 0; j < 16; j += 2) {
+                float s0, s1;
+                mul2(wa, wa, x16[j], x16[j + 1], s0, s1);
+                fma2(__uint_as_float(ra[g + j]), __uint_as_float(ra[g + j + 1]), s0, s1, acc_a[g + j], acc_a[g + j + 1]);
+                if constexpr (DUAL) {
+                  mul2(wb, wb, x16[j], x16[j + 1], s0, s1);
+                  fma2(__uint_as_float(rb[g + j]), __uint_as_float(rb[g + j + 1]), s0, s1, acc_b[g + j], acc_b[g + j + 1]);
+                }
               }
             }
           }
