@@ -218,6 +218,17 @@ def measure_batch(geo, values: dict, tokens: int, steps: int, warmup: int, flush
     ms = timed_steps(lambda: layer.forward(inputs), steps, warmup, flush)
     layer.check_device_status(tokens)
     latency_us = 1e3 * sum(ms) / len(ms)
+    # the same call replayed from a CUDA graph (what a decode loop would do): no launch cost on the host
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        layer.forward(inputs)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        graph_out = layer.forward(inputs)
+    graph_ms = timed_steps(graph.replay, max(3, steps // 2), 3, flush)
+    assert torch.equal(graph_out["y"], out["y"]), "graph replay and direct call disagree"
     # stage times: separate profiled passes, same inputs and flush protocol
     layer.profile(True)
     stages = {k: 0.0 for k in MoeLayer.STAGES}
@@ -233,6 +244,7 @@ def measure_batch(geo, values: dict, tokens: int, steps: int, warmup: int, flush
     g_bytes = gate_up_bytes(geo, distinct)
     g_gbs = g_bytes / (stages["gate_up_gemm"] * 1e-3) / 1e9
     res = {"batch": tokens, "latency_us": round(latency_us, 2), "min_us": round(1e3 * min(ms), 2),
+           "graph_replay_us": round(1e3 * sum(graph_ms) / len(graph_ms), 2),
            "distinct_experts": distinct, "algorithmic_bytes": total_bytes,
            "layer_gbs": round(total_bytes / (latency_us * 1e-6) / 1e9, 1),
            "layer_frac_of_measured_peak": round(total_bytes / (latency_us * 1e-6) / 1e9 / peak, 4),

@@ -184,6 +184,35 @@ def test_block_with_norm_and_residual(api, golden_dir, name, tokens, fp32_weight
         close(got["x"].cpu(), want_x, (want_x.float() - pinned["x"].float()), pinned["x"])
 
 
+@pytest.mark.parametrize("name,tokens", [("ds_small", 3), ("kimi_small", 40)])
+def test_layer_call_can_be_captured_in_a_cuda_graph(api, name, tokens):
+    # A decode loop replays the layer from a CUDA graph: the call makes no allocation and no
+    # synchronisation, its dependent launches become graph edges, and a replay on new token rows
+    # (same buffers) gives the bits of a direct call.
+    geo = H.small_geometries()[name]
+    values, _ = H.audited_inputs(geo, tokens)
+    other = dict(values)                        # other token rows, same weights (the graph holds their addresses)
+    other["x"] = (torch.randn(values["x"].shape, generator=torch.Generator().manual_seed(5)) * 0.7).to(torch.bfloat16)
+    layer, want = run_layer(api, geo, values)
+    want_other = layer.forward(H.to_device(other, "cuda"), check_status=True)
+    dev = H.to_device(values, "cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        layer.forward(dev)                       # warm-up on the capturing stream
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = layer.forward(dev)
+    for inputs, expect in ((values, want), (other, want_other), (values, want)):
+        dev["x"].copy_(inputs["x"])
+        graph.replay()
+        torch.cuda.synchronize()
+        layer.check_device_status(tokens)
+        for k in expect:
+            assert torch.equal(out[k], expect[k]), k
+
+
 def test_experts_with_no_rows_and_one_hot_routing(api):
     # a bias that sends every token to the same experts leaves all others empty
     geo = dataclasses.replace(H.small_geometries()["ds_small"], n_group=1, topk_group=1)
