@@ -127,10 +127,18 @@ __global__ void __launch_bounds__(kRowsWarps * 32) router_logits_rows_kernel(con
   }
 }
 
-// Larger batches: a block keeps 8 token rows in shared memory and streams 16 router rows (two per
+// Four bf16 values of a token row as fp32 (a bf16 is the upper half of an fp32).
+__device__ __forceinline__ void unpack4(const uint2& raw, float (&v)[4]) {
+  v[0] = __uint_as_float(raw.x << 16);
+  v[1] = __uint_as_float(raw.x & 0xffff0000u);
+  v[2] = __uint_as_float(raw.y << 16);
+  v[3] = __uint_as_float(raw.y & 0xffff0000u);
+}
+
+// Larger batches: a block keeps 8 token rows in shared memory and streams 32 router rows (four per
 // warp) against them, so x is read from L2 once per block.
 constexpr int kTiledWarps = 8;
-constexpr int kTiledExpertsPerWarp = 2;
+constexpr int kTiledExpertsPerWarp = 4;
 constexpr int kTiledExperts = kTiledWarps * kTiledExpertsPerWarp;
 
 __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(const __nv_bfloat16* __restrict__ x,
@@ -172,9 +180,10 @@ __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(c
   for (int j = 0; j < kTiledExpertsPerWarp; ++j)
 #pragma unroll
     for (int t = 0; t < kLogitTokens; ++t) acc[j][t] = 0.f;
-  // Four pieces per trip: all router loads of a trip are issued before the first use, so a warp
-  // keeps 4 KB in flight instead of waiting out one L2 round trip per piece.
-  constexpr int kAhead = 4;
+  // Two pieces per trip: all router loads of a trip (8 x 16 bytes per lane) are issued before the
+  // first use. The token values are converted once per piece and shared by the warp's four
+  // experts; two tokens go through every packed FMA (each half is the scalar chain of fma4).
+  constexpr int kAhead = 2;
   for (int q0 = lane; q0 < quads; q0 += 32 * kAhead) {
     float4 r[kAhead][kTiledExpertsPerWarp];
 #pragma unroll
@@ -190,10 +199,18 @@ __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(c
       const int q = q0 + 32 * u;
       if (q < quads) {
 #pragma unroll
-        for (int t = 0; t < kLogitTokens; ++t) {
-          const uint2 raw = s_x[t * quads + q];
+        for (int t = 0; t < kLogitTokens; t += 2) {
+          float xa[4], xb[4];
+          unpack4(s_x[t * quads + q], xa);
+          unpack4(s_x[(t + 1) * quads + q], xb);
 #pragma unroll
-          for (int j = 0; j < kTiledExpertsPerWarp; ++j) acc[j][t] = fma4(r[u][j], raw, acc[j][t]);
+          for (int j = 0; j < kTiledExpertsPerWarp; ++j) {
+            const float4 w = r[u][j];
+            fma2(w.x, w.x, xa[0], xb[0], acc[j][t], acc[j][t + 1]);
+            fma2(w.y, w.y, xa[1], xb[1], acc[j][t], acc[j][t + 1]);
+            fma2(w.z, w.z, xa[2], xb[2], acc[j][t], acc[j][t + 1]);
+            fma2(w.w, w.w, xa[3], xb[3], acc[j][t], acc[j][t + 1]);
+          }
         }
       }
     }
