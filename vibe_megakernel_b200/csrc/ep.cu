@@ -20,6 +20,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "quant_group.cuh"
 
 namespace moe {
 
@@ -134,22 +135,19 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(DispatchArgs a) {
   }
   // per-row, per-128-channel e4m3 quantiser (megabench/tasks/quantization.py:87-109), one warp per group
   const __nv_bfloat16* in = a.x + static_cast<size_t>(t) * H;
-  for (int g = warp; g < G; g += 8) {
-    const int k = g * kGroup + lane * 4;
-    const uint2 raw = *reinterpret_cast<const uint2*>(in + k);
-    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-    const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-    const float v0 = __bfloat162float(lo.x), v1 = __bfloat162float(lo.y);
-    const float v2 = __bfloat162float(hi.x), v3 = __bfloat162float(hi.y);
-    float amax = fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
+  constexpr int kAhead = 4;       // groups whose loads a warp issues before it uses the first
+  for (int g0 = warp; g0 < G; g0 += 8 * kAhead) {
+    float v[kAhead][4];
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-    const float scale = group_scale(amax);
-    const uint32_t packed = static_cast<uint32_t>(to_e4m3(v0, scale)) | static_cast<uint32_t>(to_e4m3(v1, scale)) << 8 |
-                            static_cast<uint32_t>(to_e4m3(v2, scale)) << 16 |
-                            static_cast<uint32_t>(to_e4m3(v3, scale)) << 24;
-    *reinterpret_cast<uint32_t*>(dst_q + k) = packed;
-    if (lane == 0) dst_s[g] = scale;
+    for (int u = 0; u < kAhead; ++u) load_group<__nv_bfloat16>(in, min(g0 + 8 * u, G - 1), H, lane, v[u]);
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      const int g = g0 + 8 * u;
+      if (g < G) {
+        const float scale = quantize_loaded(v[u], dst_q, g, H, lane);
+        if (lane == 0) dst_s[g] = scale;
+      }
+    }
   }
   // the last block to finish publishes the counts and raises one flag per owner
   __threadfence_system();

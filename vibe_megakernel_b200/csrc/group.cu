@@ -27,15 +27,22 @@ __global__ void __launch_bounds__(kGroupWarps * 32) group_rows_kernel(GroupArgs 
 
   for (int i = tid; i < groups; i += blockDim.x) s_count[i] = 0;
   __syncthreads();
-  for (int r = tid; r < a.n; r += blockDim.x) {
-    const long long id = a.ids32 ? static_cast<long long>(a.ids32[r]) : a.ids64[r];
-    const long long local = id - a.id_base;
-    // segmented input (expert-parallel arrivals): row r of segment r / seg_cap exists only below
-    // that segment's count
-    const bool present = !a.seg_counts || (r % a.seg_cap) < a.seg_counts[r / a.seg_cap];
-    const bool mine = present && local >= 0 && local < a.n_local;
-    s_ids[r] = mine ? static_cast<int16_t>(local) : static_cast<int16_t>(-1);
-    if (mine) atomicAdd(&s_count[local], 1);
+  for (int r0 = warp * 32; r0 < a.n; r0 += blockDim.x) {     // whole warps, so that the lanes can vote
+    const int r = r0 + lane;
+    int key = -1;                                             // local expert of a kept row
+    if (r < a.n) {
+      const long long id = a.ids32 ? static_cast<long long>(a.ids32[r]) : a.ids64[r];
+      const long long local = id - a.id_base;
+      // segmented input (expert-parallel arrivals): row r of segment r / seg_cap exists only below
+      // that segment's count
+      const bool present = !a.seg_counts || (r % a.seg_cap) < a.seg_counts[r / a.seg_cap];
+      if (present && local >= 0 && local < a.n_local) key = static_cast<int>(local);
+      s_ids[r] = static_cast<int16_t>(key);
+    }
+    // one shared-memory atomic per distinct expert of the warp: a hot expert (skewed routing) would
+    // otherwise serialise hundreds of them on one address, in every block
+    const unsigned same = __match_any_sync(0xffffffffu, key);
+    if (key >= 0 && lane == __ffs(same) - 1) atomicAdd(&s_count[key], __popc(same));
   }
   if (tid == 0) s_count[a.n_local] = a.shared_rows;
   __syncthreads();

@@ -13,7 +13,7 @@
 
 namespace moe {
 
-constexpr int kLogitTokens = 8;    // tokens per block of the tiled kernel
+constexpr size_t kLogitsSmemLimit = 200 * 1024;   // dynamic shared memory the logits kernels may ask for
 
 struct Sum2 {
   float hi, lo;
@@ -141,6 +141,8 @@ constexpr int kTiledWarps = 8;
 constexpr int kTiledExpertsPerWarp = 4;
 constexpr int kTiledExperts = kTiledWarps * kTiledExpertsPerWarp;
 
+// TOK token rows per block: every block streams the router rows of its experts from the L2 once.
+template <int TOK>
 __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(const __nv_bfloat16* __restrict__ x,
                                                                                const float* __restrict__ router,
                                                                                int tokens, int experts, int hidden,
@@ -153,8 +155,8 @@ __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(c
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int quads = hidden / 4;
-  const int t0 = blockIdx.y * kLogitTokens;
-  const int tcount = min(kLogitTokens, tokens - t0);
+  const int t0 = blockIdx.y * TOK;
+  const int tcount = min(TOK, tokens - t0);
   // Token rows arrive by bulk async copies (one per row, 16-byte aligned by the launcher's check);
   // rows past the batch are zero-filled by the threads.
   __shared__ uint64_t bar;
@@ -171,15 +173,15 @@ __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(c
     for (int t = 0; t < tcount; ++t)
       bulk_copy_g2s(s_x + static_cast<size_t>(t) * quads, x + static_cast<size_t>(t0 + t) * hidden, row_bytes, &bar);
   }
-  for (int i = tcount * quads + threadIdx.x; i < kLogitTokens * quads; i += blockDim.x) s_x[i] = make_uint2(0u, 0u);
+  for (int i = tcount * quads + threadIdx.x; i < TOK * quads; i += blockDim.x) s_x[i] = make_uint2(0u, 0u);
   mbar_wait(&bar, 0);           // bounded; a copy that never lands leaves wrong logits, not a hang
   __syncthreads();
   const int e0 = blockIdx.x * kTiledExperts + warp * kTiledExpertsPerWarp;
-  float acc[kTiledExpertsPerWarp][kLogitTokens];
+  float acc[kTiledExpertsPerWarp][TOK];
 #pragma unroll
   for (int j = 0; j < kTiledExpertsPerWarp; ++j)
 #pragma unroll
-    for (int t = 0; t < kLogitTokens; ++t) acc[j][t] = 0.f;
+    for (int t = 0; t < TOK; ++t) acc[j][t] = 0.f;
   // Two pieces per trip: all router loads of a trip (8 x 16 bytes per lane) are issued before the
   // first use. The token values are converted once per piece and shared by the warp's four
   // experts; two tokens go through every packed FMA (each half is the scalar chain of fma4).
@@ -199,7 +201,7 @@ __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(c
       const int q = q0 + 32 * u;
       if (q < quads) {
 #pragma unroll
-        for (int t = 0; t < kLogitTokens; t += 2) {
+        for (int t = 0; t < TOK; t += 2) {
           float xa[4], xb[4];
           unpack4(s_x[t * quads + q], xa);
           unpack4(s_x[(t + 1) * quads + q], xb);
@@ -218,7 +220,7 @@ __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(c
 #pragma unroll
   for (int j = 0; j < kTiledExpertsPerWarp; ++j)
 #pragma unroll
-    for (int t = 0; t < kLogitTokens; ++t) {
+    for (int t = 0; t < TOK; ++t) {
       if (t < tcount) {
         const float v = warp_total(acc[j][t]);
         if (lane == 0 && e0 + j < experts) logits[static_cast<size_t>(t0 + t) * experts + e0 + j] = v;
@@ -228,9 +230,9 @@ __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(c
 
 cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* router, int tokens, int experts, int hidden,
                                  float* logits, cudaStream_t stream, const L2Warm* warm_request) {
-  const size_t tile_smem = static_cast<size_t>(kLogitTokens) * hidden * sizeof(__nv_bfloat16);
+  auto tile_smem = [&](int tok) { return static_cast<size_t>(tok) * hidden * sizeof(__nv_bfloat16); };
   const int row_blocks = (experts + kRowsWarps - 1) / kRowsWarps;
-  const bool tiled_ok = tile_smem <= 200 * 1024 && !(reinterpret_cast<uintptr_t>(x) & 15) && hidden % 8 == 0;
+  const bool tiled_ok = tile_smem(8) <= kLogitsSmemLimit && hidden % 8 == 0;
   const dim3 rows_block(kRowsWarps * 32);
   L2Warm warm = {};
   int extra = 0;
@@ -265,17 +267,18 @@ cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* router, in
     cudaError_t e = launch_rows(router_logits_rows_kernel<8>, 8);
     if (e != cudaSuccess) return e;
   } else {
-    static bool configured = false;
-    if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(router_logits_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           200 * 1024);
-      if (e != cudaSuccess) return e;
-      configured = true;
-    }
     const int tiled_blocks = (experts + kTiledExperts - 1) / kTiledExperts;
-    dim3 grid(tiled_blocks + extra, (tokens + kLogitTokens - 1) / kLogitTokens);
-    launch_dependent(router_logits_tiled_kernel, grid, dim3(kTiledWarps * 32), tile_smem, stream, x, router, tokens,
-                     experts, hidden, logits, warm, tiled_blocks);
+    auto launch_tiled = [&](auto kernel, int tok) -> cudaError_t {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(kLogitsSmemLimit));
+      if (e != cudaSuccess) return e;
+      return launch_dependent(kernel, dim3(tiled_blocks + extra, (tokens + tok - 1) / tok), dim3(kTiledWarps * 32),
+                              tile_smem(tok), stream, x, router, tokens, experts, hidden, logits, warm, tiled_blocks);
+    };
+    // 8 token rows per block: 12 (the most that fit at H = 7168) measured 15-25 % slower, the extra
+    // accumulators costing more than the saved passes over the router rows
+    cudaError_t e = launch_tiled(router_logits_tiled_kernel<8>, 8);
+    if (e != cudaSuccess) return e;
   }
   return cudaGetLastError();
 }
