@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_select_regs_kernel(Rou
 // three separate kernels cost more in launch hand-overs than in work at these sizes. Same device
 // functions as the separate kernels, so the bytes are the same.
 constexpr int kFusedMaxRows = 512;     // tokens * topk
-constexpr int kFusedMaxTokens = 32;
+constexpr int kFusedMaxTokens = 32;    // at 64 the repeated selections cost 80-100 us: three kernels are faster there
 
 struct FusedArgs {
   RouteArgs r;
@@ -288,13 +288,13 @@ __global__ void __launch_bounds__(WARPS * 32) route_group_quant_kernel(FusedArgs
   dependents_may_launch();
   if (a.g.zero_status && a.g.status && publisher && tid < 8) a.g.status[tid] = 0;
 
-  if (warp < T) {
+  for (int t = warp; t < T; t += WARPS) {       // a warp per token, two rounds beyond 32 tokens
     int pick;
     float w;
-    select_in_registers<EPL>(a.r, warp, lane, pick, w);
+    select_in_registers<EPL>(a.r, t, lane, pick, w);
     if (lane < K) {
-      s_id[warp * K + lane] = static_cast<int16_t>(pick);
-      s_w[warp * K + lane] = w;
+      s_id[t * K + lane] = static_cast<int16_t>(pick);
+      s_w[t * K + lane] = w;
     }
   }
   for (int i = tid; i <= E; i += WARPS * 32) s_count[i] = 0;
