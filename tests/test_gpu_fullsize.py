@@ -90,3 +90,30 @@ def test_other_full_geometries(api, name, tokens):
     assert torch.equal(out["order"], want["order"])
     wide = O.moe_layer(spec, values, compute=torch.float32)["y_fp32"]
     print(f"{name} batch {tokens}:", H.assert_y_in_band(out["y"], want["y"], wide))
+
+
+@pytest.mark.parametrize("name,tokens", [("qwen_small", 16384), ("ds_small", 8192)])
+def test_largest_batch_the_library_takes(api, name, tokens):
+    # tokens * topk = 32768 routed rows, the limit of the permutation kernel. No oracle run at this
+    # size (and no seed passes the tie audit over so many tokens); the checks are size-independent:
+    # the permutation is the stable sort of the ids the call itself returns, and any subset of the
+    # tokens run as its own small batch gives the same bits (a token's result does not depend on the
+    # batch it arrives in). One more token is refused.
+    geo = H.small_geometries()[name]
+    assert tokens * geo.topk == 32768
+    values = synthetic.make_inputs(geo, tokens, 0, "cuda")
+    layer = api.MoeLayer(api.LayerConfig.from_geometry(geo), max_tokens=tokens)
+    out = layer.forward(values, check_status=True)
+    assert bool(torch.isfinite(out["y"].float()).all())
+    flat = out["expert_ids"].flatten()
+    assert torch.equal(out["order"], torch.sort(flat, stable=True).indices)
+    pick = torch.randperm(tokens, generator=torch.Generator().manual_seed(3))[:40].sort().values.cuda()
+    small = dict(values)
+    small["x"] = values["x"][pick].contiguous()
+    sub = api.MoeLayer(api.LayerConfig.from_geometry(geo), max_tokens=40).forward(small, check_status=True)
+    assert torch.equal(sub["expert_ids"], out["expert_ids"][pick])
+    assert torch.equal(sub["topk_weights"], out["topk_weights"][pick])
+    assert torch.equal(sub["y"], out["y"][pick])
+    from vibe_megakernel_b200 import _cabi
+    with pytest.raises(_cabi.MoeError):
+        api.MoeLayer(api.LayerConfig.from_geometry(geo), max_tokens=tokens + 1).workspace(tokens + 1)

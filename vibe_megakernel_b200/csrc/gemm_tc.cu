@@ -696,12 +696,14 @@ static int make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t c
 template <int NT, bool DUAL>
 static cudaError_t launch_typed(GemmDev dev, const CUtensorMap* maps, int grid, cudaStream_t stream) {
   using C = GemmCfg<NT, DUAL>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};      // the attribute belongs to the device the call runs on
+  int device = 0;
+  cudaGetDevice(&device);
+  if (device < 0 || device >= 64 || !configured[device]) {
     cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<NT, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kMaxSmem);
     if (e != cudaSuccess) return e;
-    configured = true;
+    if (device >= 0 && device < 64) configured[device] = true;
   }
   dev.stages = C::stages_for(dev.kblocks);
   if (dev.stages < 2) return cudaErrorInvalidValue;
@@ -711,14 +713,16 @@ static cudaError_t launch_typed(GemmDev dev, const CUtensorMap* maps, int grid, 
 }
 
 static int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
+  static int cached[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 148;
+  if (!cached[dev]) {
+    int n = 0;
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
+    cached[dev] = n > 0 ? n : 148;
   }
-  return n;
+  return cached[dev];
 }
 
 cudaError_t launch_gemm_tc(const GemmArgs& a, cudaStream_t stream, int* launches, int* driver_error) {
