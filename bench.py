@@ -244,6 +244,7 @@ def measure_batch(geo, values: dict, tokens: int, steps: int, warmup: int, flush
     g_bytes = gate_up_bytes(geo, distinct)
     g_gbs = g_bytes / (stages["gate_up_gemm"] * 1e-3) / 1e9
     res = {"batch": tokens, "latency_us": round(latency_us, 2), "min_us": round(1e3 * min(ms), 2),
+           "p50_us": round(1e3 * sorted(ms)[len(ms) // 2], 2),
            "graph_replay_us": round(1e3 * sum(graph_ms) / len(graph_ms), 2),
            "distinct_experts": distinct, "algorithmic_bytes": total_bytes,
            "layer_gbs": round(total_bytes / (latency_us * 1e-6) / 1e9, 1),
