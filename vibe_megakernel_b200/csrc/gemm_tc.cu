@@ -476,7 +476,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const int epi = warp - 3;
     const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
     const int m = quarter * 32 + lane;            // output channel inside the tile
-    const int col0 = (epi >> 2) * C::kCpt;        // first token column of this thread
+    const int group = epi >> 2;                   // with 8 epilogue warps: which share of the token columns
     const uint32_t lane_base = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
     uint32_t it = 0;
     bool failed = false;
@@ -496,6 +496,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
       const int mt = u % p.tiles_m;
       const int cols = ((ch.rows + 15) >> 4) * 16;            // token columns that were multiplied
+      // This thread's columns [col0, cend): two warp groups share the columns the item really has
+      // (16/16 of 32, 32/16 of 48, 32/32 of 64), one group takes them all with 4 epilogue warps.
+      const int split = cols <= 32 ? 16 : 32;
+      const int col0 = group ? split : 0;
+      const int cend = (C::kEpiWarps == 8 && group == 0) ? min(split, cols) : cols;
+      const int rend = min(ch.rows, cend);                     // ... and the rows among them that exist
       const uint32_t b = un & 1u, sph = (un >> 1) & 1u;
       const float* xs_all = s_scales + b * sf;
       const float* ws = xs_all + KB * NT;
@@ -526,13 +532,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         PROBE_ADD(probe_tfull, t_tfull);
         if (failed) continue;   // keep in step with the other epilogue threads up to the item's end
         tc_fence_after();
-        const bool active = col0 < cols;      // uniform per warp
+        const bool active = col0 < cend;      // uniform per warp
         uint32_t ra[C::kCpt], rb[DUAL ? C::kCpt : 1];
         if (active) {
           const uint32_t t0 = lane_base + as * C::kAccCols + col0;
 #pragma unroll
           for (int g = 0; g < C::kCpt; g += 16) {
-            if (col0 + g < cols) {
+            if (col0 + g < cend) {
               tmem_ld16(t0 + g, ra + g);
               if constexpr (DUAL) tmem_ld16(t0 + NT + g, rb + g);
             }
@@ -550,7 +556,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           const float* xs = xs_all + kb * NT + col0;
 #pragma unroll
           for (int g = 0; g < C::kCpt; g += 16) {
-            if (col0 + g < cols) {
+            if (col0 + g < cend) {
               // 16 token scales as four 16-byte loads (col0 and NT are multiples of 16)
               float x16[16];
 #pragma unroll
@@ -583,7 +589,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       // One decision for all epilogue threads: nobody may be left alone at a later barrier.
       if (epilogue_any<C::kEpiThreads>(failed || *s_abort)) break;
       if constexpr (DUAL) {
-        epilogue_swiglu_requant<C::kCpt, C::kEpiThreads>(acc_a, acc_b, m, col0, NT, ch.rows, ch.row0, mt, p.m, s_amax,
+        epilogue_swiglu_requant<C::kCpt, C::kEpiThreads>(acc_a, acc_b, m, col0, NT, rend, ch.row0, mt, p.m, s_amax,
                                                          p.aq, p.as);
         // every thread's stores were fenced before the epilogue's closing barrier: announce the tile
         if (p.progress && epi == 0 && lane == 0) {
@@ -601,7 +607,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         float* parts = p.partial + static_cast<size_t>(u) * ksplit * tile_floats;
 #pragma unroll
         for (int n = 0; n < C::kCpt; ++n)
-          if (col0 + n < ch.rows) __stcg(parts + ch.pad * tile_floats + (col0 + n) * 128 + m, acc_a[n]);
+          if (col0 + n < rend) __stcg(parts + ch.pad * tile_floats + (col0 + n) * 128 + m, acc_a[n]);
         __threadfence();
         epilogue_sync<C::kEpiThreads>();
         if (epi == 0 && lane == 0) {
@@ -614,7 +620,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (*s_last_part) {
 #pragma unroll
           for (int n = 0; n < C::kCpt; ++n) {
-            if (col0 + n < ch.rows) {
+            if (col0 + n < rend) {
               float sum = 0.f;
               for (int part = 0; part < ksplit; ++part)
                 sum = __fadd_rn(sum, __ldcg(parts + part * tile_floats + (col0 + n) * 128 + m));
@@ -625,7 +631,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       } else {
 #pragma unroll
         for (int n = 0; n < C::kCpt; ++n) {
-          if (col0 + n < ch.rows) {   // one bf16 rounding of the fp32 sum (megabench/tasks/megamoe.py:149)
+          if (col0 + n < rend) {   // one bf16 rounding of the fp32 sum (megabench/tasks/megamoe.py:149)
             const float sum = parts_here ? acc_b[n] : acc_a[n];
             p.out[static_cast<size_t>(sd[col0 + n]) * p.m + mt * kGroup + m] = __float2bfloat16_rn(sum);
           }
