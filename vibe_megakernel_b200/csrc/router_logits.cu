@@ -135,14 +135,13 @@ __device__ __forceinline__ void unpack4(const uint2& raw, float (&v)[4]) {
   v[3] = __uint_as_float(raw.y & 0xffff0000u);
 }
 
-// Larger batches: a block keeps 8 token rows in shared memory and streams 32 router rows (four per
-// warp) against them, so x is read from L2 once per block.
+// Larger batches: a block keeps TOK token rows in shared memory and streams the router rows of
+// 8 * kTiledExpertsPerWarp experts against them, so x is read from L2 once per block. Four experts
+// per warp halve the instructions per FMA (the token values are unpacked once for all of them);
+// two give twice the blocks, which wins while the grid would not fill the SMs.
 constexpr int kTiledWarps = 8;
-constexpr int kTiledExpertsPerWarp = 4;
-constexpr int kTiledExperts = kTiledWarps * kTiledExpertsPerWarp;
 
-// TOK token rows per block: every block streams the router rows of its experts from the L2 once.
-template <int TOK>
+template <int TOK, int kTiledExpertsPerWarp>
 __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(const __nv_bfloat16* __restrict__ x,
                                                                                const float* __restrict__ router,
                                                                                int tokens, int experts, int hidden,
@@ -176,7 +175,7 @@ __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(c
   for (int i = tcount * quads + threadIdx.x; i < TOK * quads; i += blockDim.x) s_x[i] = make_uint2(0u, 0u);
   mbar_wait(&bar, 0);           // bounded; a copy that never lands leaves wrong logits, not a hang
   __syncthreads();
-  const int e0 = blockIdx.x * kTiledExperts + warp * kTiledExpertsPerWarp;
+  const int e0 = (blockIdx.x * kTiledWarps + warp) * kTiledExpertsPerWarp;
   float acc[kTiledExpertsPerWarp][TOK];
 #pragma unroll
   for (int j = 0; j < kTiledExpertsPerWarp; ++j)
@@ -267,8 +266,8 @@ cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* router, in
     cudaError_t e = launch_rows(router_logits_rows_kernel<8>, 8);
     if (e != cudaSuccess) return e;
   } else {
-    const int tiled_blocks = (experts + kTiledExperts - 1) / kTiledExperts;
-    auto launch_tiled = [&](auto kernel, int tok) -> cudaError_t {
+    auto launch_tiled = [&](auto kernel, int tok, int experts_per_block) -> cudaError_t {
+      const int tiled_blocks = (experts + experts_per_block - 1) / experts_per_block;
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(kLogitsSmemLimit));
       if (e != cudaSuccess) return e;
@@ -277,7 +276,9 @@ cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* router, in
     };
     // 8 token rows per block: 12 (the most that fit at H = 7168) measured 15-25 % slower, the extra
     // accumulators costing more than the saved passes over the router rows
-    cudaError_t e = launch_tiled(router_logits_tiled_kernel<8>, 8);
+    const long long wide_grid = static_cast<long long>((experts + 31) / 32) * ((tokens + 7) / 8);
+    cudaError_t e = wide_grid >= 148 ? launch_tiled(router_logits_tiled_kernel<8, 4>, 8, 32)
+                                     : launch_tiled(router_logits_tiled_kernel<8, 2>, 8, 16);
     if (e != cudaSuccess) return e;
   }
   return cudaGetLastError();
