@@ -137,6 +137,14 @@ int moe_route_static(const moe_config_t* cfg, const void* x_bf16, const float* r
 int moe_quantize_rows(const void* x, int32_t dtype, int32_t rows, int32_t width, const int32_t* gather,
                       uint8_t* q, float* scales, void* stream);
 
+/* The same quantiser with power-of-two scales stored as biased exponents (UE8M0), one per `block` =
+ * 32 or 128 channels: the activation format of the MXFP4 MegaMoE layer. The exponent comes from the
+ * fp32 bits of the block maximum by integer arithmetic, the payload is RNE_e4m3(x * 2^-(e-127)).
+ * Replaces pack_fp8_activation(..., block=32, scale_format="e8m0")
+ * (megabench/tasks/quantization.py:62-84,87-109). scales uint8 [rows, ceil(width/block)]. */
+int moe_quantize_rows_ue8m0(const void* x, int32_t dtype, int32_t rows, int32_t width, int32_t block, uint8_t* q,
+                            uint8_t* scales, void* stream);
+
 /* Stable grouping of `n` routed rows by expert id (the token->expert permutation).
  * Replaces `torch.sort(ids, stable=True)` + `bincount` (megabench/tasks/megamoe.py:137-138,161-165).
  * ids int64 [n]; rows whose id is outside [id_base, id_base + n_local) are dropped.

@@ -28,7 +28,9 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-sys.path.insert(0, os.environ.get("MEGABENCH_ROOT", "/root/reference"))
+if "MEGABENCH_ROOT" not in os.environ:
+    raise SystemExit("set MEGABENCH_ROOT to the reference checkout (the directory that holds megabench/)")
+sys.path.insert(0, os.environ["MEGABENCH_ROOT"])
 sys.path.insert(0, str(REPO))
 
 from megabench.tasks import frontier, quantization as Q  # noqa: E402

@@ -190,3 +190,26 @@ def test_combine_is_the_slot_order_fp32_sum(api, tokens, topk, hidden, shared):
         acc = acc + rows[tokens * topk:].to(torch.float32)
     got = api.combine(rows.cuda(), w.cuda(), tokens, shared)
     assert torch.equal(got.cpu().view(torch.int16), acc.to(torch.bfloat16).view(torch.int16))
+
+
+# ---------------------------------------------------------------- power-of-two (UE8M0) scales
+def test_ue8m0_quantiser_matches_reference_vectors(api, golden_dir):
+    # edge rows of megabench/tests/test_megamoe.py:57-61 (448, its neighbours, the 1e-4 floor, zero, 896)
+    g = np.load(golden_dir / "quantizers.npz")
+    x = torch.from_numpy(g["e_in"])
+    q, s = api.quantize_rows_ue8m0(x.cuda().contiguous(), block=32)
+    assert np.array_equal(q.view(torch.uint8).cpu().numpy(), g["e_q"])
+    assert np.array_equal(s.cpu().numpy(), g["e_s"])
+
+
+@pytest.mark.parametrize("rows,width,block,dtype", [(1, 128, 32, torch.bfloat16), (7, 7168, 32, torch.bfloat16),
+                                                    (33, 2048, 128, torch.float32), (5, 259, 32, torch.float32),
+                                                    (3, 1, 32, torch.bfloat16), (130, 416, 128, torch.bfloat16)])
+def test_ue8m0_quantiser_matches_oracle(api, rows, width, block, dtype):
+    gen = torch.Generator().manual_seed(rows * 1000 + width)
+    x = (torch.randn((rows, width), generator=gen) * torch.logspace(-5, 2, rows)[:, None]).to(dtype)
+    x[0, : min(width, 4)] = 0
+    q, s = api.quantize_rows_ue8m0(x.cuda(), block=block)
+    wq, ws = O.quantize_activation(x, group=block, scale_format="e8m0")
+    assert torch.equal(q.view(torch.uint8).cpu(), wq.view(torch.uint8))
+    assert torch.equal(s.cpu(), ws)

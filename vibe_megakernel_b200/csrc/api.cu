@@ -120,6 +120,13 @@ int moe_quantize_rows(const void* x, int32_t dtype, int32_t rows, int32_t width,
                                         &launches));
 }
 
+int moe_quantize_rows_ue8m0(const void* x, int32_t dtype, int32_t rows, int32_t width, int32_t block, uint8_t* q,
+                            uint8_t* scales, void* stream) {
+  if (!x || !q || !scales || rows < 0 || width < 1 || (dtype != 0 && dtype != 1)) return MOE_ERR_BAD_ARG;
+  if (block != 32 && block != 128) return MOE_ERR_UNSUPPORTED;
+  return from_cuda(moe::launch_quantize_ue8m0(x, dtype, rows, width, block, q, scales, static_cast<cudaStream_t>(stream)));
+}
+
 int moe_group_rows(const int64_t* ids, int32_t n, int32_t id_base, int32_t n_local, int64_t* order, int32_t* counts,
                    void* stream) {
   if (!ids || !order || !counts || n < 0 || n_local < 1 || n_local > MOE_MAX_EXPERTS || n > 32768) return MOE_ERR_BAD_ARG;

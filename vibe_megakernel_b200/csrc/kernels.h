@@ -84,6 +84,10 @@ cudaError_t launch_router_fused(const moe_config_t& cfg, const __nv_bfloat16* x,
 cudaError_t launch_quantize(const void* x, int dtype, int rows, int width, const int32_t* gather, uint8_t* q,
                             float* scales, cudaStream_t stream, int* launches);
 
+// e4m3 payload with one power-of-two scale (biased exponent, uint8) per `block` = 32 or 128 channels
+cudaError_t launch_quantize_ue8m0(const void* x, int dtype, int rows, int width, int block, uint8_t* q, uint8_t* scales,
+                                  cudaStream_t stream);
+
 // residual (optional, bf16 [tokens, hidden]): y = bf16(residual + bf16(sum)) instead of bf16(sum)
 cudaError_t launch_combine(const __nv_bfloat16* slots, const float* weights, int tokens, int topk, int hidden,
                            int shared, __nv_bfloat16* y, cudaStream_t stream, int* launches,

@@ -66,3 +66,64 @@ cudaError_t launch_quantize(const void* x, int dtype, int rows, int width, const
 }
 
 }  // namespace moe
+
+// ---------------------------------------------------------------------------------------------
+// Power-of-two (UE8M0) scales per `block` channels: the activation format of the MXFP4 MegaMoE layer.
+//
+// Reference: pack_fp8_activation(value, block=32, scale_format="e8m0"),
+// megabench/tasks/quantization.py:62-84,87-109: the scale is a biased exponent taken from the fp32
+// bits of the block maximum with integer arithmetic (the exponent rises by one when the mantissa
+// exceeds that of 448 = 1.75 * 2^8, 448's exponent is removed, floor at the exponent of the 1e-4
+// clamp), the payload is RNE_e4m3(x * 2^-(e-127)), an exact multiplication. A ragged last block is
+// padded with zeros for the maximum and the padding is not stored.
+// ---------------------------------------------------------------------------------------------
+namespace moe {
+
+template <typename T>
+__global__ void __launch_bounds__(256) quantize_rows_ue8m0_kernel(const T* __restrict__ x, int rows, int width,
+                                                                  int block, uint8_t* __restrict__ q,
+                                                                  uint8_t* __restrict__ scales) {
+  dependent_wait();
+  dependents_may_launch();
+  const int pieces = (width + 127) / 128;                 // a warp takes 128 channels: 4 per lane
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = static_cast<long long>(blockIdx.x) * 8 + warp;
+  if (item >= static_cast<long long>(rows) * pieces) return;
+  const int row = static_cast<int>(item / pieces), piece = static_cast<int>(item % pieces);
+  const int k0 = piece * 128 + lane * 4;
+  const T* in = x + static_cast<size_t>(row) * width;
+  float v[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) v[j] = (k0 + j < width) ? load_as_float<T>(in + k0 + j) : 0.f;
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  const int lanes = block / 4;                            // lanes that share a scale: 8 (block 32) or 32 (block 128)
+  for (int off = 1; off < lanes; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  const int bits = __float_as_int(amax);
+  const int exponent = max((bits + (0x7FFFFF - 0x600000)) >> 23, 105 + 8) - 8;       // biased, as uint8
+  const float inverse = __int_as_float((254 - exponent) << 23);                        // exact 2^-(e-127)
+  uint8_t* out = q + static_cast<size_t>(row) * width;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (k0 + j < width)
+      out[k0 + j] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(__fmul_rn(v[j], inverse), __NV_SATFINITE, __NV_E4M3));
+  const int blocks_per_row = (width + block - 1) / block;
+  const int b = k0 / block;
+  if ((lane % lanes) == 0 && b < blocks_per_row)
+    scales[static_cast<size_t>(row) * blocks_per_row + b] = static_cast<uint8_t>(exponent);
+}
+
+cudaError_t launch_quantize_ue8m0(const void* x, int dtype, int rows, int width, int block, uint8_t* q, uint8_t* scales,
+                                  cudaStream_t stream) {
+  if (rows <= 0) return cudaSuccess;
+  const long long items = static_cast<long long>(rows) * ((width + 127) / 128);
+  const unsigned blocks = static_cast<unsigned>((items + 7) / 8);
+  if (dtype == 0)
+    launch_dependent(quantize_rows_ue8m0_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
+                     static_cast<const __nv_bfloat16*>(x), rows, width, block, q, scales);
+  else
+    launch_dependent(quantize_rows_ue8m0_kernel<float>, dim3(blocks), dim3(256), 0, stream, static_cast<const float*>(x),
+                     rows, width, block, q, scales);
+  return cudaGetLastError();
+}
+
+}  // namespace moe

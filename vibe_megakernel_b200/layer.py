@@ -327,3 +327,18 @@ def combine(rows: torch.Tensor, weights: torch.Tensor, tokens: int, shared: bool
                          y.data_ptr(), torch.cuda.current_stream(rows.device).cuda_stream)
     _cabi.check("moe_combine", rc)
     return y
+
+
+def quantize_rows_ue8m0(x: torch.Tensor, block: int = 32):
+    """e4m3 payload and power-of-two scales as biased exponents, one per ``block`` channels:
+    (q float8_e4m3fn [rows, W], scales uint8 [rows, ceil(W/block)])."""
+    lib = _cabi.load()
+    if x.dtype not in (torch.bfloat16, torch.float32) or x.dim() != 2 or not x.is_cuda or not x.is_contiguous():
+        raise TypeError("x must be a contiguous CUDA bf16/fp32 matrix")
+    rows, width = x.shape
+    q = torch.empty((rows, width), dtype=torch.uint8, device=x.device)
+    s = torch.empty((rows, -(-width // block)), dtype=torch.uint8, device=x.device)
+    rc = lib.moe_quantize_rows_ue8m0(x.data_ptr(), 0 if x.dtype == torch.bfloat16 else 1, rows, width, block,
+                                     q.data_ptr(), s.data_ptr(), torch.cuda.current_stream(x.device).cuda_stream)
+    _cabi.check("moe_quantize_rows_ue8m0", rc)
+    return q.view(torch.float8_e4m3fn), s
