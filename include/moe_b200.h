@@ -57,6 +57,12 @@ typedef struct moe_config {
   int32_t ep_world;       /* expert-parallel ranks; rank r owns experts [r*E/world, (r+1)*E/world) */
   int32_t ep_rank;
   int32_t gemm_impl;      /* MOE_GEMM_* */
+  /* The MegaMoE form of the expert MLP (megabench/tasks/megamoe.py:116-122,176-182); both 0 = the
+   * DeepSeek/GLM form of megabench/tasks/frontier.py:337,352. */
+  float swiglu_limit;             /* > 0: gate clamped to at most this, up to +- this, before SwiGLU */
+  int32_t weight_before_requant;  /* 1: the routing weight multiplies the SwiGLU output before it is
+                                   * requantised and the combine is a plain slot-order sum (one-GPU
+                                   * layer and block entry points only) */
 } moe_config_t;
 
 /* Device pointers. Layouts are the MoE-block tensors of megabench/tasks/frontier.py:157-176:

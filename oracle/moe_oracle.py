@@ -193,6 +193,8 @@ class LayerSpec:
     n_group: int = 1
     topk_group: int = 1
     scaling: float = 1.0
+    swiglu_limit: float = 0.0       # > 0: gate clamped above, up clamped both ways (megamoe.py:119-121)
+    weight_before_requant: bool = False   # routing weight inside SwiGLU (megamoe.py:122), plain sum at the combine
 
 
 def router_logits(router: torch.Tensor, x_row: torch.Tensor) -> torch.Tensor:
@@ -245,7 +247,20 @@ def _silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return g / (1 + torch.exp(-g)) * up.to(torch.float32)
 
 
-def expert_mlp(rows_q, rows_s, gate, gate_s, up, up_s, down, down_s, *, compute=torch.bfloat16):
+def _silu_mul_clamped(gate: torch.Tensor, up: torch.Tensor, bound: float, weights: torch.Tensor | None) -> torch.Tensor:
+    """The MegaMoE form: gate clamped above and up clamped both ways in the GEMM
+    output dtype, fp32 silu(gate) * up, then times the row's routing weight.
+    megabench/tasks/megamoe.py:116-122."""
+    if bound > 0:
+        gate = gate.clamp(max=bound)
+        up = up.clamp(-bound, bound)
+    g, u = gate.to(torch.float32), up.to(torch.float32)
+    a = g / (1 + torch.exp(-g)) * u
+    return a if weights is None else a * weights[:, None]
+
+
+def expert_mlp(rows_q, rows_s, gate, gate_s, up, up_s, down, down_s, *, compute=torch.bfloat16,
+               swiglu_limit: float = 0.0, row_weights: torch.Tensor | None = None):
     """One expert over its rows.
 
     Operands are dequantised and rounded to ``compute`` (bf16 for the graded
@@ -258,7 +273,10 @@ def expert_mlp(rows_q, rows_s, gate, gate_s, up, up_s, down, down_s, *, compute=
     wg = dequantize_weight(gate, gate_s).to(compute)
     wu = dequantize_weight(up, up_s).to(compute)
     wd = dequantize_weight(down, down_s).to(compute)
-    a = _silu_mul(xa @ wg.T, xa @ wu.T)
+    if swiglu_limit > 0 or row_weights is not None:
+        a = _silu_mul_clamped(xa @ wg.T, xa @ wu.T, swiglu_limit, row_weights)
+    else:
+        a = _silu_mul(xa @ wg.T, xa @ wu.T)
     aq, a_s = quantize_activation(a)
     back = dequantize_activation(aq, a_s).to(compute)
     return back @ wd.T, aq, a_s
@@ -300,18 +318,24 @@ def moe_layer(spec: LayerSpec, values: dict, *, compute=torch.bfloat16, keep_int
         k = e if expert_slot is None else expert_slot[e]
         res, aq, a_s = expert_mlp(xq[tok], xs[tok], values["gate"][k], values["gate_scale"][k],
                                   values["up"][k], values["up_scale"][k],
-                                  values["down"][k], values["down_scale"][k], compute=compute)
+                                  values["down"][k], values["down_scale"][k], compute=compute,
+                                  swiglu_limit=spec.swiglu_limit,
+                                  row_weights=ws.reshape(-1)[sel] if spec.weight_before_requant else None)
         out_rows[sel] = res
         if keep_intermediates:
             inter[e] = (aq, a_s)
     acc = torch.zeros((t, h), dtype=torch.float32, device=x.device)
     slots = out_rows.reshape(t, spec.topk, h)
     for s in range(spec.topk):
-        acc = acc + slots[:, s].to(torch.float32) * ws[:, s:s + 1]
+        if spec.weight_before_requant:      # the rows are weighted already: plain slot-order sum (megamoe.py:178-181)
+            acc = acc + slots[:, s].to(torch.float32)
+        else:
+            acc = acc + slots[:, s].to(torch.float32) * ws[:, s:s + 1]
     if spec.shared:
         sh, _, _ = expert_mlp(xq, xs, values["shared_gate"], values["shared_gate_scale"],
                               values["shared_up"], values["shared_up_scale"],
-                              values["shared_down"], values["shared_down_scale"], compute=compute)
+                              values["shared_down"], values["shared_down_scale"], compute=compute,
+                              swiglu_limit=spec.swiglu_limit)
         acc = acc + sh.to(torch.float32)
     out = {"y": acc.to(torch.bfloat16), "expert_ids": ids, "topk_weights": ws,
            "order": order, "counts": counts}

@@ -153,8 +153,13 @@ def router_vectors():
     np.savez_compressed(HERE / "routers.npz", **out)
 
 
-def reference_layer(geo, values, *, widen=False):
-    """The layer composed from reference primitives only."""
+def reference_layer(geo, values, *, widen=False, megamoe_swiglu=0.0):
+    """The layer composed from reference primitives only. ``megamoe_swiglu`` > 0 switches to the
+    MegaMoE form: ``megamoe.swiglu`` (clamp at that bound, routing weight inside, megamoe.py:116-122)
+    and an unweighted slot-order sum (megamoe.py:176-182); the shared expert's rows carry weight 1."""
+    from types import SimpleNamespace
+    from megabench.tasks import megamoe
+    case = SimpleNamespace(params={"swiglu_limit": megamoe_swiglu})
     x = values["x"]
     tokens = x.shape[0]
     bf16 = torch.bfloat16
@@ -173,12 +178,15 @@ def reference_layer(geo, values, *, widen=False):
     counts = torch.bincount(flat, minlength=geo.experts).tolist()       # megamoe.py:138
     source = torch.div(order, geo.topk, rounding_mode="floor")          # megamoe.py:165
 
-    def mlp(rows, gate, gs, up, us, down, ds):
+    def mlp(rows, gate, gs, up, us, down, ds, row_weights=None):
         xa = Q.unpack_fp8_activation(*Q.pack_fp8_activation(rows)).to(bf16)      # megamoe.py:146
         g = xa @ Q.unpack_fp8_weight(gate, gs).to(bf16).T                      # megamoe.py:147,149
         u = xa @ Q.unpack_fp8_weight(up, us).to(bf16).T
-        g32, u32 = g.float(), u.float()
-        a = g32 / (1 + torch.exp(-g32)) * u32                                   # megamoe.py:119-122
+        if megamoe_swiglu > 0:
+            a = megamoe.swiglu(case, torch.cat([g, u], dim=-1), row_weights)    # megamoe.py:116-122
+        else:
+            g32, u32 = g.float(), u.float()
+            a = g32 / (1 + torch.exp(-g32)) * u32                               # megamoe.py:119-122
         a = Q.unpack_fp8_activation(*Q.pack_fp8_activation(a)).to(bf16)         # megamoe.py:125-128
         return a @ Q.unpack_fp8_weight(down, ds).to(bf16).T                     # megamoe.py:148-149
 
@@ -192,15 +200,20 @@ def reference_layer(geo, values, *, widen=False):
         start += count
         output[selected] = mlp(rows, values["gate"][expert], values["gate_scale"][expert],
                                values["up"][expert], values["up_scale"][expert],
-                               values["down"][expert], values["down_scale"][expert])
+                               values["down"][expert], values["down_scale"][expert],
+                               ws.flatten()[selected] if megamoe_swiglu > 0 else None)
     slots = output.view(tokens, geo.topk, -1)
     combined = torch.zeros((tokens, geo.hidden), dtype=torch.float32)
     for slot in range(geo.topk):
-        combined = combined + slots[:, slot].float() * ws[:, slot:slot + 1]       # frontier.py:352
+        if megamoe_swiglu > 0:
+            combined = combined + slots[:, slot].float()                          # megamoe.py:178-181
+        else:
+            combined = combined + slots[:, slot].float() * ws[:, slot:slot + 1]   # frontier.py:352
     if geo.shared:
         combined = combined + mlp(x, values["shared_gate"], values["shared_gate_scale"],
                                   values["shared_up"], values["shared_up_scale"],
-                                  values["shared_down"], values["shared_down_scale"]).float()   # frontier.py:353
+                                  values["shared_down"], values["shared_down_scale"],
+                                  torch.ones(tokens) if megamoe_swiglu > 0 else None).float()   # frontier.py:353
     return {"y": combined if widen else combined.to(bf16), "expert_ids": ids, "topk_weights": ws, "order": order}
 
 
@@ -230,6 +243,34 @@ def layer_vectors():
         out[f"{name}_geo"] = np.array([geo.hidden, geo.inter, geo.experts, geo.topk, geo.shared,
                                        geo.n_group, geo.topk_group, tokens, seed], dtype=np.int64)
     np.savez_compressed(HERE / "layers.npz", **out)
+
+
+def megamoe_swiglu_vectors():
+    """The MegaMoE SwiGLU form on its own (megabench/tasks/megamoe.py:116-122) and inside small layers."""
+    import dataclasses
+    from types import SimpleNamespace
+    from megabench.tasks import megamoe
+    out = {}
+    gen = torch.Generator().manual_seed(41)
+    l1 = (torch.randn((9, 2 * 256), generator=gen) * 6).to(torch.bfloat16)       # many values beyond the bound
+    l1[0, :4] = torch.tensor([10.0, 10.06, -10.06, 0.0]).to(torch.bfloat16)
+    w = torch.rand((9,), generator=gen) * 2.5
+    out["l1"], out["w"] = bf16_bits(l1), w.numpy()
+    out["a"] = megamoe.swiglu(SimpleNamespace(params={"swiglu_limit": 10}), l1, w).numpy()
+    specs = {
+        "ds_small": (dataclasses.replace(synthetic.GEOMETRIES["deepseek_v3"], name="ds_small", hidden=512, inter=256,
+                                         experts=32, topk=4, n_group=4, topk_group=2, weight_std=0.2), 6, 2),
+        "qwen_small": (dataclasses.replace(synthetic.GEOMETRIES["qwen3_30b_a3b"], name="qwen_small", hidden=256,
+                                           inter=128, experts=8, topk=2, weight_std=0.2), 5, 2),
+    }
+    for name, (geo, tokens, seed) in specs.items():
+        values = synthetic.make_inputs(geo, tokens, seed, "cpu")
+        got = reference_layer(geo, values, megamoe_swiglu=1.0)                   # a bound the activations do reach
+        out[f"{name}_y"] = bf16_bits(got["y"])
+        out[f"{name}_ids"], out[f"{name}_order"] = got["expert_ids"].numpy(), got["order"].numpy()
+        out[f"{name}_geo"] = np.array([geo.hidden, geo.inter, geo.experts, geo.topk, geo.shared, geo.n_group,
+                                       geo.topk_group, tokens, seed], dtype=np.int64)
+    np.savez_compressed(HERE / "megamoe_swiglu.npz", **out)
 
 
 def block_vectors():
@@ -264,5 +305,6 @@ if __name__ == "__main__":
     router_vectors()
     layer_vectors()
     block_vectors()
+    megamoe_swiglu_vectors()
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size)

@@ -25,8 +25,8 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_struct_sizes_match_the_header():
-    # 12 four-byte fields; 14 pointers; 16 uint64 + 4 int32
-    assert C.sizeof(_cabi.Config) == 48
+    # 14 four-byte fields; 14 pointers; 16 uint64 + 4 int32
+    assert C.sizeof(_cabi.Config) == 56
     assert C.sizeof(_cabi.Weights) == 14 * C.sizeof(C.c_void_p)
     assert C.sizeof(_cabi.Layout) == 16 * 8 + 16
 
@@ -53,6 +53,12 @@ def test_workspace_layout_and_argument_checks_need_no_gpu():
     bad = _cabi.Config(7168, 2048, 256, 8, 1, 1, 7, 4, 2.5, 1, 0, 0)      # groups must divide experts
     assert lib.moe_workspace_layout(C.byref(bad), 64, None) == -1
     bad = _cabi.Config(7168, 2048, 256, 8, 2, 1, 8, 4, 2.5, 1, 0, 0)      # at most one shared expert
+    assert lib.moe_workspace_layout(C.byref(bad), 64, None) == -2
+    mega = _cabi.Config(7168, 2048, 256, 8, 1, 1, 8, 4, 2.5, 1, 0, 0, 7.0, 1)    # clamp, routing weight before the requantisation
+    assert lib.moe_workspace_layout(C.byref(mega), 64, None) == 0
+    bad = _cabi.Config(7168, 2048, 256, 8, 1, 1, 8, 4, 2.5, 1, 0, 0, -1.0, 0)
+    assert lib.moe_workspace_layout(C.byref(bad), 64, None) == -1
+    bad = _cabi.Config(7168, 2048, 256, 8, 1, 1, 8, 4, 2.5, 2, 0, 0, 7.0, 1)     # one-GPU entry points only
     assert lib.moe_workspace_layout(C.byref(bad), 64, None) == -2
     assert lib.moe_workspace_layout(None, 64, None) == -1
     assert lib.moe_layer_forward(C.byref(cfg), None, None, 64, None, None, None, None, None, 0, None) == -1

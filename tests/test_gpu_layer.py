@@ -89,6 +89,32 @@ def test_tiny_layer_matches_the_reference_vectors(api, golden_dir):
         H.assert_y_close(out["y"], want, name)
 
 
+@pytest.mark.parametrize("gemm", ["simt", "tcgen05"])
+def test_megamoe_swiglu_form(api, golden_dir, gemm):
+    # clamp and routing weight inside SwiGLU, plain slot-order sum at the combine
+    # (megabench/tasks/megamoe.py:116-122,176-182); vectors made by the reference's own swiglu()
+    g = np.load(golden_dir / "megamoe_swiglu.npz")
+    for name in ("ds_small", "qwen_small"):
+        geo = dataclasses.replace(H.small_geometries()[name], weight_std=0.2)
+        tokens, seed = int(g[f"{name}_geo"][7]), int(g[f"{name}_geo"][8])
+        values = synthetic.make_inputs(geo, tokens, seed, "cpu")
+        config = api.LayerConfig.from_geometry(geo, gemm=gemm, swiglu_limit=1.0, weight_before_requant=True)
+        out = api.MoeLayer(config, max_tokens=tokens).forward(H.to_device(values, "cuda"), check_status=True)
+        assert np.array_equal(out["expert_ids"].cpu().numpy(), g[f"{name}_ids"])
+        assert np.array_equal(out["order"].cpu().numpy(), g[f"{name}_order"])
+        H.assert_y_close(out["y"], torch.from_numpy(g[f"{name}_y"].copy()).view(torch.bfloat16), name)
+        # each switch alone against the oracle, and both must change the result
+        plain = api.MoeLayer(api.LayerConfig.from_geometry(geo, gemm=gemm), max_tokens=tokens).forward(
+            H.to_device(values, "cuda"), check_status=True)
+        for limit, early in ((1.0, False), (0.0, True), (0.73, True)):
+            spec = dataclasses.replace(H.spec_of(geo), swiglu_limit=limit, weight_before_requant=early)
+            want = O.moe_layer(spec, values)
+            config = api.LayerConfig.from_geometry(geo, gemm=gemm, swiglu_limit=limit, weight_before_requant=early)
+            got = api.MoeLayer(config, max_tokens=tokens).forward(H.to_device(values, "cuda"), check_status=True)
+            H.assert_y_close(got["y"], want["y"], f"{name} limit {limit} early {early}")
+            assert not torch.equal(got["y"], plain["y"])
+
+
 def test_tensor_core_and_check_arm_agree(api):
     geo = H.small_geometries()["kimi_small"]
     values, _ = H.audited_inputs(geo, 40)

@@ -153,6 +153,24 @@ def test_block_matches_reference_composition(golden_dir):
         assert np.array_equal(got["x"].view(torch.int16).numpy(), g[f"{name}_x_out"])
 
 
+def test_megamoe_swiglu_form(golden_dir):
+    # megabench/tasks/megamoe.py:116-122 (clamp, routing weight inside SwiGLU) and :176-182 (plain sum)
+    g = np.load(golden_dir / "megamoe_swiglu.npz")
+    l1 = torch.from_numpy(g["l1"].copy()).view(torch.bfloat16)
+    gate, up = l1.chunk(2, dim=-1)
+    a = O._silu_mul_clamped(gate, up, 10.0, torch.from_numpy(g["w"]))
+    assert np.array_equal(a.numpy(), g["a"])
+    for name in ("ds_small", "qwen_small"):
+        geo = dataclasses.replace(small_layers()[name], weight_std=0.2)
+        tokens, seed = int(g[f"{name}_geo"][7]), int(g[f"{name}_geo"][8])
+        values = synthetic.make_inputs(geo, tokens, seed, "cpu")
+        spec = dataclasses.replace(spec_of(geo), swiglu_limit=1.0, weight_before_requant=True)
+        got = O.moe_layer(spec, values)
+        assert np.array_equal(got["expert_ids"].numpy(), g[f"{name}_ids"])
+        assert np.array_equal(got["order"].numpy(), g[f"{name}_order"])
+        assert np.array_equal(got["y"].view(torch.int16).numpy(), g[f"{name}_y"])
+
+
 def test_weight_generator_uses_the_reference_block_format():
     w = torch.randn((256, 384), generator=torch.Generator().manual_seed(2)) * 0.02
     q, s = synthetic.block_quantize_weight(w)

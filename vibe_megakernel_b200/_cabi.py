@@ -19,7 +19,7 @@ class Config(C.Structure):
     _fields_ = [("hidden", C.c_int32), ("inter", C.c_int32), ("n_experts", C.c_int32), ("topk", C.c_int32),
                 ("n_shared", C.c_int32), ("scoring", C.c_int32), ("n_group", C.c_int32), ("topk_group", C.c_int32),
                 ("routed_scaling", C.c_float), ("ep_world", C.c_int32), ("ep_rank", C.c_int32),
-                ("gemm_impl", C.c_int32)]
+                ("gemm_impl", C.c_int32), ("swiglu_limit", C.c_float), ("weight_before_requant", C.c_int32)]
 
 
 WEIGHT_FIELDS = ("router", "router_bias", "gate", "gate_scale", "up", "up_scale", "down", "down_scale",

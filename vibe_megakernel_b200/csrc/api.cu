@@ -38,6 +38,8 @@ int check_config(const moe_config_t* c) {
   if (c->ep_world < 1 || c->ep_rank < 0 || c->ep_rank >= c->ep_world || c->n_experts % c->ep_world) return MOE_ERR_BAD_ARG;
   if (c->gemm_impl != MOE_GEMM_TCGEN05 && c->gemm_impl != MOE_GEMM_SIMT) return MOE_ERR_BAD_ARG;
   if (c->hidden / 128 > 112 || c->inter / 128 > 112) return MOE_ERR_UNSUPPORTED;
+  if (!(c->swiglu_limit >= 0.f) || (c->weight_before_requant != 0 && c->weight_before_requant != 1)) return MOE_ERR_BAD_ARG;
+  if (c->weight_before_requant && c->ep_world != 1) return MOE_ERR_UNSUPPORTED;
   return MOE_OK;
 }
 
@@ -287,6 +289,14 @@ static int layer_forward_impl(const moe_config_t* cfg, const moe_weights_t* w, c
   a.s_b = w->shared_up; a.s_b_scale = w->shared_up_scale;
   a.aq = aq;
   a.as = as;
+  // The clamp acts on bf16 values and gives a bf16 value (`gate.clamp(max=bound)` on the bf16 GEMM
+  // output, megabench/tasks/megamoe.py:119-121), so the bound counts rounded to bf16.
+  a.swiglu.limit = __bfloat162float(__float2bfloat16_rn(cfg->swiglu_limit));
+  if (cfg->weight_before_requant) {
+    a.swiglu.slot_weight = tw;
+    a.swiglu.row_dest = row_dest;
+    a.swiglu.routed_rows = tokens * cfg->topk;
+  }
   e = cfg->gemm_impl == MOE_GEMM_TCGEN05 ? moe::launch_gemm_tc(a, stream, &launches, &driver_error)
                                          : moe::launch_gemm_simt(a, stream, &launches);
   if (driver_error) return MOE_ERR_DRIVER;
@@ -310,6 +320,7 @@ static int layer_forward_impl(const moe_config_t* cfg, const moe_weights_t* w, c
   a.as = nullptr;
   a.out = slots;
   a.row_dest = row_dest;
+  a.swiglu = moe::SwigluMode{};
   e = cfg->gemm_impl == MOE_GEMM_TCGEN05 ? moe::launch_gemm_tc(a, stream, &launches, &driver_error)
                                          : moe::launch_gemm_simt(a, stream, &launches);
   if (driver_error) return MOE_ERR_DRIVER;
@@ -317,7 +328,7 @@ static int layer_forward_impl(const moe_config_t* cfg, const moe_weights_t* w, c
 
   // 6. weighted combine in slot order, plus the shared expert's row
   mark(5, stream);
-  e = moe::launch_combine(slots, tw, tokens, cfg->topk, cfg->hidden, cfg->n_shared, static_cast<__nv_bfloat16*>(y_bf16),
+  e = moe::launch_combine(slots, cfg->weight_before_requant ? nullptr : tw, tokens, cfg->topk, cfg->hidden, cfg->n_shared, static_cast<__nv_bfloat16*>(y_bf16),
                           stream, &launches, residual);
   mark(6, stream);
   g_last_launches = launches;

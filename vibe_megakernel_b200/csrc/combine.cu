@@ -3,7 +3,8 @@
 //
 // Reference: megabench/tasks/frontier.py:349-354 (`output + down.float()*weights[slot]`, then the
 // shared expert) and the slot-order fp32 sum with one bf16 rounding of
-// megabench/tasks/megamoe.py:176-182. The down-projection rows are already stored in slot order
+// megabench/tasks/megamoe.py:176-182 (there the routing weight was applied before the down
+// projection: weights == NULL gives that plain sum). The down-projection rows are already stored in slot order
 // (row token*topk+slot), which is the reference's `slots[order] = output` un-permutation.
 // With a residual stream the block's output is x + bf16(sum), itself rounded to bf16
 // (`x = x + output.to(x.dtype)`, megabench/tasks/frontier.py:354).
@@ -26,7 +27,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __res
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
   for (int s = 0; s < topk; ++s) {
     const size_t row = static_cast<size_t>(t) * topk + s;
-    const float w = weights[row];
+    const float w = weights ? weights[row] : 1.f;   // null: the rows carry their weight already
     const uint4 raw = *reinterpret_cast<const uint4*>(slots + row * hidden + c);
     const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&raw);
 #pragma unroll

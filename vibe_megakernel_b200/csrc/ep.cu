@@ -265,7 +265,7 @@ int ep_check(const moe_config_t* c, int max_tokens) {
   if (!c) return MOE_ERR_BAD_ARG;
   const int rc = moe_workspace_layout(c, 1, nullptr);      // geometry checks shared with the one-GPU path
   if (rc != MOE_OK) return rc;
-  if (c->ep_world > 8) return MOE_ERR_UNSUPPORTED;
+  if (c->ep_world > 8 || c->weight_before_requant) return MOE_ERR_UNSUPPORTED;
   if (max_tokens < 1) return MOE_ERR_BAD_ARG;
   if (static_cast<int64_t>(c->ep_world) * max_tokens * c->topk > 32768) return MOE_ERR_UNSUPPORTED;
   return MOE_OK;
@@ -413,6 +413,7 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* 
   a.w_a = w->gate; a.w_a_scale = w->gate_scale; a.w_b = w->up; a.w_b_scale = w->up_scale;
   a.s_a = w->shared_gate; a.s_a_scale = w->shared_gate_scale; a.s_b = w->shared_up; a.s_b_scale = w->shared_up_scale;
   a.aq = ws + P.aq; a.as = reinterpret_cast<float*>(ws + P.as);
+  a.swiglu.limit = __bfloat162float(__float2bfloat16_rn(cfg->swiglu_limit));   // the clamp gives bf16 values
   e = cfg->gemm_impl == MOE_GEMM_TCGEN05 ? moe::launch_gemm_tc(a, stream, &launches, &driver_error)
                                          : moe::launch_gemm_simt(a, stream, &launches);
   if (driver_error) return MOE_ERR_DRIVER;
@@ -427,6 +428,7 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* 
   a.w_a = w->down; a.w_a_scale = w->down_scale; a.w_b = nullptr; a.w_b_scale = nullptr;
   a.s_a = w->shared_down; a.s_a_scale = w->shared_down_scale; a.s_b = nullptr; a.s_b_scale = nullptr;
   a.aq = nullptr; a.as = nullptr;
+  a.swiglu = moe::SwigluMode{};
   a.out = reinterpret_cast<__nv_bfloat16*>(ws + P.out);
   a.row_dest = nullptr;
   e = cfg->gemm_impl == MOE_GEMM_TCGEN05 ? moe::launch_gemm_tc(a, stream, &launches, &driver_error)

@@ -71,6 +71,7 @@ int moe_experts_forward(const moe_config_t* cfg, const moe_weights_t* w, const u
   ExpertsLayout L;
   const int rc = experts_layout(cfg, n_rows, &L);
   if (rc) return rc;
+  if (cfg->weight_before_requant) return MOE_ERR_UNSUPPORTED;   // the rows' routing weights are not known here
   if (!w || !rows_q || !rows_scale || !out_bf16 || !workspace) return MOE_ERR_BAD_ARG;
   const bool shared = local_ids == nullptr;
   if (shared ? (!cfg->n_shared || !w->shared_gate || !w->shared_gate_scale || !w->shared_up || !w->shared_up_scale ||
@@ -143,6 +144,7 @@ int moe_experts_forward(const moe_config_t* cfg, const moe_weights_t* w, const u
   a.s_a = w->shared_gate; a.s_a_scale = w->shared_gate_scale; a.s_b = w->shared_up; a.s_b_scale = w->shared_up_scale;
   if (shared) { a.n_local = 0; a.w_a = nullptr; a.w_b = nullptr; }
   a.aq = ws + L.aq; a.as = reinterpret_cast<float*>(ws + L.as);
+  a.swiglu.limit = __bfloat162float(__float2bfloat16_rn(cfg->swiglu_limit));   // the clamp gives bf16 values
   e = cfg->gemm_impl == MOE_GEMM_TCGEN05 ? moe::launch_gemm_tc(a, stream, &launches, &driver_error)
                                          : moe::launch_gemm_simt(a, stream, &launches);
   if (driver_error) return MOE_ERR_DRIVER;
@@ -157,6 +159,7 @@ int moe_experts_forward(const moe_config_t* cfg, const moe_weights_t* w, const u
   a.w_a = shared ? nullptr : w->down; a.w_a_scale = w->down_scale; a.w_b = nullptr; a.w_b_scale = nullptr;
   a.s_a = w->shared_down; a.s_a_scale = w->shared_down_scale; a.s_b = nullptr; a.s_b_scale = nullptr;
   a.aq = nullptr; a.as = nullptr;
+  a.swiglu = moe::SwigluMode{};
   a.out = static_cast<__nv_bfloat16*>(out_bf16);
   a.row_dest = g.row_dest;
   e = cfg->gemm_impl == MOE_GEMM_TCGEN05 ? moe::launch_gemm_tc(a, stream, &launches, &driver_error)

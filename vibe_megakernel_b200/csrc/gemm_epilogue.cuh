@@ -4,6 +4,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "kernels.h"
 
 namespace moe {
 
@@ -26,22 +27,30 @@ __device__ __forceinline__ bool epilogue_any(bool pred) {
 
 // SwiGLU on the bf16-rounded gate/up GEMM outputs, fp32 g/(1+exp(-g))*u, then per-token
 // requantisation of this tile's 128 channels (exactly one quantisation group).
-// Reference: megabench/tasks/megamoe.py:116-128 (without clamp and routing weight) and
-// megabench/tasks/quantization.py:87-109.
+// Reference: megabench/tasks/megamoe.py:116-128 (clamp and routing weight only when `mode` asks)
+// and megabench/tasks/quantization.py:87-109.
 //   s_amax: shared float[4][nt] scratch (one row per 32-channel quarter of the tile);
 //   m: 0..127, the thread's channel inside the tile; rows: valid tokens of the chunk.
 template <int CPT, int THREADS>
 __device__ __forceinline__ void epilogue_swiglu_requant(float (&gate)[CPT], const float (&up)[CPT], int m, int col0,
                                                         int nt, int rows, int row0, int tile_m, int inter,
                                                         float* s_amax, uint8_t* __restrict__ aq,
-                                                        float* __restrict__ as) {
+                                                        float* __restrict__ as, const SwigluMode& mode) {
   const int quarter = m >> 5, lane = m & 31;
 #pragma unroll
   for (int n = 0; n < CPT; ++n) {
     if (col0 + n < rows) {      // uniform across the warp
-      const float g = bf16_round(gate[n]);
-      const float u = bf16_round(up[n]);
-      const float a = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.f, expf(-g))), u);
+      float g = bf16_round(gate[n]);
+      float u = bf16_round(up[n]);
+      if (mode.limit > 0.f) {
+        g = fminf(g, mode.limit);
+        u = fminf(fmaxf(u, -mode.limit), mode.limit);
+      }
+      float a = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.f, expf(-g))), u);
+      if (mode.slot_weight) {
+        const int dest = mode.row_dest[row0 + col0 + n];
+        if (dest < mode.routed_rows) a = __fmul_rn(a, mode.slot_weight[dest]);
+      }
       gate[n] = a;
       const unsigned bits = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(a)));
       if (lane == 0) s_amax[quarter * nt + col0 + n] = __uint_as_float(bits);

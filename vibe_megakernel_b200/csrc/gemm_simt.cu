@@ -20,6 +20,7 @@ struct SimtDev {
   const uint8_t* s_b; const float* s_b_scale;
   uint8_t* aq; float* as;
   __nv_bfloat16* out; const int32_t* row_dest;
+  SwigluMode swiglu;
 };
 
 __device__ __forceinline__ void unpack16(const uint4& v, float* f) {
@@ -89,7 +90,7 @@ __global__ void __launch_bounds__(128) grouped_gemm_simt_kernel(const SimtDev p)
     }
   }
   if constexpr (DUAL) {
-    epilogue_swiglu_requant<NT, 128>(acc_a, acc_b, m, 0, NT, ch.rows, ch.row0, mt, p.m, s_amax, p.aq, p.as);
+    epilogue_swiglu_requant<NT, 128>(acc_a, acc_b, m, 0, NT, ch.rows, ch.row0, mt, p.m, s_amax, p.aq, p.as, p.swiglu);
   } else {
     epilogue_store_rows<NT>(acc_a, m, 0, ch.rows, ch.row0, mt, p.m, p.row_dest, p.out);
   }
@@ -98,7 +99,7 @@ __global__ void __launch_bounds__(128) grouped_gemm_simt_kernel(const SimtDev p)
 cudaError_t launch_gemm_simt(const GemmArgs& a, cudaStream_t stream, int* launches) {
   if (a.k % 128 || a.m % 128) return cudaErrorInvalidValue;
   SimtDev d{a.chunks, a.n_chunks, a.m / 128, a.k / 128, a.m, a.k, a.n_local, a.act, a.act_scale, a.w_a, a.w_a_scale,
-            a.w_b, a.w_b_scale, a.s_a, a.s_a_scale, a.s_b, a.s_b_scale, a.aq, a.as, a.out, a.row_dest};
+            a.w_b, a.w_b_scale, a.s_a, a.s_a_scale, a.s_b, a.s_b_scale, a.aq, a.as, a.out, a.row_dest, a.swiglu};
   const int grid = a.max_units > 0 ? a.max_units : 1;
 #define MOE_SIMT(NT, DUAL) grouped_gemm_simt_kernel<NT, DUAL><<<grid, 128, 0, stream>>>(d)
   if (a.dual) {

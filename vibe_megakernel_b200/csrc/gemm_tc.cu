@@ -158,6 +158,7 @@ struct GemmDev {
   int ksplit;              // down GEMM: parts the contraction is cut in (1 = whole)
   float* partial;          // ksplit > 1: fp32 [tile index][part][NT columns][128 channels]
   int32_t* parts_done;     // ksplit > 1: per (chunk, channel tile) count of finished parts, zero on entry
+  SwigluMode swiglu;       // DUAL: clamp and routing weight of the MegaMoE form, off by default
 };
 
 template <int NT, bool DUAL>
@@ -590,7 +591,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if (epilogue_any<C::kEpiThreads>(failed || *s_abort)) break;
       if constexpr (DUAL) {
         epilogue_swiglu_requant<C::kCpt, C::kEpiThreads>(acc_a, acc_b, m, col0, NT, rend, ch.row0, mt, p.m, s_amax,
-                                                         p.aq, p.as);
+                                                         p.aq, p.as, p.swiglu);
         // every thread's stores were fenced before the epilogue's closing barrier: announce the tile
         if (p.progress && epi == 0 && lane == 0) {
           __threadfence();
@@ -752,7 +753,7 @@ cudaError_t launch_gemm_tc(const GemmArgs& a, cudaStream_t stream, int* launches
   }
   GemmDev dev{a.chunks, a.n_chunks, a.m / 128, a.k / 128, a.m, a.n_local, 0, a.act_scale, a.w_a_scale, a.w_b_scale,
               a.s_a_scale, a.s_b_scale, a.aq, a.as, a.out, a.row_dest, a.status, a.progress, a.max_chunks,
-              a.tiles_before, 1, nullptr, nullptr};
+              a.tiles_before, 1, nullptr, nullptr, a.swiglu};
   if (!a.dual && a.ksplit > 1) {
     const int per = (a.k / 128 + a.ksplit - 1) / a.ksplit;
     if (!a.partial || !a.parts_done || (a.ksplit - 1) * per >= a.k / 128 || a.ksplit > 255) return cudaErrorInvalidValue;

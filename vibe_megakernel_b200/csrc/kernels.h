@@ -150,6 +150,17 @@ inline WorkListLayout work_list_layout(int max_chunks, int hidden, int inter, in
   return w;
 }
 
+// The two optional steps of the MegaMoE form of SwiGLU (megabench/tasks/megamoe.py:116-122):
+// gate clamped to at most `limit` and up to +-limit on the bf16 GEMM outputs (limit > 0), and the
+// fp32 product multiplied by the row's routing weight before requantisation (slot_weight != null;
+// a routed row's slot is row_dest[row] < routed_rows, the shared expert's rows keep weight 1).
+struct SwigluMode {
+  float limit = 0.f;
+  const float* slot_weight = nullptr;
+  const int32_t* row_dest = nullptr;
+  int routed_rows = 0;
+};
+
 struct GemmArgs {
   bool dual;                 // true: gate+up with SwiGLU + requantisation; false: down projection
   int tile;                  // tokens per MMA tile: 16, 32 or 64
@@ -188,6 +199,7 @@ struct GemmArgs {
   int ksplit;
   float* partial;
   int32_t* parts_done;
+  SwigluMode swiglu;         // dual only
 };
 cudaError_t launch_gemm_tc(const GemmArgs& a, cudaStream_t stream, int* launches, int* driver_error);
 cudaError_t launch_gemm_simt(const GemmArgs& a, cudaStream_t stream, int* launches);

@@ -4,8 +4,10 @@ Protocol: megabench/README.md:83-104 and megabench/harness/runner.py:69-87. ``ca
 harness' case dict; the layer geometry is read from ``case["params"]`` (integers, as the
 reference's Case admits) with the non-integer knobs in ``case["moe"]``:
 
-    params: hidden, intermediate, experts, topk, shared_experts, router_groups, router_top_groups
-    moe:    {"scoring": "sigmoid"|"softmax", "scaling": float}
+    params: hidden, intermediate, experts, topk, shared_experts, router_groups, router_top_groups,
+            swiglu_limit (the clamp of megabench/tasks/megamoe.py:43-44,116-122; absent or 0 = none)
+    moe:    {"scoring": "sigmoid"|"softmax"|"sqrt_softplus"|"softmax_biased", "scaling": float,
+             "weight_before_requant": bool (routing weight inside SwiGLU, megamoe.py:122,176-182)}
 
 ``run`` takes the tensors named in megabench/tasks/frontier.py:157-176 (without the layer prefix)
 and returns ``y`` (bf16 [T, H]), ``expert_ids`` (int64 [T, topk], choice order) and ``order``
@@ -29,7 +31,8 @@ def build(case: dict):
     config = LayerConfig(hidden=p["hidden"], inter=p["intermediate"], experts=p["experts"], topk=p["topk"],
                          shared=p.get("shared_experts", 0), scoring=extra.get("scoring", "sigmoid"),
                          n_group=p.get("router_groups", 1), topk_group=p.get("router_top_groups", 1),
-                         scaling=float(extra.get("scaling", 1.0)))
+                         scaling=float(extra.get("scaling", 1.0)), swiglu_limit=float(p.get("swiglu_limit", 0.0)),
+                         weight_before_requant=bool(extra.get("weight_before_requant", False)))
     if case.get("gpus", 1) != 1:
         raise NotImplementedError("expert-parallel execution is built through vibe_megakernel_b200.ep")
     layer = MoeLayer(config, max_tokens=p.get("tokens", p.get("batch", 1)))
