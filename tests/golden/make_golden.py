@@ -273,6 +273,46 @@ def megamoe_swiglu_vectors():
     np.savez_compressed(HERE / "megamoe_swiglu.npz", **out)
 
 
+def megamoe_native_vectors():
+    """MXFP4 packing (megabench/tasks/quantization.py:13-51) and the routed experts in their native
+    formats: ``megamoe.reference(case, values, serial=True)`` on two reductions of the reference's
+    development geometry (megabench/verify_megamoe.py:32-37)."""
+    from dataclasses import replace
+    from megabench.cases import select_cases
+    from megabench.tasks import megamoe
+    from megabench.verify_megamoe import development
+    out = {}
+    gen = torch.Generator().manual_seed(43)
+    m = torch.randn((24, 128), generator=gen) * torch.logspace(-3, 3, 24)[:, None]
+    # exact ties between neighbouring E2M1 magnitudes (the group's largest value is 6 * 2**k)
+    m[0, :9] = torch.tensor([6.0, 0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -2.5])
+    m[1, :9] = torch.tensor([6.0, 0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -2.5]) * 2.0 ** -9
+    m[2, :4] = torch.tensor([-6.0, -0.75, -1.75, -3.5])
+    m[3] = 0.0
+    m[4, 32:64] = 0.0
+    m[5, :2] = torch.tensor([6.0001, -5.9999])
+    out["mx_in"] = m.numpy()
+    blocks, scales = Q.pack_mxfp4(m)
+    out["mx_blocks"], out["mx_scales"] = blocks.numpy(), scales.numpy()
+    out["mx_back"] = Q.unpack_mxfp4(blocks, scales).numpy()
+    catalog = [case for case in select_cases("all") if case.family == "megamoe_layer"][0]
+    dev = replace(development(catalog, 1), ready=True)
+    cases = {      # the development geometry scaled down to keep the fixture small, and a ragged one
+        "dev": (replace(dev, params=dev.params | {"hidden": 128, "intermediate": 64}), 7),
+        "wide": (replace(dev, params=dev.params | {"tokens": 5, "experts": 12, "topk": 6, "hidden": 160,
+                                                   "intermediate": 96, "swiglu_limit": 3}), 11),
+    }
+    for name, (case, seed) in cases.items():
+        values = megamoe.make_inputs(case, seed, "cpu", rank=0)
+        for key, value in values.items():
+            out[f"{name}_{key}"] = u8(value) if value.dtype == torch.float8_e4m3fn else value.numpy()
+        out[f"{name}_y"] = bf16_bits(megamoe.reference(case, values, serial=True)["y"])
+        p = case.params
+        out[f"{name}_geo"] = np.array([p["tokens"], p["experts"], p["topk"], p["hidden"], p["intermediate"],
+                                       p["swiglu_limit"], seed], dtype=np.int64)
+    np.savez_compressed(HERE / "megamoe_native.npz", **out)
+
+
 def block_vectors():
     """RMSNorm -> layer -> residual add, as megabench/tasks/frontier.py:335-354 strings them together."""
     import dataclasses
@@ -306,5 +346,6 @@ if __name__ == "__main__":
     layer_vectors()
     block_vectors()
     megamoe_swiglu_vectors()
+    megamoe_native_vectors()
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size)

@@ -5,6 +5,7 @@ import dataclasses
 import numpy as np
 import torch
 
+from oracle import megamoe_oracle as M
 from oracle import moe_oracle as O
 from vibe_megakernel_b200 import synthetic
 
@@ -168,6 +169,38 @@ def test_megamoe_swiglu_form(golden_dir):
         got = O.moe_layer(spec, values)
         assert np.array_equal(got["expert_ids"].numpy(), g[f"{name}_ids"])
         assert np.array_equal(got["order"].numpy(), g[f"{name}_order"])
+        assert np.array_equal(got["y"].view(torch.int16).numpy(), g[f"{name}_y"])
+
+
+def test_mxfp4_packing(golden_dir):
+    # megabench/tasks/quantization.py:13-51; the vectors hold exact ties and all-zero groups
+    g = np.load(golden_dir / "megamoe_native.npz")
+    blocks, scales = M.pack_mxfp4(torch.from_numpy(g["mx_in"]))
+    assert np.array_equal(blocks.numpy(), g["mx_blocks"])
+    assert np.array_equal(scales.numpy(), g["mx_scales"])
+    back = M.unpack_mxfp4(torch.from_numpy(g["mx_blocks"]), torch.from_numpy(g["mx_scales"]))
+    assert np.array_equal(back.numpy(), g["mx_back"])
+    bad = torch.from_numpy(g["mx_scales"].copy())
+    bad[0, 0] = 255                                   # the E8M0 NaN encoding
+    assert torch.isnan(M.unpack_mxfp4(torch.from_numpy(g["mx_blocks"]), bad)[0, :32]).all()
+
+
+def megamoe_native_inputs(g, name):
+    keys = ("x", "x_scales", "topk_idx", "topk_weights", "l1_blocks", "l1_scales", "l2_blocks", "l2_scales")
+    values = {k: torch.from_numpy(g[f"{name}_{k}"].copy()) for k in keys}
+    values["x"] = values["x"].view(torch.float8_e4m3fn)
+    return values
+
+
+def test_megamoe_native_layer(golden_dir):
+    # megabench/tasks/megamoe.py:131-182 with serial=True, on inputs from its own make_inputs
+    g = np.load(golden_dir / "megamoe_native.npz")
+    for name in ("dev", "wide"):
+        tokens, experts, topk, hidden, inter, limit, _ = (int(v) for v in g[f"{name}_geo"])
+        values = megamoe_native_inputs(g, name)
+        assert values["l1_blocks"].shape == (experts, 2 * inter, hidden // 32, 16)
+        assert values["x_scales"].shape == (tokens, hidden // 32)
+        got = M.megamoe_layer(values, topk, float(limit))
         assert np.array_equal(got["y"].view(torch.int16).numpy(), g[f"{name}_y"])
 
 
