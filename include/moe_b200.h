@@ -151,6 +151,30 @@ int moe_quantize_rows(const void* x, int32_t dtype, int32_t rows, int32_t width,
 int moe_quantize_rows_ue8m0(const void* x, int32_t dtype, int32_t rows, int32_t width, int32_t block, uint8_t* q,
                             uint8_t* scales, void* stream);
 
+/* The routed experts in the MegaMoE-native formats: MXFP4 weights and E4M3 token rows, both with one
+ * E8M0 scale per 32 input channels; routing is an input. Replaces `megamoe.reference(case, values,
+ * serial=True)` (megabench/tasks/megamoe.py:131-182): rows grouped per expert in (token, slot) order,
+ * linear1 -> clamped SwiGLU times the routing weight -> E4M3/E8M0 requantisation -> linear2, then the
+ * fp32 slot-order sum rounded once to bf16. Device pointers, layouts as megamoe.make_inputs
+ * (megabench/tasks/megamoe.py:86-113). */
+typedef struct moe_mx_weights {
+  const uint8_t* l1_blocks;   /* [E, 2I, H/32, 16] E2M1 codes, low nibble = even channel; gate rows, then up rows */
+  const uint8_t* l1_scales;   /* [E, 2I, H/32] E8M0 */
+  const uint8_t* l2_blocks;   /* [E, H, I/32, 16] */
+  const uint8_t* l2_scales;   /* [E, H, I/32] */
+} moe_mx_weights_t;
+
+/* Uses cfg->hidden, inter (multiples of 128), n_experts, topk and swiglu_limit; n_shared must be 0 and
+ * ep_world 1. tokens * topk <= 32768. */
+int moe_mx_workspace(const moe_config_t* cfg, int32_t tokens, uint64_t* bytes);
+
+/* x_q e4m3 [tokens, H]; x_scales uint8 [tokens, H/32]; topk_idx int64 [tokens, topk] (distinct per
+ * token); topk_weights fp32 [tokens, topk]; y bf16 [tokens, H]; order (optional) int64 [tokens*topk].
+ * workspace: 256-byte aligned, moe_mx_workspace() bytes. Weight pointers 32-byte aligned. */
+int moe_mx_forward(const moe_config_t* cfg, const moe_mx_weights_t* w, const uint8_t* x_q, const uint8_t* x_scales,
+                   const int64_t* topk_idx, const float* topk_weights, int32_t tokens, void* y_bf16, int64_t* order,
+                   void* workspace, size_t workspace_bytes, void* stream);
+
 /* Stable grouping of `n` routed rows by expert id (the token->expert permutation).
  * Replaces `torch.sort(ids, stable=True)` + `bincount` (megabench/tasks/megamoe.py:137-138,161-165).
  * ids int64 [n]; rows whose id is outside [id_base, id_base + n_local) are dropped.

@@ -105,3 +105,21 @@ def assert_y_in_band(got: torch.Tensor, want: torch.Tensor, exact: torch.Tensor,
               f"max|y| {float(x.abs().max()):.3g}")
     assert ok, detail
     return detail
+
+
+def megamoe_inputs(tokens: int, experts: int, topk: int, hidden: int, inter: int, seed: int) -> dict:
+    """Seeded inputs in the formats of megabench/tasks/megamoe.py:86-113 (CPU tensors): E4M3 rows with
+    E8M0 scales per 32 channels, distinct experts per token, weights that sum to 2.5, MXFP4 expert
+    matrices with linear1 outputs of standard deviation 4 so that some reach the clamp."""
+    from oracle import megamoe_oracle as M
+    gen = torch.Generator().manual_seed(seed)
+    x, x_scales = O.quantize_activation(torch.randn((tokens, hidden), generator=gen), group=32, scale_format="e8m0")
+    idx = torch.rand((tokens, experts), generator=gen).topk(topk, dim=-1).indices
+    score = torch.nn.functional.softplus(torch.randn((tokens, topk), generator=gen)).sqrt()
+    weights = score / score.sum(-1, keepdim=True) * 2.5
+    l1 = torch.randn((experts, 2 * inter, hidden), generator=gen) * (4.0 / hidden ** 0.5)
+    l2 = torch.randn((experts, hidden, inter), generator=gen) * inter ** -0.5
+    l1_blocks, l1_scales = M.pack_mxfp4(l1)
+    l2_blocks, l2_scales = M.pack_mxfp4(l2)
+    return {"x": x, "x_scales": x_scales, "topk_idx": idx, "topk_weights": weights, "l1_blocks": l1_blocks,
+            "l1_scales": l1_scales, "l2_blocks": l2_blocks, "l2_scales": l2_scales}

@@ -1,0 +1,74 @@
+"""GPU parity of the routed experts in the MegaMoE-native formats (MXFP4 weights, E4M3 rows, E8M0
+scales per 32 channels) through the C ABI, against the oracle and the reference's vectors."""
+
+import pytest
+import torch
+
+from oracle import megamoe_oracle as M
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def api():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from vibe_megakernel_b200 import megamoe
+    return megamoe
+
+
+CASES = {
+    # tokens, experts, topk, hidden, inter, limit
+    "reference_development": (8, 16, 4, 256, 128, 10.0),       # megabench/verify_megamoe.py:32
+    "one_token": (1, 16, 4, 256, 128, 10.0),
+    "two_chunks_per_expert": (70, 8, 2, 512, 256, 10.0),       # 17.5 rows per expert on tiles of 32
+    "ragged_scale_rows": (200, 4, 2, 384, 640, 3.0),           # 3 and 5 K blocks: scale rows of 12 and 20 bytes; tiles of 64
+    "idle_experts": (3, 64, 2, 256, 256, 0.0),                 # most experts get no row; no clamp
+}
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_matches_the_oracle(api, name):
+    tokens, experts, topk, hidden, inter, limit = CASES[name]
+    values = H.megamoe_inputs(tokens, experts, topk, hidden, inter, seed=len(name))
+    want = M.megamoe_layer(values, topk, limit)
+    layer = api.MegaMoe(api.MegaMoeConfig(hidden, inter, experts, topk, limit), max_tokens=tokens)
+    device = H.to_device(values, "cuda")
+    before = {k: v.clone() for k, v in device.items()}
+    got = layer.run(device, check_status=True, want_order=True)
+    for k, v in device.items():
+        assert torch.equal(v.view(torch.uint8), before[k].view(torch.uint8)), f"input {k} was modified"
+    assert torch.equal(got["order"].cpu(), want["order"])
+    H.assert_y_close(got["y"], want["y"], name)
+    again = layer.run(device, check_status=True)
+    assert torch.equal(again["y"], got["y"])
+
+
+def test_depends_on_every_input(api):
+    tokens, experts, topk, hidden, inter, limit = CASES["reference_development"]
+    values = H.megamoe_inputs(tokens, experts, topk, hidden, inter, seed=5)
+    layer = api.MegaMoe(api.MegaMoeConfig(hidden, inter, experts, topk, limit), max_tokens=tokens)
+    base = layer.run(H.to_device(values, "cuda"), check_status=True)["y"]
+    # megabench/tests/test_megamoe.py:113-117
+    changes = {"x_scales": values["x_scales"] + 1, "l1_blocks": values["l1_blocks"] ^ 0x11,
+               "l2_scales": values["l2_scales"] - 1, "topk_weights": values["topk_weights"] * 0.5,
+               "topk_idx": (values["topk_idx"] + 1) % experts}
+    for key, changed in changes.items():
+        other = dict(values)
+        other[key] = changed
+        got = layer.run(H.to_device(other, "cuda"), check_status=True)["y"]
+        assert not torch.equal(got, base), key
+        H.assert_y_close(got, M.megamoe_layer(other, topk, limit)["y"], key)
+
+
+def test_bad_arguments_are_refused(api):
+    with pytest.raises(Exception):
+        api.MegaMoe(api.MegaMoeConfig(250, 128, 16, 4), max_tokens=4)        # hidden must be a multiple of 128
+    with pytest.raises(Exception):
+        api.MegaMoe(api.MegaMoeConfig(256, 128, 16, 4), max_tokens=10000)    # more than 32768 routed rows
+    layer = api.MegaMoe(api.MegaMoeConfig(256, 128, 16, 4), max_tokens=4)
+    values = H.to_device(H.megamoe_inputs(4, 16, 4, 256, 128, seed=1), "cuda")
+    values["x_scales"] = values["x_scales"].float()
+    with pytest.raises(TypeError):
+        layer.run(values)

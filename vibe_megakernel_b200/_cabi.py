@@ -35,6 +35,10 @@ LAYOUT_OFFSETS = ("total_bytes", "status", "logits", "topk_ids", "topk_weights",
                   "chunks", "row_token", "row_dest", "xq", "xs", "aq", "as_", "slots")
 
 
+class MxWeights(C.Structure):
+    _fields_ = [(name, C.c_void_p) for name in ("l1_blocks", "l1_scales", "l2_blocks", "l2_scales")]
+
+
 class Layout(C.Structure):
     _fields_ = [(name, C.c_uint64) for name in LAYOUT_OFFSETS] + [
         ("rows", C.c_int32), ("max_chunks", C.c_int32), ("token_tile", C.c_int32), ("reserved", C.c_int32)]
@@ -79,6 +83,9 @@ EXPORTS = {
     "moe_block_forward": (C.c_int, [C.POINTER(Config), C.POINTER(Weights), C.c_void_p, C.c_void_p, C.c_float, C.c_int32,
                                     C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                                     C.c_void_p]),
+    "moe_mx_workspace": (C.c_int, [C.POINTER(Config), C.c_int32, C.POINTER(C.c_uint64)]),
+    "moe_mx_forward": (C.c_int, [C.POINTER(Config), C.POINTER(MxWeights), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                 C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "moe_device_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]),
     "moe_last_launch_count": (C.c_int, []),
     "moe_profile_enable": (C.c_int, [C.c_int32]),

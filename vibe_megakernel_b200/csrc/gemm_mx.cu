@@ -1,0 +1,451 @@
+// Persistent grouped GEMM for the MegaMoE-native formats on tcgen05 block-scaled tensor cores.
+//
+//   D[m, n] = sum over 32-wide K blocks b of  2^(sw[m,b]-127) * 2^(sx[n,b]-127) * sum_k W[m,k] * X[n,k]
+//
+// W: MXFP4 weights (E2M1 codes, two per byte, one E8M0 scale per 32 input channels,
+// megabench/tasks/quantization.py:13-51); X: E4M3 token rows with one E8M0 scale per 32 channels
+// (megabench/tasks/megamoe.py:37,125-128). `tcgen05.mma.kind::mxf8f6f4.block_scale` applies both
+// scales inside the MMA (K = 32 per instruction = one scale block) and accumulates the whole
+// contraction in one fp32 TMEM accumulator, so the epilogue reads each tile once.
+//
+// Orientation as in the FP8 kernel: weights are the M side (128 output channels per tile), the
+// tokens of one expert the N side (16..NT columns). Weight tiles arrive by TMA with the
+// 16U4_ALIGN16B element type, which expands the packed 4-bit codes to the one-byte-per-value
+// layout the MMA reads from shared memory (HBM traffic stays 4 bits per weight).
+//
+// Scale factors live in TMEM next to the accumulators: per pipeline stage 4 columns for the gate
+// (or down) rows, 4 for the up rows, up to 2 for the tokens; row r of a tile sits in lane r % 32
+// (replicated in all four lane quarters), column r / 32, byte = 32-wide K block inside the
+// 128-wide stage. Four warps, one per lane quarter, load them from global memory and store them
+// with tcgen05.st.
+//
+// Roles: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2-5 = scale writers,
+// warps 6-9 = epilogue (a thread owns one output channel). Every wait is bounded: on expiry the
+// role records MOE_ERR_DEVICE_TIMEOUT, raises the CTA's abort flag and all roles fall through to
+// the common exit, which waits (bounded) for copies in flight and frees TMEM.
+//
+// Reference arithmetic: megabench/tasks/megamoe.py:131-150 (operands dequantised exactly to bf16,
+// fp32 accumulation, bf16 results), :116-128 (clamped SwiGLU with the routing weight, E4M3
+// requantisation with E8M0 scales per 32 channels).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace moe {
+
+constexpr int kMxMaxStages = 8;
+constexpr int kMxSmem = 232448;       // 227 KiB per CTA
+constexpr int kMxSfCols = 16;         // TMEM columns of scale factors per stage
+constexpr int kMxThreads = 320;
+
+template <int NT, bool DUAL>
+struct MxCfg {
+  static constexpr int kABytes = 128 * 128;     // one byte per value in shared memory
+  static constexpr int kATxBytes = 128 * 64;    // what a weight tile counts on the mbarrier: the packed bytes it read
+  static constexpr int kXBytes = NT * 128;
+  static constexpr int kStageBytes = (DUAL ? 2 : 1) * kABytes + kXBytes;
+  static constexpr int kAccCols = (DUAL ? 2 : 1) * NT;
+  static constexpr int kSfBase = 2 * kAccCols;  // two accumulator buffers, then the scale factors
+  static constexpr int kTailBytes = (2 * kMxMaxStages + 4) * 8 + 64;
+  static constexpr int kFit = (kMxSmem - 1024 - kTailBytes) / kStageBytes;
+  static constexpr int kStages = kFit < kMxMaxStages ? kFit : kMxMaxStages;
+  static_assert(kSfBase + kStages * kMxSfCols <= 512, "TMEM columns");
+};
+
+struct MxDev {
+  const Chunk* chunks;
+  const int32_t* n_chunks;
+  int tiles_m, kblocks, m;
+  int rows_per_expert;        // rows of the weight matrix one expert owns (2I for linear1, H for linear2)
+  int up_offset;              // DUAL: rows between a gate row and its up row (I)
+  const uint8_t* w_scales;    // [experts * rows_per_expert, K/32]
+  const uint8_t* x_scales;    // [rows, K/32]
+  uint8_t* aq;                // DUAL: e4m3 [rows, m]
+  uint8_t* as;                // DUAL: E8M0 [rows, m/32]
+  __nv_bfloat16* out;         // single: bf16 rows [*, m] at row_dest
+  const int32_t* row_dest;
+  const float* slot_weight;   // DUAL: routing weight of slot row_dest[row] (NULL = 1)
+  float limit;                // DUAL: clamp, 0 = none
+  int32_t* status;
+};
+
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st2(uint32_t taddr, uint32_t a, uint32_t b) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};" ::"r"(taddr), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Instruction descriptor, kind::mxf8f6f4 with block scales: A = E2M1, B = E4M3, both K-major,
+// E8M0 scales, M = 128; `sf` picks the byte (32-wide K block) of the scale columns for both sides.
+__device__ __forceinline__ uint32_t idesc_mx(int n, uint32_t sf) {
+  return (sf << 4) | (5u << 7) | (0u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (1u << 23) |
+         (static_cast<uint32_t>(128 >> 4) << 24) | (sf << 29);
+}
+__device__ __forceinline__ void mma_mx(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                       uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+      : "memory");
+}
+
+// Scale bytes of K blocks [4g, 4g+4) of one row: 16-byte load when the row length allows, else
+// up to four 4-byte loads (a 128-wide stage always has its four bytes).
+__device__ __forceinline__ void load_scale_group(const uint8_t* row, int g, int kblocks, bool vec, uint32_t (&v)[4]) {
+  if (vec) {
+    const uint4 t = __ldg(reinterpret_cast<const uint4*>(row) + g);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = 4 * g + j < kblocks ? __ldg(reinterpret_cast<const uint32_t*>(row) + 4 * g + j) : 0u;
+  }
+}
+
+template <int NT, bool DUAL>
+__global__ void __launch_bounds__(kMxThreads, 1)
+mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const MxDev p) {
+  using C = MxCfg<NT, DUAL>;
+  constexpr int S = C::kStages;
+  constexpr int XC = NT > 32 ? NT / 32 : 1;       // scale columns of the token side
+  extern __shared__ uint8_t smem_raw[];
+  const int KB = p.kblocks;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* stages = base;
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(base + S * C::kStageBytes);
+  uint64_t* bar_empty = bar_full + kMxMaxStages;
+  uint64_t* bar_tfull = bar_empty + kMxMaxStages;
+  uint64_t* bar_tempty = bar_tfull + 2;
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bar_tempty + 2);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  volatile uint32_t* s_issued = reinterpret_cast<volatile uint32_t*>(s_tmem + 2);    // K blocks whose TMA was issued
+  volatile uint32_t* s_consumed = reinterpret_cast<volatile uint32_t*>(s_tmem + 3);  // K blocks whose data arrived
+  volatile uint32_t* s_committed = reinterpret_cast<volatile uint32_t*>(s_tmem + 4); // accumulators committed
+  volatile uint32_t* s_drained = reinterpret_cast<volatile uint32_t*>(s_tmem + 5);   // accumulators read
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) { mbar_init(bar_full + s, 1 + 4); mbar_init(bar_empty + s, 1); }   // TMA + four scale warps
+    for (int s = 0; s < 2; ++s) { mbar_init(bar_tfull + s, 1); mbar_init(bar_tempty + s, 128); }
+    *s_abort = 0; *s_issued = 0; *s_consumed = 0; *s_committed = 0; *s_drained = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tmap(&tm_w); prefetch_tmap(&tm_x);
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+
+  dependent_wait();
+  dependents_may_launch();
+  const int n_units = *p.n_chunks * p.tiles_m;
+  const int first = blockIdx.x, stride = gridDim.x;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    const uint64_t pol_w = policy_evict_first();
+    const uint64_t pol_x = policy_evict_last();
+    uint32_t it = 0, s = 0, ph = 0;
+    bool ok = true;
+    for (int u = first; ok && u < n_units; u += stride) {
+      const Chunk ch = p.chunks[u / p.tiles_m];
+      const int mt = u % p.tiles_m;
+      const int wrow = ch.expert * p.rows_per_expert + mt * 128;
+      const int n16 = (ch.rows + 15) >> 4;
+      const uint32_t bytes = (DUAL ? 2 : 1) * C::kATxBytes + n16 * 2048;
+      for (int kb = 0; kb < KB; ++kb, ++it) {
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + s, ph ^ 1u, s_abort))) {
+          if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 21); *s_abort = 1; }
+          ok = false;
+          break;
+        }
+        uint8_t* st = stages + s * C::kStageBytes;
+        if (elect_one()) {
+          mbar_expect_tx(bar_full + s, bytes);
+          tma_load_2d(st, &tm_w, kb * 128, wrow, bar_full + s, pol_w);               // x in 4-bit elements
+          if constexpr (DUAL) tma_load_2d(st + C::kABytes, &tm_w, kb * 128, wrow + p.up_offset, bar_full + s, pol_w);
+          uint8_t* sx = st + (DUAL ? 2 : 1) * C::kABytes;
+          for (int j = 0; j < n16; ++j) tma_load_2d(sx + j * 2048, &tm_x, kb * 128, ch.row0 + j * 16, bar_full + s, pol_x);
+          *s_issued = it + 1;
+        }
+        __syncwarp();
+        if (++s == S) { s = 0; ph ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    uint32_t s = 0, ph = 0, item = 0, it = 0;
+    bool ok = true;
+    for (int u = first; ok && u < n_units; u += stride, ++item) {
+      const Chunk ch = p.chunks[u / p.tiles_m];
+      const int n = ((ch.rows + 15) >> 4) * 16;
+      const uint32_t ab = item & 1u, aph = (item >> 1) & 1u;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_tempty + ab, aph ^ 1u, s_abort))) {
+        if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 22); *s_abort = 1; }
+        break;
+      }
+      const uint32_t d0 = tmem + ab * C::kAccCols;
+      for (int kb = 0; kb < KB; ++kb, ++it) {
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_full + s, ph, s_abort))) {
+          if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 23); *s_abort = 1; }
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(stages + s * C::kStageBytes);
+        const uint32_t sx = sa + (DUAL ? 2 : 1) * C::kABytes;
+        const uint32_t sf = tmem + C::kSfBase + s * kMxSfCols;
+        if (elect_one()) {
+          *s_consumed = it + 1;
+#pragma unroll
+          for (uint32_t k4 = 0; k4 < 4; ++k4) {
+            const uint32_t idesc = idesc_mx(n, k4);
+            const uint32_t acc = (kb > 0 || k4 > 0) ? 1u : 0u;
+            const uint64_t xd = smem_desc_sw128(sx + k4 * 32);
+            mma_mx(d0, smem_desc_sw128(sa + k4 * 32), xd, idesc, sf, sf + 8, acc);
+            if constexpr (DUAL) mma_mx(d0 + NT, smem_desc_sw128(sa + C::kABytes + k4 * 32), xd, idesc, sf + 4, sf + 8, acc);
+          }
+          mma_commit(bar_empty + s);                 // stage and scale columns may be refilled once these MMAs are done
+          if (kb == KB - 1) { mma_commit(bar_tfull + ab); *s_committed = item + 1; }
+        }
+        __syncwarp();
+        if (++s == S) { s = 0; ph ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // ------------------------------ scale writers ------------------------------
+    // Warp w fills lane quarter w % 4; the four warps store the same values (the MMA wants the
+    // scale of tile row r in lane r % 32 of every quarter). The loads of the next four K blocks
+    // are in flight while the current four are stored.
+    const uint32_t quarter = warp & 3u;
+    const int KS = KB * 4;                         // scale bytes per row
+    const bool vec = (KS % 16) == 0;
+    const int groups = (KB + 3) / 4;
+    uint32_t s = 0, ph = 0;
+    bool ok = true;
+    for (int u = first; ok && u < n_units; u += stride) {
+      const Chunk ch = p.chunks[u / p.tiles_m];
+      const int mt = u % p.tiles_m;
+      const size_t wrow = static_cast<size_t>(ch.expert) * p.rows_per_expert + mt * 128 + lane;
+      const uint8_t* wa = p.w_scales + wrow * KS;
+      const uint8_t* xs = p.x_scales + static_cast<size_t>(ch.row0 + lane) * KS;
+      uint32_t a[4][4], b[4][4], x[XC][4];          // the group being stored
+      uint32_t na[4][4], nb[4][4], nx[XC][4];       // the next group, in flight
+      auto fetch = [&](int g, uint32_t (&fa)[4][4], uint32_t (&fb)[4][4], uint32_t (&fx)[XC][4]) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          load_scale_group(wa + static_cast<size_t>(32 * c) * KS, g, KB, vec, fa[c]);
+          if constexpr (DUAL) load_scale_group(wa + static_cast<size_t>(p.up_offset + 32 * c) * KS, g, KB, vec, fb[c]);
+        }
+#pragma unroll
+        for (int c = 0; c < XC; ++c) {
+          if (32 * c + lane < ch.rows) {
+            load_scale_group(xs + static_cast<size_t>(32 * c) * KS, g, KB, vec, fx[c]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) fx[c][j] = 0x7f7f7f7fu;   // columns past the chunk: scale 1, results unused
+          }
+        }
+      };
+      fetch(0, a, b, x);
+      for (int g = 0; ok && g < groups; ++g) {
+        if (g + 1 < groups) fetch(g + 1, na, nb, nx);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (4 * g + j >= KB) break;
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + s, ph ^ 1u, s_abort))) {
+            if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 24); *s_abort = 1; }
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t t = tmem + ((quarter * 32u) << 16) + C::kSfBase + s * kMxSfCols;
+          tmem_st4(t, a[0][j], a[1][j], a[2][j], a[3][j]);
+          if constexpr (DUAL) tmem_st4(t + 4, b[0][j], b[1][j], b[2][j], b[3][j]);
+          tmem_st2(t + 8, x[0][j], x[XC - 1][j]);
+          tmem_wait_st();
+          tc_fence_before();
+          if (lane == 0) mbar_arrive(bar_full + s);
+          __syncwarp();
+          if (++s == S) { s = 0; ph ^= 1u; }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            a[c][j] = na[c][j];
+            if constexpr (DUAL) b[c][j] = nb[c][j];
+            if (c < XC) x[c < XC ? c : 0][j] = nx[c < XC ? c : 0][j];
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue -----------------------------------
+    const uint32_t quarter = warp & 3u;
+    const int m = quarter * 32 + lane;             // channel inside the tile
+    uint32_t item = 0;
+    for (int u = first; u < n_units; u += stride, ++item) {
+      const Chunk ch = p.chunks[u / p.tiles_m];
+      const int mt = u % p.tiles_m;
+      const int n16 = (ch.rows + 15) >> 4;
+      const uint32_t ab = item & 1u, aph = (item >> 1) & 1u;
+      if (!mbar_wait(bar_tfull + ab, aph, s_abort)) {
+        if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 25); *s_abort = 1; }
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t = tmem + ((quarter * 32u) << 16) + ab * C::kAccCols;
+      for (int j = 0; j < n16; ++j) {
+        uint32_t g[16], v[16];
+        tmem_ld16(t + j * 16, g);
+        if constexpr (DUAL) tmem_ld16(t + NT + j * 16, v);
+        tmem_wait_ld();
+        if (j == n16 - 1) {                        // every column of this accumulator is in registers
+          tc_fence_before();
+          mbar_arrive(bar_tempty + ab);
+          if (threadIdx.x == 6 * 32) *s_drained = item + 1;
+        }
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const int col = j * 16 + c;
+          if (col >= ch.rows) break;               // uniform across the CTA
+          const size_t row = static_cast<size_t>(ch.row0 + col);
+          if constexpr (DUAL) {
+            // megabench/tasks/megamoe.py:116-122: bf16 GEMM outputs, clamp, fp32 SwiGLU, routing weight
+            float gate = bf16_round(__uint_as_float(g[c]));
+            float up = bf16_round(__uint_as_float(v[c]));
+            if (p.limit > 0.f) {
+              gate = fminf(gate, p.limit);
+              up = fminf(fmaxf(up, -p.limit), p.limit);
+            }
+            float act = __fmul_rn(__fdiv_rn(gate, __fadd_rn(1.f, expf(-gate))), up);
+            if (p.slot_weight) act = __fmul_rn(act, p.slot_weight[p.row_dest[row]]);
+            // megabench/tasks/quantization.py:62-84: the warp's 32 channels are one scale block
+            const unsigned bits = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(act)));
+            const int exponent = max((static_cast<int>(bits) + (0x7FFFFF - 0x600000)) >> 23, 105 + 8) - 8;
+            const float inverse = __int_as_float((254 - exponent) << 23);
+            p.aq[row * p.m + mt * 128 + m] =
+                static_cast<uint8_t>(__nv_cvt_float_to_fp8(__fmul_rn(act, inverse), __NV_SATFINITE, __NV_E4M3));
+            if (lane == 0) p.as[row * (p.m / 32) + mt * 4 + quarter] = static_cast<uint8_t>(exponent);
+          } else {
+            // one bf16 rounding of the fp32 sum (megabench/tasks/megamoe.py:149)
+            const size_t dest = static_cast<size_t>(p.row_dest ? p.row_dest[row] : static_cast<int>(row));
+            p.out[dest * p.m + mt * 128 + m] = __float2bfloat16_rn(__uint_as_float(g[c]));
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------ common exit ---------------------------------
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (*s_abort && threadIdx.x == 0) {
+    // Give copies and MMAs that were issued but never consumed a bounded chance to land.
+    for (uint32_t it = *s_consumed; it < *s_issued; ++it) mbar_wait(bar_full + it % S, (it / S) & 1u);
+    for (uint32_t it = *s_drained; it < *s_committed; ++it) mbar_wait(bar_tfull + (it & 1u), (it >> 1) & 1u);
+    // how far the roles of the first CTA that gave up had come (spare status words)
+    if (atomicCAS(p.status + 2, 0, 1 + static_cast<int>(blockIdx.x)) == 0) {
+      p.status[3] = *s_issued; p.status[4] = *s_consumed; p.status[5] = *s_committed; p.status[6] = *s_drained;
+      p.status[7] = DUAL ? 1 : 2;
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*MxEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static MxEncodeFn mx_encode_fn() {
+  static MxEncodeFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<MxEncodeFn>(sym);
+  }
+  return fn;
+}
+
+// [rows, k] values; packed 4-bit codes (k/2 bytes per row, box 128 x 128 values, expanded to one
+// byte per value in shared memory) or bytes (box 128 bytes x box_rows); 128-byte swizzle.
+static int mx_make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t k, bool four_bit, uint32_t box_rows) {
+  MxEncodeFn fn = mx_encode_fn();
+  if (!fn) return -1;
+  const uint64_t row_bytes = four_bit ? k / 2 : k;
+  if (reinterpret_cast<uintptr_t>(ptr) & 31 || k % 128 || row_bytes % 32) return -2;
+  cuuint64_t dims[2] = {k, rows};
+  cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, four_bit ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                  const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+template <int NT, bool DUAL>
+static cudaError_t mx_launch_typed(const MxDev& dev, const CUtensorMap* maps, int grid, cudaStream_t stream) {
+  using C = MxCfg<NT, DUAL>;
+  static bool configured[64] = {};      // the attribute belongs to the device the call runs on
+  int device = 0;
+  cudaGetDevice(&device);
+  if (device < 0 || device >= 64 || !configured[device]) {
+    cudaError_t e = cudaFuncSetAttribute(mx_gemm_kernel<NT, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMxSmem);
+    if (e != cudaSuccess) return e;
+    if (device >= 0 && device < 64) configured[device] = true;
+  }
+  const int smem = 1024 + C::kStages * C::kStageBytes + C::kTailBytes;
+  return launch_dependent(mx_gemm_kernel<NT, DUAL>, dim3(grid), dim3(kMxThreads), smem, stream, maps[0], maps[1], dev);
+}
+
+cudaError_t launch_gemm_mx(const MxGemmArgs& a, cudaStream_t stream, int* launches, int* driver_error) {
+  if (a.k % 128 || a.m % 128 || a.n_experts < 1 || (a.tile != 16 && a.tile != 32 && a.tile != 64)) return cudaErrorInvalidValue;
+  const int rows_per_expert = a.dual ? 2 * a.m : a.m;
+  CUtensorMap maps[2];
+  int rc = mx_make_map(&maps[0], a.w_blocks, static_cast<uint64_t>(a.n_experts) * rows_per_expert, a.k, true, 128);
+  rc = rc ? rc : mx_make_map(&maps[1], a.act, a.total_rows, a.k, false, 16);      // token rows move in boxes of 16
+  if (rc) {
+    if (driver_error) *driver_error = rc;
+    return cudaErrorUnknown;
+  }
+  MxDev dev{a.chunks, a.n_chunks, a.m / 128, a.k / 128, a.m, rows_per_expert, a.dual ? a.m : 0, a.w_scales, a.act_scales,
+            a.aq, a.as, a.out, a.row_dest, a.slot_weight, a.limit, a.status};
+  int device = 0, sms = 148;
+  cudaGetDevice(&device);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  const int grid = max(1, min(sms, a.max_units));
+  cudaError_t e;
+  if (a.dual) {
+    e = a.tile == 16 ? mx_launch_typed<16, true>(dev, maps, grid, stream)
+      : a.tile == 32 ? mx_launch_typed<32, true>(dev, maps, grid, stream)
+                     : mx_launch_typed<64, true>(dev, maps, grid, stream);
+  } else {
+    e = a.tile == 16 ? mx_launch_typed<16, false>(dev, maps, grid, stream)
+      : a.tile == 32 ? mx_launch_typed<32, false>(dev, maps, grid, stream)
+                     : mx_launch_typed<64, false>(dev, maps, grid, stream);
+  }
+  if (launches) *launches += 1;
+  return e;
+}
+
+}  // namespace moe

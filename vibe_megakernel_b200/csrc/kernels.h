@@ -202,6 +202,35 @@ struct GemmArgs {
   SwigluMode swiglu;         // dual only
 };
 cudaError_t launch_gemm_tc(const GemmArgs& a, cudaStream_t stream, int* launches, int* driver_error);
+
+// Grouped GEMM in the MegaMoE-native formats (MXFP4 weights, E4M3 rows, E8M0 scales per 32 channels
+// on both sides), block-scaled tensor-core MMA. dual: linear1 ([E, 2m, k]: gate rows then up rows) with
+// clamped SwiGLU, routing weight and requantisation; else linear2 ([E, m, k]) into bf16 slot rows.
+struct MxGemmArgs {
+  bool dual;
+  int tile;                   // tokens per MMA tile: 16, 32 or 64
+  int k, m;                   // contraction length; output channels per expert (I for linear1, H for linear2)
+  int n_experts;
+  int total_rows;             // rows of the activation buffer
+  int max_units;              // upper bound of chunks * (m / 128)
+  const Chunk* chunks;
+  const int32_t* n_chunks;
+  const uint8_t* act;         // e4m3 [total_rows, k], grouped by expert
+  const uint8_t* act_scales;  // E8M0 [total_rows, k/32]
+  const uint8_t* w_blocks;    // packed E2M1, [n_experts * rows, k/2] bytes
+  const uint8_t* w_scales;    // E8M0 [n_experts * rows, k/32]
+  uint8_t* aq;                // dual: e4m3 [total_rows, m]
+  uint8_t* as;                // dual: E8M0 [total_rows, m/32]
+  __nv_bfloat16* out;         // single: bf16 rows [*, m] addressed through row_dest
+  const int32_t* row_dest;
+  const float* slot_weight;   // dual: routing weight of slot row_dest[row]; NULL = 1
+  float limit;                // dual: clamp of gate/up, 0 = none
+  int32_t* status;
+};
+cudaError_t launch_gemm_mx(const MxGemmArgs& a, cudaStream_t stream, int* launches, int* driver_error);
+// Grouped row r <- row row_token[r] of e4m3 [*, hidden] with its hidden/32 scale bytes.
+cudaError_t launch_gather_mx_rows(const uint8_t* x, const uint8_t* x_scales, const int32_t* row_token, int rows, int hidden,
+                                  uint8_t* xg, uint8_t* xgs, cudaStream_t stream, int* launches);
 cudaError_t launch_gemm_simt(const GemmArgs& a, cudaStream_t stream, int* launches);
 
 }  // namespace moe
