@@ -13,11 +13,12 @@
 // 16U4_ALIGN16B element type, which expands the packed 4-bit codes to the one-byte-per-value
 // layout the MMA reads from shared memory (HBM traffic stays 4 bits per weight).
 //
-// Scale factors live in TMEM next to the accumulators: per pipeline stage 4 columns for the gate
-// (or down) rows, 4 for the up rows, up to 2 for the tokens; row r of a tile sits in lane r % 32
-// (replicated in all four lane quarters), column r / 32, byte = 32-wide K block inside the
-// 128-wide stage. Four warps, one per lane quarter, load them from global memory and store them
-// with tcgen05.st.
+// Scale factors live in TMEM next to the accumulators: per 128-wide K block 4 columns for the
+// gate (or down) rows, 4 for the up rows, up to 2 for the tokens; row r of a tile sits in lane
+// r % 32 (replicated in all four lane quarters), column r / 32, byte = 32-wide K block inside the
+// 128-wide one. Four warps, one per lane quarter, bring them from global memory through a ring in
+// shared memory (cp.async, several groups of four K blocks ahead) and store them with tcgen05.st,
+// a group at a time.
 //
 // Roles: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2-5 = scale writers,
 // warps 6-9 = epilogue (a thread owns one output channel). Every wait is bounded: on expiry the
@@ -32,9 +33,14 @@
 
 namespace moe {
 
-constexpr int kMxMaxStages = 8;
+constexpr int kMxMaxStages = 12;
 constexpr int kMxSmem = 232448;       // 227 KiB per CTA
-constexpr int kMxSfCols = 16;         // TMEM columns of scale factors per stage
+constexpr int kMxSfCols = 16;         // TMEM columns of scale factors per K block of 128
+constexpr int kMxSfGroup = 4;         // K blocks whose scale factors are written and released together (16 bytes per row)
+constexpr int kMxSfSlots = 4;         // groups that fit in TMEM at a time
+constexpr int kMxSfAhead = 2;         // groups whose scale bytes are on their way to shared memory
+constexpr int kMxSfRing = kMxSfAhead + 2;   // + the group being read + the one a faster thread may already refill
+constexpr int kMxKPerStage = 2;       // K blocks per pipeline stage: one wait, one release per pair (divides kMxSfGroup)
 constexpr int kMxThreads = 320;
 
 template <int NT, bool DUAL>
@@ -42,13 +48,23 @@ struct MxCfg {
   static constexpr int kABytes = 128 * 128;     // one byte per value in shared memory
   static constexpr int kATxBytes = 128 * 64;    // what a weight tile counts on the mbarrier: the packed bytes it read
   static constexpr int kXBytes = NT * 128;
-  static constexpr int kStageBytes = (DUAL ? 2 : 1) * kABytes + kXBytes;
+  static constexpr int kSubBytes = (DUAL ? 2 : 1) * kABytes + kXBytes;   // one K block of a stage
+  static constexpr int kStageBytes = kMxKPerStage * kSubBytes;
   static constexpr int kAccCols = (DUAL ? 2 : 1) * NT;
-  static constexpr int kSfBase = 2 * kAccCols;  // two accumulator buffers, then the scale factors
-  static constexpr int kTailBytes = (2 * kMxMaxStages + 4) * 8 + 64;
-  static constexpr int kFit = (kMxSmem - 1024 - kTailBytes) / kStageBytes;
+  // MMAs into the same accumulator run one after the other (about 160 cycles each, measured,
+  // whatever N is), which with four K = 32 instructions per K block is slower than HBM delivers
+  // 4-bit weights. K block kb therefore adds into partial accumulator kb % kKSplit, independent
+  // chains the tensor pipe overlaps, and the epilogue adds the partials in index order.
+  static constexpr int kKSplit = NT == 16 ? 4 : NT == 32 ? (DUAL ? 2 : 4) : (DUAL ? 1 : 2);
+  static constexpr int kBufCols = kKSplit * kAccCols;
+  static constexpr int kSfBase = 2 * kBufCols;  // two accumulator buffers, then the scale factors
+  static constexpr int kTailBytes = (2 * kMxMaxStages + 4 + 2 * kMxSfSlots) * 8 + 64;
+  // a group's scale bytes in shared memory: 16 per tile row (gate/down, up), then 16 per token row
+  static constexpr int kSfXOffset = (DUAL ? 2 : 1) * 2048;
+  static constexpr int kSfSlotBytes = kSfXOffset + 1024;
+  static constexpr int kFit = (kMxSmem - 1024 - kTailBytes - kMxSfRing * kSfSlotBytes) / kStageBytes;
   static constexpr int kStages = kFit < kMxMaxStages ? kFit : kMxMaxStages;
-  static_assert(kSfBase + kStages * kMxSfCols <= 512, "TMEM columns");
+  static_assert(kSfBase + kMxSfSlots * kMxSfGroup * kMxSfCols <= 512, "TMEM columns");
 };
 
 struct MxDev {
@@ -76,7 +92,6 @@ __device__ __forceinline__ void tmem_st2(uint32_t taddr, uint32_t a, uint32_t b)
   asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};" ::"r"(taddr), "r"(a), "r"(b) : "memory");
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
 // Instruction descriptor, kind::mxf8f6f4 with block scales: A = E2M1, B = E4M3, both K-major,
 // E8M0 scales, M = 128; `sf` picks the byte (32-wide K block) of the scale columns for both sides.
 __device__ __forceinline__ uint32_t idesc_mx(int n, uint32_t sf) {
@@ -92,16 +107,32 @@ __device__ __forceinline__ void mma_mx(uint32_t tmem_d, uint64_t adesc, uint64_t
       : "memory");
 }
 
-// Scale bytes of K blocks [4g, 4g+4) of one row: 16-byte load when the row length allows, else
-// up to four 4-byte loads (a 128-wide stage always has its four bytes).
-__device__ __forceinline__ void load_scale_group(const uint8_t* row, int g, int kblocks, bool vec, uint32_t (&v)[4]) {
+// Scale bytes of K blocks [4g, 4g+4) of one row, asynchronously into 16 bytes of shared memory:
+// one 16-byte copy when the row length allows, else up to four 4-byte copies (a 128-wide K block
+// always has its four bytes); K blocks past the end read as zero.
+__device__ __forceinline__ void copy_scale_group(uint8_t* dst, const uint8_t* row, int g, int kblocks, bool vec) {
   if (vec) {
-    const uint4 t = __ldg(reinterpret_cast<const uint4*>(row) + g);
-    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(row + 16 * g) : "memory");
   } else {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = 4 * g + j < kblocks ? __ldg(reinterpret_cast<const uint32_t*>(row) + 4 * g + j) : 0u;
+    for (int j = 0; j < 4; ++j) {
+      if (4 * g + j < kblocks)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst + 4 * j)), "l"(row + 4 * (4 * g + j)) : "memory");
+      else
+        *reinterpret_cast<uint32_t*>(dst + 4 * j) = 0u;
+    }
   }
+}
+// Barrier over the 128 scale-writer threads that also returns the OR of `pred`: one exit decision
+// for all of them, and what each wrote to shared memory before it is visible to the others after.
+__device__ __forceinline__ bool scale_writers_any(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n.reg .pred p, q;\nsetp.ne.u32 p, %1, 0;\nbar.red.or.pred q, 1, 128, p;\nselp.u32 %0, 1, 0, q;\n}\n"
+      : "=r"(r)
+      : "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return r != 0;
 }
 
 template <int NT, bool DUAL>
@@ -114,11 +145,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   const int KB = p.kblocks;
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* stages = base;
-  uint64_t* bar_full = reinterpret_cast<uint64_t*>(base + S * C::kStageBytes);
+  uint8_t* sf_ring = base + S * C::kStageBytes;                       // [kMxSfRing][kSfSlotBytes]
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(sf_ring + kMxSfRing * C::kSfSlotBytes);
   uint64_t* bar_empty = bar_full + kMxMaxStages;
   uint64_t* bar_tfull = bar_empty + kMxMaxStages;
   uint64_t* bar_tempty = bar_tfull + 2;
-  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bar_tempty + 2);
+  uint64_t* bar_sffull = bar_tempty + 2;           // a group's scale factors are in TMEM
+  uint64_t* bar_sfempty = bar_sffull + kMxSfSlots; // the MMAs that read a group are done
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bar_sfempty + kMxSfSlots);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   volatile uint32_t* s_issued = reinterpret_cast<volatile uint32_t*>(s_tmem + 2);    // K blocks whose TMA was issued
   volatile uint32_t* s_consumed = reinterpret_cast<volatile uint32_t*>(s_tmem + 3);  // K blocks whose data arrived
@@ -127,8 +161,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < S; ++s) { mbar_init(bar_full + s, 1 + 4); mbar_init(bar_empty + s, 1); }   // TMA + four scale warps
+    for (int s = 0; s < S; ++s) { mbar_init(bar_full + s, 1); mbar_init(bar_empty + s, 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(bar_tfull + s, 1); mbar_init(bar_tempty + s, 128); }
+    for (int s = 0; s < kMxSfSlots; ++s) { mbar_init(bar_sffull + s, 4); mbar_init(bar_sfempty + s, 1); }   // four scale warps
     *s_abort = 0; *s_issued = 0; *s_consumed = 0; *s_committed = 0; *s_drained = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tmap(&tm_w); prefetch_tmap(&tm_x);
@@ -159,20 +194,24 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       const int mt = u % p.tiles_m;
       const int wrow = ch.expert * p.rows_per_expert + mt * 128;
       const int n16 = (ch.rows + 15) >> 4;
-      const uint32_t bytes = (DUAL ? 2 : 1) * C::kATxBytes + n16 * 2048;
-      for (int kb = 0; kb < KB; ++kb, ++it) {
+      const uint32_t bytes = (DUAL ? 2 : 1) * C::kATxBytes + n16 * 2048;      // per K block
+      for (int kb0 = 0; kb0 < KB; kb0 += kMxKPerStage, ++it) {
         if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + s, ph ^ 1u, s_abort))) {
           if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 21); *s_abort = 1; }
           ok = false;
           break;
         }
-        uint8_t* st = stages + s * C::kStageBytes;
+        const int nk = min(kMxKPerStage, KB - kb0);
         if (elect_one()) {
-          mbar_expect_tx(bar_full + s, bytes);
-          tma_load_2d(st, &tm_w, kb * 128, wrow, bar_full + s, pol_w);               // x in 4-bit elements
-          if constexpr (DUAL) tma_load_2d(st + C::kABytes, &tm_w, kb * 128, wrow + p.up_offset, bar_full + s, pol_w);
-          uint8_t* sx = st + (DUAL ? 2 : 1) * C::kABytes;
-          for (int j = 0; j < n16; ++j) tma_load_2d(sx + j * 2048, &tm_x, kb * 128, ch.row0 + j * 16, bar_full + s, pol_x);
+          mbar_expect_tx(bar_full + s, bytes * nk);
+          for (int kk = 0; kk < nk; ++kk) {
+            uint8_t* st = stages + s * C::kStageBytes + kk * C::kSubBytes;
+            const int kx = (kb0 + kk) * 128;
+            tma_load_2d(st, &tm_w, kx, wrow, bar_full + s, pol_w);               // x in 4-bit elements
+            if constexpr (DUAL) tma_load_2d(st + C::kABytes, &tm_w, kx, wrow + p.up_offset, bar_full + s, pol_w);
+            uint8_t* sx = st + (DUAL ? 2 : 1) * C::kABytes;
+            for (int j = 0; j < n16; ++j) tma_load_2d(sx + j * 2048, &tm_x, kx, ch.row0 + j * 16, bar_full + s, pol_x);
+          }
           *s_issued = it + 1;
         }
         __syncwarp();
@@ -182,7 +221,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
-    uint32_t s = 0, ph = 0, item = 0, it = 0;
+    uint32_t s = 0, ph = 0, item = 0, it = 0, gi = 0;      // gi: scale-factor groups so far
     bool ok = true;
     for (int u = first; ok && u < n_units; u += stride, ++item) {
       const Chunk ch = p.chunks[u / p.tiles_m];
@@ -192,103 +231,125 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 22); *s_abort = 1; }
         break;
       }
-      const uint32_t d0 = tmem + ab * C::kAccCols;
-      for (int kb = 0; kb < KB; ++kb, ++it) {
-        if (!__all_sync(0xffffffffu, mbar_wait(bar_full + s, ph, s_abort))) {
+      for (int kb0 = 0; kb0 < KB; kb0 += kMxKPerStage, ++it) {
+        // a stage's K blocks lie inside one scale-factor group (kMxKPerStage divides kMxSfGroup)
+        const uint32_t slot = gi % kMxSfSlots, in_group0 = kb0 % kMxSfGroup;
+        const int nk = min(kMxKPerStage, KB - kb0);
+        bool got = mbar_wait(bar_full + s, ph, s_abort);
+        if (in_group0 == 0) got = got && mbar_wait(bar_sffull + slot, (gi / kMxSfSlots) & 1u, s_abort);
+        if (!__all_sync(0xffffffffu, got)) {
           if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 23); *s_abort = 1; }
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t sa = smem_u32(stages + s * C::kStageBytes);
-        const uint32_t sx = sa + (DUAL ? 2 : 1) * C::kABytes;
-        const uint32_t sf = tmem + C::kSfBase + s * kMxSfCols;
+        const bool last = kb0 + nk == KB;
+        const bool group_done = in_group0 + nk == kMxSfGroup || last;
         if (elect_one()) {
           *s_consumed = it + 1;
+          for (int kk = 0; kk < nk; ++kk) {
+            const int kb = kb0 + kk;
+            const uint32_t d0 = tmem + ab * C::kBufCols + (kb % C::kKSplit) * C::kAccCols;
+            const uint32_t sa = smem_u32(stages + s * C::kStageBytes + kk * C::kSubBytes);
+            const uint32_t sx = sa + (DUAL ? 2 : 1) * C::kABytes;
+            const uint32_t sf = tmem + C::kSfBase + (slot * kMxSfGroup + in_group0 + kk) * kMxSfCols;
 #pragma unroll
-          for (uint32_t k4 = 0; k4 < 4; ++k4) {
-            const uint32_t idesc = idesc_mx(n, k4);
-            const uint32_t acc = (kb > 0 || k4 > 0) ? 1u : 0u;
-            const uint64_t xd = smem_desc_sw128(sx + k4 * 32);
-            mma_mx(d0, smem_desc_sw128(sa + k4 * 32), xd, idesc, sf, sf + 8, acc);
-            if constexpr (DUAL) mma_mx(d0 + NT, smem_desc_sw128(sa + C::kABytes + k4 * 32), xd, idesc, sf + 4, sf + 8, acc);
+            for (uint32_t k4 = 0; k4 < 4; ++k4) {
+              const uint32_t idesc = idesc_mx(n, k4);
+              const uint32_t acc = (kb >= C::kKSplit || k4 > 0) ? 1u : 0u;   // a partial's first MMA overwrites
+              const uint64_t xd = smem_desc_sw128(sx + k4 * 32);
+              mma_mx(d0, smem_desc_sw128(sa + k4 * 32), xd, idesc, sf, sf + 8, acc);
+              if constexpr (DUAL) mma_mx(d0 + NT, smem_desc_sw128(sa + C::kABytes + k4 * 32), xd, idesc, sf + 4, sf + 8, acc);
+            }
           }
-          mma_commit(bar_empty + s);                 // stage and scale columns may be refilled once these MMAs are done
-          if (kb == KB - 1) { mma_commit(bar_tfull + ab); *s_committed = item + 1; }
+          mma_commit(bar_empty + s);                 // the stage may be refilled once these MMAs are done
+          if (group_done) mma_commit(bar_sfempty + slot);   // and the group's scale columns rewritten
+          if (last) { mma_commit(bar_tfull + ab); *s_committed = item + 1; }
         }
         __syncwarp();
+        if (group_done) ++gi;
         if (++s == S) { s = 0; ph ^= 1u; }
       }
     }
     __syncwarp();
   } else if (warp < 6) {
     // ------------------------------ scale writers ------------------------------
-    // Warp w fills lane quarter w % 4; the four warps store the same values (the MMA wants the
-    // scale of tile row r in lane r % 32 of every quarter). The loads of the next four K blocks
-    // are in flight while the current four are stored.
+    // A group = four K blocks = 16 scale bytes per row. The 128 threads copy the groups to come
+    // into a ring in shared memory (cp.async, kMxSfAhead groups ahead across work items: thread t
+    // takes tile row t of the weights, of the up rows, and token row t), so that the latency of
+    // these small strided reads never meets the MMA. Then warp w fills lane quarter w % 4 of the
+    // group's TMEM columns; the four warps store the same values (the MMA wants the scale of tile
+    // row r in lane r % 32 of every quarter).
+    const int t = static_cast<int>(threadIdx.x) - 64;      // 0..127
     const uint32_t quarter = warp & 3u;
     const int KS = KB * 4;                         // scale bytes per row
     const bool vec = (KS % 16) == 0;
     const int groups = (KB + 3) / 4;
-    uint32_t s = 0, ph = 0;
-    bool ok = true;
-    for (int u = first; ok && u < n_units; u += stride) {
-      const Chunk ch = p.chunks[u / p.tiles_m];
-      const int mt = u % p.tiles_m;
-      const size_t wrow = static_cast<size_t>(ch.expert) * p.rows_per_expert + mt * 128 + lane;
-      const uint8_t* wa = p.w_scales + wrow * KS;
-      const uint8_t* xs = p.x_scales + static_cast<size_t>(ch.row0 + lane) * KS;
-      uint32_t a[4][4], b[4][4], x[XC][4];          // the group being stored
-      uint32_t na[4][4], nb[4][4], nx[XC][4];       // the next group, in flight
-      auto fetch = [&](int g, uint32_t (&fa)[4][4], uint32_t (&fb)[4][4], uint32_t (&fx)[XC][4]) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          load_scale_group(wa + static_cast<size_t>(32 * c) * KS, g, KB, vec, fa[c]);
-          if constexpr (DUAL) load_scale_group(wa + static_cast<size_t>(p.up_offset + 32 * c) * KS, g, KB, vec, fb[c]);
+    // the copies' own walk over (work item, group), kMxSfAhead groups ahead of the stores
+    int iu = first, ig = 0;
+    uint32_t issued = 0;
+    Chunk ich = iu < n_units ? p.chunks[iu / p.tiles_m] : Chunk{0, 0, 0, 0};
+    auto issue = [&]() {
+      if (iu < n_units) {
+        uint8_t* slot = sf_ring + (issued % kMxSfRing) * C::kSfSlotBytes;
+        const size_t wrow = static_cast<size_t>(ich.expert) * p.rows_per_expert + (iu % p.tiles_m) * 128 + t;
+        copy_scale_group(slot + t * 16, p.w_scales + wrow * KS, ig, KB, vec);
+        if constexpr (DUAL) copy_scale_group(slot + 2048 + t * 16, p.w_scales + (wrow + p.up_offset) * KS, ig, KB, vec);
+        if (t < NT) {
+          uint8_t* dst = slot + C::kSfXOffset + t * 16;
+          if (t < ich.rows) copy_scale_group(dst, p.x_scales + static_cast<size_t>(ich.row0 + t) * KS, ig, KB, vec);
+          else *reinterpret_cast<uint4*>(dst) = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);   // past the chunk: scale 1, results unused
         }
-#pragma unroll
-        for (int c = 0; c < XC; ++c) {
-          if (32 * c + lane < ch.rows) {
-            load_scale_group(xs + static_cast<size_t>(32 * c) * KS, g, KB, vec, fx[c]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) fx[c][j] = 0x7f7f7f7fu;   // columns past the chunk: scale 1, results unused
-          }
-        }
-      };
-      fetch(0, a, b, x);
-      for (int g = 0; ok && g < groups; ++g) {
-        if (g + 1 < groups) fetch(g + 1, na, nb, nx);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (4 * g + j >= KB) break;
-          if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + s, ph ^ 1u, s_abort))) {
-            if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 24); *s_abort = 1; }
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t t = tmem + ((quarter * 32u) << 16) + C::kSfBase + s * kMxSfCols;
-          tmem_st4(t, a[0][j], a[1][j], a[2][j], a[3][j]);
-          if constexpr (DUAL) tmem_st4(t + 4, b[0][j], b[1][j], b[2][j], b[3][j]);
-          tmem_st2(t + 8, x[0][j], x[XC - 1][j]);
-          tmem_wait_st();
-          tc_fence_before();
-          if (lane == 0) mbar_arrive(bar_full + s);
-          __syncwarp();
-          if (++s == S) { s = 0; ph ^= 1u; }
-        }
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            a[c][j] = na[c][j];
-            if constexpr (DUAL) b[c][j] = nb[c][j];
-            if (c < XC) x[c < XC ? c : 0][j] = nx[c < XC ? c : 0][j];
-          }
+        if (++ig == groups) {
+          ig = 0;
+          iu += stride;
+          if (iu < n_units) ich = p.chunks[iu / p.tiles_m];
         }
       }
+      asm volatile("cp.async.commit_group;" ::: "memory");   // an empty group past the end keeps the count uniform
+      ++issued;
+    };
+    for (int i = 0; i < kMxSfAhead; ++i) issue();
+    uint32_t gi = 0;                               // groups stored so far
+    bool ok = true;
+    for (int u = first; ok && u < n_units; u += stride) {
+      for (int g = 0; g < groups; ++g, ++gi) {
+        issue();
+        asm volatile("cp.async.wait_group %0;" ::"n"(kMxSfAhead) : "memory");   // this thread's copies of group gi have landed
+        const uint32_t slot = gi % kMxSfSlots;
+        const bool late = !mbar_wait(bar_sfempty + slot, ((gi / kMxSfSlots) & 1u) ^ 1u, s_abort);
+        if (scale_writers_any(late)) {
+          if (t == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 24); *s_abort = 1; }
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint8_t* src = sf_ring + (gi % kMxSfRing) * C::kSfSlotBytes;
+        uint4 a[4], b[4], x[XC];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          a[c] = *reinterpret_cast<const uint4*>(src + (32 * c + lane) * 16);
+          if constexpr (DUAL) b[c] = *reinterpret_cast<const uint4*>(src + 2048 + (32 * c + lane) * 16);
+        }
+#pragma unroll
+        for (int c = 0; c < XC; ++c) x[c] = *reinterpret_cast<const uint4*>(src + C::kSfXOffset + (32 * c + lane) * 16);
+        const uint32_t t0 = tmem + ((quarter * 32u) << 16) + C::kSfBase + slot * kMxSfGroup * kMxSfCols;
+#define MX_WORD(v, j) ((j) == 0 ? (v).x : (j) == 1 ? (v).y : (j) == 2 ? (v).z : (v).w)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {              // a ragged last group stores spare columns nobody reads
+          const uint32_t tj = t0 + j * kMxSfCols;
+          tmem_st4(tj, MX_WORD(a[0], j), MX_WORD(a[1], j), MX_WORD(a[2], j), MX_WORD(a[3], j));
+          if constexpr (DUAL) tmem_st4(tj + 4, MX_WORD(b[0], j), MX_WORD(b[1], j), MX_WORD(b[2], j), MX_WORD(b[3], j));
+          tmem_st2(tj + 8, MX_WORD(x[0], j), MX_WORD(x[XC - 1], j));
+        }
+#undef MX_WORD
+        tmem_wait_st();
+        tc_fence_before();
+        if (lane == 0) mbar_arrive(bar_sffull + slot);
+        __syncwarp();
+      }
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");
   } else {
     // ------------------------------ epilogue -----------------------------------
     const uint32_t quarter = warp & 3u;
@@ -304,12 +365,24 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         break;
       }
       tc_fence_after();
-      const uint32_t t = tmem + ((quarter * 32u) << 16) + ab * C::kAccCols;
+      const uint32_t t = tmem + ((quarter * 32u) << 16) + ab * C::kBufCols;
+      const int parts = min(C::kKSplit, KB);       // partial accumulators that were written
       for (int j = 0; j < n16; ++j) {
         uint32_t g[16], v[16];
         tmem_ld16(t + j * 16, g);
         if constexpr (DUAL) tmem_ld16(t + NT + j * 16, v);
         tmem_wait_ld();
+        for (int part = 1; part < parts; ++part) {   // fp32 sum of the partials in index order
+          uint32_t pg[16], pv[16];
+          tmem_ld16(t + part * C::kAccCols + j * 16, pg);
+          if constexpr (DUAL) tmem_ld16(t + part * C::kAccCols + NT + j * 16, pv);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            g[c] = __float_as_uint(__fadd_rn(__uint_as_float(g[c]), __uint_as_float(pg[c])));
+            if constexpr (DUAL) v[c] = __float_as_uint(__fadd_rn(__uint_as_float(v[c]), __uint_as_float(pv[c])));
+          }
+        }
         if (j == n16 - 1) {                        // every column of this accumulator is in registers
           tc_fence_before();
           mbar_arrive(bar_tempty + ab);
@@ -414,7 +487,8 @@ static cudaError_t mx_launch_typed(const MxDev& dev, const CUtensorMap* maps, in
     if (e != cudaSuccess) return e;
     if (device >= 0 && device < 64) configured[device] = true;
   }
-  const int smem = 1024 + C::kStages * C::kStageBytes + C::kTailBytes;
+  constexpr int smem = 1024 + C::kStages * C::kStageBytes + kMxSfRing * C::kSfSlotBytes + C::kTailBytes;
+  static_assert(smem <= kMxSmem, "shared memory of one CTA");
   return launch_dependent(mx_gemm_kernel<NT, DUAL>, dim3(grid), dim3(kMxThreads), smem, stream, maps[0], maps[1], dev);
 }
 

@@ -76,7 +76,7 @@ cudaError_t launch_group_rows(const GroupArgs& a, cudaStream_t stream, int* laun
   if (a.n > kMaxGroupRows || a.n_local > MOE_MAX_EXPERTS) return cudaErrorInvalidValue;
   const int blocks = max(1, (a.n_local + kGroupWarps - 1) / kGroupWarps);
   const size_t smem = static_cast<size_t>(a.n > 0 ? a.n : 1) * sizeof(int16_t);
-  if (smem > 48 * 1024) {
+  if (smem > 32 * 1024) {      // with the kernel's static tables the default 48 KB would be exceeded
     cudaError_t e = cudaFuncSetAttribute(group_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
     if (e != cudaSuccess) return e;
   }
