@@ -51,12 +51,7 @@ struct MxCfg {
   static constexpr int kSubBytes = (DUAL ? 2 : 1) * kABytes + kXBytes;   // one K block of a stage
   static constexpr int kStageBytes = kMxKPerStage * kSubBytes;
   static constexpr int kAccCols = (DUAL ? 2 : 1) * NT;
-  // MMAs into the same accumulator run one after the other (about 160 cycles each, measured,
-  // whatever N is), which with four K = 32 instructions per K block is slower than HBM delivers
-  // 4-bit weights. K block kb therefore adds into partial accumulator kb % kKSplit, independent
-  // chains the tensor pipe overlaps, and the epilogue adds the partials in index order.
-  static constexpr int kKSplit = NT == 16 ? 4 : NT == 32 ? (DUAL ? 2 : 4) : (DUAL ? 1 : 2);
-  static constexpr int kBufCols = kKSplit * kAccCols;
+  static constexpr int kBufCols = kAccCols;
   static constexpr int kSfBase = 2 * kBufCols;  // two accumulator buffers, then the scale factors
   static constexpr int kTailBytes = (2 * kMxMaxStages + 4 + 2 * kMxSfSlots) * 8 + 64;
   // a group's scale bytes in shared memory: 16 per tile row (gate/down, up), then 16 per token row
@@ -249,14 +244,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           *s_consumed = it + 1;
           for (int kk = 0; kk < nk; ++kk) {
             const int kb = kb0 + kk;
-            const uint32_t d0 = tmem + ab * C::kBufCols + (kb % C::kKSplit) * C::kAccCols;
+            const uint32_t d0 = tmem + ab * C::kBufCols;
             const uint32_t sa = smem_u32(stages + s * C::kStageBytes + kk * C::kSubBytes);
             const uint32_t sx = sa + (DUAL ? 2 : 1) * C::kABytes;
             const uint32_t sf = tmem + C::kSfBase + (slot * kMxSfGroup + in_group0 + kk) * kMxSfCols;
 #pragma unroll
             for (uint32_t k4 = 0; k4 < 4; ++k4) {
               const uint32_t idesc = idesc_mx(n, k4);
-              const uint32_t acc = (kb >= C::kKSplit || k4 > 0) ? 1u : 0u;   // a partial's first MMA overwrites
+              const uint32_t acc = (kb > 0 || k4 > 0) ? 1u : 0u;   // the item's first MMA overwrites
               const uint64_t xd = smem_desc_sw128(sx + k4 * 32);
               mma_mx(d0, smem_desc_sw128(sa + k4 * 32), xd, idesc, sf, sf + 8, acc);
               if constexpr (DUAL) mma_mx(d0 + NT, smem_desc_sw128(sa + C::kABytes + k4 * 32), xd, idesc, sf + 4, sf + 8, acc);
@@ -360,29 +355,28 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       const int mt = u % p.tiles_m;
       const int n16 = (ch.rows + 15) >> 4;
       const uint32_t ab = item & 1u, aph = (item >> 1) & 1u;
+      // Destination slot and routing weight of the chunk's rows, one row per lane (two rounds for
+      // 64 columns), fetched while the MMAs still run; the column loop reads them by shuffle.
+      int dest_of[XC];
+      float weight_of[XC];
+#pragma unroll
+      for (int c = 0; c < XC; ++c) {
+        const int col = 32 * c + lane;
+        const int row = ch.row0 + col;
+        dest_of[c] = col < ch.rows ? (p.row_dest ? p.row_dest[row] : row) : 0;
+        weight_of[c] = (DUAL && p.slot_weight && col < ch.rows) ? p.slot_weight[dest_of[c]] : 1.f;
+      }
       if (!mbar_wait(bar_tfull + ab, aph, s_abort)) {
         if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 25); *s_abort = 1; }
         break;
       }
       tc_fence_after();
       const uint32_t t = tmem + ((quarter * 32u) << 16) + ab * C::kBufCols;
-      const int parts = min(C::kKSplit, KB);       // partial accumulators that were written
       for (int j = 0; j < n16; ++j) {
         uint32_t g[16], v[16];
         tmem_ld16(t + j * 16, g);
         if constexpr (DUAL) tmem_ld16(t + NT + j * 16, v);
         tmem_wait_ld();
-        for (int part = 1; part < parts; ++part) {   // fp32 sum of the partials in index order
-          uint32_t pg[16], pv[16];
-          tmem_ld16(t + part * C::kAccCols + j * 16, pg);
-          if constexpr (DUAL) tmem_ld16(t + part * C::kAccCols + NT + j * 16, pv);
-          tmem_wait_ld();
-#pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            g[c] = __float_as_uint(__fadd_rn(__uint_as_float(g[c]), __uint_as_float(pg[c])));
-            if constexpr (DUAL) v[c] = __float_as_uint(__fadd_rn(__uint_as_float(v[c]), __uint_as_float(pv[c])));
-          }
-        }
         if (j == n16 - 1) {                        // every column of this accumulator is in registers
           tc_fence_before();
           mbar_arrive(bar_tempty + ab);
@@ -393,6 +387,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           const int col = j * 16 + c;
           if (col >= ch.rows) break;               // uniform across the CTA
           const size_t row = static_cast<size_t>(ch.row0 + col);
+          const bool upper = XC > 1 && col >= 32;
+          const int dest_here = __shfl_sync(0xffffffffu, upper ? dest_of[XC - 1] : dest_of[0], col & 31);
+          const float weight_here = __shfl_sync(0xffffffffu, upper ? weight_of[XC - 1] : weight_of[0], col & 31);
           if constexpr (DUAL) {
             // megabench/tasks/megamoe.py:116-122: bf16 GEMM outputs, clamp, fp32 SwiGLU, routing weight
             float gate = bf16_round(__uint_as_float(g[c]));
@@ -402,7 +399,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
               up = fminf(fmaxf(up, -p.limit), p.limit);
             }
             float act = __fmul_rn(__fdiv_rn(gate, __fadd_rn(1.f, expf(-gate))), up);
-            if (p.slot_weight) act = __fmul_rn(act, p.slot_weight[p.row_dest[row]]);
+            if (p.slot_weight) act = __fmul_rn(act, weight_here);
             // megabench/tasks/quantization.py:62-84: the warp's 32 channels are one scale block
             const unsigned bits = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(act)));
             const int exponent = max((static_cast<int>(bits) + (0x7FFFFF - 0x600000)) >> 23, 105 + 8) - 8;
@@ -412,8 +409,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             if (lane == 0) p.as[row * (p.m / 32) + mt * 4 + quarter] = static_cast<uint8_t>(exponent);
           } else {
             // one bf16 rounding of the fp32 sum (megabench/tasks/megamoe.py:149)
-            const size_t dest = static_cast<size_t>(p.row_dest ? p.row_dest[row] : static_cast<int>(row));
-            p.out[dest * p.m + mt * 128 + m] = __float2bfloat16_rn(__uint_as_float(g[c]));
+            p.out[static_cast<size_t>(dest_here) * p.m + mt * 128 + m] = __float2bfloat16_rn(__uint_as_float(g[c]));
           }
         }
       }
