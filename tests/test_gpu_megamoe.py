@@ -25,6 +25,7 @@ CASES = {
     "two_chunks_per_expert": (70, 8, 2, 512, 256, 10.0),       # 17.5 rows per expert on tiles of 32
     "ragged_scale_rows": (200, 4, 2, 384, 640, 3.0),           # 3 and 5 K blocks: scale rows of 12 and 20 bytes; tiles of 64
     "idle_experts": (3, 64, 2, 256, 256, 0.0),                 # most experts get no row; no clamp
+    "catalog_width": (3, 2, 2, 7168, 3072, 10.0),              # megabench/cases.py:384-385: 56 and 24 K blocks per row
 }
 
 
