@@ -170,7 +170,9 @@ int moe_mx_workspace(const moe_config_t* cfg, int32_t tokens, uint64_t* bytes);
 
 /* x_q e4m3 [tokens, H]; x_scales uint8 [tokens, H/32]; topk_idx int64 [tokens, topk] (distinct per
  * token); topk_weights fp32 [tokens, topk]; y bf16 [tokens, H]; order (optional) int64 [tokens*topk].
- * workspace: 256-byte aligned, moe_mx_workspace() bytes. Weight pointers 32-byte aligned. */
+ * workspace: 256-byte aligned, moe_mx_workspace() bytes. Block pointers 32-byte, scale pointers
+ * 16-byte aligned (MOE_ERR_BAD_ARG otherwise). Expert ids are taken as given: a row whose id is
+ * outside [0, E) is skipped and leaves its slot of the sum undefined. */
 int moe_mx_forward(const moe_config_t* cfg, const moe_mx_weights_t* w, const uint8_t* x_q, const uint8_t* x_scales,
                    const int64_t* topk_idx, const float* topk_weights, int32_t tokens, void* y_bf16, int64_t* order,
                    void* workspace, size_t workspace_bytes, void* stream);

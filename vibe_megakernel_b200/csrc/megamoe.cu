@@ -102,6 +102,10 @@ int moe_mx_forward(const moe_config_t* cfg, const moe_mx_weights_t* w, const uin
     return MOE_ERR_BAD_ARG;
   if (workspace_bytes < L.total) return MOE_ERR_WORKSPACE;
   if (reinterpret_cast<uintptr_t>(workspace) & 255 || reinterpret_cast<uintptr_t>(x_q) & 15) return MOE_ERR_BAD_ARG;
+  // the weight tiles move by TMA as packed 4-bit values (32-byte aligned base), the scale rows by 16-byte copies
+  if (reinterpret_cast<uintptr_t>(w->l1_blocks) & 31 || reinterpret_cast<uintptr_t>(w->l2_blocks) & 31 ||
+      reinterpret_cast<uintptr_t>(w->l1_scales) & 15 || reinterpret_cast<uintptr_t>(w->l2_scales) & 15)
+    return MOE_ERR_BAD_ARG;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   int32_t* status = reinterpret_cast<int32_t*>(ws + L.status);
