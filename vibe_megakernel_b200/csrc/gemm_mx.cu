@@ -87,6 +87,14 @@ __device__ __forceinline__ void tmem_st2(uint32_t taddr, uint32_t a, uint32_t b)
   asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};" ::"r"(taddr), "r"(a), "r"(b) : "memory");
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, int32_t x, int32_t y, int32_t z, uint64_t* bar,
+                                            uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%2, %3, %4}], [%5], %6;"
+      ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
 // Instruction descriptor, kind::mxf8f6f4 with block scales: A = E2M1, B = E4M3, both K-major,
 // E8M0 scales, M = 128; `sf` picks the byte (32-wide K block) of the scale columns for both sides.
 __device__ __forceinline__ uint32_t idesc_mx(int n, uint32_t sf) {
@@ -202,8 +210,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           for (int kk = 0; kk < nk; ++kk) {
             uint8_t* st = stages + s * C::kStageBytes + kk * C::kSubBytes;
             const int kx = (kb0 + kk) * 128;
-            tma_load_2d(st, &tm_w, kx, wrow, bar_full + s, pol_w);               // x in 4-bit elements
-            if constexpr (DUAL) tma_load_2d(st + C::kABytes, &tm_w, kx, wrow + p.up_offset, bar_full + s, pol_w);
+            if constexpr (DUAL) tma_load_3d(st, &tm_w, kx, mt * 128, 2 * ch.expert, bar_full + s, pol_w);   // gate tile, then up tile
+            else tma_load_2d(st, &tm_w, kx, wrow, bar_full + s, pol_w);                                      // x in 4-bit elements
             uint8_t* sx = st + (DUAL ? 2 : 1) * C::kABytes;
             for (int j = 0; j < n16; ++j) tma_load_2d(sx + j * 2048, &tm_x, kx, ch.row0 + j * 16, bar_full + s, pol_x);
           }
@@ -472,6 +480,23 @@ static int mx_make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+// linear1 weights [experts, 2 halves (gate, up), m rows, k values] as a 3-D map whose box takes the
+// same 128-row tile of both halves: one request of 16 KB instead of two of 8 KB (the number of
+// requests a CTA has in flight, not their size, limits what it can keep on its way from HBM).
+static int mx_make_pair_map(CUtensorMap* map, const void* ptr, uint64_t experts, uint64_t m, uint64_t k) {
+  MxEncodeFn fn = mx_encode_fn();
+  if (!fn) return -1;
+  if (reinterpret_cast<uintptr_t>(ptr) & 31 || k % 128 || (k / 2) % 32) return -2;
+  cuuint64_t dims[3] = {k, m, 2 * experts};
+  cuuint64_t strides[2] = {k / 2, m * (k / 2)};
+  cuuint32_t box[3] = {128, 128, 2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
 template <int NT, bool DUAL>
 static cudaError_t mx_launch_typed(const MxDev& dev, const CUtensorMap* maps, int grid, cudaStream_t stream) {
   using C = MxCfg<NT, DUAL>;
@@ -492,7 +517,8 @@ cudaError_t launch_gemm_mx(const MxGemmArgs& a, cudaStream_t stream, int* launch
   if (a.k % 128 || a.m % 128 || a.n_experts < 1 || (a.tile != 16 && a.tile != 32 && a.tile != 64)) return cudaErrorInvalidValue;
   const int rows_per_expert = a.dual ? 2 * a.m : a.m;
   CUtensorMap maps[2];
-  int rc = mx_make_map(&maps[0], a.w_blocks, static_cast<uint64_t>(a.n_experts) * rows_per_expert, a.k, true, 128);
+  int rc = a.dual ? mx_make_pair_map(&maps[0], a.w_blocks, a.n_experts, a.m, a.k)
+                  : mx_make_map(&maps[0], a.w_blocks, static_cast<uint64_t>(a.n_experts) * rows_per_expert, a.k, true, 128);
   rc = rc ? rc : mx_make_map(&maps[1], a.act, a.total_rows, a.k, false, 16);      // token rows move in boxes of 16
   if (rc) {
     if (driver_error) *driver_error = rc;
