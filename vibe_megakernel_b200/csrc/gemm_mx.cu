@@ -229,6 +229,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     for (int u = first; ok && u < n_units; u += stride, ++item) {
       const Chunk ch = p.chunks[u / p.tiles_m];
       const int n = ((ch.rows + 15) >> 4) * 16;
+      const uint32_t idesc4[4] = {idesc_mx(n, 0), idesc_mx(n, 1), idesc_mx(n, 2), idesc_mx(n, 3)};
       const uint32_t ab = item & 1u, aph = (item >> 1) & 1u;
       if (!__all_sync(0xffffffffu, mbar_wait(bar_tempty + ab, aph ^ 1u, s_abort))) {
         if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 22); *s_abort = 1; }
@@ -250,19 +251,23 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const bool group_done = in_group0 + nk == kMxSfGroup || last;
         if (elect_one()) {
           *s_consumed = it + 1;
-          for (int kk = 0; kk < nk; ++kk) {
-            const int kb = kb0 + kk;
-            const uint32_t d0 = tmem + ab * C::kBufCols;
-            const uint32_t sa = smem_u32(stages + s * C::kStageBytes + kk * C::kSubBytes);
-            const uint32_t sx = sa + (DUAL ? 2 : 1) * C::kABytes;
-            const uint32_t sf = tmem + C::kSfBase + (slot * kMxSfGroup + in_group0 + kk) * kMxSfCols;
+          // every operand descriptor of the stage is the first one plus a constant (the start
+          // address field counts 16-byte units and no sum leaves it)
+          const uint64_t desc0 = smem_desc_sw128(smem_u32(stages + s * C::kStageBytes));
+          const uint32_t d0 = tmem + ab * C::kBufCols;
+          const uint32_t sf0 = tmem + C::kSfBase + (slot * kMxSfGroup + in_group0) * kMxSfCols;
 #pragma unroll
-            for (uint32_t k4 = 0; k4 < 4; ++k4) {
-              const uint32_t idesc = idesc_mx(n, k4);
-              const uint32_t acc = (kb > 0 || k4 > 0) ? 1u : 0u;   // the item's first MMA overwrites
-              const uint64_t xd = smem_desc_sw128(sx + k4 * 32);
-              mma_mx(d0, smem_desc_sw128(sa + k4 * 32), xd, idesc, sf, sf + 8, acc);
-              if constexpr (DUAL) mma_mx(d0 + NT, smem_desc_sw128(sa + C::kABytes + k4 * 32), xd, idesc, sf + 4, sf + 8, acc);
+          for (int kk = 0; kk < kMxKPerStage; ++kk) {
+            if (kk < nk) {
+              const uint32_t sf = sf0 + kk * kMxSfCols;
+#pragma unroll
+              for (uint32_t k4 = 0; k4 < 4; ++k4) {
+                const uint32_t acc = (kb0 + kk > 0 || k4 > 0) ? 1u : 0u;   // the item's first MMA overwrites
+                const uint64_t ad = desc0 + ((kk * C::kSubBytes + k4 * 32) >> 4);
+                const uint64_t xd = ad + (((DUAL ? 2 : 1) * C::kABytes) >> 4);
+                mma_mx(d0, ad, xd, idesc4[k4], sf, sf + 8, acc);
+                if constexpr (DUAL) mma_mx(d0 + NT, ad + (C::kABytes >> 4), xd, idesc4[k4], sf + 4, sf + 8, acc);
+              }
             }
           }
           mma_commit(bar_empty + s);                 // the stage may be refilled once these MMAs are done
