@@ -378,15 +378,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           }
           tc_fence_after();
           const uint32_t sa = smem_u32(stages + s * C::kStageBytes);
-          const uint32_t sb = sa + (DUAL ? 2 : 1) * C::kABytes;
           const uint32_t d0 = tmem + as * C::kAccCols;
           if (elect_one()) {
             *s_consumed = it + 1;
 #pragma unroll
+            // every operand descriptor of the stage is the first one plus a constant (the start
+            // address field counts 16-byte units and no sum leaves it): fewer instructions for
+            // the one lane whose instruction stream feeds the tensor pipe
+            const uint64_t desc0 = smem_desc_sw128(sa);
             for (int k4 = 0; k4 < 4; ++k4) {
-              const uint64_t bd = smem_desc_sw128(sb + k4 * 32);
-              mma_f8(d0, smem_desc_sw128(sa + k4 * 32), bd, idesc, k4 > 0 ? 1u : 0u);
-              if constexpr (DUAL) mma_f8(d0 + NT, smem_desc_sw128(sa + C::kABytes + k4 * 32), bd, idesc, k4 > 0 ? 1u : 0u);
+              const uint64_t ad = desc0 + ((k4 * 32) >> 4);
+              const uint64_t bd = ad + (((DUAL ? 2 : 1) * C::kABytes) >> 4);
+              mma_f8(d0, ad, bd, idesc, k4 > 0 ? 1u : 0u);
+              if constexpr (DUAL) mma_f8(d0 + NT, ad + (C::kABytes >> 4), bd, idesc, k4 > 0 ? 1u : 0u);
             }
             mma_commit(bar_empty + s);     // the stage may be refilled once these MMAs have read it
             mma_commit(bar_tfull + as);    // the accumulator is complete
