@@ -64,6 +64,23 @@ def test_workspace_layout_and_argument_checks_need_no_gpu():
     assert lib.moe_layer_forward(C.byref(cfg), None, None, 64, None, None, None, None, None, 0, None) == -1
 
 
+def test_megamoe_native_argument_checks_need_no_gpu():
+    lib = _cabi.load()
+    need = C.c_uint64(0)
+    cfg = _cabi.Config(7168, 3072, 384, 6, 0, 0, 1, 1, 1.0, 1, 0, 0, 10.0, 1)       # megabench/cases.py:384-385
+    assert lib.moe_mx_workspace(C.byref(cfg), 512, C.byref(need)) == 0
+    rows = 512 * 6
+    assert need.value >= rows * (7168 + 3072) + 2 * rows * 7168                       # grouped rows, requantised rows, slot rows
+    assert lib.moe_mx_workspace(C.byref(cfg), 5462, C.byref(need)) == -2               # more than 32768 routed rows
+    for bad in (_cabi.Config(7168, 3000, 384, 6, 0, 0, 1, 1, 1.0, 1, 0, 0, 10.0, 1),   # intermediate not a multiple of 128
+                _cabi.Config(7168, 3072, 384, 6, 1, 0, 1, 1, 1.0, 1, 0, 0, 10.0, 1),   # no shared expert in this task
+                _cabi.Config(7168, 3072, 384, 6, 0, 0, 1, 1, 1.0, 2, 0, 0, 10.0, 1)):  # one rank only
+        assert lib.moe_mx_workspace(C.byref(bad), 8, C.byref(need)) == -2
+    assert lib.moe_mx_workspace(C.byref(_cabi.Config(7168, 3072, 384, 500, 0, 0, 1, 1, 1.0, 1, 0, 0, 10.0, 1)), 8,
+                                C.byref(need)) == -1                                   # topk above the expert count
+    assert lib.moe_mx_forward(C.byref(cfg), None, None, None, None, None, 8, None, None, None, 0, None) == -1
+
+
 def test_product_does_not_import_the_oracle():
     for path in (ROOT / "vibe_megakernel_b200").rglob("*.py"):
         assert "oracle" not in path.read_text().replace("the oracle", ""), path
