@@ -73,3 +73,32 @@ def test_bad_arguments_are_refused(api):
     values["x_scales"] = values["x_scales"].float()
     with pytest.raises(TypeError):
         layer.run(values)
+
+
+def test_call_can_be_captured_in_a_cuda_graph(api):
+    # no allocation and no synchronisation inside the call: a replay on other token rows and another
+    # routing (same buffers) gives the bits of a direct call
+    tokens, experts, topk, hidden, inter, limit = CASES["two_chunks_per_expert"]
+    values = H.megamoe_inputs(tokens, experts, topk, hidden, inter, seed=21)
+    other = dict(values)
+    for key in ("x", "x_scales", "topk_idx", "topk_weights"):
+        other[key] = H.megamoe_inputs(tokens, experts, topk, hidden, inter, seed=22)[key]
+    layer = api.MegaMoe(api.MegaMoeConfig(hidden, inter, experts, topk, limit), max_tokens=tokens)
+    want = layer.run(H.to_device(values, "cuda"), check_status=True)["y"].clone()
+    want_other = layer.run(H.to_device(other, "cuda"), check_status=True)["y"].clone()
+    assert not torch.equal(want, want_other)
+    dev = H.to_device(values, "cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        layer.run(dev)                           # warm-up on the capturing stream
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = layer.run(dev)["y"]
+    for inputs, expect in ((values, want), (other, want_other), (values, want)):
+        for key in ("x", "x_scales", "topk_idx", "topk_weights"):
+            dev[key].view(torch.uint8).copy_(inputs[key].view(torch.uint8))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, expect)
