@@ -716,7 +716,9 @@ static cudaError_t launch_typed(GemmDev dev, const CUtensorMap* maps, int grid, 
     if (e != cudaSuccess) return e;
     if (device >= 0 && device < 64) configured[device] = true;
   }
+  const int cap = dev.stages;           // the caller's cap, 0 = none
   dev.stages = C::stages_for(dev.kblocks);
+  if (cap > 0 && cap < dev.stages) dev.stages = cap;
   if (dev.stages < 2) return cudaErrorInvalidValue;
   const int smem = 1024 + dev.stages * C::kStageBytes + C::tail_bytes(dev.kblocks);
   return launch_dependent(grouped_gemm_kernel<NT, DUAL>, dim3(grid), dim3(C::kThreads), smem, stream, maps[0], maps[1],
@@ -755,7 +757,7 @@ cudaError_t launch_gemm_tc(const GemmArgs& a, cudaStream_t stream, int* launches
     if (driver_error) *driver_error = rc;
     return cudaErrorUnknown;
   }
-  GemmDev dev{a.chunks, a.n_chunks, a.m / 128, a.k / 128, a.m, a.n_local, 0, a.act_scale, a.w_a_scale, a.w_b_scale,
+  GemmDev dev{a.chunks, a.n_chunks, a.m / 128, a.k / 128, a.m, a.n_local, a.max_stages, a.act_scale, a.w_a_scale, a.w_b_scale,
               a.s_a_scale, a.s_b_scale, a.aq, a.as, a.out, a.row_dest, a.status, a.progress, a.max_chunks,
               a.tiles_before, 1, nullptr, nullptr, a.swiglu};
   if (!a.dual && a.ksplit > 1) {

@@ -200,6 +200,7 @@ struct GemmArgs {
   float* partial;
   int32_t* parts_done;
   SwigluMode swiglu;         // dual only
+  int max_stages;            // > 0: cap of the shared-memory ring, so that the CTAs of the call's two GEMMs fit on an SM together
 };
 cudaError_t launch_gemm_tc(const GemmArgs& a, cudaStream_t stream, int* launches, int* driver_error);
 
