@@ -326,6 +326,17 @@ def main_single(args) -> dict:
         "block_with_norm_and_residual_us": round(extra["block_us"], 2),
         "sweep": sweep,
     }
+    if not args.no_sweep:
+        # The routed experts in the MegaMoE-native formats (MXFP4 weights, E4M3 rows with E8M0 scales;
+        # megabench/cases.py:380-388, all 384 experts on this GPU) at decode batch sizes, as extra lines
+        # beside the headline: they do not enter `value`.
+        from vibe_megakernel_b200 import megamoe_bench
+        line["megamoe_native"] = []
+        for tokens in (1, 64):
+            m = megamoe_bench.measure(tokens, steps=max(5, args.steps // 2), warmup=3, seed=args.seed, device=dev, flush=flush)
+            line["megamoe_native"].append({"tokens": tokens, "latency_us": m["value"], "experts_hit": m["experts_hit"],
+                                           "algorithmic_bytes": m["algorithmic_bytes"],
+                                           "frac_of_measured_peak": m["roofline"]["frac"], "workload": m["config"]["workload"]})
     if not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
         per_step, scaled_us, what = cpu_oracle_sample(geo, values, args.sample_tokens, extra["distinct"], threads)

@@ -5,9 +5,9 @@
 Geometry: the reference's ``megamoe-layer-deepseek-v4-pro`` cases (megabench/cases.py:380-388: 384
 experts, top-6, hidden 7168, intermediate 3072), every expert on this GPU (its ``serial`` form).
 Inputs are seeded random codes in the right formats, made on the device: packed E2M1 weight bytes with
-E8M0 scales around 2^-6, E4M3 rows with scales around 1, routing drawn like the reference's ``route``
+E8M0 scales near 2^-7, E4M3 rows with scales near 2^-7, routing drawn like the reference's ``route``
 (log-normal expert popularity, Gumbel top-k, weights that sum to 2.5; megabench/tasks/megamoe.py:65-80).
-Timing: CUDA events around every call on the current stream, the L2 flushed before each step; prints
+Timing: CUDA events on the current stream for every call, the L2 flushed before each step; prints
 one JSON line with the median latency, the bytes of the experts that were hit, and the fraction of the
 measured copy bandwidth that they stand for.
 """
@@ -57,6 +57,50 @@ def measured_hbm_peak() -> tuple[float, str]:
     return 6650.0, "of fallback"
 
 
+def measure(tokens: int, experts: int = 384, topk: int = 6, hidden: int = 7168, inter: int = 3072, steps: int = 10,
+            warmup: int = 3, seed: int = 0, device=None, flush: torch.Tensor | None = None) -> dict:
+    """One measurement as a dict (the JSON line of ``main``)."""
+    device = torch.device(device if device is not None else "cuda:0")
+    values = make_inputs(tokens, experts, topk, hidden, inter, seed, device)
+    layer = MegaMoe(MegaMoeConfig(hidden, inter, experts, topk, 10.0), max_tokens=tokens, device=device)
+    if flush is None:
+        flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
+    for _ in range(warmup):
+        flush_l2(flush)
+        layer.run(values, check_status=True)
+    torch.cuda.synchronize(device)
+    times = []
+    for _ in range(steps):
+        flush_l2(flush)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        layer.run(values)
+        b.record()
+        torch.cuda.synchronize(device)
+        times.append(a.elapsed_time(b) * 1e3)
+    layer.run(values, check_status=True)
+    times.sort()
+    median = times[len(times) // 2]
+    hit = int(torch.unique(values["topk_idx"]).numel())
+    rows = tokens * topk
+    per_expert = 3 * hidden * inter // 2 + 3 * hidden * inter // 32       # codes + scales
+    algorithmic = hit * per_expert + rows * (hidden + hidden // 32) * 2 + rows * (inter + inter // 32) * 2
+    flops = 2.0 * rows * 3 * hidden * inter
+    peak, kind = measured_hbm_peak()
+    gbs = algorithmic / median / 1e3
+    return {
+        "metric": "MXFP4 MegaMoE routed experts latency", "value": round(median, 2), "unit": "us",
+        "min_us": round(times[0], 2), "steps": steps, "warmup": warmup,
+        "config": {"workload": f"megamoe-layer-deepseek-v4-pro shape, all experts on one GPU: T={tokens} "
+                               f"E={experts} top{topk} H={hidden} I={inter}",
+                   "l2": "flushed before every step", "data": "synthetic"},
+        "experts_hit": hit, "routed_rows": rows, "algorithmic_bytes": algorithmic,
+        "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4),
+                     "peak_kind": kind},
+        "tflops": round(flops / median / 1e6, 1), "dtype": "mxfp4 x e4m3 -> f32",
+    }
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=512)
@@ -68,45 +112,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--seed", type=int, default=0)
     args = ap.parse_args()
-    device = torch.device("cuda:0")
-    torch.cuda.set_device(device)
-    values = make_inputs(args.tokens, args.experts, args.topk, args.hidden, args.inter, args.seed, device)
-    layer = MegaMoe(MegaMoeConfig(args.hidden, args.inter, args.experts, args.topk, 10.0), max_tokens=args.tokens)
-    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
-    for _ in range(args.warmup):
-        flush_l2(flush)
-        layer.run(values, check_status=True)
-    torch.cuda.synchronize()
-    times = []
-    for _ in range(args.steps):
-        flush_l2(flush)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        layer.run(values)
-        b.record()
-        torch.cuda.synchronize()
-        times.append(a.elapsed_time(b) * 1e3)
-    layer.run(values, check_status=True)
-    times.sort()
-    median = times[len(times) // 2]
-    hit = int(torch.unique(values["topk_idx"]).numel())
-    rows = args.tokens * args.topk
-    per_expert = 3 * args.hidden * args.inter // 2 + 3 * args.hidden * args.inter // 32       # codes + scales
-    algorithmic = hit * per_expert + rows * (args.hidden + args.hidden // 32) * 2 + rows * (args.inter + args.inter // 32) * 2
-    flops = 2.0 * rows * 3 * args.hidden * args.inter
-    peak, kind = measured_hbm_peak()
-    gbs = algorithmic / median / 1e3
-    print(json.dumps({
-        "metric": "MXFP4 MegaMoE routed experts latency", "value": round(median, 2), "unit": "us",
-        "min_us": round(times[0], 2), "steps": args.steps, "warmup": args.warmup,
-        "config": {"workload": f"megamoe-layer-deepseek-v4-pro shape, all experts on one GPU: T={args.tokens} "
-                               f"E={args.experts} top{args.topk} H={args.hidden} I={args.inter}",
-                   "l2": "flushed before every step", "data": "synthetic"},
-        "experts_hit": hit, "routed_rows": rows, "algorithmic_bytes": algorithmic,
-        "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4),
-                     "peak_kind": kind},
-        "tflops": round(flops / median / 1e6, 1), "dtype": "mxfp4 x e4m3 -> f32",
-    }))
+    torch.cuda.set_device(0)
+    print(json.dumps(measure(args.tokens, args.experts, args.topk, args.hidden, args.inter, args.steps, args.warmup,
+                             args.seed)))
 
 
 if __name__ == "__main__":
