@@ -138,6 +138,17 @@ __device__ __forceinline__ bool scale_writers_any(bool pred) {
   return r != 0;
 }
 
+// The chunk of walk position u, or an empty one past the end: every role fetches the chunk of its
+// next item while it works on the current one, so that the load's latency is not paid per item.
+__device__ __forceinline__ Chunk chunk_at(const Chunk* chunks, int u, int tiles_m, int n_units) {
+  Chunk c{0, 0, 0, 0};
+  if (u < n_units) {
+    const int4 v = __ldg(reinterpret_cast<const int4*>(chunks + u / tiles_m));
+    c.expert = v.x; c.row0 = v.y; c.rows = v.z; c.pad = v.w;
+  }
+  return c;
+}
+
 template <int NT, bool DUAL>
 __global__ void __launch_bounds__(kMxThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const MxDev p) {
@@ -192,8 +203,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     const uint64_t pol_x = policy_evict_last();
     uint32_t it = 0, s = 0, ph = 0;
     bool ok = true;
+    Chunk ahead = chunk_at(p.chunks, first, p.tiles_m, n_units);
     for (int u = first; ok && u < n_units; u += stride) {
-      const Chunk ch = p.chunks[u / p.tiles_m];
+      const Chunk ch = ahead;
+      ahead = chunk_at(p.chunks, u + stride, p.tiles_m, n_units);
       const int mt = u % p.tiles_m;
       const int wrow = ch.expert * p.rows_per_expert + mt * 128;
       const int n16 = (ch.rows + 15) >> 4;
@@ -226,8 +239,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     // ------------------------------ MMA issuer --------------------------------
     uint32_t s = 0, ph = 0, item = 0, it = 0, gi = 0;      // gi: scale-factor groups so far
     bool ok = true;
+    Chunk ahead = chunk_at(p.chunks, first, p.tiles_m, n_units);
     for (int u = first; ok && u < n_units; u += stride, ++item) {
-      const Chunk ch = p.chunks[u / p.tiles_m];
+      const Chunk ch = ahead;
+      ahead = chunk_at(p.chunks, u + stride, p.tiles_m, n_units);
       const int n = ((ch.rows + 15) >> 4) * 16;
       const uint32_t idesc4[4] = {idesc_mx(n, 0), idesc_mx(n, 1), idesc_mx(n, 2), idesc_mx(n, 3)};
       const uint32_t ab = item & 1u, aph = (item >> 1) & 1u;
@@ -363,8 +378,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     const uint32_t quarter = warp & 3u;
     const int m = quarter * 32 + lane;             // channel inside the tile
     uint32_t item = 0;
+    Chunk ahead = chunk_at(p.chunks, first, p.tiles_m, n_units);
     for (int u = first; u < n_units; u += stride, ++item) {
-      const Chunk ch = p.chunks[u / p.tiles_m];
+      const Chunk ch = ahead;
+      ahead = chunk_at(p.chunks, u + stride, p.tiles_m, n_units);
       const int mt = u % p.tiles_m;
       const int n16 = (ch.rows + 15) >> 4;
       const uint32_t ab = item & 1u, aph = (item >> 1) & 1u;
