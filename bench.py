@@ -53,6 +53,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--experts", type=int, default=0, help="shrink the routed expert count (profiling captures only)")
     ap.add_argument("--sample-tokens", type=int, default=8, help="tokens per CPU-oracle step")
+    ap.add_argument("--expert-load", action="store_true",
+                    help="print the per-expert load of --config at --batch under the GPU router, and exit")
     return ap.parse_args()
 
 
@@ -130,7 +132,7 @@ def layer_case(geo, tokens: int) -> dict:
 def timed_steps(fn, steps: int, warmup: int, flush: torch.Tensor, barrier=None) -> list[float]:
     """Per-step device times in ms: L2 is flushed (a 512 MiB write, then read back) before every step,
     outside its events."""
-    from vibe_megakernel_b200.ep_bench import flush_l2
+    from bench_ep import flush_l2
     for _ in range(warmup):
         flush_l2(flush)
         fn()
@@ -233,7 +235,7 @@ def measure_batch(geo, values: dict, tokens: int, steps: int, warmup: int, flush
     layer.profile(True)
     stages = {k: 0.0 for k in MoeLayer.STAGES}
     reps = max(3, min(steps, 10))
-    from vibe_megakernel_b200.ep_bench import flush_l2
+    from bench_ep import flush_l2
     for _ in range(reps):
         flush_l2(flush)
         layer.forward(inputs)
@@ -330,7 +332,7 @@ def main_single(args) -> dict:
         # The routed experts in the MegaMoE-native formats (MXFP4 weights, E4M3 rows with E8M0 scales;
         # megabench/cases.py:380-388, all 384 experts on this GPU) at decode batch sizes, as extra lines
         # beside the headline: they do not enter `value`.
-        from vibe_megakernel_b200 import megamoe_bench
+        import bench_megamoe as megamoe_bench
         line["megamoe_native"] = []
         for tokens in (1, 64):
             m = megamoe_bench.measure(tokens, steps=max(5, args.steps // 2), warmup=3, seed=args.seed, device=dev, flush=flush)
@@ -391,14 +393,48 @@ def main_reference(args) -> dict | None:
             "gpu_launches": 0}
 
 
+def expert_load(args) -> None:
+    """How many routed rows each expert receives at --batch (the library's router on cuda:0, whose ids
+    are those of the CPU oracle), and the rows each rank owns with the experts split over 2, 4 and 8."""
+    from vibe_megakernel_b200.layer import LayerConfig, MoeLayer
+    geo = geometry_of(args)
+    tokens, seed = args.batch, args.seed
+    x = synthetic.normal_rows(seed, "x", tokens, geo.hidden, 1.0, "cuda").to(torch.bfloat16)
+    router = synthetic.normal_rows(seed, "router", geo.experts, geo.hidden, geo.router_std, "cuda")
+    ids, _ = MoeLayer(LayerConfig.from_geometry(geo), max_tokens=tokens).route(x, router, synthetic.router_bias(geo, seed, "cuda"))
+    load = torch.bincount(ids.flatten().cpu(), minlength=geo.experts)
+    rows = tokens * geo.topk
+    mean = rows / geo.experts
+    print(f"{geo.name}, {tokens} tokens, seed {seed}: {rows} routed rows over {geo.experts} experts (mean {mean:.1f})")
+    print(f"  experts hit {int((load > 0).sum())}, hottest {int(load.max())} rows ({load.max() / mean:.1f}x mean), "
+          f"median {int(load.median())}, coldest {int(load.min())}")
+    top = torch.sort(load, descending=True).values
+    for share in (1, 5, 10, 25, 50):
+        k = max(1, geo.experts * share // 100)
+        print(f"  hottest {share:2d} % of the experts ({k:3d}) take {100 * int(top[:k].sum()) / rows:5.1f} % of the rows")
+    edges = [0, 1, 2, 4, 8, 16, 32, 64, 128, 256, 1 << 30]
+    for lo, hi in zip(edges[:-1], edges[1:]):
+        n = int(((load >= lo) & (load < hi)).sum())
+        if n:
+            print(f"  {lo:4d} <= rows < {hi if hi < (1 << 30) else 'inf':>4}: {n:3d} experts")
+    for world in (2, 4, 8):
+        if geo.experts % world == 0:
+            per = load.reshape(world, -1).sum(1).tolist()
+            hit = (load.reshape(world, -1) > 0).sum(1).tolist()
+            print(f"  {world} ranks: rows per rank {per}, experts hit per rank {hit}")
+
+
 def main():
     args = parse_args()
+    if args.expert_load:
+        expert_load(args)
+        return
     if args.impl == "reference":
         line = main_reference(args)
     elif args.gpus == 1:
         line = main_single(args)
     else:
-        from vibe_megakernel_b200 import ep_bench
+        import bench_ep as ep_bench
         peak, peak_kind = measured_peaks()
         line = ep_bench.run(args, geometry_of(args), METRIC, peak, peak_kind, ClockSampler)
     if line is not None:

@@ -20,10 +20,10 @@ import time
 import torch
 import torch.distributed as dist
 
-from . import synthetic
-from .ep import EpMoeLayer
-from .ep_collective import EpCollectiveLayer
-from .layer import LayerConfig
+from vibe_megakernel_b200 import synthetic
+from vibe_megakernel_b200.ep import EpMoeLayer
+from vibe_megakernel_b200.ep_collective import EpCollectiveLayer
+from vibe_megakernel_b200.layer import LayerConfig
 
 L2_FLUSH_BYTES = 512 << 20
 LAUNCHES_PER_CALL = 11   # router 2, dispatch, wait, group, gather, 2 GEMMs, return, wait, combine

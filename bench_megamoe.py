@@ -1,12 +1,10 @@
 """Latency of the routed experts in the MegaMoE-native formats on one GPU.
 
-    python -m vibe_megakernel_b200.megamoe_bench --tokens 512 --steps 10 --warmup 3
+    python bench_megamoe.py --tokens 512 --steps 10 --warmup 3
 
 Geometry: the reference's ``megamoe-layer-deepseek-v4-pro`` cases (megabench/cases.py:380-388: 384
 experts, top-6, hidden 7168, intermediate 3072), every expert on this GPU (its ``serial`` form).
-Inputs are seeded random codes in the right formats, made on the device: packed E2M1 weight bytes with
-E8M0 scales near 2^-7, E4M3 rows with scales near 2^-7, routing drawn like the reference's ``route``
-(log-normal expert popularity, Gumbel top-k, weights that sum to 2.5; megabench/tasks/megamoe.py:65-80).
+Inputs are seeded random codes in the right formats, made on the device (``synthetic.megamoe_inputs``).
 Timing: CUDA events on the current stream for every call, the L2 flushed before each step; prints
 one JSON line with the median latency, the bytes of the experts that were hit, and the fraction of the
 measured copy bandwidth that they stand for.
@@ -16,42 +14,21 @@ from __future__ import annotations
 
 import argparse
 import json
+import sys
 from pathlib import Path
 
 import torch
 
-from .ep_bench import L2_FLUSH_BYTES, flush_l2
-from .megamoe import MegaMoe, MegaMoeConfig
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
 
-
-def make_inputs(tokens: int, experts: int, topk: int, hidden: int, inter: int, seed: int, device) -> dict:
-    gen = torch.Generator(device=device).manual_seed(seed)
-    u8 = torch.uint8
-
-    def codes(*shape):
-        return torch.randint(0, 256, shape, dtype=u8, device=device, generator=gen)
-
-    def scales(center, *shape):
-        return torch.randint(center - 2, center + 3, shape, dtype=u8, device=device, generator=gen)
-
-    values = {}
-    x = (torch.randn((tokens, hidden), device=device, generator=gen) * 50.0).clamp(-448.0, 448.0)
-    values["x"] = x.to(torch.float8_e4m3fn)
-    values["x_scales"] = scales(120, tokens, hidden // 32)
-    popularity = 0.4 * torch.randn((experts,), device=device, generator=gen)
-    uniform = torch.rand((tokens, experts), device=device, generator=gen).clamp(1e-12, 1 - 1e-7)
-    values["topk_idx"] = (popularity - torch.log(-torch.log(uniform))).topk(topk, -1).indices
-    score = torch.nn.functional.softplus(torch.randn((tokens, topk), device=device, generator=gen)).sqrt()
-    values["topk_weights"] = score / score.sum(-1, keepdim=True) * 2.5
-    values["l1_blocks"] = codes(experts, 2 * inter, hidden // 32, 16)
-    values["l1_scales"] = scales(120, experts, 2 * inter, hidden // 32)
-    values["l2_blocks"] = codes(experts, hidden, inter // 32, 16)
-    values["l2_scales"] = scales(121, experts, hidden, inter // 32)
-    return values
+from bench_ep import L2_FLUSH_BYTES, flush_l2  # noqa: E402
+from vibe_megakernel_b200.megamoe import MegaMoe, MegaMoeConfig  # noqa: E402
+from vibe_megakernel_b200.synthetic import megamoe_inputs as make_inputs  # noqa: E402
 
 
 def measured_hbm_peak() -> tuple[float, str]:
-    path = Path(__file__).resolve().parent.parent / "MEASURED_PEAKS.json"
+    path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
         return float(json.loads(path.read_text())["hbm_gbs"]), "of measured"
     return 6650.0, "of fallback"

@@ -40,6 +40,10 @@ extern "C" {
 
 #define MOE_GEMM_TCGEN05 0 /* tcgen05 FP8 MMA, TMEM accumulators, TMA-fed (the product path) */
 #define MOE_GEMM_SIMT 1    /* plain CUDA-core check arm used by the tests to localise faults */
+/* CUDA-core check arm with the rounding schedule of megabench/tasks/megamoe.py:146-149: both operands
+ * dequantised and rounded to bf16, fp32 accumulation over the whole contraction, one bf16 rounding.
+ * It shows how much of the tensor-core path's distance to that reference is operand rounding. */
+#define MOE_GEMM_SIMT_BF16 2
 
 #define MOE_MAX_EXPERTS 512
 #define MOE_MAX_TOPK 16
@@ -113,7 +117,12 @@ typedef struct moe_workspace_layout {
 /* Scratch a call with `tokens` rows needs; fills *layout when it is not NULL. */
 int moe_workspace_layout(const moe_config_t* cfg, int32_t tokens, moe_workspace_layout_t* layout);
 
-/* Router: fp32 logits (fp64 accumulation) and top-k selection for `tokens` bf16 rows.
+/* Router: fp32 logits and top-k selection for `tokens` bf16 rows. A logit is summed with fp32 FMAs
+ * in 32 per-lane chains that are merged with error-free two-float additions and rounded once
+ * (absolute error about 1e-7 at the magnitudes of this layer); the result of a token does not
+ * depend on the batch it arrives in. The weight tensors (router, bias, expert matrices) must be
+ * complete before the stream operation that precedes a call: kernels fetch them before they
+ * wait for that predecessor.
  * Replaces `router.float() @ x.float()` + frontier.route (megabench/tasks/frontier.py:229-242,343)
  * and the stable softmax top-k of megabench/tasks/distributed.py:174-176.
  * expert_ids int64 [T, topk] in choice order; weights fp32 [T, topk]; either may be NULL.

@@ -32,7 +32,7 @@ def unpack_mxfp4(blocks: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     """
     assert blocks.dtype == torch.uint8 and scales.dtype == torch.uint8
     assert blocks.shape[:-1] == scales.shape and blocks.shape[-1] == MX_BLOCK // 2
-    table = torch.tensor(E2M1_MAGNITUDES + tuple(-m for m in E2M1_MAGNITUDES), dtype=torch.float32)
+    table = torch.tensor(E2M1_MAGNITUDES + tuple(-m for m in E2M1_MAGNITUDES), dtype=torch.float32, device=blocks.device)
     low, high = blocks & 15, blocks >> 4
     codes = torch.stack((low, high), dim=-1).reshape(*blocks.shape[:-1], MX_BLOCK)
     value = torch.ldexp(table[codes.long()], scales.to(torch.int32)[..., None] - 127)
@@ -89,7 +89,7 @@ def experts(values: dict, rows_q, rows_s, local_ids, weights, limit: float, *, k
     """
     n_local = values["l1_blocks"].shape[0]
     hidden = values["l2_blocks"].shape[1]
-    out = torch.empty((rows_q.shape[0], hidden), dtype=torch.bfloat16)
+    out = torch.empty((rows_q.shape[0], hidden), dtype=torch.bfloat16, device=rows_q.device)
     order, counts = O.expert_order(local_ids, n_local)
     start = 0
     for e, n in enumerate(counts.tolist()):
@@ -118,11 +118,11 @@ def megamoe_layer(values: dict, topk: int, limit: float, *, keep: dict | None = 
     tokens = values["x"].shape[0]
     flat = values["topk_idx"].reshape(-1)
     # one rank owns everything: the owner sort is the identity and rows arrive in (token, slot) order
-    source = torch.div(torch.arange(flat.numel()), topk, rounding_mode="floor")
+    source = torch.div(torch.arange(flat.numel(), device=flat.device), topk, rounding_mode="floor")
     out = experts(values, values["x"][source], values["x_scales"][source], flat,
                   values["topk_weights"].reshape(-1), limit, keep=keep)
     slots = out.reshape(tokens, topk, -1)
-    acc = torch.zeros((tokens, slots.shape[-1]), dtype=torch.float32)
+    acc = torch.zeros((tokens, slots.shape[-1]), dtype=torch.float32, device=slots.device)
     for s in range(topk):
         acc = acc + slots[:, s].to(torch.float32)
     return {"y": acc.to(torch.bfloat16), "order": O.expert_order(flat, values["l1_blocks"].shape[0])[0]}

@@ -259,31 +259,56 @@ def _silu_mul_clamped(gate: torch.Tensor, up: torch.Tensor, bound: float, weight
     return a if weights is None else a * weights[:, None]
 
 
+def fp8_linear(rows_q, rows_s, weight, weight_s, *, compute=torch.bfloat16, operands: str = "bf16") -> torch.Tensor:
+    """rows [n, K] (e4m3 + 1x128 fp32 scales) times an FP8 block-scaled matrix [M, K]: [n, M] in ``compute``.
+
+    The reference multiplies dequantised operands in two ways:
+      * ``operands="bf16"`` (megabench/tasks/megamoe.py:146-149, deepseek_checkpoint.py:457): both
+        operands are rounded to ``compute`` (bf16) first, the GEMM accumulates in fp32 and rounds
+        once to ``compute``. This is the graded "dequantize-then-bf16" path.
+      * ``operands="fp32"`` (megabench/tasks/frontier.py:184-186, ``linear``): the fp32 dequantised
+        operands are multiplied as they are and only the result is rounded to ``compute``. A
+        block-scaled tensor-core GEMM (exact FP8 products, fp32 scaling) is numerically this one.
+    With ``compute=torch.float32`` the two coincide (the widened noise-floor path, oracle.py:35-53).
+
+    The reference calls ``linear`` token by token (a matrix-vector product); on the CPU, for up to
+    64 rows, so does this function, which makes it bit-identical to the reference's vectors. Larger
+    or CUDA inputs use one matrix-matrix product: a different fp32 summation order, which moves
+    about one bf16 result in a thousand by one ulp.
+    """
+    xa = dequantize_activation(rows_q, rows_s)
+    wd = dequantize_weight(weight, weight_s)
+    if operands == "fp32":
+        if xa.device.type == "cpu" and xa.dim() == 2 and xa.shape[0] <= 64:
+            return torch.stack([wd @ row for row in xa]).to(compute) if xa.shape[0] else (xa @ wd.T).to(compute)
+        return (xa @ wd.T).to(compute)
+    if operands != "bf16":
+        raise ValueError(f"unknown operand convention {operands!r}")
+    return xa.to(compute) @ wd.to(compute).T
+
+
 def expert_mlp(rows_q, rows_s, gate, gate_s, up, up_s, down, down_s, *, compute=torch.bfloat16,
-               swiglu_limit: float = 0.0, row_weights: torch.Tensor | None = None):
+               swiglu_limit: float = 0.0, row_weights: torch.Tensor | None = None, operands: str = "bf16"):
     """One expert over its rows.
 
-    Operands are dequantised and rounded to ``compute`` (bf16 for the graded
-    path, fp32 for the widened noise-floor path), the GEMMs accumulate in
-    fp32 and round to ``compute``; SwiGLU is fp32; its result is requantised
-    per row per 128 channels. megabench/tasks/megamoe.py:146-149,125-128.
+    Each GEMM is ``fp8_linear`` (operand convention ``operands``, fp32 accumulation, result in
+    ``compute``: bf16 for the graded path, fp32 for the widened noise-floor path); SwiGLU is
+    fp32; its result is requantised per row per 128 channels.
+    megabench/tasks/megamoe.py:146-149,125-128.
     Returns (rows [n, H] in ``compute``, requantised payload, its scales).
     """
-    xa = dequantize_activation(rows_q, rows_s).to(compute)
-    wg = dequantize_weight(gate, gate_s).to(compute)
-    wu = dequantize_weight(up, up_s).to(compute)
-    wd = dequantize_weight(down, down_s).to(compute)
+    g = fp8_linear(rows_q, rows_s, gate, gate_s, compute=compute, operands=operands)
+    u = fp8_linear(rows_q, rows_s, up, up_s, compute=compute, operands=operands)
     if swiglu_limit > 0 or row_weights is not None:
-        a = _silu_mul_clamped(xa @ wg.T, xa @ wu.T, swiglu_limit, row_weights)
+        a = _silu_mul_clamped(g, u, swiglu_limit, row_weights)
     else:
-        a = _silu_mul(xa @ wg.T, xa @ wu.T)
+        a = _silu_mul(g, u)
     aq, a_s = quantize_activation(a)
-    back = dequantize_activation(aq, a_s).to(compute)
-    return back @ wd.T, aq, a_s
+    return fp8_linear(aq, a_s, down, down_s, compute=compute, operands=operands), aq, a_s
 
 
 def moe_layer(spec: LayerSpec, values: dict, *, compute=torch.bfloat16, keep_intermediates: bool = False,
-              expert_slot: dict | None = None):
+              expert_slot: dict | None = None, operands: str = "bf16"):
     """Whole layer on one rank holding every expert.
 
     values: x bf16 [T,H]; router fp32 [E,H]; router_bias fp32 [E] (sigmoid);
@@ -296,6 +321,7 @@ def moe_layer(spec: LayerSpec, values: dict, *, compute=torch.bfloat16, keep_int
     flattened ids by expert); counts int64 [E].
     ``expert_slot`` maps an expert id to its index in the weight tensors when only
     the experts that are hit were materialised (default: identity).
+    ``operands`` is the operand convention of every expert GEMM (see ``fp8_linear``).
     Combine: fp32 sum over slots in slot order of row*weight, then the shared
     expert's row, one rounding to bf16 (frontier.py:349-354, megamoe.py:176-182).
     """
@@ -319,7 +345,7 @@ def moe_layer(spec: LayerSpec, values: dict, *, compute=torch.bfloat16, keep_int
         res, aq, a_s = expert_mlp(xq[tok], xs[tok], values["gate"][k], values["gate_scale"][k],
                                   values["up"][k], values["up_scale"][k],
                                   values["down"][k], values["down_scale"][k], compute=compute,
-                                  swiglu_limit=spec.swiglu_limit,
+                                  swiglu_limit=spec.swiglu_limit, operands=operands,
                                   row_weights=ws.reshape(-1)[sel] if spec.weight_before_requant else None)
         out_rows[sel] = res
         if keep_intermediates:
@@ -335,7 +361,7 @@ def moe_layer(spec: LayerSpec, values: dict, *, compute=torch.bfloat16, keep_int
         sh, _, _ = expert_mlp(xq, xs, values["shared_gate"], values["shared_gate_scale"],
                               values["shared_up"], values["shared_up_scale"],
                               values["shared_down"], values["shared_down_scale"], compute=compute,
-                              swiglu_limit=spec.swiglu_limit)
+                              swiglu_limit=spec.swiglu_limit, operands=operands)
         acc = acc + sh.to(torch.float32)
     out = {"y": acc.to(torch.bfloat16), "expert_ids": ids, "topk_weights": ws,
            "order": order, "counts": counts}

@@ -153,10 +153,12 @@ def router_vectors():
     np.savez_compressed(HERE / "routers.npz", **out)
 
 
-def reference_layer(geo, values, *, widen=False, megamoe_swiglu=0.0):
+def reference_layer(geo, values, *, widen=False, megamoe_swiglu=0.0, fp32_operands=False):
     """The layer composed from reference primitives only. ``megamoe_swiglu`` > 0 switches to the
     MegaMoE form: ``megamoe.swiglu`` (clamp at that bound, routing weight inside, megamoe.py:116-122)
-    and an unweighted slot-order sum (megamoe.py:176-182); the shared expert's rows carry weight 1."""
+    and an unweighted slot-order sum (megamoe.py:176-182); the shared expert's rows carry weight 1.
+    ``fp32_operands`` replaces every expert GEMM by the expression of ``frontier.linear``
+    (frontier.py:184-186): fp32 dequantised operands, one rounding of the result to bf16."""
     from types import SimpleNamespace
     from megabench.tasks import megamoe
     case = SimpleNamespace(params={"swiglu_limit": megamoe_swiglu})
@@ -178,7 +180,17 @@ def reference_layer(geo, values, *, widen=False, megamoe_swiglu=0.0):
     counts = torch.bincount(flat, minlength=geo.experts).tolist()       # megamoe.py:138
     source = torch.div(order, geo.topk, rounding_mode="floor")          # megamoe.py:165
 
+    def linear_rows(rows, weight, scale):
+        # frontier.py:185-186, row by row as the reference calls it; `rows` may be fp32 (the SwiGLU output)
+        return torch.stack([(Q.unpack_fp8_weight(weight, scale) @ Q.unpack_fp8_activation(*Q.pack_fp8_activation(r))).to(bf16)
+                            for r in rows])
+
     def mlp(rows, gate, gs, up, us, down, ds, row_weights=None):
+        if fp32_operands:
+            g = torch.stack([frontier.linear(r, gate, gs, False) for r in rows])    # frontier.py:180-186
+            u = torch.stack([frontier.linear(r, up, us, False) for r in rows])
+            g32, u32 = g.float(), u.float()
+            return linear_rows(g32 / (1 + torch.exp(-g32)) * u32, down, ds)
         xa = Q.unpack_fp8_activation(*Q.pack_fp8_activation(rows)).to(bf16)      # megamoe.py:146
         g = xa @ Q.unpack_fp8_weight(gate, gs).to(bf16).T                      # megamoe.py:147,149
         u = xa @ Q.unpack_fp8_weight(up, us).to(bf16).T
@@ -243,6 +255,33 @@ def layer_vectors():
         out[f"{name}_geo"] = np.array([geo.hidden, geo.inter, geo.experts, geo.topk, geo.shared,
                                        geo.n_group, geo.topk_group, tokens, seed], dtype=np.int64)
     np.savez_compressed(HERE / "layers.npz", **out)
+
+
+def linear_vectors():
+    """``frontier.linear`` (fp32 dequantised operands, bf16 result; frontier.py:180-186) on its own and
+    as the GEMM of small layers: the second operand convention of the reference."""
+    import dataclasses
+    out = {}
+    gen = torch.Generator().manual_seed(61)
+    for name, m, k in (("a", 256, 512), ("b", 384, 1024), ("ragged", 137, 259)):
+        weight = torch.randn((m, k), generator=gen) * 0.02
+        wq, ws = Q.pack_fp8_weight(weight)
+        x = torch.randn((5, k), generator=gen).to(torch.bfloat16)
+        out[f"{name}_w"], out[f"{name}_ws"], out[f"{name}_x"] = u8(wq), ws.numpy(), bf16_bits(x)
+        out[f"{name}_y"] = bf16_bits(torch.stack([frontier.linear(r, wq, ws, False) for r in x]))
+    specs = {
+        "tiny": (synthetic.GEOMETRIES["tiny"], 4, 0),
+        "ds_small": (dataclasses.replace(synthetic.GEOMETRIES["deepseek_v3"], name="ds_small", hidden=512, inter=256,
+                                         experts=32, topk=4, n_group=4, topk_group=2), 6, 0),
+    }
+    for name, (geo, tokens, seed) in specs.items():
+        values = synthetic.make_inputs(geo, tokens, seed, "cpu")
+        got = reference_layer(geo, values, fp32_operands=True)
+        out[f"{name}_layer_y"] = bf16_bits(got["y"])
+        out[f"{name}_layer_ids"] = got["expert_ids"].numpy()
+        out[f"{name}_geo"] = np.array([geo.hidden, geo.inter, geo.experts, geo.topk, geo.shared,
+                                       geo.n_group, geo.topk_group, tokens, seed], dtype=np.int64)
+    np.savez_compressed(HERE / "linears.npz", **out)
 
 
 def megamoe_swiglu_vectors():
@@ -347,5 +386,6 @@ if __name__ == "__main__":
     block_vectors()
     megamoe_swiglu_vectors()
     megamoe_native_vectors()
+    linear_vectors()
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size)

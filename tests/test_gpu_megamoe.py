@@ -46,6 +46,44 @@ def test_matches_the_oracle(api, name):
     assert torch.equal(again["y"], got["y"])
 
 
+def test_a_row_with_an_expert_id_out_of_range_is_dropped(api):
+    # the header documents such a row as skipped: it must not be gathered (its source index was never
+    # written), the other tokens keep their bits, and the unused tail of `order` reads -1
+    tokens, experts, topk, hidden, inter, limit = CASES["reference_development"]
+    values = H.to_device(H.megamoe_inputs(tokens, experts, topk, hidden, inter, seed=9), "cuda")
+    layer = api.MegaMoe(api.MegaMoeConfig(hidden, inter, experts, topk, limit), max_tokens=tokens)
+    layer.workspace.zero_()                  # every index a kernel could read is then in range
+    base = layer.run(values, check_status=True, want_order=True)
+    bad = dict(values)
+    bad["topk_idx"] = values["topk_idx"].clone()
+    bad["topk_idx"][2, 1] = -1
+    bad["topk_idx"][5, 0] = experts
+    layer.workspace.zero_()
+    got = layer.run(bad, check_status=True, want_order=True)
+    others = [t for t in range(tokens) if t not in (2, 5)]
+    assert torch.equal(got["y"][others], base["y"][others])
+    flat = bad["topk_idx"].flatten().cpu()
+    kept = ((flat >= 0) & (flat < experts)).nonzero().flatten()
+    want_order = kept[torch.sort(flat[kept], stable=True).indices]
+    assert torch.equal(got["order"].cpu()[: kept.numel()], want_order)
+    assert got["order"].cpu()[kept.numel():].tolist() == [-1, -1]
+
+
+def test_catalog_geometry_matches_the_oracle(api):
+    # 384 experts, top-6, hidden 7168, intermediate 3072 (megabench/cases.py:380-388) at 64 tokens, every
+    # expert on this GPU; inputs are random codes made on the device and the oracle runs on CUDA tensors
+    from vibe_megakernel_b200 import synthetic
+    tokens, experts, topk, hidden, inter, limit = 64, 384, 6, 7168, 3072, 10.0
+    values = synthetic.megamoe_inputs(tokens, experts, topk, hidden, inter, 0, "cuda")
+    want = M.megamoe_layer(values, topk, limit)
+    layer = api.MegaMoe(api.MegaMoeConfig(hidden, inter, experts, topk, limit), max_tokens=tokens)
+    got = layer.run(values, check_status=True, want_order=True)
+    assert torch.equal(got["order"], want["order"])
+    max_abs, cos = H.assert_y_close(got["y"], want["y"], "catalog geometry")
+    print(f"MXFP4 catalog geometry, 64 tokens: max-abs {max_abs:.4g}, cosine {cos:.6f}, "
+          f"{int((got['y'] != want['y']).sum())} of {got['y'].numel()} values differ")
+
+
 def test_depends_on_every_input(api):
     tokens, experts, topk, hidden, inter, limit = CASES["reference_development"]
     values = H.megamoe_inputs(tokens, experts, topk, hidden, inter, seed=5)

@@ -145,6 +145,35 @@ def test_router_ties_go_to_the_lower_index(api):
     assert ids.cpu().tolist() == [[0, 1, 2]] * 3
 
 
+def test_router_near_ties_follow_the_exact_order_down_to_the_logit_error(api):
+    # Two experts whose logits differ by a chosen gap: expert 9's router row is expert 3's plus a
+    # multiple of one basis vector, so the gap is delta * x[k] exactly. The kernel's logit error is
+    # about 1e-7, so a gap of 1e-6 and more must be decided as exact arithmetic decides it; at an
+    # exact tie the lower index wins; below the error either of the two may come first, nothing else.
+    geo = dataclasses.replace(synthetic.GEOMETRIES["qwen3_30b_a3b"], name="near_tie", hidden=2048, experts=32, topk=2,
+                              router_std=0.01)
+    layer = api.MoeLayer(api.LayerConfig.from_geometry(geo), max_tokens=1)
+    gen = torch.Generator().manual_seed(17)
+    x = torch.randn((1, geo.hidden), generator=gen).to(torch.bfloat16)
+    k = int(x[0].float().abs().argmax())
+    base = torch.randn((geo.experts, geo.hidden), generator=gen) * geo.router_std
+    base[3] += 0.05 * x[0].float() / x[0].float().norm()       # experts 3 and 9 lead the field by a wide margin
+    base[3, k] = 0.0                                           # so that adding delta to this entry is exact
+    for gap in (1e-4, 1e-5, 1e-6, 0.0, -1e-6, -1e-5, 1e-9, -1e-9):
+        router = base.clone()
+        router[9] = router[3]
+        router[9, k] = float(gap) / float(x[0, k])
+        exact = (router.double() @ x[0].double())
+        true_gap = float(exact[9] - exact[3])
+        ids, _ = layer.route(x.cuda(), router.cuda(), None)
+        got = ids.cpu()[0].tolist()
+        assert sorted(got) == [3, 9], (gap, got)
+        if abs(true_gap) >= 5e-7:
+            assert got == ([9, 3] if true_gap > 0 else [3, 9]), (gap, true_gap, got)
+        elif true_gap == 0.0:
+            assert got == [3, 9], "an exact tie goes to the lower index"
+
+
 # ---------------------------------------------------------------- experts over quantised rows
 @pytest.mark.parametrize("name,n", [("ds_small", 23), ("kimi_small", 150), ("mixtral_small", 70)])
 def test_experts_entry_point_matches_the_oracle_and_the_layer(api, name, n):

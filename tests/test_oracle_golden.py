@@ -138,6 +138,28 @@ def test_layer_matches_reference_composition(golden_dir):
         assert np.array_equal(wide["y_fp32"].numpy(), g[f"{name}_y_fp32"])
 
 
+def test_fp32_operand_convention_matches_frontier_linear(golden_dir):
+    # the reference's second operand convention: megabench/tasks/frontier.py:180-186 (`linear`)
+    g = np.load(golden_dir / "linears.npz")
+    for name in ("a", "b", "ragged"):
+        w = torch.from_numpy(g[f"{name}_w"].copy()).view(torch.float8_e4m3fn)
+        ws = torch.from_numpy(g[f"{name}_ws"].copy())
+        x = bf16(g[f"{name}_x"])
+        xq, xs = O.quantize_activation(x)
+        got = O.fp8_linear(xq, xs, w, ws, operands="fp32")
+        assert np.array_equal(got.view(torch.int16).numpy(), g[f"{name}_y"]), name
+        # the other convention rounds the operands first and is a different function
+        other = O.fp8_linear(xq, xs, w, ws, operands="bf16")
+        assert not torch.equal(other, got), name
+    for name in ("tiny", "ds_small"):
+        geo = small_layers()[name]
+        tokens, seed = int(g[f"{name}_geo"][7]), int(g[f"{name}_geo"][8])
+        values = synthetic.make_inputs(geo, tokens, seed, "cpu")
+        got = O.moe_layer(spec_of(geo), values, operands="fp32")
+        assert np.array_equal(got["expert_ids"].numpy(), g[f"{name}_layer_ids"])
+        assert np.array_equal(got["y"].view(torch.int16).numpy(), g[f"{name}_layer_y"]), name
+
+
 def test_block_matches_reference_composition(golden_dir):
     # RMSNorm (megabench/tasks/common.py:13-21) -> layer -> residual add (megabench/tasks/frontier.py:335-354)
     g = np.load(golden_dir / "blocks.npz")

@@ -12,6 +12,7 @@ import ctypes as C
 import pytest
 import torch
 
+from oracle import moe_oracle as O
 from tests import helpers as H
 from vibe_megakernel_b200 import synthetic
 
@@ -31,22 +32,36 @@ def test_static_router_matches_the_workspace_router_twice_in_a_row(api, name, to
     geo = synthetic.GEOMETRIES[name]
     config = api.LayerConfig.from_geometry(geo)
     reference = api.MoeLayer(config, max_tokens=tokens)
-    for call, seed in enumerate((0, 1)):                      # two calls in a row, different inputs
-        x = synthetic.normal_rows(seed, "x", tokens, geo.hidden, 1.0, "cpu").to(torch.bfloat16).cuda()
-        router = synthetic.normal_rows(seed, "router", geo.experts, geo.hidden, geo.router_std, "cuda")
-        bias = synthetic.router_bias(geo, seed, "cuda")
+    first_seed = 0
+    for call in range(2):                                     # two calls in a row, different inputs
+        x_cpu, router_cpu, bias_cpu, seed = H.audited_routing_inputs(geo, tokens, first_seed=first_seed)
+        first_seed = seed + 1
+        x, router = x_cpu.cuda(), router_cpu.cuda()
+        bias = None if bias_cpu is None else bias_cpu.cuda()
         want_ids, want_w = reference.route(x, router, bias)
         # outputs are allocated by the caller; the entry point itself allocates nothing
         ids = torch.full((tokens, geo.topk), -1, dtype=torch.int64, device="cuda")
         w = torch.full((tokens, geo.topk), float("nan"), dtype=torch.float32, device="cuda")
+        if call == 0:
+            # the first call on a device also looks the static array up (and the driver may load the
+            # kernels lazily): let that happen before free memory is compared
+            api.route_static(config, x, router, bias, ids, w)
+            ids.fill_(-1)
+            w.fill_(float("nan"))
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]            # the driver's view: sees a cudaMalloc inside the library too
         api.route_static(config, x, router, bias, ids, w)
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
-        # same kernels, same arithmetic: identical results, not merely close
+        assert torch.cuda.mem_get_info()[0] == free_before, "device memory was allocated during the call"
+        # same kernels, same arithmetic as the workspace entry point: identical results, not merely close
         assert torch.equal(ids, want_ids), f"call {call}"
         assert torch.equal(w, want_w), f"call {call}"
+        # and the expert ids are the CPU oracle's, bit for bit
+        oracle_ids, oracle_w = O.route_tokens(H.spec_of(geo), x_cpu, router_cpu, bias_cpu)
+        assert torch.equal(ids.cpu(), oracle_ids), f"call {call}, seed {seed}"
+        torch.testing.assert_close(w.cpu(), oracle_w, rtol=2e-5, atol=1e-7)
 
 
 def test_static_router_refuses_what_does_not_fit(api):

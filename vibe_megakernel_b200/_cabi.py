@@ -12,7 +12,8 @@ ERRORS = {-1: "bad argument", -2: "unsupported geometry", -3: "workspace too sma
           -4: "device wait timed out", -5: "tensor-map encode failed", -6: "device index out of range",
           -7: "request exceeds the static scratch limit"}
 SCORING = {"softmax": 0, "sigmoid": 1, "sqrt_softplus": 2, "softmax_biased": 3}
-GEMM_TCGEN05, GEMM_SIMT = 0, 1
+GEMM_TCGEN05, GEMM_SIMT, GEMM_SIMT_BF16 = 0, 1, 2
+GEMM_IMPL = {"tcgen05": GEMM_TCGEN05, "simt": GEMM_SIMT, "simt_bf16": GEMM_SIMT_BF16}
 
 
 class Config(C.Structure):

@@ -36,7 +36,7 @@ int check_config(const moe_config_t* c) {
   if (c->n_group < 1 || c->n_group > 32 || c->n_experts % c->n_group) return MOE_ERR_BAD_ARG;
   if (c->topk_group < 1 || c->topk_group > c->n_group) return MOE_ERR_BAD_ARG;
   if (c->ep_world < 1 || c->ep_rank < 0 || c->ep_rank >= c->ep_world || c->n_experts % c->ep_world) return MOE_ERR_BAD_ARG;
-  if (c->gemm_impl != MOE_GEMM_TCGEN05 && c->gemm_impl != MOE_GEMM_SIMT) return MOE_ERR_BAD_ARG;
+  if (c->gemm_impl < MOE_GEMM_TCGEN05 || c->gemm_impl > MOE_GEMM_SIMT_BF16) return MOE_ERR_BAD_ARG;
   if (c->hidden / 128 > 112 || c->inter / 128 > 112) return MOE_ERR_UNSUPPORTED;
   if (!(c->swiglu_limit >= 0.f) || (c->weight_before_requant != 0 && c->weight_before_requant != 1)) return MOE_ERR_BAD_ARG;
   if (c->weight_before_requant && c->ep_world != 1) return MOE_ERR_UNSUPPORTED;
@@ -318,8 +318,7 @@ static int layer_forward_impl(const moe_config_t* cfg, const moe_weights_t* w, c
     a.swiglu.row_dest = row_dest;
     a.swiglu.routed_rows = tokens * cfg->topk;
   }
-  e = cfg->gemm_impl == MOE_GEMM_TCGEN05 ? moe::launch_gemm_tc(a, stream, &launches, &driver_error)
-                                         : moe::launch_gemm_simt(a, stream, &launches);
+  e = moe::launch_gemm(cfg->gemm_impl, a, stream, &launches, &driver_error);
   if (driver_error) return MOE_ERR_DRIVER;
   if (e != cudaSuccess) return from_cuda(e);
 
@@ -343,8 +342,7 @@ static int layer_forward_impl(const moe_config_t* cfg, const moe_weights_t* w, c
   a.out = slots;
   a.row_dest = row_dest;
   a.swiglu = moe::SwigluMode{};
-  e = cfg->gemm_impl == MOE_GEMM_TCGEN05 ? moe::launch_gemm_tc(a, stream, &launches, &driver_error)
-                                         : moe::launch_gemm_simt(a, stream, &launches);
+  e = moe::launch_gemm(cfg->gemm_impl, a, stream, &launches, &driver_error);
   if (driver_error) return MOE_ERR_DRIVER;
   if (e != cudaSuccess) return from_cuda(e);
 

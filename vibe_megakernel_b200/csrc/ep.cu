@@ -414,8 +414,7 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* 
   a.s_a = w->shared_gate; a.s_a_scale = w->shared_gate_scale; a.s_b = w->shared_up; a.s_b_scale = w->shared_up_scale;
   a.aq = ws + P.aq; a.as = reinterpret_cast<float*>(ws + P.as);
   a.swiglu.limit = __bfloat162float(__float2bfloat16_rn(cfg->swiglu_limit));   // the clamp gives bf16 values
-  e = cfg->gemm_impl == MOE_GEMM_TCGEN05 ? moe::launch_gemm_tc(a, stream, &launches, &driver_error)
-                                         : moe::launch_gemm_simt(a, stream, &launches);
+  e = moe::launch_gemm(cfg->gemm_impl, a, stream, &launches, &driver_error);
   if (driver_error) return MOE_ERR_DRIVER;
   if (e != cudaSuccess) return cuda_rc(e);
   a.dual = false;
@@ -431,8 +430,7 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* 
   a.swiglu = moe::SwigluMode{};
   a.out = reinterpret_cast<__nv_bfloat16*>(ws + P.out);
   a.row_dest = nullptr;
-  e = cfg->gemm_impl == MOE_GEMM_TCGEN05 ? moe::launch_gemm_tc(a, stream, &launches, &driver_error)
-                                         : moe::launch_gemm_simt(a, stream, &launches);
+  e = moe::launch_gemm(cfg->gemm_impl, a, stream, &launches, &driver_error);
   if (driver_error) return MOE_ERR_DRIVER;
   if (e != cudaSuccess) return cuda_rc(e);
 

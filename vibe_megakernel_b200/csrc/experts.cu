@@ -145,8 +145,7 @@ int moe_experts_forward(const moe_config_t* cfg, const moe_weights_t* w, const u
   if (shared) { a.n_local = 0; a.w_a = nullptr; a.w_b = nullptr; }
   a.aq = ws + L.aq; a.as = reinterpret_cast<float*>(ws + L.as);
   a.swiglu.limit = __bfloat162float(__float2bfloat16_rn(cfg->swiglu_limit));   // the clamp gives bf16 values
-  e = cfg->gemm_impl == MOE_GEMM_TCGEN05 ? moe::launch_gemm_tc(a, stream, &launches, &driver_error)
-                                         : moe::launch_gemm_simt(a, stream, &launches);
+  e = moe::launch_gemm(cfg->gemm_impl, a, stream, &launches, &driver_error);
   if (driver_error) return MOE_ERR_DRIVER;
   if (e != cudaSuccess) return cuda_rc(e);
   a.dual = false;
@@ -162,8 +161,7 @@ int moe_experts_forward(const moe_config_t* cfg, const moe_weights_t* w, const u
   a.swiglu = moe::SwigluMode{};
   a.out = static_cast<__nv_bfloat16*>(out_bf16);
   a.row_dest = g.row_dest;
-  e = cfg->gemm_impl == MOE_GEMM_TCGEN05 ? moe::launch_gemm_tc(a, stream, &launches, &driver_error)
-                                         : moe::launch_gemm_simt(a, stream, &launches);
+  e = moe::launch_gemm(cfg->gemm_impl, a, stream, &launches, &driver_error);
   if (driver_error) return MOE_ERR_DRIVER;
   return cuda_rc(e);
 }

@@ -381,11 +381,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           const uint32_t d0 = tmem + as * C::kAccCols;
           if (elect_one()) {
             *s_consumed = it + 1;
-#pragma unroll
             // every operand descriptor of the stage is the first one plus a constant (the start
             // address field counts 16-byte units and no sum leaves it): fewer instructions for
             // the one lane whose instruction stream feeds the tensor pipe
             const uint64_t desc0 = smem_desc_sw128(sa);
+#pragma unroll
             for (int k4 = 0; k4 < 4; ++k4) {
               const uint64_t ad = desc0 + ((k4 * 32) >> 4);
               const uint64_t bd = ad + (((DUAL ? 2 : 1) * C::kABytes) >> 4);

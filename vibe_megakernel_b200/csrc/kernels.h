@@ -201,6 +201,7 @@ struct GemmArgs {
   int32_t* parts_done;
   SwigluMode swiglu;         // dual only
   int max_stages;            // > 0: cap of the shared-memory ring, so that the CTAs of the call's two GEMMs fit on an SM together
+  bool bf16_operands;        // CUDA-core arm only: operands dequantised and rounded to bf16 first (MOE_GEMM_SIMT_BF16)
 };
 cudaError_t launch_gemm_tc(const GemmArgs& a, cudaStream_t stream, int* launches, int* driver_error);
 
@@ -229,9 +230,16 @@ struct MxGemmArgs {
   int32_t* status;
 };
 cudaError_t launch_gemm_mx(const MxGemmArgs& a, cudaStream_t stream, int* launches, int* driver_error);
-// Grouped row r <- row row_token[r] of e4m3 [*, hidden] with its hidden/32 scale bytes.
-cudaError_t launch_gather_mx_rows(const uint8_t* x, const uint8_t* x_scales, const int32_t* row_token, int rows, int hidden,
-                                  uint8_t* xg, uint8_t* xgs, cudaStream_t stream, int* launches);
+// Grouped row r < *kept <- row row_token[r] of e4m3 [tokens, hidden] with its hidden/32 scale bytes.
+cudaError_t launch_gather_mx_rows(const uint8_t* x, const uint8_t* x_scales, const int32_t* row_token, const int32_t* kept,
+                                  int rows, int tokens, int hidden, uint8_t* xg, uint8_t* xgs, cudaStream_t stream,
+                                  int* launches);
 cudaError_t launch_gemm_simt(const GemmArgs& a, cudaStream_t stream, int* launches);
+// The arm `impl` (MOE_GEMM_*) asks for.
+inline cudaError_t launch_gemm(int impl, GemmArgs& a, cudaStream_t stream, int* launches, int* driver_error) {
+  if (impl == MOE_GEMM_TCGEN05) return launch_gemm_tc(a, stream, launches, driver_error);
+  a.bf16_operands = impl == MOE_GEMM_SIMT_BF16;
+  return launch_gemm_simt(a, stream, launches);
+}
 
 }  // namespace moe

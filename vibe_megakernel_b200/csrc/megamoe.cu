@@ -10,14 +10,20 @@
 
 namespace moe {
 
-// One block per grouped row: 16-byte pieces of the payload, then the scale bytes.
+// One block per grouped row: 16-byte pieces of the payload, then the scale bytes. Only the first
+// *kept rows exist: a routed row whose expert id is out of range was dropped by the grouping and
+// the tail of row_token is not written.
 __global__ void __launch_bounds__(128) gather_mx_rows_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ x_scales,
-                                                             const int32_t* __restrict__ row_token, int hidden,
+                                                             const int32_t* __restrict__ row_token,
+                                                             const int32_t* __restrict__ kept, int tokens, int hidden,
                                                              uint8_t* __restrict__ xg, uint8_t* __restrict__ xgs) {
   dependent_wait();
   dependents_may_launch();
   const size_t row = blockIdx.x;
-  const size_t src = static_cast<size_t>(row_token[row]);
+  if (static_cast<int>(blockIdx.x) >= *kept) return;
+  const int token = row_token[row];
+  if (token < 0 || token >= tokens) return;
+  const size_t src = static_cast<size_t>(token);
   const uint4* in = reinterpret_cast<const uint4*>(x + src * hidden);
   uint4* out = reinterpret_cast<uint4*>(xg + row * hidden);
   for (int i = threadIdx.x; i < hidden / 16; i += blockDim.x) out[i] = in[i];
@@ -25,10 +31,12 @@ __global__ void __launch_bounds__(128) gather_mx_rows_kernel(const uint8_t* __re
   for (int i = threadIdx.x; i < ks; i += blockDim.x) xgs[row * ks + i] = x_scales[src * ks + i];
 }
 
-cudaError_t launch_gather_mx_rows(const uint8_t* x, const uint8_t* x_scales, const int32_t* row_token, int rows, int hidden,
-                                  uint8_t* xg, uint8_t* xgs, cudaStream_t stream, int* launches) {
+cudaError_t launch_gather_mx_rows(const uint8_t* x, const uint8_t* x_scales, const int32_t* row_token, const int32_t* kept,
+                                  int rows, int tokens, int hidden, uint8_t* xg, uint8_t* xgs, cudaStream_t stream,
+                                  int* launches) {
   if (rows <= 0) return cudaSuccess;
-  launch_dependent(gather_mx_rows_kernel, dim3(rows), dim3(128), 0, stream, x, x_scales, row_token, hidden, xg, xgs);
+  launch_dependent(gather_mx_rows_kernel, dim3(rows), dim3(128), 0, stream, x, x_scales, row_token, kept, tokens, hidden, xg,
+                   xgs);
   if (launches) *launches += 1;
   return cudaGetLastError();
 }
@@ -137,7 +145,8 @@ int moe_mx_forward(const moe_config_t* cfg, const moe_mx_weights_t* w, const uin
   // 2. rows into expert order
   uint8_t* xg = ws + L.xg;
   uint8_t* xgs = ws + L.xgs;
-  e = moe::launch_gather_mx_rows(x_q, x_scales, g.row_token, L.rows, cfg->hidden, xg, xgs, stream, &launches);
+  e = moe::launch_gather_mx_rows(x_q, x_scales, g.row_token, g.offsets + cfg->n_experts, L.rows, tokens, cfg->hidden, xg, xgs,
+                                 stream, &launches);
   if (e != cudaSuccess) return from_cuda(e);
 
   // 3. linear1 + SwiGLU + requantisation; 4. linear2 into slot rows

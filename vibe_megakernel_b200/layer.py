@@ -25,7 +25,9 @@ class LayerConfig:
     n_group: int = 1
     topk_group: int = 1
     scaling: float = 1.0
-    gemm: str = "tcgen05"       # "tcgen05" (product path) or "simt" (check arm)
+    # "tcgen05" (product path); check arms on CUDA cores: "simt" (the same arithmetic) and "simt_bf16"
+    # (the reference's dequantize-then-bf16 rounding schedule, megabench/tasks/megamoe.py:146-149)
+    gemm: str = "tcgen05"
     # The MegaMoE form of the expert MLP (megabench/tasks/megamoe.py:116-122,176-182): gate/up clamped
     # before SwiGLU, and the routing weight applied before the requantisation instead of at the combine.
     swiglu_limit: float = 0.0
@@ -41,7 +43,7 @@ class LayerConfig:
     def c_struct(self, world: int = 1, rank: int = 0) -> _cabi.Config:
         return _cabi.Config(self.hidden, self.inter, self.experts, self.topk, self.shared,
                             _cabi.SCORING[self.scoring], self.n_group, self.topk_group, float(self.scaling),
-                            world, rank, _cabi.GEMM_SIMT if self.gemm == "simt" else _cabi.GEMM_TCGEN05,
+                            world, rank, _cabi.GEMM_IMPL[self.gemm],
                             float(self.swiglu_limit), int(self.weight_before_requant))
 
 

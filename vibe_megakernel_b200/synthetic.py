@@ -162,3 +162,33 @@ def algorithmic_bytes(geo: MoeGeometry, tokens: int, distinct_experts: int) -> i
     not counted (megabench/sol.py:160-188 counts weights the same way)."""
     return ((distinct_experts + geo.shared) * geo.expert_bytes()
             + 4 * geo.experts * geo.hidden + 4 * tokens * geo.hidden)
+
+
+def megamoe_inputs(tokens: int, experts: int, topk: int, hidden: int, inter: int, seed: int, device) -> dict:
+    """Seeded random inputs of the routed experts in the MegaMoE-native formats, made on ``device``
+    (tensor names and layouts of megabench/tasks/megamoe.py:86-113): packed E2M1 weight bytes with E8M0
+    scales near 2^-7, E4M3 rows with scales near 2^-7, routing drawn like the reference's ``route``
+    (log-normal expert popularity, Gumbel top-k, weights that sum to 2.5; megabench/tasks/megamoe.py:65-80)."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    u8 = torch.uint8
+
+    def codes(*shape):
+        return torch.randint(0, 256, shape, dtype=u8, device=device, generator=gen)
+
+    def scales(center, *shape):
+        return torch.randint(center - 2, center + 3, shape, dtype=u8, device=device, generator=gen)
+
+    values = {}
+    x = (torch.randn((tokens, hidden), device=device, generator=gen) * 50.0).clamp(-448.0, 448.0)
+    values["x"] = x.to(torch.float8_e4m3fn)
+    values["x_scales"] = scales(120, tokens, hidden // 32)
+    popularity = 0.4 * torch.randn((experts,), device=device, generator=gen)
+    uniform = torch.rand((tokens, experts), device=device, generator=gen).clamp(1e-12, 1 - 1e-7)
+    values["topk_idx"] = (popularity - torch.log(-torch.log(uniform))).topk(topk, -1).indices
+    score = torch.nn.functional.softplus(torch.randn((tokens, topk), device=device, generator=gen)).sqrt()
+    values["topk_weights"] = score / score.sum(-1, keepdim=True) * 2.5
+    values["l1_blocks"] = codes(experts, 2 * inter, hidden // 32, 16)
+    values["l1_scales"] = scales(120, experts, 2 * inter, hidden // 32)
+    values["l2_blocks"] = codes(experts, hidden, inter // 32, 16)
+    values["l2_scales"] = scales(121, experts, hidden, inter // 32)
+    return values
