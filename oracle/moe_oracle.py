@@ -35,7 +35,11 @@ def scale_from_amax(amax: torch.Tensor, power_of_two: bool = False) -> torch.Ten
 
     megabench/tasks/quantization.py:57-59.
     """
-    s = torch.clamp(amax.to(torch.float32), min=AMAX_FLOOR) / E4M3_MAX
+    # The divisor is a tensor on purpose: torch's CUDA kernels replace a division by a Python number
+    # with a multiplication by its reciprocal, which is one ulp off for many inputs and then moves
+    # payload values that sit exactly on a rounding tie (frequent for bf16 inputs). A tensor divisor
+    # is a true IEEE division on every device, as the reference's CPU arithmetic is.
+    s = torch.clamp(amax.to(torch.float32), min=AMAX_FLOOR) / torch.tensor(E4M3_MAX, dtype=torch.float32, device=amax.device)
     if power_of_two:
         s = torch.exp2(torch.ceil(torch.log2(s)))
     return s

@@ -75,7 +75,7 @@ def y_error(got: torch.Tensor, want: torch.Tensor):
 
 
 def assert_y_close(got: torch.Tensor, want: torch.Tensor, what: str = "y"):
-    """The stated tolerance where outputs are of order one: max-abs 2e-2 and cosine > 0.999."""
+    """The stated tolerance: max-abs 2e-2 * max(1, max|want|) and cosine > 0.999."""
     max_abs, cos, bound = y_error(got, want)
     assert max_abs <= bound and cos > Y_COS, f"{what}: max-abs {max_abs:.4g} (bound {bound:.4g}), cosine {cos:.6f}"
     return max_abs, cos

@@ -8,8 +8,10 @@ point is checked three ways:
   * integer outputs (expert ids, permutation) bit-exact against the oracle;
   * the product path (tcgen05 GEMMs) against the oracle in the operand convention it computes in,
     fp32-dequantised operands (megabench/tasks/frontier.py:180-186): ASSERTED within
-    max-abs <= 2e-2 * max(1, max|y|) and cosine > 0.999; its distance to the bf16-operand oracle
-    (megabench/tasks/megamoe.py:146-149) and the reference harness' band are reported beside it;
+    max-abs <= 2e-2 * max(1, max|y|) and cosine > 0.999; against the bf16-operand oracle
+    (megabench/tasks/megamoe.py:146-149) it is ASSERTED to be no farther than the reference's two
+    conventions are from one another (plus one bf16 step), with cosine > 0.999 and inside the
+    reference harness' band, and the report says whether it is inside 2e-2 * max(1, max|y|) too;
   * the check arm with the bf16-operand rounding schedule (MOE_GEMM_SIMT_BF16) against the
     bf16-operand oracle: ASSERTED within the same bound.
 
@@ -91,15 +93,19 @@ def test_every_benchmark_point_matches_the_oracle(api, name, tokens):
     torch.testing.assert_close(out["topk_weights"], want["topk_weights"], rtol=2e-5, atol=1e-7)
     tc32_abs, tc32_cos = H.assert_y_close(out["y"], want32["y"], f"{name} batch {tokens}, tcgen05 vs fp32-operand oracle")
     tc16_abs, tc16_cos, bound = H.y_error(out["y"], want["y"])
-    assert tc16_cos > H.Y_COS
+    o_abs, o_cos, _ = H.y_error(want32["y"], want["y"])
+    # against the bf16-operand oracle the product path is held to the distance between the
+    # reference's own two conventions plus one bf16 step of the largest output (it is within 2e-2 *
+    # max|y| of that oracle at nearly every point; the report line says where it is not)
+    ulp = 2.0 ** -7 * float(want["y"].float().abs().max())
+    assert tc16_cos > H.Y_COS and tc16_abs <= o_abs + ulp, (tc16_abs, o_abs, ulp)
     band = H.assert_y_in_band(out["y"], want["y"], wide)
     arm = api.MoeLayer(api.LayerConfig.from_geometry(geo, gemm="simt_bf16"), max_tokens=tokens).forward(inputs, check_status=True)
     assert torch.equal(arm["order"], want["order"])
     arm_abs, arm_cos = H.assert_y_close(arm["y"], want["y"], f"{name} batch {tokens}, bf16-operand arm vs bf16-operand oracle")
-    o_abs, o_cos, _ = H.y_error(want32["y"], want["y"])
     report(f"PARITY {name} batch {tokens} seed {seed}: max|y| {float(want['y'].abs().max()):.3g} bound {bound:.4g} | "
            f"tcgen05 vs fp32-operand oracle {tc32_abs:.4g} cos {tc32_cos:.6f} | tcgen05 vs bf16-operand oracle "
-           f"{tc16_abs:.4g} cos {tc16_cos:.6f} | bf16-operand arm vs bf16-operand oracle {arm_abs:.4g} cos {arm_cos:.6f} | "
+           f"{tc16_abs:.4g} cos {tc16_cos:.6f} ({'within' if tc16_abs <= bound else 'OUTSIDE'} the bound) | bf16-operand arm vs bf16-operand oracle {arm_abs:.4g} cos {arm_cos:.6f} | "
            f"the two oracles apart {o_abs:.4g} cos {o_cos:.6f} | band: {band}")
 
 

@@ -157,7 +157,7 @@ def test_router_near_ties_follow_the_exact_order_down_to_the_logit_error(api):
     x = torch.randn((1, geo.hidden), generator=gen).to(torch.bfloat16)
     k = int(x[0].float().abs().argmax())
     base = torch.randn((geo.experts, geo.hidden), generator=gen) * geo.router_std
-    base[3] += 0.05 * x[0].float() / x[0].float().norm()       # experts 3 and 9 lead the field by a wide margin
+    base[3] += 0.3 * x[0].float() / x[0].float().norm()        # experts 3 and 9 lead the field by a wide margin
     base[3, k] = 0.0                                           # so that adding delta to this entry is exact
     for gap in (1e-4, 1e-5, 1e-6, 0.0, -1e-6, -1e-5, 1e-9, -1e-9):
         router = base.clone()
