@@ -259,8 +259,9 @@ typedef struct moe_ep_layout {
   uint64_t recv_count;       /* int32[world] rows received from each source */
   uint64_t recv_expert;      /* int32[world*cap] local expert id of every received row */
   uint64_t recv_slot;        /* int32[world*cap] slot row (token*topk+slot) at the source */
+  uint64_t recv_weight;      /* fp32 [world*cap] routing weight of every received row (MegaMoE form only) */
   uint64_t recv_q;           /* e4m3 [world*cap, H] */
-  uint64_t recv_s;           /* fp32 [world*cap, H/128] */
+  uint64_t recv_s;           /* fp32 [world*cap, H/128]; MegaMoE form: E8M0 bytes [world*cap, H/32] */
   uint64_t slots;            /* bf16 [cap + max_tokens, H] down-projection rows coming home */
   int32_t cap;               /* rows one source can send to one owner: max_tokens*topk */
   int32_t rows;              /* world*cap + max_tokens: rows this rank may have to multiply */
@@ -271,12 +272,35 @@ typedef struct moe_ep_layout {
 int moe_ep_layout(const moe_config_t* cfg, int32_t max_tokens, moe_ep_layout_t* layout);
 
 /* One layer call of this rank. `exchange` is void*[world]: every rank's exchange buffer (own one at
- * index ep_rank). `epoch` must increase by one with every call and be the same on all ranks.
- * x bf16 [tokens, H] -> y bf16 [tokens, H]; expert_ids / topk_weights optional as in moe_layer_forward.
+ * index ep_rank). `epoch` is 1 on the first call that uses a given `local` buffer (that call clears the
+ * buffer's block counters; a first call with another epoch leaves them undefined and every peer then
+ * runs into its 2 s wait), grows by one with every call and is the same on all ranks.
+ * x bf16 [tokens, H] -> y bf16 [tokens, H]; expert_ids / topk_weights optional as in moe_layer_forward;
+ * order (optional) int64 [tokens*topk]: this rank's routed rows in the stable order of their owning
+ * rank, the dispatch permutation of megabench/tasks/megamoe.py:161-164.
  * On a bounded wait running out the call still returns; moe_device_status(local, ...) reports it. */
 int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* weights, const void* x_bf16, int32_t tokens,
-                   int32_t max_tokens, void* y_bf16, int64_t* expert_ids, float* topk_weights,
+                   int32_t max_tokens, void* y_bf16, int64_t* expert_ids, float* topk_weights, int64_t* order,
                    void* const* exchange, void* local, size_t local_bytes, uint64_t epoch, void* stream);
+
+/* The routed experts in the MegaMoE-native formats, expert-parallel: the form the reference grades
+ * (megabench/cases.py:380-388, `reference(case, values)` of megabench/tasks/megamoe.py:153-182 without
+ * `serial`). Every rank passes its own token rows with their routing and the MXFP4 matrices of its
+ * experts [rank*E/world, (rank+1)*E/world); the dispatching kernel stores payload, scale bytes, local
+ * expert id and routing weight of every routed row into the owner's receive buffer (the four
+ * dispatched tensors of megabench/tasks/megamoe.py:167-173), the owner runs linear1 -> clamped SwiGLU
+ * times the weight -> requantisation -> linear2 and stores the bf16 rows back into the source's slot
+ * rows, the source adds them in slot order. Results equal moe_mx_forward on the whole problem bit
+ * for bit (megabench/verify_megamoe.py:44-56,104-105). cfg as for moe_mx_forward with ep_world / ep_rank
+ * set and n_experts the experts of the whole layer; tokens and max_tokens count this rank's rows;
+ * exchange, local, epoch as for moe_ep_forward, sized by moe_mx_ep_layout. order (optional) int64
+ * [tokens*topk]: the stable order of this rank's routed rows by owning rank (rows whose expert id is out
+ * of range have no owner, are not sent, and come last). */
+int moe_mx_ep_layout(const moe_config_t* cfg, int32_t max_tokens, moe_ep_layout_t* layout);
+int moe_mx_ep_forward(const moe_config_t* cfg, const moe_mx_weights_t* w, const uint8_t* x_q, const uint8_t* x_scales,
+                      const int64_t* topk_idx, const float* topk_weights, int32_t tokens, int32_t max_tokens,
+                      void* y_bf16, int64_t* order, void* const* exchange, void* local, size_t local_bytes,
+                      uint64_t epoch, void* stream);
 
 /* The bounded wait the expert-parallel layer uses for its arrival and return flags, on its own:
  * waits until flags[0..world) >= epoch or `timeout_ns` (at most 2 s) has passed; on expiry it writes
@@ -299,7 +323,8 @@ int moe_ep_buffer_free(void* ptr);
  * refused an out-of-range index. *detail (may be NULL) receives a code naming the place. */
 int moe_device_status(const void* workspace, void* stream, int32_t* detail);
 
-/* Number of kernels the last moe_layer_forward call on this thread launched. */
+/* Number of kernels the last layer call of this thread launched (moe_layer_forward, moe_block_forward,
+ * moe_ep_forward, moe_experts_forward, moe_mx_forward, moe_mx_ep_forward). */
 int moe_last_launch_count(void);
 
 /* Stage timing for measurements (no counterpart in the reference, whose harness times whole calls

@@ -45,8 +45,37 @@ def main(out_path: str) -> None:
             rows = slice(rank * tokens_per_rank, (rank + 1) * tokens_per_rank)
             ok = ok and torch.equal(got["y"], want["y"][rows]) and torch.equal(got["expert_ids"], want["expert_ids"][rows])
             ok = ok and torch.equal(got["topk_weights"], want["topk_weights"][rows])
+            owner = torch.div(got["expert_ids"].flatten(), geo.experts // world, rounding_mode="floor")
+            ok = ok and torch.equal(got["order"], torch.sort(owner, stable=True).indices)   # megabench/tasks/megamoe.py:161-164
             alt = collective.forward(mine)
             ok = ok and torch.equal(alt["y"], got["y"]) and torch.equal(alt["expert_ids"], got["expert_ids"])
+        flags = [None] * world
+        dist.all_gather_object(flags, bool(ok))
+        report[name] = flags
+        layer.close()
+    # the routed experts in the MegaMoE-native formats: expert-parallel == serial, bit for bit
+    # (megabench/verify_megamoe.py:44-56,104-105), fresh inputs every call, buffers reused
+    from vibe_megakernel_b200 import megamoe
+    for name, (tokens_per_rank, experts, topk, hidden, inter, limit) in {
+            "megamoe_dev": (8, 16, 4, 256, 128, 10.0), "megamoe_chunks": (40, 8, 2, 512, 256, 3.0)}.items():
+        if experts % world:
+            continue
+        config = megamoe.MegaMoeConfig(hidden, inter, experts, topk, limit)
+        layer = megamoe.MegaMoeEp(config, max_tokens=tokens_per_rank, device=dev)
+        serial = megamoe.MegaMoe(config, max_tokens=tokens_per_rank * world, device=dev)
+        ok = True
+        local = experts // world
+        for call in range(3):
+            full = {k: v.to(dev) for k, v in H.megamoe_inputs(tokens_per_rank * world, experts, topk, hidden, inter,
+                                                              seed=100 + call).items()}
+            rows = slice(rank * tokens_per_rank, (rank + 1) * tokens_per_rank)
+            mine = {k: (v[rows].contiguous() if k in ("x", "x_scales", "topk_idx", "topk_weights")
+                        else v[rank * local:(rank + 1) * local].contiguous()) for k, v in full.items()}
+            got = layer.run(mine, check_status=True, want_order=True)
+            want = serial.run(full, check_status=True)
+            ok = ok and torch.equal(got["y"], want["y"][rows])
+            owner = torch.div(mine["topk_idx"].flatten(), local, rounding_mode="floor")
+            ok = ok and torch.equal(got["order"], torch.sort(owner, stable=True).indices)
         flags = [None] * world
         dist.all_gather_object(flags, bool(ok))
         report[name] = flags

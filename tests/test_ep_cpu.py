@@ -49,7 +49,33 @@ def test_exchange_layout_through_the_c_abi():
     assert lib.moe_ep_layout(C.byref(too_many), 16, None) == -2
     uneven = _cabi.Config(7168, 2048, 250, 8, 1, 1, 1, 1, 2.5, 8, 0, 0)
     assert lib.moe_ep_layout(C.byref(uneven), 16, None) == -1
-    assert lib.moe_ep_forward(C.byref(cfg), None, None, 1, 16, None, None, None, None, None, 0, 1, None) == -1
+    assert lib.moe_ep_forward(C.byref(cfg), None, None, 1, 16, None, None, None, None, None, None, 0, 1, None) == -1
+    # epochs start at 1 on a given local buffer: 0 is refused before anything is launched
+    w = _cabi.Weights()
+    for name in _cabi.WEIGHT_FIELDS:
+        setattr(w, name, 256)
+    dummy = C.c_void_p(256)
+    peers = (C.c_void_p * 8)(*([256] * 8))
+    assert lib.moe_ep_forward(C.byref(cfg), C.byref(w), dummy, 1, 16, dummy, None, None, None, peers, dummy, 1 << 40, 0,
+                              None) == -1
+
+
+def test_megamoe_exchange_layout_through_the_c_abi():
+    # the reference's expert-parallel cases: 384 experts over 8 ranks, top-6 (megabench/cases.py:380-388)
+    lib = _cabi.load()
+    cfg = _cabi.Config(7168, 3072, 384, 6, 0, 0, 1, 1, 1.0, 8, 5, 0, 10.0, 1)
+    lay = _cabi.EpLayout()
+    assert lib.moe_mx_ep_layout(C.byref(cfg), 512, C.byref(lay)) == 0
+    assert lay.cap == 512 * 6 and lay.rows == 8 * lay.cap and lay.token_tile == 64
+    offsets = [getattr(lay, n) for n in _cabi.EP_LAYOUT_OFFSETS[2:]]
+    assert offsets == sorted(offsets) and all(o % 256 == 0 for o in offsets)
+    assert lay.recv_s - lay.recv_q >= lay.rows * 7168 and lay.slots - lay.recv_s >= lay.rows * 7168 // 32
+    assert lay.recv_q - lay.recv_weight >= 4 * lay.rows
+    assert lay.exchange_bytes >= lay.slots + 2 * lay.cap * 7168
+    assert lib.moe_mx_ep_layout(C.byref(cfg), 683, None) == -2          # more than 32768 rows could arrive at one rank
+    shared = _cabi.Config(7168, 3072, 384, 6, 1, 0, 1, 1, 1.0, 8, 5, 0, 10.0, 1)
+    assert lib.moe_mx_ep_layout(C.byref(shared), 16, None) == -2
+    assert lib.moe_mx_ep_forward(C.byref(cfg), None, None, None, None, None, 1, 16, None, None, None, None, 0, 1, None) == -1
 
 
 def test_two_rank_gloo_run_equals_the_serial_oracle(tmp_path):

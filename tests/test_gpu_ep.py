@@ -57,6 +57,80 @@ def test_single_rank_exchange_path_equals_the_one_gpu_layer(single_rank_group, n
         layer.close()
 
 
+def test_plugin_accepts_the_execution_context_of_the_reference_harness(single_rank_group):
+    # megabench/harness/distributed.py:68-74 hands build() the case dict with case["execution"]; the
+    # run it returns is backed by the expert-parallel layer (here a group of one rank)
+    from vibe_megakernel_b200 import submission
+    from vibe_megakernel_b200.ep import EpMoeLayer
+    from vibe_megakernel_b200.layer import LayerConfig, MoeLayer
+    geo = H.small_geometries()["kimi_small"]
+    tokens = 24
+    case = {"id": "fp8-moe-layer-kimi-small-ep1", "family": "fp8_moe_layer", "model": geo.name, "phase": "moe_layer",
+            "gpus": 1, "tp": 1, "ep": 1,
+            "params": {"tokens": tokens, "hidden": geo.hidden, "intermediate": geo.inter, "experts": geo.experts,
+                       "topk": geo.topk, "shared_experts": geo.shared, "router_groups": geo.n_group,
+                       "router_top_groups": geo.topk_group},
+            "moe": {"scoring": geo.scoring, "scaling": geo.scaling},
+            "execution": {"rank": 0, "world_size": 1, "tp_rank": 0, "ep_rank": 0, "backend": dist.get_backend(),
+                          "device": "cuda:0", "tp_group": None, "ep_group": None}}
+    run = submission.build(case)
+    assert isinstance(run.layer, EpMoeLayer)
+    try:
+        values = H.to_device(synthetic.make_inputs(geo, tokens, 3, "cpu"), "cuda")
+        before = {k: v.clone() for k, v in values.items()}
+        got = run(values)
+        want = MoeLayer(LayerConfig.from_geometry(geo), max_tokens=tokens).forward(values, check_status=True)
+        assert set(got) == {"y", "expert_ids", "order"}
+        assert torch.equal(got["y"], want["y"]) and torch.equal(got["expert_ids"], want["expert_ids"])
+        # one owner: the stable order by owning rank is the identity (megabench/tasks/megamoe.py:161-164)
+        assert torch.equal(got["order"].cpu(), torch.arange(tokens * geo.topk))
+        for k, v in values.items():
+            assert torch.equal(v.view(torch.uint8), before[k].view(torch.uint8)), f"input {k} was modified"
+        assert run.layer.launches() == 9
+    finally:
+        run.layer.close()
+    # without an execution context a case on several GPUs cannot be built
+    with pytest.raises(ValueError):
+        submission.build({**{k: v for k, v in case.items() if k != "execution"}, "gpus": 2})
+
+
+@pytest.mark.parametrize("tokens,experts,topk,hidden,inter,limit", [(8, 16, 4, 256, 128, 10.0), (70, 8, 2, 512, 256, 3.0),
+                                                                    (3, 64, 2, 256, 256, 0.0)])
+def test_megamoe_single_rank_exchange_equals_the_serial_call(single_rank_group, tokens, experts, topk, hidden, inter, limit):
+    # the expert-parallel form of the MXFP4 experts with one rank: every peer store lands in the rank's
+    # own buffer; bits must equal the serial entry point (megabench/verify_megamoe.py:104-105), also
+    # through the plugin file with the family name of the reference's cases
+    from vibe_megakernel_b200 import megamoe, submission
+    values = H.to_device(H.megamoe_inputs(tokens, experts, topk, hidden, inter, seed=tokens), "cuda")
+    config = megamoe.MegaMoeConfig(hidden, inter, experts, topk, limit)
+    serial = megamoe.MegaMoe(config, max_tokens=tokens).run(values, check_status=True, want_order=True)
+    layer = megamoe.MegaMoeEp(config, max_tokens=tokens + 3)
+    case = {"id": "megamoe-layer-test-ep1", "family": "megamoe_layer", "gpus": 1, "tp": 1, "ep": 1,
+            "params": {"tokens": tokens, "hidden": hidden, "intermediate": inter, "experts": experts, "topk": topk,
+                       "swiglu_limit": limit},
+            "execution": {"rank": 0, "world_size": 1, "tp_rank": 0, "ep_rank": 0, "backend": dist.get_backend(),
+                          "device": "cuda:0", "tp_group": None, "ep_group": None}}
+    try:
+        for _ in range(2):                                         # buffers and flags are reused from call to call
+            got = layer.run(values, check_status=True, want_order=True)
+            assert torch.equal(got["y"], serial["y"])
+            assert torch.equal(got["order"].cpu(), torch.arange(tokens * topk))    # one owner: the identity
+        assert layer.launches() == 7
+        fewer = {k: (v[: max(1, tokens // 2)].contiguous() if k in ("x", "x_scales", "topk_idx", "topk_weights") else v)
+                 for k, v in values.items()}
+        got = layer.run(fewer, check_status=True)
+        assert torch.equal(got["y"], serial["y"][: max(1, tokens // 2)])
+    finally:
+        layer.close()
+    # the plugin file builds the expert-parallel layer from the case and the execution context
+    from vibe_megakernel_b200.megamoe import MegaMoeEp
+    run = submission.build(case)
+    out = run(values)
+    assert set(out) == {"y"} and torch.equal(out["y"], serial["y"])
+    run_serial = submission.build({k: v for k, v in case.items() if k != "execution"})
+    assert torch.equal(run_serial(values)["y"], serial["y"])
+
+
 def test_deepseek_shape_single_rank_exchange(single_rank_group):
     from vibe_megakernel_b200 import ep
     from vibe_megakernel_b200.layer import LayerConfig, MoeLayer

@@ -46,7 +46,7 @@ class Layout(C.Structure):
 
 
 EP_LAYOUT_OFFSETS = ("exchange_bytes", "local_bytes", "flags_dispatch", "flags_return", "recv_count", "recv_expert",
-                     "recv_slot", "recv_q", "recv_s", "slots")
+                     "recv_slot", "recv_weight", "recv_q", "recv_s", "slots")
 
 
 class EpLayout(C.Structure):
@@ -60,8 +60,12 @@ EXPORTS = {
                                       C.c_int32, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "moe_ep_layout": (C.c_int, [C.POINTER(Config), C.c_int32, C.POINTER(EpLayout)]),
     "moe_ep_forward": (C.c_int, [C.POINTER(Config), C.POINTER(Weights), C.c_void_p, C.c_int32, C.c_int32, C.c_void_p,
-                                 C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_void_p, C.c_size_t, C.c_uint64,
-                                 C.c_void_p]),
+                                 C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_void_p, C.c_size_t,
+                                 C.c_uint64, C.c_void_p]),
+    "moe_mx_ep_layout": (C.c_int, [C.POINTER(Config), C.c_int32, C.POINTER(EpLayout)]),
+    "moe_mx_ep_forward": (C.c_int, [C.POINTER(Config), C.POINTER(MxWeights), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                    C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_void_p,
+                                    C.c_size_t, C.c_uint64, C.c_void_p]),
     "moe_ep_wait_flags": (C.c_int, [C.c_void_p, C.c_int32, C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p]),
     "moe_ep_buffer_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]),
     "moe_ep_buffer_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),

@@ -104,6 +104,10 @@ inline int from_cuda(cudaError_t e) { return e == cudaSuccess ? MOE_OK : static_
 
 }  // namespace
 
+namespace moe {
+void note_launches(int n) { g_last_launches = n; }
+}  // namespace moe
+
 extern "C" {
 
 int moe_workspace_layout(const moe_config_t* cfg, int32_t tokens, moe_workspace_layout_t* layout) {

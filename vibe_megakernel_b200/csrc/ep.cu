@@ -47,6 +47,7 @@ static void ep_layouts(const moe_config_t& c, int max_tokens, moe_ep_layout_t* L
   L->recv_count = take(4ull * world);
   L->recv_expert = take(4ull * world * cap);
   L->recv_slot = take(4ull * world * cap);
+  L->recv_weight = take(4ull * world * cap);
   L->recv_q = take(static_cast<uint64_t>(world) * cap * H);
   L->recv_s = take(4ull * world * cap * (H / 128));
   L->slots = take(2ull * (cap + max_tokens) * H);
@@ -92,10 +93,12 @@ struct DispatchArgs {
   float* xs_home;
   int32_t* done;
   uint64_t epoch;
+  int64_t* order;            // optional [tokens*topk]: the stable order of the routed rows by owning rank
 };
 
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(DispatchArgs a) {
   __shared__ int s_part[8];
+  __shared__ int s_lower[8];
   __shared__ int s_counts[8];
   __shared__ int s_last;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -112,14 +115,22 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(DispatchArgs a) {
     const int e = a.ids[r];
     const int d = e / a.n_local;
     int before = 0;                      // earlier rows of this rank bound for the same owner
+    int lower = 0;                       // rows bound for owners of lower rank (only counted when the order is wanted)
     for (int q = tid; q < r; q += 256) before += (a.ids[q] / a.n_local == d);
+    if (a.order)
+      for (int q = tid; q < routed; q += 256) lower += (a.ids[q] / a.n_local < d);
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) before += __shfl_xor_sync(0xffffffffu, before, off);
-    if (lane == 0) s_part[warp] = before;
+    for (int off = 16; off > 0; off >>= 1) {
+      before += __shfl_xor_sync(0xffffffffu, before, off);
+      lower += __shfl_xor_sync(0xffffffffu, lower, off);
+    }
+    if (lane == 0) { s_part[warp] = before; s_lower[warp] = lower; }
     __syncthreads();
-    int j = 0;
+    int j = 0, below = 0;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) j += s_part[w];
+    for (int w = 0; w < 8; ++w) { j += s_part[w]; below += s_lower[w]; }
+    // position of row r in `torch.sort(owner, stable=True)` (megabench/tasks/megamoe.py:161-164)
+    if (a.order && tid == 0) a.order[below + j] = r;
     const size_t row = static_cast<size_t>(a.rank) * a.cap + j;
     uint8_t* peer = a.peers.base[d];
     dst_q = peer + a.off_q + row * H;
@@ -254,6 +265,148 @@ __global__ void __launch_bounds__(128) ep_return_kernel(ReturnArgs a) {
   if (threadIdx.x == 0) *a.done = 0;
 }
 
+// =============================================================================================
+// The same exchange for the routed experts in the MegaMoE-native formats (MXFP4 weights, E4M3 rows
+// with one E8M0 scale per 32 channels): the expert-parallel form of megabench/tasks/megamoe.py:153-182.
+// Routing is an input and the rows arrive quantised, so the dispatching kernel only copies: payload,
+// scale bytes, local expert id, slot to return to, and the fp32 routing weight (the four dispatched
+// tensors of megabench/tasks/megamoe.py:167-173). The owner multiplies the weight into the SwiGLU
+// output before requantisation, so the source's combine is a plain slot-order sum.
+// =============================================================================================
+struct MxEpLocal {
+  uint64_t status, counters, counts, offsets, n_chunks, chunks, row_source, xq, xs, aq, as, out, total;
+};
+
+static void mx_ep_layouts(const moe_config_t& c, int max_tokens, moe_ep_layout_t* L, MxEpLocal* P) {
+  const int world = c.ep_world;
+  const int n_local = c.n_experts / world;
+  const uint64_t H = c.hidden, I = c.inter;
+  const int cap = max_tokens * c.topk;
+  const int rows = world * cap;
+  const int tile = moe::pick_token_tile(rows, c.n_experts);
+  const int max_chunks = std::min(rows, n_local) + rows / tile + 1;
+  uint64_t off = 0;
+  auto take = [&](uint64_t bytes) { const uint64_t at = off; off = up256(off + bytes); return at; };
+  std::memset(L, 0, sizeof(*L));
+  L->flags_dispatch = take(8ull * world);
+  L->flags_return = take(8ull * world);
+  L->recv_count = take(4ull * world);
+  L->recv_expert = take(4ull * rows);
+  L->recv_slot = take(4ull * rows);
+  L->recv_weight = take(4ull * rows);
+  L->recv_q = take(static_cast<uint64_t>(rows) * H);
+  L->recv_s = take(static_cast<uint64_t>(rows) * (H / 32));
+  L->slots = take(2ull * cap * H);
+  L->exchange_bytes = off;
+  L->cap = cap;
+  L->rows = rows;
+  L->max_chunks = max_chunks;
+  L->token_tile = tile;
+  off = 0;
+  P->status = take(32);
+  P->counters = take(32);
+  P->counts = take(4ull * (n_local + 1));
+  P->offsets = take(4ull * (n_local + 2));
+  P->n_chunks = take(4);
+  P->chunks = take(16ull * max_chunks);
+  P->row_source = take(4ull * rows);
+  P->xq = take(static_cast<uint64_t>(rows) * H);
+  P->xs = take(static_cast<uint64_t>(rows) * (H / 32));
+  P->aq = take(static_cast<uint64_t>(rows) * I);
+  P->as = take(static_cast<uint64_t>(rows) * (I / 32));
+  P->out = take(2ull * rows * H);
+  P->total = off;
+  L->local_bytes = off;
+}
+
+struct MxDispatchArgs {
+  const uint8_t* x;          // e4m3 [tokens, H]
+  const uint8_t* x_scales;   // E8M0 [tokens, H/32]
+  const int64_t* ids;        // [tokens*topk] global expert ids, (token, slot) order
+  const float* weights;      // [tokens*topk]
+  int tokens, hidden, topk, world, rank, n_local, cap;
+  Peers peers;
+  uint64_t off_count, off_expert, off_slot, off_weight, off_q, off_s, off_flags;
+  int32_t* done;
+  uint64_t epoch;
+  int64_t* order;            // optional: stable order of the routed rows by owning rank (rows without an owner last)
+};
+
+// owner of a routed row, -1 when its expert id is out of range (such a row is not sent)
+__device__ __forceinline__ int mx_owner(long long id, int n_local, int world) {
+  return (id >= 0 && id < static_cast<long long>(n_local) * world) ? static_cast<int>(id / n_local) : -1;
+}
+
+__global__ void __launch_bounds__(256) mx_ep_dispatch_kernel(MxDispatchArgs a) {
+  __shared__ int s_part[8];
+  __shared__ int s_lower[8];
+  __shared__ int s_counts[8];
+  __shared__ int s_last;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int routed = a.tokens * a.topk;
+  const int r = blockIdx.x;
+  const int H = a.hidden;
+  dependent_wait();
+  dependents_may_launch();
+  const long long id = a.ids[r];
+  const int d = mx_owner(id, a.n_local, a.world);
+  int before = 0, lower = 0;
+  for (int q = tid; q < r; q += 256) before += (mx_owner(a.ids[q], a.n_local, a.world) == d);
+  if (a.order)
+    for (int q = tid; q < routed; q += 256) {
+      const int o = mx_owner(a.ids[q], a.n_local, a.world);
+      lower += d >= 0 ? (o >= 0 && o < d) : (o >= 0);
+    }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    before += __shfl_xor_sync(0xffffffffu, before, off);
+    lower += __shfl_xor_sync(0xffffffffu, lower, off);
+  }
+  if (lane == 0) { s_part[warp] = before; s_lower[warp] = lower; }
+  __syncthreads();
+  int j = 0, below = 0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) { j += s_part[w]; below += s_lower[w]; }
+  if (a.order && tid == 0) a.order[below + j] = r;       // megabench/tasks/megamoe.py:161-164
+  if (d >= 0) {
+    const int t = r / a.topk;
+    const size_t row = static_cast<size_t>(a.rank) * a.cap + j;
+    uint8_t* peer = a.peers.base[d];
+    uint4* dq = reinterpret_cast<uint4*>(peer + a.off_q + row * H);
+    const uint4* sq = reinterpret_cast<const uint4*>(a.x + static_cast<size_t>(t) * H);
+    for (int i = tid; i < H / 16; i += 256) dq[i] = sq[i];
+    uint32_t* ds = reinterpret_cast<uint32_t*>(peer + a.off_s + row * (H / 32));
+    const uint32_t* ss = reinterpret_cast<const uint32_t*>(a.x_scales + static_cast<size_t>(t) * (H / 32));
+    for (int i = tid; i < H / 128; i += 256) ds[i] = ss[i];
+    if (tid == 0) {
+      reinterpret_cast<int32_t*>(peer + a.off_expert)[row] = static_cast<int>(id - static_cast<long long>(d) * a.n_local);
+      reinterpret_cast<int32_t*>(peer + a.off_slot)[row] = r;
+      reinterpret_cast<float*>(peer + a.off_weight)[row] = a.weights[r];
+    }
+  }
+  // the last block to finish publishes the counts and raises one flag per owner
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) s_last = (atomicAdd(a.done, 1) == static_cast<int>(gridDim.x) - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence_system();
+  if (tid < 8) s_counts[tid] = 0;
+  __syncthreads();
+  for (int q = tid; q < routed; q += 256) {
+    const int o = mx_owner(a.ids[q], a.n_local, a.world);
+    if (o >= 0) atomicAdd(&s_counts[o], 1);
+  }
+  __syncthreads();
+  if (tid < a.world) {
+    uint8_t* peer = a.peers.base[tid];
+    reinterpret_cast<int32_t*>(peer + a.off_count)[a.rank] = s_counts[tid];
+    __threadfence_system();
+    store_release_sys(reinterpret_cast<uint64_t*>(peer + a.off_flags) + a.rank, a.epoch);
+  }
+  if (tid == 0) *a.done = 0;
+}
+
 }  // namespace moe
 
 // ---------------------------------------------------------------------------------------------
@@ -288,7 +441,7 @@ int moe_ep_layout(const moe_config_t* cfg, int32_t max_tokens, moe_ep_layout_t* 
 }
 
 int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* x_bf16, int32_t tokens,
-                   int32_t max_tokens, void* y_bf16, int64_t* expert_ids, float* topk_weights,
+                   int32_t max_tokens, void* y_bf16, int64_t* expert_ids, float* topk_weights, int64_t* order,
                    void* const* exchange, void* local, size_t local_bytes, uint64_t epoch, void* stream_) {
   const int rc = ep_check(cfg, max_tokens);
   if (rc) return rc;
@@ -352,6 +505,7 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* 
   d.xs_home = reinterpret_cast<float*>(ws + P.xs_home);
   d.done = counters;
   d.epoch = epoch;
+  d.order = order;
   moe::launch_dependent(moe::ep_dispatch_kernel, dim3(tokens * cfg->topk + tokens), dim3(256), 0, stream, d);
   ++launches;
 
@@ -449,6 +603,164 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* 
   const moe::FlagWait home{reinterpret_cast<const uint64_t*>(mine + L.flags_return), world, epoch, moe::kWaitNs, status, 300};
   e = moe::launch_combine(reinterpret_cast<const __nv_bfloat16*>(mine + L.slots), tw, tokens, cfg->topk, H, cfg->n_shared,
                           static_cast<__nv_bfloat16*>(y_bf16), stream, &launches, nullptr, &home);
+  moe::note_launches(launches);
+  return cuda_rc(e);
+}
+
+static int mx_ep_check(const moe_config_t* c, int max_tokens) {
+  if (!c) return MOE_ERR_BAD_ARG;
+  if (c->hidden < 128 || c->inter < 128 || c->n_experts < 1 || c->topk < 1 || c->topk > c->n_experts || max_tokens < 1 ||
+      !(c->swiglu_limit >= 0.f) || c->ep_world < 1 || c->ep_rank < 0 || c->ep_rank >= c->ep_world)
+    return MOE_ERR_BAD_ARG;
+  if (c->hidden % 128 || c->inter % 128 || c->n_experts > MOE_MAX_EXPERTS || c->n_shared != 0 || c->ep_world > 8 ||
+      c->n_experts % c->ep_world || static_cast<int64_t>(c->ep_world) * max_tokens * c->topk > 32768)
+    return MOE_ERR_UNSUPPORTED;
+  return MOE_OK;
+}
+
+int moe_mx_ep_layout(const moe_config_t* cfg, int32_t max_tokens, moe_ep_layout_t* layout) {
+  const int rc = mx_ep_check(cfg, max_tokens);
+  if (rc) return rc;
+  moe_ep_layout_t L;
+  moe::MxEpLocal P;
+  moe::mx_ep_layouts(*cfg, max_tokens, &L, &P);
+  if (layout) *layout = L;
+  return MOE_OK;
+}
+
+int moe_mx_ep_forward(const moe_config_t* cfg, const moe_mx_weights_t* w, const uint8_t* x_q, const uint8_t* x_scales,
+                      const int64_t* topk_idx, const float* topk_weights, int32_t tokens, int32_t max_tokens, void* y_bf16,
+                      int64_t* order, void* const* exchange, void* local, size_t local_bytes, uint64_t epoch,
+                      void* stream_) {
+  const int rc = mx_ep_check(cfg, max_tokens);
+  if (rc) return rc;
+  if (!w || !w->l1_blocks || !w->l1_scales || !w->l2_blocks || !w->l2_scales || !x_q || !x_scales || !topk_idx ||
+      !topk_weights || !y_bf16 || !exchange || !local || tokens < 1 || tokens > max_tokens || epoch == 0)
+    return MOE_ERR_BAD_ARG;
+  if (reinterpret_cast<uintptr_t>(w->l1_blocks) & 31 || reinterpret_cast<uintptr_t>(w->l2_blocks) & 31 ||
+      reinterpret_cast<uintptr_t>(w->l1_scales) & 15 || reinterpret_cast<uintptr_t>(w->l2_scales) & 15 ||
+      reinterpret_cast<uintptr_t>(x_q) & 15 || reinterpret_cast<uintptr_t>(x_scales) & 3)
+    return MOE_ERR_BAD_ARG;
+  moe_ep_layout_t L;
+  moe::MxEpLocal P;
+  moe::mx_ep_layouts(*cfg, max_tokens, &L, &P);
+  if (local_bytes < L.local_bytes) return MOE_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(local) & 255) return MOE_ERR_BAD_ARG;
+  const int world = cfg->ep_world, rank = cfg->ep_rank;
+  moe::Peers peers;
+  for (int i = 0; i < 8; ++i) peers.base[i] = nullptr;
+  for (int i = 0; i < world; ++i) {
+    if (!exchange[i] || (reinterpret_cast<uintptr_t>(exchange[i]) & 255)) return MOE_ERR_BAD_ARG;
+    peers.base[i] = static_cast<uint8_t*>(exchange[i]);
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  uint8_t* ws = static_cast<uint8_t*>(local);
+  uint8_t* mine = peers.base[rank];
+  int32_t* status = reinterpret_cast<int32_t*>(ws + P.status);
+  int32_t* counters = reinterpret_cast<int32_t*>(ws + P.counters);
+  int32_t* offsets = reinterpret_cast<int32_t*>(ws + P.offsets);
+  int32_t* row_source = reinterpret_cast<int32_t*>(ws + P.row_source);
+  const int n_local = cfg->n_experts / world;
+  const int H = cfg->hidden;
+  int launches = 0;
+  cudaError_t e = cudaMemsetAsync(status, 0, epoch == 1 ? 64 + 256 : 32, stream);
+  if (e != cudaSuccess) return cuda_rc(e);
+
+  // 1. dispatch (peer stores): payload, scale bytes, local expert id, slot, routing weight
+  moe::MxDispatchArgs d;
+  d.x = x_q; d.x_scales = x_scales; d.ids = topk_idx; d.weights = topk_weights;
+  d.tokens = tokens; d.hidden = H; d.topk = cfg->topk; d.world = world; d.rank = rank; d.n_local = n_local; d.cap = L.cap;
+  d.peers = peers;
+  d.off_count = L.recv_count; d.off_expert = L.recv_expert; d.off_slot = L.recv_slot; d.off_weight = L.recv_weight;
+  d.off_q = L.recv_q; d.off_s = L.recv_s; d.off_flags = L.flags_dispatch;
+  d.done = counters;
+  d.epoch = epoch;
+  d.order = order;
+  moe::launch_dependent(moe::mx_ep_dispatch_kernel, dim3(tokens * cfg->topk), dim3(256), 0, stream, d);
+  ++launches;
+
+  // 2. wait for every source (bounded), group the arrivals by local expert
+  moe::GroupArgs g;
+  std::memset(&g, 0, sizeof(g));
+  g.wait = moe::FlagWait{reinterpret_cast<const uint64_t*>(mine + L.flags_dispatch), world, epoch, moe::kWaitNs, status, 200};
+  g.ids32 = reinterpret_cast<const int32_t*>(mine + L.recv_expert);
+  g.n = world * L.cap;
+  g.id_base = 0;
+  g.n_local = n_local;
+  g.topk = 1;
+  g.shared_rows = 0;
+  g.tile = L.token_tile;
+  g.max_chunks = L.max_chunks;
+  g.counts = reinterpret_cast<int32_t*>(ws + P.counts);
+  g.offsets = offsets;
+  g.n_chunks = reinterpret_cast<int32_t*>(ws + P.n_chunks);
+  g.chunks = reinterpret_cast<moe::Chunk*>(ws + P.chunks);
+  g.row_token = row_source;
+  g.status = status;
+  g.seg_counts = reinterpret_cast<const int32_t*>(mine + L.recv_count);
+  g.seg_cap = L.cap;
+  e = moe::launch_group_rows(g, stream, &launches);
+  if (e != cudaSuccess) return cuda_rc(e);
+
+  // 3. arrivals into expert order
+  uint8_t* xg = ws + P.xq;
+  uint8_t* xgs = ws + P.xs;
+  e = moe::launch_gather_mx_rows(mine + L.recv_q, mine + L.recv_s, row_source, offsets + n_local, world * L.cap,
+                                 world * L.cap, H, xg, xgs, stream, &launches);
+  if (e != cudaSuccess) return cuda_rc(e);
+
+  // 4. linear1 + clamped SwiGLU * routing weight + requantisation; linear2
+  moe::MxGemmArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.tile = L.token_tile;
+  a.n_experts = n_local;
+  a.total_rows = L.rows;
+  a.chunks = g.chunks;
+  a.n_chunks = g.n_chunks;
+  a.status = status;
+  int driver_error = 0;
+  a.dual = true;
+  a.k = H; a.m = cfg->inter;
+  a.max_units = L.max_chunks * (cfg->inter / 128);
+  a.act = xg; a.act_scales = xgs;
+  a.w_blocks = w->l1_blocks; a.w_scales = w->l1_scales;
+  a.aq = ws + P.aq; a.as = ws + P.as;
+  a.row_dest = row_source;                                               // grouped row -> arrival index ...
+  a.slot_weight = reinterpret_cast<const float*>(mine + L.recv_weight);  // ... whose routing weight travelled with it
+  a.limit = __bfloat162float(__float2bfloat16_rn(cfg->swiglu_limit));
+  e = moe::launch_gemm_mx(a, stream, &launches, &driver_error);
+  if (driver_error) return MOE_ERR_DRIVER;
+  if (e != cudaSuccess) return cuda_rc(e);
+  a.dual = false;
+  a.k = cfg->inter; a.m = H;
+  a.max_units = L.max_chunks * (H / 128);
+  a.act = ws + P.aq; a.act_scales = ws + P.as;
+  a.w_blocks = w->l2_blocks; a.w_scales = w->l2_scales;
+  a.aq = nullptr; a.as = nullptr;
+  a.out = reinterpret_cast<__nv_bfloat16*>(ws + P.out);
+  a.row_dest = nullptr;
+  a.slot_weight = nullptr;
+  a.limit = 0.f;
+  e = moe::launch_gemm_mx(a, stream, &launches, &driver_error);
+  if (driver_error) return MOE_ERR_DRIVER;
+  if (e != cudaSuccess) return cuda_rc(e);
+
+  // 5. rows go home; 6. wait for all owners, plain slot-order sum
+  moe::ReturnArgs r;
+  r.out = a.out; r.row_source = row_source; r.offsets = offsets;
+  r.recv_slot = reinterpret_cast<const int32_t*>(mine + L.recv_slot);
+  r.n_local = n_local; r.shared_rows = 0; r.hidden = H; r.cap = L.cap; r.world = world; r.rank = rank;
+  r.home_tokens = tokens; r.topk = cfg->topk;
+  r.peers = peers;
+  r.off_slots = L.slots; r.off_flags = L.flags_return;
+  r.done = counters + 1;
+  r.epoch = epoch;
+  moe::launch_dependent(moe::ep_return_kernel, dim3(world * L.cap), dim3(128), 0, stream, r);
+  ++launches;
+  const moe::FlagWait home{reinterpret_cast<const uint64_t*>(mine + L.flags_return), world, epoch, moe::kWaitNs, status, 300};
+  e = moe::launch_combine(reinterpret_cast<const __nv_bfloat16*>(mine + L.slots), nullptr, tokens, cfg->topk, H, 0,
+                          static_cast<__nv_bfloat16*>(y_bf16), stream, &launches, nullptr, &home);
+  moe::note_launches(launches);
   return cuda_rc(e);
 }
 

@@ -163,6 +163,7 @@ int moe_experts_forward(const moe_config_t* cfg, const moe_weights_t* w, const u
   a.row_dest = g.row_dest;
   e = moe::launch_gemm(cfg->gemm_impl, a, stream, &launches, &driver_error);
   if (driver_error) return MOE_ERR_DRIVER;
+  moe::note_launches(launches);
   return cuda_rc(e);
 }
 

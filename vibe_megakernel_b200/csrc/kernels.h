@@ -14,6 +14,9 @@
 
 namespace moe {
 
+// Records how many kernels the entry point that just ran on this thread launched (moe_last_launch_count).
+void note_launches(int n);
+
 // Launch with programmatic stream serialization: the kernel may start while the previous kernel of
 // the stream drains; it must call dependent_wait() before reading what that kernel wrote.
 template <typename... Params, typename... Args>

@@ -198,6 +198,7 @@ int moe_mx_forward(const moe_config_t* cfg, const moe_mx_weights_t* w, const uin
   // 5. fp32 sum over the slots in slot order, one bf16 rounding (megabench/tasks/megamoe.py:176-182)
   e = moe::launch_combine(reinterpret_cast<const __nv_bfloat16*>(ws + L.slots), nullptr, tokens, cfg->topk, cfg->hidden, 0,
                           static_cast<__nv_bfloat16*>(y_bf16), stream, &launches);
+  moe::note_launches(launches);
   return from_cuda(e);
 }
 

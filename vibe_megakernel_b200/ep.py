@@ -52,6 +52,53 @@ def shard_inputs(values: dict[str, torch.Tensor], experts: int, world: int, rank
     return out
 
 
+class PeerBuffers:
+    """One peer-visible exchange buffer per rank and this rank's view of all of them.
+
+    Allocation, CUDA IPC hand-over (the handles travel over ``group``) and release; ``pointers`` is the
+    ``void*[world]`` array the C ABI takes. ``close`` is collective."""
+
+    def __init__(self, lib, exchange_bytes: int, group, device: torch.device):
+        self.lib, self.group, self.device = lib, group, device
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        with torch.cuda.device(device):
+            own = C.c_void_p()
+            handle = C.create_string_buffer(64)
+            _cabi.check("moe_ep_buffer_alloc", lib.moe_ep_buffer_alloc(int(exchange_bytes), C.byref(own), handle))
+            self._own = own.value
+            handles: list = [None] * self.world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            self._opened: list[int] = []
+            ptrs = []
+            for r, raw in enumerate(handles):
+                if r == self.rank:
+                    ptrs.append(self._own)
+                    continue
+                peer = C.c_void_p()
+                _cabi.check("moe_ep_buffer_open", lib.moe_ep_buffer_open(C.create_string_buffer(raw, 64), C.byref(peer)))
+                self._opened.append(peer.value)
+                ptrs.append(peer.value)
+            self.pointers = (C.c_void_p * self.world)(*ptrs)
+
+    def close(self) -> None:
+        if self._own is None:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        for p in self._opened:
+            self.lib.moe_ep_buffer_close(p)
+        dist.barrier(group=self.group)
+        self.lib.moe_ep_buffer_free(self._own)
+        self._own = None
+
+
+def aligned_scratch(nbytes: int, device: torch.device) -> torch.Tensor:
+    buf = torch.empty(int(nbytes) + 256, dtype=torch.uint8, device=device)
+    skew = (-buf.data_ptr()) % 256
+    return buf[skew:skew + int(nbytes)]
+
+
 class EpMoeLayer:
     """The layer of one rank of an expert-parallel group (all ranks on one node, one GPU each)."""
 
@@ -70,28 +117,9 @@ class EpMoeLayer:
         self.cfg = config.c_struct(self.world, self.rank)
         self.layout = _cabi.EpLayout()
         _cabi.check("moe_ep_layout", self.lib.moe_ep_layout(C.byref(self.cfg), max_tokens, C.byref(self.layout)))
-        with torch.cuda.device(self.device):
-            own = C.c_void_p()
-            handle = C.create_string_buffer(64)
-            _cabi.check("moe_ep_buffer_alloc",
-                        self.lib.moe_ep_buffer_alloc(int(self.layout.exchange_bytes), C.byref(own), handle))
-            self._own = own.value
-            handles: list = [None] * self.world
-            dist.all_gather_object(handles, handle.raw, group=group)
-            self._opened: list[int] = []
-            ptrs = []
-            for r, raw in enumerate(handles):
-                if r == self.rank:
-                    ptrs.append(self._own)
-                    continue
-                peer = C.c_void_p()
-                _cabi.check("moe_ep_buffer_open", self.lib.moe_ep_buffer_open(C.create_string_buffer(raw, 64), C.byref(peer)))
-                self._opened.append(peer.value)
-                ptrs.append(peer.value)
-            self._exchange = (C.c_void_p * self.world)(*ptrs)
-            buf = torch.empty(int(self.layout.local_bytes) + 256, dtype=torch.uint8, device=self.device)
-            skew = (-buf.data_ptr()) % 256
-            self._local = buf[skew:skew + int(self.layout.local_bytes)]
+        self._peers = PeerBuffers(self.lib, int(self.layout.exchange_bytes), group, self.device)
+        self._exchange = self._peers.pointers
+        self._local = aligned_scratch(int(self.layout.local_bytes), self.device)
         self.epoch = 0
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)
@@ -109,15 +137,16 @@ class EpMoeLayer:
         y = torch.empty_like(x)
         ids = torch.empty((tokens, c.topk), dtype=torch.int64, device=x.device)
         tw = torch.empty((tokens, c.topk), dtype=torch.float32, device=x.device)
+        order = torch.empty((tokens * c.topk,), dtype=torch.int64, device=x.device)
         self.epoch += 1
         stream = torch.cuda.current_stream(x.device).cuda_stream
         rc = self.lib.moe_ep_forward(C.byref(self.cfg), C.byref(w), x.data_ptr(), tokens, self.max_tokens, y.data_ptr(),
-                                     ids.data_ptr(), tw.data_ptr(), self._exchange, self._local.data_ptr(),
-                                     self._local.numel(), self.epoch, stream)
+                                     ids.data_ptr(), tw.data_ptr(), order.data_ptr(), self._exchange,
+                                     self._local.data_ptr(), self._local.numel(), self.epoch, stream)
         _cabi.check("moe_ep_forward", rc)
         if check_status:
             self.check_device_status()
-        return {"y": y, "expert_ids": ids, "topk_weights": tw}
+        return {"y": y, "expert_ids": ids, "topk_weights": tw, "order": order}
 
     __call__ = forward
 
@@ -128,14 +157,10 @@ class EpMoeLayer:
         if rc != 0:
             raise _cabi.MoeError("device status", rc, detail.value)
 
+    def launches(self) -> int:
+        """Kernels the last ``forward`` of this thread launched."""
+        return int(self.lib.moe_last_launch_count())
+
     def close(self) -> None:
         """Collective: every rank must call it, with no layer call in flight."""
-        if self._own is None:
-            return
-        torch.cuda.synchronize(self.device)
-        dist.barrier(group=self.group)
-        for p in self._opened:
-            self.lib.moe_ep_buffer_close(p)
-        dist.barrier(group=self.group)
-        self.lib.moe_ep_buffer_free(self._own)
-        self._own = None
+        self._peers.close()
