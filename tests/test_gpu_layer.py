@@ -151,13 +151,16 @@ def test_run_twice_is_bit_identical_and_depends_on_every_input(api):
         assert not torch.equal(first["y"], other["y"]), f"output ignores {name}"
 
 
-@pytest.mark.parametrize("name,tokens", [("ds_small", 40), ("kimi_small", 7), ("mixtral_small", 130), ("long_k", 21)])
+@pytest.mark.parametrize("name,tokens", [("ds_small", 40), ("kimi_small", 7), ("mixtral_small", 130), ("long_k", 21),
+                                         ("long_k", 5), ("ds_small", 16), ("tiny", 1)])
 def test_gemm_handover_and_separate_kernels_agree(api, name, tokens):
-    # Stage timing runs the two GEMMs strictly one after the other; a plain call lets the down
-    # GEMM start on finished chunks of the gate/up GEMM. Both orders give the same bits.
+    # Stage timing runs the two GEMMs strictly one after the other and the combine as a kernel of its
+    # own; a plain call lets the down GEMM start on finished chunks of the gate/up GEMM and, up to 16
+    # tokens, do the combine itself (the CTA that stores a token's last row). Same bits either way.
     geo = H.small_geometries()[name]
     values, _ = H.audited_inputs(geo, tokens)
     layer, plain = run_layer(api, geo, values)
+    plain_launches = layer.launches()
     dev = H.to_device(values, "cuda")
     layer.profile(True)
     try:
@@ -166,6 +169,7 @@ def test_gemm_handover_and_separate_kernels_agree(api, name, tokens):
     finally:
         layer.profile(False)
     assert set(stages) == set(layer.STAGES) and all(v >= 0 for v in stages.values())
+    assert layer.launches() == 7 and plain_launches <= (6 if tokens <= 16 else 7)     # no combine launch up to 16 tokens
     for _ in range(3):
         again = layer.forward(dev, check_status=True)
         for k in plain:

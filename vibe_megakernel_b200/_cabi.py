@@ -3,6 +3,7 @@
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 from . import build as _build
@@ -101,7 +102,9 @@ _lib = None
 
 
 def library_path() -> Path:
-    return _build.LIB
+    """The in-tree library, or the one MOE_B200_LIB names (a build with other compile-time options)."""
+    override = os.environ.get("MOE_B200_LIB")
+    return Path(override) if override else _build.LIB
 
 
 def load(build_if_missing: bool = True) -> C.CDLL:

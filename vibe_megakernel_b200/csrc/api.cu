@@ -44,6 +44,11 @@ int check_config(const moe_config_t* c) {
 }
 
 
+// Tokens whose combine the down GEMM does itself (0: the combine kernel runs): small batches on one GPU.
+inline int fold_tokens(const moe_config_t* c, int tokens) {
+  return (c->ep_world == 1 && tokens <= moe::kFoldMaxTokens) ? tokens : 0;
+}
+
 int layout_of(const moe_config_t* c, int tokens, moe_workspace_layout_t* L) {
   const int rc = check_config(c);
   if (rc) return rc;
@@ -65,7 +70,7 @@ int layout_of(const moe_config_t* c, int tokens, moe_workspace_layout_t* L) {
   l.counts = take(4ull * (n_local + 1));
   l.offsets = take(4ull * (n_local + 2));
   l.n_chunks = take(4);
-  l.chunks = take(moe::work_list_layout(max_chunks, c->hidden, c->inter, tile).bytes);   // work items, counters, partial tiles
+  l.chunks = take(moe::work_list_layout(max_chunks, c->hidden, c->inter, tile, fold_tokens(c, tokens)).bytes);   // work items, counters, partial tiles
   l.row_token = take(4ull * rows);
   l.row_dest = take(4ull * rows);
   l.xq = take(static_cast<uint64_t>(rows) * H);
@@ -242,13 +247,15 @@ static int layer_forward_impl(const moe_config_t* cfg, const moe_weights_t* w, c
   g.order = order;
   g.status = status;
   g.zero_status = 1;       // no kernel before the permutation reports, so no memset node in front of the call
-  const moe::WorkListLayout W = moe::work_list_layout(L.max_chunks, cfg->hidden, cfg->inter, L.token_tile);
+  const moe::WorkListLayout W = moe::work_list_layout(L.max_chunks, cfg->hidden, cfg->inter, L.token_tile,
+                                                      fold_tokens(cfg, tokens));
   g.progress = reinterpret_cast<int32_t*>(ws + L.chunks + W.counters);
   g.progress_len = W.counters_len;
 
   // The shared expert's weights are needed whatever the router decides: the logits kernel asks
   // the L2 for them while HBM has little else to do.
   moe::L2Warm warm = {};
+  warm.stamp = status;
   if (cfg->n_shared) {
     const uint64_t bytes = static_cast<uint64_t>(cfg->inter) * cfg->hidden;
     warm.ptr[0] = w->shared_gate; warm.bytes[0] = bytes;
@@ -295,14 +302,15 @@ static int layer_forward_impl(const moe_config_t* cfg, const moe_weights_t* w, c
   int driver_error = 0;
 
   // One tile of rows in all (batch 1) and a partial last wave of gate/up items: the CTAs of the two GEMMs
-  // are sized to be resident on an SM together, so that down items run beside the last gate/up items.
+  // are sized to be resident on an SM together (rings of 3 and 2 steps), so that down items run beside the
+  // last gate/up items.
   // (Only when the gate/up items make more than one wave: a single full wave streams at the HBM rate
   // and would only lose its deeper ring. Measured at batch 1: Mixtral shape 101 -> 90 us with, DeepSeek
   // shape 110 -> 114 us with.)
   const bool together = a.progress != nullptr && L.rows <= 16 &&
                         static_cast<long long>(std::min(L.rows, n_local + cfg->n_shared)) * (cfg->inter / 128) > sm_count();
   a.dual = true;
-  a.max_stages = together ? 4 : 0;
+  a.max_stages = together ? 3 : 0;
   a.k = cfg->hidden;
   a.m = cfg->inter;
   a.max_units = L.max_chunks * (cfg->inter / 128);
@@ -328,7 +336,7 @@ static int layer_forward_impl(const moe_config_t* cfg, const moe_weights_t* w, c
 
   mark(4, stream);
   a.dual = false;
-  a.max_stages = together ? 3 : 0;
+  a.max_stages = together ? 2 : 0;
   a.k = cfg->inter;
   a.m = cfg->hidden;
   a.max_units = L.max_chunks * (cfg->hidden / 128);
@@ -346,14 +354,27 @@ static int layer_forward_impl(const moe_config_t* cfg, const moe_weights_t* w, c
   a.out = slots;
   a.row_dest = row_dest;
   a.swiglu = moe::SwigluMode{};
+  // Small batches: the CTA that stores a token's last slot row of a channel tile adds the rows up
+  // itself (the combine kernel's arithmetic on the same stored rows), which saves the launch.
+  const bool fold = !g_profile && cfg->gemm_impl == MOE_GEMM_TCGEN05 && fold_tokens(cfg, tokens) > 0;
+  if (fold) {
+    a.fold.y = static_cast<__nv_bfloat16*>(y_bf16);
+    a.fold.weights = cfg->weight_before_requant ? nullptr : tw;
+    a.fold.residual = residual;
+    a.fold.count = reinterpret_cast<int32_t*>(ws + L.chunks + W.fold_count);
+    a.fold.tokens = tokens;
+    a.fold.topk = cfg->topk;
+    a.fold.shared = cfg->n_shared;
+  }
   e = moe::launch_gemm(cfg->gemm_impl, a, stream, &launches, &driver_error);
   if (driver_error) return MOE_ERR_DRIVER;
   if (e != cudaSuccess) return from_cuda(e);
 
   // 6. weighted combine in slot order, plus the shared expert's row
   mark(5, stream);
-  e = moe::launch_combine(slots, cfg->weight_before_requant ? nullptr : tw, tokens, cfg->topk, cfg->hidden, cfg->n_shared, static_cast<__nv_bfloat16*>(y_bf16),
-                          stream, &launches, residual);
+  if (!fold)
+    e = moe::launch_combine(slots, cfg->weight_before_requant ? nullptr : tw, tokens, cfg->topk, cfg->hidden, cfg->n_shared,
+                            static_cast<__nv_bfloat16*>(y_bf16), stream, &launches, residual);
   mark(6, stream);
   g_last_launches = launches;
   return from_cuda(e);

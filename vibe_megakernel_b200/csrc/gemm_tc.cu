@@ -76,10 +76,14 @@ struct GemmCfg {
   static constexpr int kEpiThreads = kEpiWarps * 32;
   static constexpr int kThreads = 96 + kEpiThreads;
   static constexpr int kCpt = NT / (kEpiWarps / 4);   // token columns per epilogue thread
+  // A pipeline step carries two weight tiles and feeds two accumulators: gate and up of one K block
+  // (DUAL), or two consecutive K blocks of the down projection with their token tiles. The fixed cost
+  // of a step in the MMA warp (waits, election, commits: 500-600 cycles) is the same either way; with
+  // one 16 KB tile per step it, not HBM, set the pace of a down-projection CTA at small batches.
   static constexpr int kABytes = 128 * 128;
   static constexpr int kBBytes = NT * 128;
-  static constexpr int kStageBytes = (DUAL ? 2 : 1) * kABytes + kBBytes;
-  static constexpr int kAccCols = (DUAL ? 2 : 1) * NT;
+  static constexpr int kStageBytes = 2 * kABytes + (DUAL ? 1 : 2) * kBBytes;
+  static constexpr int kAccCols = 2 * NT;
   static constexpr int kAcc = 512 / kAccCols < kMaxAccStages ? 512 / kAccCols : kMaxAccStages;
   static constexpr int kTmemCols = kAcc * kAccCols < 32 ? 32 : kAcc * kAccCols;   // a power of two
   // Shared memory after the stage ring, for a contraction of kb K blocks:
@@ -139,6 +143,14 @@ __device__ __forceinline__ void k_range(int kblocks, int parts, int part, int& l
   hi = min(kblocks, lo + per);
 }
 
+// K blocks of the step that starts at `kb` in an item covering [.., hi): two for the down
+// projection unless the item ends or a part of a split contraction ends after the first.
+template <bool DUAL>
+__device__ __forceinline__ int step_blocks(int kb, int hi, int part_len) {
+  if constexpr (DUAL) return 1;
+  return (kb + 1 < hi && (kb + 1) % part_len != 0) ? 2 : 1;
+}
+
 struct GemmDev {
   const Chunk* chunks;
   const int32_t* n_chunks;
@@ -159,6 +171,7 @@ struct GemmDev {
   float* partial;          // ksplit > 1: fp32 [tile index][part][NT columns][128 channels]
   int32_t* parts_done;     // ksplit > 1: per (chunk, channel tile) count of finished parts, zero on entry
   SwigluMode swiglu;       // DUAL: clamp and routing weight of the MegaMoE form, off by default
+  FoldCombine fold;        // !DUAL: the combine, done by whoever stores a token's last slot row of a channel tile
 };
 
 template <int NT, bool DUAL>
@@ -222,6 +235,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const bool handover = !DUAL && p.progress != nullptr;
   if (!handover) dependent_wait();
   dependents_may_launch();
+  if (DUAL && threadIdx.x == 0) MOE_STAMP_FIRST(p.status, 5);
   PROBE_START(t_cta);
   const int n_chunks = *p.n_chunks;
   // A long contraction of the down GEMM is summed in `ksplit` parts, each from zero, added in part
@@ -236,6 +250,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     if (spread) k_range(KB, ksplit, part, lo, hi);
     else { lo = 0; hi = KB; }
   };
+  const int part_len = (KB + ksplit - 1) / ksplit;     // K blocks per part (the whole contraction when it is not split)
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -312,10 +327,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const CUtensorMap* mb = shared_e ? &tm_sb : &tm_b;
         const int wrow = (shared_e ? 0 : ch.expert * p.m) + mt * 128;
         const int n16 = (ch.rows + 15) >> 4;
-        const uint32_t bytes = (DUAL ? 2 : 1) * C::kABytes + n16 * 2048;
         int kb_lo, kb_hi;
         item_range(part, kb_lo, kb_hi);
-        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
+        for (int kb = kb_lo; kb < kb_hi; ++it) {
+          const int len = step_blocks<DUAL>(kb, kb_hi, part_len);
+          const uint32_t bytes = (DUAL ? 2 : len) * C::kABytes + (DUAL ? 1 : len) * n16 * 2048;
           PROBE_START(t_stage);
           if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + s, ph ^ 1u, s_abort))) {
             if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 1); *s_abort = 1; }
@@ -326,14 +342,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           uint8_t* st = stages + s * C::kStageBytes;
           if (elect_one()) {
             mbar_expect_tx(bar_full + s, bytes);
+            uint8_t* sb = st + 2 * C::kABytes;
             tma_load_2d(st, ma, kb * 128, wrow, bar_full + s, pol_w);
-            if constexpr (DUAL) tma_load_2d(st + C::kABytes, mb, kb * 128, wrow, bar_full + s, pol_w);
-            uint8_t* sb = st + (DUAL ? 2 : 1) * C::kABytes;
+            if constexpr (DUAL) {
+              tma_load_2d(st + C::kABytes, mb, kb * 128, wrow, bar_full + s, pol_w);
+            } else if (len == 2) {
+              tma_load_2d(st + C::kABytes, ma, (kb + 1) * 128, wrow, bar_full + s, pol_w);
+              for (int j = 0; j < n16; ++j)
+                tma_load_2d(sb + C::kBBytes + j * 2048, &tm_x, (kb + 1) * 128, ch.row0 + j * 16, bar_full + s, pol_x);
+            }
             for (int j = 0; j < n16; ++j) tma_load_2d(sb + j * 2048, &tm_x, kb * 128, ch.row0 + j * 16, bar_full + s, pol_x);
             *s_issued = it + 1;
           }
           __syncwarp();
           if (++s == static_cast<uint32_t>(S)) { s = 0; ph ^= 1u; }
+          kb += len;
         }
       }
     }
@@ -363,7 +386,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const uint32_t idesc = idesc_e4m3(128, ((ch.rows + 15) >> 4) * 16);
         int kb_lo, kb_hi;
         item_range(ch.pad, kb_lo, kb_hi);
-        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
+        for (int kb = kb_lo; kb < kb_hi; ++it) {
+          const int len = step_blocks<DUAL>(kb, kb_hi, part_len);
           const uint32_t as = it % C::kAcc, aph = (it / C::kAcc) & 1u;
           PROBE_START(t_acc);
           bool got = mbar_wait(bar_tempty + as, aph ^ 1u, s_abort);
@@ -388,16 +412,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
             for (int k4 = 0; k4 < 4; ++k4) {
               const uint64_t ad = desc0 + ((k4 * 32) >> 4);
-              const uint64_t bd = ad + (((DUAL ? 2 : 1) * C::kABytes) >> 4);
+              const uint64_t bd = ad + ((2 * C::kABytes) >> 4);
               mma_f8(d0, ad, bd, idesc, k4 > 0 ? 1u : 0u);
-              if constexpr (DUAL) mma_f8(d0 + NT, ad + (C::kABytes >> 4), bd, idesc, k4 > 0 ? 1u : 0u);
+              if constexpr (DUAL) {
+                mma_f8(d0 + NT, ad + (C::kABytes >> 4), bd, idesc, k4 > 0 ? 1u : 0u);
+              } else if (len == 2) {     // the next K block: its own weight tile, token tile and accumulator
+                mma_f8(d0 + NT, ad + (C::kABytes >> 4), bd + (C::kBBytes >> 4), idesc, k4 > 0 ? 1u : 0u);
+              }
             }
             mma_commit(bar_empty + s);     // the stage may be refilled once these MMAs have read it
-            mma_commit(bar_tfull + as);    // the accumulator is complete
+            mma_commit(bar_tfull + as);    // the accumulators are complete
             *s_committed = it + 1;
           }
           __syncwarp();
           if (++s == static_cast<uint32_t>(S)) { s = 0; ph ^= 1u; }
+          kb += len;
         }
       }
     }
@@ -526,8 +555,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       // one CTA runs every part of a split contraction: acc_a restarts at each part's first K
       // block and acc_b (unused by the down GEMM otherwise) keeps the sum of the finished parts
       const bool parts_here = !DUAL && ksplit > 1 && !spread;
-      const int part_len = (KB + ksplit - 1) / ksplit;
-      for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
+      for (int kb = kb_lo; kb < kb_hi; ++it) {
+        const int len = step_blocks<DUAL>(kb, kb_hi, part_len);
+        const bool second = DUAL || len == 2;          // the step's second accumulator holds something
         const uint32_t as = it % C::kAcc, aph = (it / C::kAcc) & 1u;
         PROBE_START(t_tfull);
         if (!failed && !mbar_wait(bar_tfull + as, aph, s_abort)) {
@@ -535,30 +565,33 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           failed = true;
         }
         PROBE_ADD(probe_tfull, t_tfull);
-        if (failed) continue;   // keep in step with the other epilogue threads up to the item's end
+        if (failed) { kb += len; continue; }   // keep in step with the other epilogue threads up to the item's end
         tc_fence_after();
         const bool active = col0 < cend;      // uniform per warp
-        uint32_t ra[C::kCpt], rb[DUAL ? C::kCpt : 1];
+        uint32_t ra[C::kCpt], rb[C::kCpt];
         if (active) {
           const uint32_t t0 = lane_base + as * C::kAccCols + col0;
 #pragma unroll
           for (int g = 0; g < C::kCpt; g += 16) {
             if (col0 + g < cend) {
               tmem_ld16(t0 + g, ra + g);
-              if constexpr (DUAL) tmem_ld16(t0 + NT + g, rb + g);
+              if (second) tmem_ld16(t0 + NT + g, rb + g);
             }
           }
           tmem_wait_ld();
         }
-        // The values are in registers: hand the accumulator back before folding them, which
+        // The values are in registers: hand the accumulators back before folding them, which
         // shortens the round trip that bounds the K blocks per microsecond.
         tc_fence_before();
         mbar_arrive(bar_tempty + as);
         if (m == 0 && epi < 4) *s_drained = it + 1;
         if (active) {
+          // DUAL: gate and up of K block kb share the token scales; else K blocks kb and kb + 1 of
+          // the down projection, folded one after the other into the same sums
           const float wa = ws[kb];
-          const float wb = DUAL ? ws[KB + kb] : 0.f;
+          const float wb = DUAL ? ws[KB + kb] : (second ? ws[kb + 1] : 0.f);
           const float* xs = xs_all + kb * NT + col0;
+          const float* xs2 = DUAL ? xs : xs + NT;
 #pragma unroll
           for (int g = 0; g < C::kCpt; g += 16) {
             if (col0 + g < cend) {
@@ -573,15 +606,28 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 float s0, s1;
                 mul2(wa, wa, x16[j], x16[j + 1], s0, s1);
                 fma2(__uint_as_float(ra[g + j]), __uint_as_float(ra[g + j + 1]), s0, s1, acc_a[g + j], acc_a[g + j + 1]);
-                if constexpr (DUAL) {
+              }
+              if (second) {
+                if constexpr (!DUAL) {
+#pragma unroll
+                  for (int j = 0; j < 16; j += 4)
+                    *reinterpret_cast<float4*>(x16 + j) = *reinterpret_cast<const float4*>(xs2 + g + j);
+                }
+#pragma unroll
+                for (int j = 0; j < 16; j += 2) {
+                  float s0, s1;
                   mul2(wb, wb, x16[j], x16[j + 1], s0, s1);
-                  fma2(__uint_as_float(rb[g + j]), __uint_as_float(rb[g + j + 1]), s0, s1, acc_b[g + j], acc_b[g + j + 1]);
+                  if constexpr (DUAL)
+                    fma2(__uint_as_float(rb[g + j]), __uint_as_float(rb[g + j + 1]), s0, s1, acc_b[g + j], acc_b[g + j + 1]);
+                  else
+                    fma2(__uint_as_float(rb[g + j]), __uint_as_float(rb[g + j + 1]), s0, s1, acc_a[g + j], acc_a[g + j + 1]);
                 }
               }
             }
           }
           if constexpr (!DUAL) {
-            if (parts_here && ((kb + 1) % part_len == 0 || kb + 1 == KB)) {   // a part ends here
+            const int last = kb + len;          // K blocks folded so far
+            if (parts_here && (last % part_len == 0 || last == KB)) {   // a part ends here
 #pragma unroll
               for (int n = 0; n < C::kCpt; ++n) {
                 acc_b[n] = __fadd_rn(acc_b[n], acc_a[n]);
@@ -590,6 +636,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
           }
         }
+        kb += len;
       }
       // One decision for all epilogue threads: nobody may be left alone at a later barrier.
       if (epilogue_any<C::kEpiThreads>(failed || *s_abort)) break;
@@ -601,44 +648,46 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           __threadfence();
           atomicAdd(p.progress + u / p.tiles_m, 1);
         }
-      } else if (spread) {
-        // This part's fp32 sums go to global memory; the CTA that finishes a tile's last part adds
-        // all parts in part order (so the result does not depend on which one that is) and rounds.
-        // destination rows were staged by the scale loader together with the scales
-        int dest[C::kCpt];
+      } else {
+        if (spread) {
+          // This part's fp32 sums go to global memory; the CTA that finishes a tile's last part adds
+          // all parts in part order (so the result does not depend on which one that is) and rounds.
+          // destination rows were staged by the scale loader together with the scales
+          int dest[C::kCpt];
 #pragma unroll
-        for (int n = 0; n < C::kCpt; ++n) dest[n] = sd[col0 + n];
-        const size_t tile_floats = static_cast<size_t>(NT) * 128;
-        float* parts = p.partial + static_cast<size_t>(u) * ksplit * tile_floats;
+          for (int n = 0; n < C::kCpt; ++n) dest[n] = sd[col0 + n];
+          const size_t tile_floats = static_cast<size_t>(NT) * 128;
+          float* parts = p.partial + static_cast<size_t>(u) * ksplit * tile_floats;
 #pragma unroll
-        for (int n = 0; n < C::kCpt; ++n)
-          if (col0 + n < rend) __stcg(parts + ch.pad * tile_floats + (col0 + n) * 128 + m, acc_a[n]);
-        __threadfence();
-        epilogue_sync<C::kEpiThreads>();
-        if (epi == 0 && lane == 0) {
+          for (int n = 0; n < C::kCpt; ++n)
+            if (col0 + n < rend) __stcg(parts + ch.pad * tile_floats + (col0 + n) * 128 + m, acc_a[n]);
           __threadfence();
-          const int before = atomicAdd(p.parts_done + u, 1);
-          __threadfence();
-          *s_last_part = before == ksplit - 1 ? 1 : 0;
-        }
-        epilogue_sync<C::kEpiThreads>();
-        if (*s_last_part) {
+          epilogue_sync<C::kEpiThreads>();
+          if (epi == 0 && lane == 0) {
+            __threadfence();
+            const int before = atomicAdd(p.parts_done + u, 1);
+            __threadfence();
+            *s_last_part = before == ksplit - 1 ? 1 : 0;
+          }
+          epilogue_sync<C::kEpiThreads>();
+          if (*s_last_part) {
 #pragma unroll
-          for (int n = 0; n < C::kCpt; ++n) {
-            if (col0 + n < rend) {
-              float sum = 0.f;
-              for (int part = 0; part < ksplit; ++part)
-                sum = __fadd_rn(sum, __ldcg(parts + part * tile_floats + (col0 + n) * 128 + m));
-              p.out[static_cast<size_t>(dest[n]) * p.m + mt * kGroup + m] = __float2bfloat16_rn(sum);
+            for (int n = 0; n < C::kCpt; ++n) {
+              if (col0 + n < rend) {
+                float sum = 0.f;
+                for (int part = 0; part < ksplit; ++part)
+                  sum = __fadd_rn(sum, __ldcg(parts + part * tile_floats + (col0 + n) * 128 + m));
+                p.out[static_cast<size_t>(dest[n]) * p.m + mt * kGroup + m] = __float2bfloat16_rn(sum);
+              }
             }
           }
-        }
-      } else {
+        } else {
 #pragma unroll
-        for (int n = 0; n < C::kCpt; ++n) {
-          if (col0 + n < rend) {   // one bf16 rounding of the fp32 sum (megabench/tasks/megamoe.py:149)
-            const float sum = parts_here ? acc_b[n] : acc_a[n];
-            p.out[static_cast<size_t>(sd[col0 + n]) * p.m + mt * kGroup + m] = __float2bfloat16_rn(sum);
+          for (int n = 0; n < C::kCpt; ++n) {
+            if (col0 + n < rend) {   // one bf16 rounding of the fp32 sum (megabench/tasks/megamoe.py:149)
+              const float sum = parts_here ? acc_b[n] : acc_a[n];
+              p.out[static_cast<size_t>(sd[col0 + n]) * p.m + mt * kGroup + m] = __float2bfloat16_rn(sum);
+            }
           }
         }
       }
@@ -650,6 +699,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (threadIdx.x == 0) MOE_STAMP_LAST(p.status, DUAL ? 6 : 7);
   if (threadIdx.x == 0) {
     PROBE_DECL(probe_cta);
     PROBE_ADD(probe_cta, t_cta);
@@ -663,6 +713,55 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kTmemCols) : "memory");
+  }
+  if constexpr (!DUAL) {
+    if (p.fold.y) {
+      // Small batches: the combine without a launch of its own. Every CTA of this grid is resident
+      // (at most one per SM, and nothing it waits for depends on a CTA that is not), so the grid can
+      // meet here: each CTA announces that its slot rows are stored, waits (bounded) for all the
+      // others, and then adds up its share of the output in slot order, the combine kernel's
+      // arithmetic on the same stored rows.
+      if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(p.fold.count, 1);
+        if (!wait_counter(p.fold.count, static_cast<int>(gridDim.x))) report(p.status, MOE_ERR_DEVICE_TIMEOUT, 10);
+        __threadfence();
+      }
+      __syncthreads();
+      const int vectors = p.m / 8;                      // 8 channels per thread
+      const int routed = p.fold.tokens * p.fold.topk;
+      for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < p.fold.tokens * vectors; v += gridDim.x * blockDim.x) {
+        const int t = v / vectors, c = (v - t * vectors) * 8;
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+        for (int slot = 0; slot < p.fold.topk; ++slot) {
+          const size_t row = static_cast<size_t>(t) * p.fold.topk + slot;
+          const float w = p.fold.weights ? p.fold.weights[row] : 1.f;
+          const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(p.out + row * p.m + c));
+          const __nv_bfloat16* x8 = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(__bfloat162float(x8[i]), w));
+        }
+        if (p.fold.shared) {
+          const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(p.out + (static_cast<size_t>(routed) + t) * p.m + c));
+          const __nv_bfloat16* x8 = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __bfloat162float(x8[i]));
+        }
+        uint4 packed;
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&packed);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = __float2bfloat16_rn(acc[i]);
+        if (p.fold.residual) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(p.fold.residual + static_cast<size_t>(t) * p.m + c);
+          const __nv_bfloat16* x8 = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = __float2bfloat16_rn(__fadd_rn(__bfloat162float(x8[i]), __bfloat162float(o[i])));
+        }
+        *reinterpret_cast<uint4*>(p.fold.y + static_cast<size_t>(t) * p.m + c) = packed;
+      }
+    }
   }
   // Keep the stream's ordering for whatever follows: this grid does not complete before the
   // gate/up grid has (a CTA that found the dispenser empty idles here until that grid's last
@@ -759,7 +858,7 @@ cudaError_t launch_gemm_tc(const GemmArgs& a, cudaStream_t stream, int* launches
   }
   GemmDev dev{a.chunks, a.n_chunks, a.m / 128, a.k / 128, a.m, a.n_local, a.max_stages, a.act_scale, a.w_a_scale, a.w_b_scale,
               a.s_a_scale, a.s_b_scale, a.aq, a.as, a.out, a.row_dest, a.status, a.progress, a.max_chunks,
-              a.tiles_before, 1, nullptr, nullptr, a.swiglu};
+              a.tiles_before, 1, nullptr, nullptr, a.swiglu, a.dual ? FoldCombine{} : a.fold};
   if (!a.dual && a.ksplit > 1) {
     const int per = (a.k / 128 + a.ksplit - 1) / a.ksplit;
     if (!a.partial || !a.parts_done || (a.ksplit - 1) * per >= a.k / 128 || a.ksplit > 255) return cudaErrorInvalidValue;

@@ -41,6 +41,7 @@ inline cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 b
 struct L2Warm {
   const uint8_t* ptr[3];
   uint64_t bytes[3];
+  int32_t* stamp;      // status words for the optional timeline (-DMOE_TIMELINE), else unused
 };
 
 cudaError_t launch_router(const moe_config_t& cfg, const __nv_bfloat16* x, const float* router, const float* bias,
@@ -134,17 +135,25 @@ inline int down_ksplit(int inter) {
 // The work list's region of a workspace: the chunks, then the int32 counters the permutation
 // kernel zeroes (per-chunk gate/up progress, 4 spare words of which the first is the down GEMM's
 // dispenser, and with a split contraction one counter per down tile), then the fp32 partial tiles.
+// Small batches of the one-GPU layer: the combine is done by the down GEMM itself. Its CTAs meet
+// at the kernel's end (one counter, bounded wait) and then share out the sum of the slot rows, in
+// slot order, exactly as the combine kernel would (same bits: the sum is a function of the stored
+// bf16 rows). Saves a launch where a layer call is a few tens of microseconds.
+constexpr int kFoldMaxTokens = 16;
+
 struct WorkListLayout {
-  uint64_t counters, parts_done, partial, bytes;   // byte offsets from the first chunk
+  uint64_t counters, parts_done, fold_count, partial, bytes;   // byte offsets from the first chunk
   int counters_len;
 };
-inline WorkListLayout work_list_layout(int max_chunks, int hidden, int inter, int tile) {
+inline WorkListLayout work_list_layout(int max_chunks, int hidden, int inter, int tile, int fold_tokens = 0) {
   const int ksplit = down_ksplit(inter);
   const int tiles_down = hidden / 128;
   WorkListLayout w;
   w.counters = 16ull * max_chunks;
-  w.counters_len = max_chunks + 4 + (ksplit > 1 ? max_chunks * tiles_down : 0);
+  const int parts_len = ksplit > 1 ? max_chunks * tiles_down : 0;
+  w.counters_len = max_chunks + 4 + parts_len + (fold_tokens > 0 ? 4 : 0);
   w.parts_done = w.counters + 4ull * (max_chunks + 4);
+  w.fold_count = w.parts_done + 4ull * parts_len;
   uint64_t off = w.counters + 4ull * w.counters_len;
   off = (off + 255) / 256 * 256;
   w.partial = off;
@@ -162,6 +171,15 @@ struct SwigluMode {
   const float* slot_weight = nullptr;
   const int32_t* row_dest = nullptr;
   int routed_rows = 0;
+};
+
+// The combine folded into the down GEMM (see kFoldMaxTokens).
+struct FoldCombine {
+  __nv_bfloat16* y = nullptr;            // [tokens, hidden]; NULL = off
+  const float* weights = nullptr;        // [tokens*topk], NULL = the rows carry their weight already
+  const __nv_bfloat16* residual = nullptr;   // optional [tokens, hidden]: y = bf16(residual + bf16(sum))
+  int32_t* count = nullptr;              // one counter of the CTAs that have stored their rows, zero on entry
+  int tokens = 0, topk = 0, shared = 0;
 };
 
 struct GemmArgs {
@@ -203,6 +221,7 @@ struct GemmArgs {
   float* partial;
   int32_t* parts_done;
   SwigluMode swiglu;         // dual only
+  FoldCombine fold;          // down GEMM only: the combine done by the last tile of every token (y == NULL: off)
   int max_stages;            // > 0: cap of the shared-memory ring, so that the CTAs of the call's two GEMMs fit on an SM together
   bool bf16_operands;        // CUDA-core arm only: operands dequantised and rounded to bf16 first (MOE_GEMM_SIMT_BF16)
 };

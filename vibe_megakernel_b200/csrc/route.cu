@@ -286,7 +286,12 @@ __global__ void __launch_bounds__(WARPS * 32) route_group_quant_kernel(FusedArgs
   const int my_row = static_cast<int>(blockIdx.x) - 1;
   dependent_wait();
   dependents_may_launch();
+#ifdef MOE_TIMELINE
+  if (tid == 0) MOE_STAMP_LAST(a.g.status, 3);
+  if (a.g.zero_status && a.g.status && publisher && tid < 2) a.g.status[tid] = 0;
+#else
   if (a.g.zero_status && a.g.status && publisher && tid < 8) a.g.status[tid] = 0;
+#endif
 
   for (int t = warp; t < T; t += WARPS) {       // a warp per token, two rounds beyond 32 tokens
     int pick;
@@ -351,6 +356,10 @@ __global__ void __launch_bounds__(WARPS * 32) route_group_quant_kernel(FusedArgs
     __syncthreads();
     group_publish(a.g, s_count, s_offset, s_chunk0, tid, WARPS * 32);
   }
+#ifdef MOE_TIMELINE
+  __syncthreads();
+  if (tid == 0) MOE_STAMP_LAST(a.g.status, 4);
+#endif
 }
 
 // True when the register variant applies: E fills whole lanes and groups are whole power-of-two

@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(kRowsWarps * 32) router_logits_rows_kernel(con
                                                                               float* __restrict__ logits,
                                                                               const L2Warm warm, int logit_blocks) {
   extern __shared__ __align__(128) uint8_t s_rows_raw[];
+  if (threadIdx.x == 0) MOE_STAMP_FIRST(warm.stamp, 2);
   if (static_cast<int>(blockIdx.x) >= logit_blocks) {   // weights do not change: no need to wait for anything
     if (blockIdx.y == 0) warm_l2(warm, blockIdx.x - logit_blocks, gridDim.x - logit_blocks);
     return;
@@ -235,6 +236,7 @@ cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* router, in
   const dim3 rows_block(kRowsWarps * 32);
   L2Warm warm = {};
   int extra = 0;
+  if (warm_request) warm.stamp = warm_request->stamp;
   if (warm_request) {
     for (int r = 0; r < 3; ++r) {
       if (warm_request->ptr[r] && !(reinterpret_cast<uintptr_t>(warm_request->ptr[r]) & 15)) {
