@@ -11,14 +11,17 @@ namespace moe {
 
 // Exclusive prefix of rows and of chunks per expert, by one warp: each lane owns a run of experts.
 // s_count[groups] in, s_offset[groups + 1] and s_chunk0[groups + 1] out (the caller synchronises).
+// `tile` is a power of two (1, 16, 32 or 64): the chunk counts are shifts, not divisions (a serial
+// run of divisions per lane was a microsecond of the small-batch routing kernel's critical path).
 __device__ __forceinline__ void group_prefix(const int* s_count, int* s_offset, int* s_chunk0, int groups, int tile,
                                              int lane) {
   const int per = (groups + 31) / 32;
   const int first = lane * per, last = min(first + per, groups);
+  const int shift = __ffs(tile) - 1;
   int rows = 0, chunks = 0;
   for (int e = first; e < last; ++e) {
     rows += s_count[e];
-    chunks += (s_count[e] + tile - 1) / tile;
+    chunks += (s_count[e] + tile - 1) >> shift;
   }
   int rows_before = rows, chunks_before = chunks;
 #pragma unroll
@@ -33,7 +36,7 @@ __device__ __forceinline__ void group_prefix(const int* s_count, int* s_offset, 
     s_offset[e] = rows_before;
     s_chunk0[e] = chunks_before;
     rows_before += s_count[e];
-    chunks_before += (s_count[e] + tile - 1) / tile;
+    chunks_before += (s_count[e] + tile - 1) >> shift;
   }
   if (last == groups && first < groups) {   // the lane holding the final expert closes the prefix
     s_offset[groups] = rows_before;
@@ -56,7 +59,7 @@ __device__ __forceinline__ void group_publish(const GroupArgs& a, const int* s_c
   for (int i = tid; i < groups; i += nthreads) {
     a.counts[i] = s_count[i];
     const int c = s_count[i];
-    const int nch = (c + a.tile - 1) / a.tile;
+    const int nch = (c + a.tile - 1) >> (__ffs(a.tile) - 1);      // the tile is a power of two
     for (int j = 0; a.chunks && j < nch; ++j) {
       const int slot = i == a.n_local ? j : shared_chunks + s_chunk0[i] + j;
       if (slot < a.max_chunks) {

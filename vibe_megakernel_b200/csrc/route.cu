@@ -148,8 +148,10 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_select_kernel(RouteArg
 // step is shuffles over registers instead of shared-memory sweeps. Same rules, same tie order
 // (larger value first, lower expert index on equal values).
 // One warp selects for token t; lane j < topk returns choice j and its weight.
+// `bias_regs` (optional): this lane's EPL bias values, loaded by the caller ahead of time.
 template <int EPL>
-__device__ __forceinline__ void select_in_registers(const RouteArgs& a, int t, int lane, int& pick, float& weight) {
+__device__ __forceinline__ void select_in_registers(const RouteArgs& a, int t, int lane, int& pick, float& weight,
+                                                    const float* bias_regs = nullptr) {
   const int E = a.experts;
   const float ninf = __int_as_float(0xff800000);
   const bool sigmoid = normalised_scoring(a.scoring);    // sigmoid-like: grouped, normalised weights
@@ -160,7 +162,7 @@ __device__ __forceinline__ void select_in_registers(const RouteArgs& a, int t, i
   for (int i = 0; i < EPL; ++i) s[i] = __ldg(a.logits + static_cast<size_t>(t) * E + e0 + i);
   const bool biased = a.scoring != MOE_SCORING_SOFTMAX && a.bias != nullptr;
 #pragma unroll
-  for (int i = 0; i < EPL; ++i) b[i] = biased ? __ldg(a.bias + e0 + i) : 0.f;
+  for (int i = 0; i < EPL; ++i) b[i] = !biased ? 0.f : bias_regs ? bias_regs[i] : __ldg(a.bias + e0 + i);
 #pragma unroll
   for (int i = 0; i < EPL; ++i) score_of(a.scoring, s[i], b[i], p[i], c[i]);
   if (sigmoid && a.n_group > 1) {
@@ -284,6 +286,12 @@ __global__ void __launch_bounds__(WARPS * 32) route_group_quant_kernel(FusedArgs
   const int T = a.r.tokens, K = a.r.topk, R = T * K, E = a.r.experts;
   const bool publisher = blockIdx.x == 0;      // block 0 publishes the tables, block 1 + i quantises grouped row i
   const int my_row = static_cast<int>(blockIdx.x) - 1;
+  // The selection bias is a weight, not a result of the logits kernel: it is fetched while this
+  // kernel still waits for that one (from HBM when the L2 does not hold it, two microseconds).
+  float bias_regs[EPL];
+#pragma unroll
+  for (int i = 0; i < EPL; ++i)
+    bias_regs[i] = (a.r.bias && a.r.scoring != MOE_SCORING_SOFTMAX) ? __ldg(a.r.bias + lane * EPL + i) : 0.f;
   dependent_wait();
   dependents_may_launch();
 #ifdef MOE_TIMELINE
@@ -296,7 +304,7 @@ __global__ void __launch_bounds__(WARPS * 32) route_group_quant_kernel(FusedArgs
   for (int t = warp; t < T; t += WARPS) {       // a warp per token, two rounds beyond 32 tokens
     int pick;
     float w;
-    select_in_registers<EPL>(a.r, t, lane, pick, w);
+    select_in_registers<EPL>(a.r, t, lane, pick, w, bias_regs);
     if (lane < K) {
       s_id[t * K + lane] = static_cast<int16_t>(pick);
       s_w[t * K + lane] = w;
@@ -305,6 +313,9 @@ __global__ void __launch_bounds__(WARPS * 32) route_group_quant_kernel(FusedArgs
   for (int i = tid; i <= E; i += WARPS * 32) s_count[i] = 0;
   if (tid == 0) s_src = 0;
   __syncthreads();
+#if defined(MOE_TIMELINE) && MOE_TIMELINE == 2
+  if (tid == 0) MOE_STAMP_LAST(a.g.status, 5);      // selection done
+#endif
 
   // Stable position of every row: rows of lower experts first, then earlier rows of the same one.
   for (int r = tid; r < R; r += WARPS * 32) {
@@ -321,6 +332,9 @@ __global__ void __launch_bounds__(WARPS * 32) route_group_quant_kernel(FusedArgs
   if (my_row >= R && tid == 0) s_src = my_row - R;   // a row of the shared expert
   if (publisher && tid == 0) s_count[E] = a.g.shared_rows;
   __syncthreads();
+#if defined(MOE_TIMELINE) && MOE_TIMELINE == 2
+  if (tid == 0) MOE_STAMP_LAST(a.g.status, 6);      // positions known
+#endif
 
   if (!publisher) {   // this block's row
     const int groups = (a.hidden + kGroup - 1) / kGroup;
@@ -354,11 +368,15 @@ __global__ void __launch_bounds__(WARPS * 32) route_group_quant_kernel(FusedArgs
       if (a.g.row_dest) a.g.row_dest[pos] = r;
     }
     __syncthreads();
+#if defined(MOE_TIMELINE) && MOE_TIMELINE == 2
+    if (tid == 0) MOE_STAMP_LAST(a.g.status, 7);    // publisher: prefix and per-row outputs written
+#endif
     group_publish(a.g, s_count, s_offset, s_chunk0, tid, WARPS * 32);
   }
 #ifdef MOE_TIMELINE
   __syncthreads();
   if (tid == 0) MOE_STAMP_LAST(a.g.status, 4);
+
 #endif
 }
 
