@@ -235,7 +235,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const bool handover = !DUAL && p.progress != nullptr;
   if (!handover) dependent_wait();
   dependents_may_launch();
+#if !defined(MOE_TIMELINE) || MOE_TIMELINE == 1
   if (DUAL && threadIdx.x == 0) MOE_STAMP_FIRST(p.status, 5);
+#endif
   PROBE_START(t_cta);
   const int n_chunks = *p.n_chunks;
   // A long contraction of the down GEMM is summed in `ksplit` parts, each from zero, added in part
@@ -699,7 +701,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+#if !defined(MOE_TIMELINE) || MOE_TIMELINE == 1
   if (threadIdx.x == 0) MOE_STAMP_LAST(p.status, DUAL ? 6 : 7);
+#endif
   if (threadIdx.x == 0) {
     PROBE_DECL(probe_cta);
     PROBE_ADD(probe_cta, t_cta);
