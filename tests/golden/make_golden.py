@@ -352,6 +352,45 @@ def megamoe_native_vectors():
     np.savez_compressed(HERE / "megamoe_native.npz", **out)
 
 
+def kimi_latent_vectors():
+    """The MoE block of the Kimi-K3 layer: ``kimi_layer.moe(case, values, normalized, serial=True,
+    group=None)`` (megabench/tasks/kimi_layer.py:189-230) on two reductions of the catalog geometry
+    (megabench/cases.py:315-324), inputs from the reference's own generator."""
+    from dataclasses import replace
+    from megabench.cases import select_cases
+    from megabench.tasks import kimi_layer
+    from megabench.tasks.distributed import matrix
+    out = {}
+    catalog = [case for case in select_cases("all") if case.id == "kimi-k3-kda-layer-ep8"][0]
+    cases = {
+        "small": (replace(catalog, gpus=1, ep=1, params=catalog.params | {
+            "batch": 5, "experts": 12, "topk": 4, "hidden": 128, "latent_hidden": 128, "intermediate": 128,
+            "shared_experts": 2}), 3),
+        "one": (replace(catalog, gpus=1, ep=1, params=catalog.params | {
+            "batch": 1, "experts": 16, "topk": 6, "hidden": 256, "latent_hidden": 128, "intermediate": 128,
+            "shared_experts": 1}), 8),
+    }
+    keys = ("router", "router_bias", "latent_down", "latent_up", "latent_norm", "gate_blocks", "gate_scales", "up_blocks",
+            "up_scales", "down_blocks", "down_scales", "shared_gate", "shared_up", "shared_down")
+    for name, (case, seed) in cases.items():
+        p = case.params
+        # only the tensors of the MoE block (kimi_layer.make_inputs also builds the attention block's)
+        values = {k: v for k, v in kimi_layer.make_inputs(case, seed, "cpu", rank=0).items() if k in keys}
+        normalized = matrix(seed, "normalized", p["batch"], p["hidden"], 1, "cpu")
+        y, sorted_ids = kimi_layer.moe(case, values, normalized, serial=True, group=None)
+        for k, v in values.items():
+            out[f"{name}_{k}"] = bf16_bits(v) if v.dtype == torch.bfloat16 else v.numpy()
+        out[f"{name}_normalized"] = bf16_bits(normalized)
+        out[f"{name}_y"], out[f"{name}_sorted_ids"] = bf16_bits(y), sorted_ids.numpy()
+        out[f"{name}_geo"] = np.array([p["batch"], p["experts"], p["topk"], p["hidden"], p["latent_hidden"],
+                                       p["intermediate"], p["shared_experts"], seed], dtype=np.int64)
+    a = (torch.randn((7, 96), generator=torch.Generator().manual_seed(4)) * 8).to(torch.bfloat16)
+    b = (torch.randn((7, 96), generator=torch.Generator().manual_seed(5)) * 40).to(torch.bfloat16)
+    from megabench.tasks.kimi import situ
+    out["situ_gate"], out["situ_up"], out["situ_out"] = bf16_bits(a), bf16_bits(b), bf16_bits(situ(a, b))
+    np.savez_compressed(HERE / "kimi_latent.npz", **out)
+
+
 def block_vectors():
     """RMSNorm -> layer -> residual add, as megabench/tasks/frontier.py:335-354 strings them together."""
     import dataclasses
@@ -387,5 +426,6 @@ if __name__ == "__main__":
     megamoe_swiglu_vectors()
     megamoe_native_vectors()
     linear_vectors()
+    kimi_latent_vectors()
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size)

@@ -5,6 +5,7 @@ import dataclasses
 import numpy as np
 import torch
 
+from oracle import kimi_oracle as K
 from oracle import megamoe_oracle as M
 from oracle import moe_oracle as O
 from vibe_megakernel_b200 import synthetic
@@ -224,6 +225,27 @@ def test_megamoe_native_layer(golden_dir):
         assert values["x_scales"].shape == (tokens, hidden // 32)
         got = M.megamoe_layer(values, topk, float(limit))
         assert np.array_equal(got["y"].view(torch.int16).numpy(), g[f"{name}_y"])
+
+
+def kimi_golden_case(g, name):
+    """(values, normalized, topk) of a stored Kimi latent-MoE case."""
+    bf = ("router", "latent_down", "latent_up", "latent_norm", "shared_gate", "shared_up", "shared_down")
+    raw = ("router_bias", "gate_blocks", "gate_scales", "up_blocks", "up_scales", "down_blocks", "down_scales")
+    values = {k: bf16(g[f"{name}_{k}"]) for k in bf}
+    values.update({k: torch.from_numpy(g[f"{name}_{k}"].copy()) for k in raw})
+    return values, bf16(g[f"{name}_normalized"]), int(g[f"{name}_geo"][2])
+
+
+def test_kimi_latent_moe_block(golden_dir):
+    # megabench/tasks/kimi_layer.py:189-230 (serial) and the situ activation of megabench/tasks/kimi.py:134-135
+    g = np.load(golden_dir / "kimi_latent.npz")
+    got = K.situ(bf16(g["situ_gate"]), bf16(g["situ_up"]))
+    assert np.array_equal(got.view(torch.int16).numpy(), g["situ_out"])
+    for name in ("small", "one"):
+        values, normalized, topk = kimi_golden_case(g, name)
+        out = K.latent_moe(values, normalized, topk)
+        assert np.array_equal(out["sorted_ids"].numpy(), g[f"{name}_sorted_ids"])
+        assert np.array_equal(out["y"].view(torch.int16).numpy(), g[f"{name}_y"]), name
 
 
 def test_weight_generator_uses_the_reference_block_format():
