@@ -45,7 +45,7 @@ extern "C" {
  * It shows how much of the tensor-core path's distance to that reference is operand rounding. */
 #define MOE_GEMM_SIMT_BF16 2
 
-#define MOE_MAX_EXPERTS 512
+#define MOE_MAX_EXPERTS 1024
 #define MOE_MAX_TOPK 16
 
 typedef struct moe_config {
@@ -136,11 +136,13 @@ int moe_route(const moe_config_t* cfg, const void* x_bf16, const float* router, 
  * while serving; an FFI wrapper without an allocator). It has no counterpart in the reference.
  * Same arguments and results as moe_route without the workspace: the scratch lives in a static
  * device array inside the library (about 544 KiB held by every GPU that loads the library).
- * Limits: tokens <= MOE_STATIC_ROUTE_MAX_TOKENS, else MOE_ERR_TOO_LARGE and nothing is launched.
+ * Limits: tokens <= MOE_STATIC_ROUTE_MAX_TOKENS and n_experts <= MOE_STATIC_ROUTE_MAX_EXPERTS, else
+ * MOE_ERR_TOO_LARGE and nothing is launched.
  * The first call on a device looks up the array's address: make it outside any stream capture.
  * All calls on a GPU share the array, so calls that can overlap on the GPU race; keep them on
  * one stream. Calls no cudaMalloc/cudaFree and no allocating library routine. */
 #define MOE_STATIC_ROUTE_MAX_TOKENS 256
+#define MOE_STATIC_ROUTE_MAX_EXPERTS 512
 #define MOE_ERR_TOO_LARGE (-7)
 int moe_route_static(const moe_config_t* cfg, const void* x_bf16, const float* router, const float* router_bias,
                      int32_t tokens, int64_t* expert_ids, float* weights, void* stream);
@@ -185,6 +187,52 @@ int moe_mx_workspace(const moe_config_t* cfg, int32_t tokens, uint64_t* bytes);
 int moe_mx_forward(const moe_config_t* cfg, const moe_mx_weights_t* w, const uint8_t* x_q, const uint8_t* x_scales,
                    const int64_t* topk_idx, const float* topk_weights, int32_t tokens, void* y_bf16, int64_t* order,
                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* The MoE block of the Kimi-K3 decoder layer, all experts on one GPU. Replaces `moe(case, values,
+ * normalized, serial=True, group=None)` of megabench/tasks/kimi_layer.py:189-230: sigmoid top-k routing
+ * with a selection bias (scaling 1, no groups), a bf16 down-projection of every token into the latent
+ * width, routed experts with MXFP4 weights over the bf16 latent rows and the situ activation
+ * (megabench/tasks/kimi_layer.py:175-186, megabench/tasks/kimi.py:134-135), the fp32 slot-order weighted
+ * sum rounded to bf16, RMSNorm and up-projection of the latent sum, and the shared experts on the
+ * full-width token; the two results are added. Device pointers; layouts as
+ * megabench/tasks/kimi_layer.py:107-125 makes them. */
+typedef struct moe_latent_config {
+  int32_t hidden;      /* H, multiple of 128 */
+  int32_t latent;      /* latent width L, multiple of 128 */
+  int32_t inter;       /* expert intermediate width I, multiple of 128 */
+  int32_t n_experts;   /* routed experts, at most MOE_MAX_EXPERTS */
+  int32_t topk;
+  int32_t n_shared;    /* shared experts: their matrices are n_shared * I wide */
+  float latent_eps;    /* epsilon of the latent RMSNorm (1e-5 in the reference) */
+} moe_latent_config_t;
+
+typedef struct moe_latent_weights {
+  const float* router;          /* fp32 [E, H] (the reference's bf16 router widened: router.float()) */
+  const float* router_bias;     /* fp32 [E], may be NULL */
+  const void* latent_down;      /* bf16 [L, H] */
+  const void* latent_up;        /* bf16 [H, L] */
+  const void* latent_norm;      /* bf16 [L] */
+  const uint8_t* gate_blocks;   /* [E, I, L/32, 16] E2M1 codes, low nibble = even channel */
+  const uint8_t* gate_scales;   /* [E, I, L/32] E8M0 */
+  const uint8_t* up_blocks;
+  const uint8_t* up_scales;
+  const uint8_t* down_blocks;   /* [E, L, I/32, 16] */
+  const uint8_t* down_scales;   /* [E, L, I/32] */
+  const void* shared_gate;      /* bf16 [n_shared * I, H] */
+  const void* shared_up;
+  const void* shared_down;      /* bf16 [H, n_shared * I] */
+} moe_latent_weights_t;
+
+/* tokens * topk <= 16384 (every routed row travels as two E4M3 rows). */
+int moe_latent_workspace(const moe_latent_config_t* cfg, int32_t tokens, uint64_t* bytes);
+
+/* x bf16 [tokens, H] (the layer's normalised tokens) -> y bf16 [tokens, H]; expert_ids int64 [tokens, topk]
+ * in choice order and topk_weights fp32 [tokens, topk] are optional outputs (the reference returns the
+ * ids sorted per token, megabench/tasks/kimi_layer.py:230). workspace: 256-byte aligned,
+ * moe_latent_workspace() bytes. Block pointers 32-byte, scale pointers 16-byte aligned. */
+int moe_latent_forward(const moe_latent_config_t* cfg, const moe_latent_weights_t* w, const void* x_bf16, int32_t tokens,
+                       void* y_bf16, int64_t* expert_ids, float* topk_weights, void* workspace, size_t workspace_bytes,
+                       void* stream);
 
 /* Stable grouping of `n` routed rows by expert id (the token->expert permutation).
  * Replaces `torch.sort(ids, stable=True)` + `bincount` (megabench/tasks/megamoe.py:137-138,161-165).
@@ -324,7 +372,7 @@ int moe_ep_buffer_free(void* ptr);
 int moe_device_status(const void* workspace, void* stream, int32_t* detail);
 
 /* Number of kernels the last layer call of this thread launched (moe_layer_forward, moe_block_forward,
- * moe_ep_forward, moe_experts_forward, moe_mx_forward, moe_mx_ep_forward). */
+ * moe_ep_forward, moe_experts_forward, moe_mx_forward, moe_mx_ep_forward, moe_latent_forward). */
 int moe_last_launch_count(void);
 
 /* Stage timing for measurements (no counterpart in the reference, whose harness times whole calls

@@ -81,6 +81,20 @@ def test_megamoe_native_argument_checks_need_no_gpu():
     assert lib.moe_mx_forward(C.byref(cfg), None, None, None, None, None, 8, None, None, None, 0, None) == -1
 
 
+def test_latent_moe_argument_checks_need_no_gpu():
+    lib = _cabi.load()
+    need = C.c_uint64(0)
+    cfg = _cabi.LatentConfig(7168, 3584, 3072, 896, 16, 2, 1e-5)                       # megabench/cases.py:315-324
+    assert lib.moe_latent_workspace(C.byref(cfg), 8, C.byref(need)) == 0
+    rows2 = 2 * 8 * 16
+    assert need.value >= rows2 * (3584 + 3072) + 2 * 8 * 16 * 3584                       # split rows, requantised rows, slot rows
+    assert lib.moe_latent_workspace(C.byref(cfg), 1025, None) == -2                      # more than 16384 routed rows
+    assert lib.moe_latent_workspace(C.byref(_cabi.LatentConfig(7168, 3500, 3072, 896, 16, 2, 1e-5)), 8, None) == -2
+    assert lib.moe_latent_workspace(C.byref(_cabi.LatentConfig(7168, 3584, 3072, 2000, 16, 2, 1e-5)), 8, None) == -2
+    assert lib.moe_latent_workspace(C.byref(_cabi.LatentConfig(7168, 3584, 3072, 896, 16, 0, 1e-5)), 8, None) == -1
+    assert lib.moe_latent_forward(C.byref(cfg), None, None, 8, None, None, None, None, 0, None) == -1
+
+
 def test_product_does_not_import_the_oracle():
     for path in (ROOT / "vibe_megakernel_b200").rglob("*.py"):
         assert "oracle" not in path.read_text().replace("the oracle", ""), path

@@ -41,6 +41,19 @@ class MxWeights(C.Structure):
     _fields_ = [(name, C.c_void_p) for name in ("l1_blocks", "l1_scales", "l2_blocks", "l2_scales")]
 
 
+class LatentConfig(C.Structure):
+    _fields_ = [("hidden", C.c_int32), ("latent", C.c_int32), ("inter", C.c_int32), ("n_experts", C.c_int32),
+                ("topk", C.c_int32), ("n_shared", C.c_int32), ("latent_eps", C.c_float)]
+
+
+LATENT_WEIGHT_FIELDS = ("router", "router_bias", "latent_down", "latent_up", "latent_norm", "gate_blocks", "gate_scales",
+                        "up_blocks", "up_scales", "down_blocks", "down_scales", "shared_gate", "shared_up", "shared_down")
+
+
+class LatentWeights(C.Structure):
+    _fields_ = [(name, C.c_void_p) for name in LATENT_WEIGHT_FIELDS]
+
+
 class Layout(C.Structure):
     _fields_ = [(name, C.c_uint64) for name in LAYOUT_OFFSETS] + [
         ("rows", C.c_int32), ("max_chunks", C.c_int32), ("token_tile", C.c_int32), ("reserved", C.c_int32)]
@@ -92,6 +105,9 @@ EXPORTS = {
     "moe_mx_workspace": (C.c_int, [C.POINTER(Config), C.c_int32, C.POINTER(C.c_uint64)]),
     "moe_mx_forward": (C.c_int, [C.POINTER(Config), C.POINTER(MxWeights), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "moe_latent_workspace": (C.c_int, [C.POINTER(LatentConfig), C.c_int32, C.POINTER(C.c_uint64)]),
+    "moe_latent_forward": (C.c_int, [C.POINTER(LatentConfig), C.POINTER(LatentWeights), C.c_void_p, C.c_int32, C.c_void_p,
+                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "moe_device_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]),
     "moe_last_launch_count": (C.c_int, []),
     "moe_profile_enable": (C.c_int, [C.c_int32]),

@@ -30,6 +30,7 @@
 // requantisation with E8M0 scales per 32 channels).
 #include "common.cuh"
 #include "kernels.h"
+#include "split_e4m3.cuh"
 
 namespace moe {
 
@@ -77,6 +78,9 @@ struct MxDev {
   const float* slot_weight;   // DUAL: routing weight of slot row_dest[row] (NULL = 1)
   float limit;                // DUAL: clamp, 0 = none
   int32_t* status;
+  const uint8_t* w_scales_b;  // DUAL: scales of the up rows when they are a tensor of their own (then tm_w2 maps it), else NULL
+  int activation;             // DUAL: 0 = clamped SwiGLU, 1 = situ
+  int pairs;                  // token columns 2j, 2j+1 are the two E4M3 pieces of one bf16 row
 };
 
 __device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
@@ -151,7 +155,8 @@ __device__ __forceinline__ Chunk chunk_at(const Chunk* chunks, int u, int tiles_
 
 template <int NT, bool DUAL>
 __global__ void __launch_bounds__(kMxThreads, 1)
-mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const MxDev p) {
+mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_w2,
+               const __grid_constant__ CUtensorMap tm_x, const MxDev p) {
   using C = MxCfg<NT, DUAL>;
   constexpr int S = C::kStages;
   constexpr int XC = NT > 32 ? NT / 32 : 1;       // scale columns of the token side
@@ -223,8 +228,16 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           for (int kk = 0; kk < nk; ++kk) {
             uint8_t* st = stages + s * C::kStageBytes + kk * C::kSubBytes;
             const int kx = (kb0 + kk) * 128;
-            if constexpr (DUAL) tma_load_3d(st, &tm_w, kx, mt * 128, 2 * ch.expert, bar_full + s, pol_w);   // gate tile, then up tile
-            else tma_load_2d(st, &tm_w, kx, wrow, bar_full + s, pol_w);                                      // x in 4-bit elements
+            if constexpr (DUAL) {
+              if (p.w_scales_b) {     // gate and up rows in tensors of their own: two requests
+                tma_load_2d(st, &tm_w, kx, wrow, bar_full + s, pol_w);
+                tma_load_2d(st + C::kABytes, &tm_w2, kx, wrow, bar_full + s, pol_w);
+              } else {
+                tma_load_3d(st, &tm_w, kx, mt * 128, 2 * ch.expert, bar_full + s, pol_w);   // gate tile, then up tile
+              }
+            } else {
+              tma_load_2d(st, &tm_w, kx, wrow, bar_full + s, pol_w);                        // x in 4-bit elements
+            }
             uint8_t* sx = st + (DUAL ? 2 : 1) * C::kABytes;
             for (int j = 0; j < n16; ++j) tma_load_2d(sx + j * 2048, &tm_x, kx, ch.row0 + j * 16, bar_full + s, pol_x);
           }
@@ -317,7 +330,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         uint8_t* slot = sf_ring + (issued % kMxSfRing) * C::kSfSlotBytes;
         const size_t wrow = static_cast<size_t>(ich.expert) * p.rows_per_expert + (iu % p.tiles_m) * 128 + t;
         copy_scale_group(slot + t * 16, p.w_scales + wrow * KS, ig, KB, vec);
-        if constexpr (DUAL) copy_scale_group(slot + 2048 + t * 16, p.w_scales + (wrow + p.up_offset) * KS, ig, KB, vec);
+        if constexpr (DUAL)
+          copy_scale_group(slot + 2048 + t * 16, p.w_scales_b ? p.w_scales_b + wrow * KS : p.w_scales + (wrow + p.up_offset) * KS,
+                           ig, KB, vec);
         if (t < NT) {
           uint8_t* dst = slot + C::kSfXOffset + t * 16;
           if (t < ich.rows) copy_scale_group(dst, p.x_scales + static_cast<size_t>(ich.row0 + t) * KS, ig, KB, vec);
@@ -411,6 +426,45 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           tc_fence_before();
           mbar_arrive(bar_tempty + ab);
           if (threadIdx.x == 6 * 32) *s_drained = item + 1;
+        }
+        if (p.pairs) {
+          // columns 2q, 2q+1 are the two E4M3 pieces of one bf16 row: their results add up to that
+          // row's (exact products either way, fp32 sums)
+#pragma unroll
+          for (int c = 0; c < 16; c += 2) {
+            const int col = j * 16 + c;
+            if (col >= ch.rows) break;             // uniform across the CTA
+            const size_t row = static_cast<size_t>(ch.row0 + col);      // the hi piece's row; the lo piece follows
+            const bool upper = XC > 1 && col >= 32;
+            const int dest_here = __shfl_sync(0xffffffffu, upper ? dest_of[XC - 1] : dest_of[0], col & 31);
+            if constexpr (DUAL) {
+              const float gate = bf16_round(__fadd_rn(__uint_as_float(g[c]), __uint_as_float(g[c + 1])));
+              const float up = bf16_round(__fadd_rn(__uint_as_float(v[c]), __uint_as_float(v[c + 1])));
+              // megabench/tasks/kimi.py:134-135 (situ) or megabench/tasks/megamoe.py:116-122; one bf16 rounding
+              float act;
+              if (p.activation == 1) {
+                act = situ_f32(gate, up);
+              } else {
+                float gc = gate, uc = up;
+                if (p.limit > 0.f) { gc = fminf(gc, p.limit); uc = fminf(fmaxf(uc, -p.limit), p.limit); }
+                act = __fmul_rn(__fdiv_rn(gc, __fadd_rn(1.f, expf(-gc))), uc);
+              }
+              const float one[1] = {bf16_round(act)};
+              uint8_t hi[1], lo[1];
+              int e_hi, e_lo;
+              split_e4m3(one, 32, hi, lo, e_hi, e_lo);       // the warp's 32 channels are one scale block
+              p.aq[row * p.m + mt * 128 + m] = hi[0];
+              p.aq[(row + 1) * p.m + mt * 128 + m] = lo[0];
+              if (lane == 0) {
+                p.as[row * (p.m / 32) + mt * 4 + quarter] = static_cast<uint8_t>(e_hi);
+                p.as[(row + 1) * (p.m / 32) + mt * 4 + quarter] = static_cast<uint8_t>(e_lo);
+              }
+            } else {
+              p.out[static_cast<size_t>(dest_here >> 1) * p.m + mt * 128 + m] =
+                  __float2bfloat16_rn(__fadd_rn(__uint_as_float(g[c]), __uint_as_float(g[c + 1])));
+            }
+          }
+          continue;
         }
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
@@ -532,22 +586,27 @@ static cudaError_t mx_launch_typed(const MxDev& dev, const CUtensorMap* maps, in
   }
   constexpr int smem = 1024 + C::kStages * C::kStageBytes + kMxSfRing * C::kSfSlotBytes + C::kTailBytes;
   static_assert(smem <= kMxSmem, "shared memory of one CTA");
-  return launch_dependent(mx_gemm_kernel<NT, DUAL>, dim3(grid), dim3(kMxThreads), smem, stream, maps[0], maps[1], dev);
+  return launch_dependent(mx_gemm_kernel<NT, DUAL>, dim3(grid), dim3(kMxThreads), smem, stream, maps[0], maps[2], maps[1], dev);
 }
 
 cudaError_t launch_gemm_mx(const MxGemmArgs& a, cudaStream_t stream, int* launches, int* driver_error) {
   if (a.k % 128 || a.m % 128 || a.n_experts < 1 || (a.tile != 16 && a.tile != 32 && a.tile != 64)) return cudaErrorInvalidValue;
-  const int rows_per_expert = a.dual ? 2 * a.m : a.m;
-  CUtensorMap maps[2];
-  int rc = a.dual ? mx_make_pair_map(&maps[0], a.w_blocks, a.n_experts, a.m, a.k)
-                  : mx_make_map(&maps[0], a.w_blocks, static_cast<uint64_t>(a.n_experts) * rows_per_expert, a.k, true, 128);
+  const bool apart = a.dual && a.w_blocks_b != nullptr;      // gate and up rows in tensors of their own
+  if (apart != (a.dual && a.w_scales_b != nullptr) || (a.pairs && a.tile % 2)) return cudaErrorInvalidValue;
+  const int rows_per_expert = (a.dual && !apart) ? 2 * a.m : a.m;
+  CUtensorMap maps[3];
+  int rc = (a.dual && !apart) ? mx_make_pair_map(&maps[0], a.w_blocks, a.n_experts, a.m, a.k)
+                              : mx_make_map(&maps[0], a.w_blocks, static_cast<uint64_t>(a.n_experts) * rows_per_expert, a.k, true, 128);
   rc = rc ? rc : mx_make_map(&maps[1], a.act, a.total_rows, a.k, false, 16);      // token rows move in boxes of 16
+  if (apart) rc = rc ? rc : mx_make_map(&maps[2], a.w_blocks_b, static_cast<uint64_t>(a.n_experts) * a.m, a.k, true, 128);
+  else maps[2] = maps[0];
   if (rc) {
     if (driver_error) *driver_error = rc;
     return cudaErrorUnknown;
   }
   MxDev dev{a.chunks, a.n_chunks, a.m / 128, a.k / 128, a.m, rows_per_expert, a.dual ? a.m : 0, a.w_scales, a.act_scales,
-            a.aq, a.as, a.out, a.row_dest, a.slot_weight, a.limit, a.status};
+            a.aq, a.as, a.out, a.row_dest, a.slot_weight, a.limit, a.status, apart ? a.w_scales_b : nullptr, a.activation,
+            a.pairs ? 1 : 0};
   int device = 0, sms = 148;
   cudaGetDevice(&device);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);

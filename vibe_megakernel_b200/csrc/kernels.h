@@ -250,6 +250,15 @@ struct MxGemmArgs {
   const float* slot_weight;   // dual: routing weight of slot row_dest[row]; NULL = 1
   float limit;                // dual: clamp of gate/up, 0 = none
   int32_t* status;
+  // dual, optional: the up rows live in a tensor of their own ([n_experts * m, k/2] bytes and scales) instead of
+  // following the gate rows inside w_blocks / w_scales (megabench/tasks/kimi_layer.py:113-120 stores them apart)
+  const uint8_t* w_blocks_b;
+  const uint8_t* w_scales_b;
+  int activation;             // dual: 0 = clamped SwiGLU (megabench/tasks/megamoe.py:116-122), 1 = situ (megabench/tasks/kimi.py:134-135)
+  // Rows come in (hi, lo) pairs, the two E4M3 pieces of one bf16 row (grouped rows 2p and 2p+1): the
+  // epilogue adds a pair's two results. dual: the activation's bf16 value is split again into two
+  // rows of aq / as; single: one bf16 row per pair at out[row_dest[2p] / 2].
+  bool pairs;
 };
 cudaError_t launch_gemm_mx(const MxGemmArgs& a, cudaStream_t stream, int* launches, int* driver_error);
 // Grouped row r < *kept <- row row_token[r] of e4m3 [tokens, hidden] with its hidden/32 scale bytes.

@@ -1,0 +1,373 @@
+// The Kimi-K3 latent MoE block: kernels that the FP8 layer does not have, and its C ABI entry.
+//
+// Reference: megabench/tasks/kimi_layer.py:189-230 (`moe`, serial form) with the experts of :175-186
+// and the activation of megabench/tasks/kimi.py:134-135:
+//   per token: sigmoid top-k routing (scaling 1, no groups); latent = latent_down @ token (bf16);
+//   per routed slot: situ(latent @ gate^T, latent @ up^T) @ down^T with MXFP4 weights dequantised to
+//   bf16 and bf16 activations; fp32 slot-order weighted sum, rounded to bf16, RMSNorm (latent_norm),
+//   latent_up; plus shared_down @ situ(shared_gate @ token, shared_up @ token); the two are added.
+//
+// The routed experts multiply bf16 rows with 4-bit weights. The block-scaled tensor-core MMA wants
+// 8-bit (or narrower) operands on both sides, so every bf16 row travels as TWO E4M3 rows with E8M0
+// scales per 32 channels: hi = the value rounded to E4M3 under its block's scale, lo = the
+// remainder under the remainder's own block scale. A bf16 number has 8 significant bits and an
+// E4M3 number 4, so hi + lo is the bf16 value exactly (for elements more than 2^15 below their
+// block's largest the error is below 2^-23 of that largest: under the fp32 accumulation's own
+// rounding). The weights keep streaming as 4 bits per value and W x = W hi + W lo is what the
+// reference computes: exact products of the dequantised weights and the bf16 row, summed in fp32.
+#include <algorithm>
+#include <cstring>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "split_e4m3.cuh"
+
+namespace moe {
+
+// Grouped pair p (rows 2p and 2p+1 of the split buffers) <- bf16 row row_token[2p] of x. One block
+// per pair, a warp takes 128 channels (4 per lane: 8 lanes share a scale block).
+__global__ void __launch_bounds__(256) split_rows_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ row_token,
+                                                         const int32_t* __restrict__ kept, int tokens, int width,
+                                                         uint8_t* __restrict__ q, uint8_t* __restrict__ scales) {
+  dependent_wait();
+  dependents_may_launch();
+  const int pos = 2 * blockIdx.x;
+  if (pos >= *kept) return;
+  const int token = row_token[pos];
+  if (token < 0 || token >= tokens) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const __nv_bfloat16* in = x + static_cast<size_t>(token) * width;
+  const int blocks = width / 32;
+  for (int k0 = warp * 128; k0 < width; k0 += 8 * 128) {
+    const int k = k0 + lane * 4;
+    const uint2 raw = *reinterpret_cast<const uint2*>(in + k);
+    float v[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16),
+                  __uint_as_float(raw.y & 0xffff0000u)};
+    uint8_t hi[4], lo[4];
+    int e_hi, e_lo;
+    split_e4m3(v, 8, hi, lo, e_hi, e_lo);
+    *reinterpret_cast<uint32_t*>(q + static_cast<size_t>(pos) * width + k) = hi[0] | (hi[1] << 8) | (hi[2] << 16) | (hi[3] << 24);
+    *reinterpret_cast<uint32_t*>(q + static_cast<size_t>(pos + 1) * width + k) = lo[0] | (lo[1] << 8) | (lo[2] << 16) | (lo[3] << 24);
+    if ((lane & 7) == 0) {
+      scales[static_cast<size_t>(pos) * blocks + k / 32] = static_cast<uint8_t>(e_hi);
+      scales[static_cast<size_t>(pos + 1) * blocks + k / 32] = static_cast<uint8_t>(e_lo);
+    }
+  }
+}
+
+// ids2[2r] = ids2[2r+1] = ids[r]: the two pieces of a routed row go to the same expert, side by side.
+__global__ void duplicate_ids_kernel(const int32_t* __restrict__ ids, int n, int32_t* __restrict__ ids2) {
+  dependent_wait();
+  dependents_may_launch();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < 2 * n) ids2[i] = ids[i >> 1];
+}
+
+// ---- dense bf16 rows: y[t][n] = f( sum_k W[n][k] x[t][k] ) for a handful of tokens --------------------
+// W bf16 [N, K] row-major, x bf16 [T, K]; fp32 accumulation, bf16 results (`W @ token` of the
+// reference, megabench/tasks/kimi_layer.py:203,227-228). Decode batches: the weights stream once from
+// HBM, the token rows sit in L1. A warp owns kDenseRows output channels (lane-strided 16-byte weight
+// loads, lane partial sums added by a butterfly) for up to kDenseTokens tokens per pass.
+//   MODE 0: y = bf16(sum)
+//   MODE 1: y = situ(bf16(sum over W), bf16(sum over W2))     (gate and up rows of the shared experts)
+//   MODE 2: y = bf16(bf16(sum) + other[t][n])                 (routed + shared)
+constexpr int kDenseTokens = 8;
+constexpr int kDenseWarps = 8;
+
+template <int ROWS, int MODE>
+__global__ void __launch_bounds__(kDenseWarps * 32) dense_rows_kernel(const __nv_bfloat16* __restrict__ w,
+                                                                      const __nv_bfloat16* __restrict__ w2,
+                                                                      const __nv_bfloat16* __restrict__ x, int tokens, int n, int k,
+                                                                      const __nv_bfloat16* __restrict__ other,
+                                                                      __nv_bfloat16* __restrict__ y) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = (blockIdx.x * kDenseWarps + warp) * ROWS;      // first output channel of this warp
+  dependent_wait();
+  dependents_may_launch();
+  if (n0 >= n) return;
+  constexpr int MATS = MODE == 1 ? 2 : 1;
+  for (int t0 = 0; t0 < tokens; t0 += kDenseTokens) {
+    float acc[MATS][ROWS][kDenseTokens];
+#pragma unroll
+    for (int a = 0; a < MATS; ++a)
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+        for (int t = 0; t < kDenseTokens; ++t) acc[a][r][t] = 0.f;
+    for (int c = lane * 8; c < k; c += 32 * 8) {
+      uint4 wv[MATS][ROWS];
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        const int row = min(n0 + r, n - 1);
+        wv[0][r] = __ldg(reinterpret_cast<const uint4*>(w + static_cast<size_t>(row) * k + c));
+        if constexpr (MODE == 1) wv[1][r] = __ldg(reinterpret_cast<const uint4*>(w2 + static_cast<size_t>(row) * k + c));
+      }
+#pragma unroll
+      for (int t = 0; t < kDenseTokens; t += 2) {
+        const int ta = min(t0 + t, tokens - 1), tb = min(t0 + t + 1, tokens - 1);
+        const uint4 xa = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(ta) * k + c);
+        const uint4 xb = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(tb) * k + c);
+        const uint32_t* pa = reinterpret_cast<const uint32_t*>(&xa);
+        const uint32_t* pb = reinterpret_cast<const uint32_t*>(&xb);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float a0 = __uint_as_float(pa[j] << 16), a1 = __uint_as_float(pa[j] & 0xffff0000u);
+          const float b0 = __uint_as_float(pb[j] << 16), b1 = __uint_as_float(pb[j] & 0xffff0000u);
+#pragma unroll
+          for (int a = 0; a < MATS; ++a)
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+              const uint32_t word = reinterpret_cast<const uint32_t*>(&wv[a][r])[j];
+              const float w0 = __uint_as_float(word << 16), w1 = __uint_as_float(word & 0xffff0000u);
+              fma2(w0, w0, a0, b0, acc[a][r][t], acc[a][r][t + 1]);
+              fma2(w1, w1, a1, b1, acc[a][r][t], acc[a][r][t + 1]);
+            }
+        }
+      }
+    }
+#pragma unroll
+    for (int a = 0; a < MATS; ++a)
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+        for (int t = 0; t < kDenseTokens; ++t)
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) acc[a][r][t] = __fadd_rn(acc[a][r][t], __shfl_xor_sync(0xffffffffu, acc[a][r][t], off));
+    if (lane == 0) {
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        if (n0 + r >= n) break;
+#pragma unroll
+        for (int t = 0; t < kDenseTokens; ++t) {
+          if (t0 + t >= tokens) break;
+          const size_t at = static_cast<size_t>(t0 + t) * n + n0 + r;
+          float v = bf16_round(acc[0][r][t]);
+          if constexpr (MODE == 1) v = bf16_round(situ_f32(v, bf16_round(acc[1][r][t])));
+          if constexpr (MODE == 2) v = bf16_round(__fadd_rn(v, __bfloat162float(other[at])));
+          y[at] = __float2bfloat16_rn(v);
+        }
+      }
+    }
+  }
+}
+
+template <int MODE>
+static cudaError_t launch_dense(const __nv_bfloat16* w, const __nv_bfloat16* w2, const __nv_bfloat16* x, int tokens, int n, int k,
+                                const __nv_bfloat16* other, __nv_bfloat16* y, cudaStream_t stream, int* launches) {
+  if (k % 8 || ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w2)) & 15))
+    return cudaErrorInvalidValue;
+  constexpr int ROWS = MODE == 1 ? 2 : 4;
+  const int blocks = (n + kDenseWarps * ROWS - 1) / (kDenseWarps * ROWS);
+  launch_dependent(dense_rows_kernel<ROWS, MODE>, dim3(blocks), dim3(kDenseWarps * 32), 0, stream, w, w2, x, tokens, n, k, other, y);
+  if (launches) *launches += 1;
+  return cudaGetLastError();
+}
+
+}  // namespace moe
+
+// ---------------------------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+inline uint64_t up256(uint64_t v) { return (v + 255) / 256 * 256; }
+inline int cuda_rc(cudaError_t e) { return e == cudaSuccess ? MOE_OK : static_cast<int>(e); }
+
+struct LatentLayout {
+  uint64_t status, logits, ids32, weights, ids2, counts, offsets, n_chunks, chunks, row_token, row_dest, latent, xq, xs, aq, as,
+      slots, sum, normed, act, shared, total;
+  int rows2, tile, max_chunks;
+};
+
+int latent_layout(const moe_latent_config_t* c, int tokens, LatentLayout* L) {
+  if (!c) return MOE_ERR_BAD_ARG;
+  if (c->hidden < 128 || c->latent < 128 || c->inter < 128 || c->n_experts < 1 || c->topk < 1 || c->topk > c->n_experts ||
+      c->n_shared < 1 || tokens < 1 || !(c->latent_eps >= 0.f))
+    return MOE_ERR_BAD_ARG;
+  if (c->hidden % 128 || c->latent % 128 || c->inter % 128 || c->n_experts > MOE_MAX_EXPERTS || c->topk > MOE_MAX_TOPK ||
+      2ll * tokens * c->topk > 32768)
+    return MOE_ERR_UNSUPPORTED;
+  const uint64_t H = c->hidden, LH = c->latent, I = c->inter, E = c->n_experts;
+  const int rows = tokens * c->topk, rows2 = 2 * rows;
+  LatentLayout l;
+  l.rows2 = rows2;
+  l.tile = moe::pick_token_tile(rows2, c->n_experts);
+  l.max_chunks = std::min(rows2, c->n_experts) + rows2 / l.tile + 1;
+  uint64_t off = 0;
+  auto take = [&](uint64_t bytes) { const uint64_t at = off; off = up256(off + bytes); return at; };
+  l.status = take(32);
+  l.logits = take(4ull * tokens * E);
+  l.ids32 = take(4ull * rows);
+  l.weights = take(4ull * rows);
+  l.ids2 = take(4ull * rows2);
+  l.counts = take(4ull * (E + 1));
+  l.offsets = take(4ull * (E + 2));
+  l.n_chunks = take(4);
+  l.chunks = take(16ull * l.max_chunks);
+  l.row_token = take(4ull * rows2);
+  l.row_dest = take(4ull * rows2);
+  l.latent = take(2ull * tokens * LH);
+  l.xq = take(static_cast<uint64_t>(rows2) * LH);
+  l.xs = take(static_cast<uint64_t>(rows2) * (LH / 32));
+  l.aq = take(static_cast<uint64_t>(rows2) * I);
+  l.as = take(static_cast<uint64_t>(rows2) * (I / 32));
+  l.slots = take(2ull * rows * LH);
+  l.sum = take(2ull * tokens * LH);
+  l.normed = take(2ull * tokens * LH);
+  l.act = take(2ull * tokens * c->n_shared * I);
+  l.shared = take(2ull * tokens * H);
+  l.total = off;
+  *L = l;
+  return MOE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int moe_latent_workspace(const moe_latent_config_t* cfg, int32_t tokens, uint64_t* bytes) {
+  LatentLayout L;
+  const int rc = latent_layout(cfg, tokens, &L);
+  if (rc) return rc;
+  if (bytes) *bytes = L.total;
+  return MOE_OK;
+}
+
+int moe_latent_forward(const moe_latent_config_t* cfg, const moe_latent_weights_t* w, const void* x_bf16, int32_t tokens,
+                       void* y_bf16, int64_t* expert_ids, float* topk_weights, void* workspace, size_t workspace_bytes,
+                       void* stream_) {
+  LatentLayout L;
+  const int rc = latent_layout(cfg, tokens, &L);
+  if (rc) return rc;
+  if (!w || !x_bf16 || !y_bf16 || !workspace) return MOE_ERR_BAD_ARG;
+  const void* need[] = {w->router, w->latent_down, w->latent_up, w->latent_norm, w->gate_blocks, w->gate_scales, w->up_blocks,
+                        w->up_scales, w->down_blocks, w->down_scales, w->shared_gate, w->shared_up, w->shared_down};
+  for (const void* ptr : need)
+    if (!ptr) return MOE_ERR_BAD_ARG;
+  if (workspace_bytes < L.total) return MOE_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return MOE_ERR_BAD_ARG;
+  // the weight tiles move by TMA as packed 4-bit values (32-byte aligned base), the scale rows by 16-byte copies
+  if ((reinterpret_cast<uintptr_t>(w->gate_blocks) | reinterpret_cast<uintptr_t>(w->up_blocks) |
+       reinterpret_cast<uintptr_t>(w->down_blocks)) & 31 ||
+      (reinterpret_cast<uintptr_t>(w->gate_scales) | reinterpret_cast<uintptr_t>(w->up_scales) |
+       reinterpret_cast<uintptr_t>(w->down_scales)) & 15)
+    return MOE_ERR_BAD_ARG;
+  using bf16 = __nv_bfloat16;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  int32_t* status = reinterpret_cast<int32_t*>(ws + L.status);
+  int32_t* ids32 = reinterpret_cast<int32_t*>(ws + L.ids32);
+  float* tw = reinterpret_cast<float*>(ws + L.weights);
+  int32_t* ids2 = reinterpret_cast<int32_t*>(ws + L.ids2);
+  int32_t* offsets = reinterpret_cast<int32_t*>(ws + L.offsets);
+  int32_t* row_token = reinterpret_cast<int32_t*>(ws + L.row_token);
+  int32_t* row_dest = reinterpret_cast<int32_t*>(ws + L.row_dest);
+  bf16* latent = reinterpret_cast<bf16*>(ws + L.latent);
+  bf16* slots = reinterpret_cast<bf16*>(ws + L.slots);
+  bf16* sum = reinterpret_cast<bf16*>(ws + L.sum);
+  bf16* normed = reinterpret_cast<bf16*>(ws + L.normed);
+  bf16* act = reinterpret_cast<bf16*>(ws + L.act);
+  bf16* shared = reinterpret_cast<bf16*>(ws + L.shared);
+  const bf16* x = static_cast<const bf16*>(x_bf16);
+  const int H = cfg->hidden, LH = cfg->latent, I = cfg->inter, E = cfg->n_experts, K = cfg->topk;
+  const int rows = tokens * K;
+  int launches = 0;
+  cudaError_t e = cudaMemsetAsync(status, 0, 32, stream);
+  if (e != cudaSuccess) return cuda_rc(e);
+
+  // 1. router: sigmoid scores plus selection bias, no groups, weights normalised with scaling 1
+  //    (megabench/tasks/kimi_layer.py:200-201)
+  moe_config_t rc_cfg;
+  std::memset(&rc_cfg, 0, sizeof(rc_cfg));
+  rc_cfg.hidden = H; rc_cfg.inter = I; rc_cfg.n_experts = E; rc_cfg.topk = K; rc_cfg.scoring = MOE_SCORING_SIGMOID;
+  rc_cfg.n_group = 1; rc_cfg.topk_group = 1; rc_cfg.routed_scaling = 1.f; rc_cfg.ep_world = 1;
+  e = moe::launch_router(rc_cfg, x, w->router, w->router_bias, tokens, reinterpret_cast<float*>(ws + L.logits), ids32, tw,
+                         expert_ids, topk_weights, stream, &launches);
+  if (e != cudaSuccess) return cuda_rc(e);
+
+  // 2. latent rows (megabench/tasks/kimi_layer.py:203)
+  e = moe::launch_dense<0>(static_cast<const bf16*>(w->latent_down), nullptr, x, tokens, LH, H, nullptr, latent, stream, &launches);
+  if (e != cudaSuccess) return cuda_rc(e);
+
+  // 3. every routed row becomes a pair of E4M3 rows; the pairs are grouped by expert
+  moe::launch_dependent(moe::duplicate_ids_kernel, dim3((2 * rows + 255) / 256), dim3(256), 0, stream,
+                        static_cast<const int32_t*>(ids32), rows, ids2);
+  ++launches;
+  moe::GroupArgs g;
+  std::memset(&g, 0, sizeof(g));
+  g.ids32 = ids2;
+  g.n = L.rows2;
+  g.n_local = E;
+  g.topk = 2 * K;                  // split row r belongs to token r / (2 topk)
+  g.tile = L.tile;
+  g.max_chunks = L.max_chunks;
+  g.counts = reinterpret_cast<int32_t*>(ws + L.counts);
+  g.offsets = offsets;
+  g.n_chunks = reinterpret_cast<int32_t*>(ws + L.n_chunks);
+  g.chunks = reinterpret_cast<moe::Chunk*>(ws + L.chunks);
+  g.row_token = row_token;
+  g.row_dest = row_dest;
+  g.status = status;
+  e = moe::launch_group_rows(g, stream, &launches);
+  if (e != cudaSuccess) return cuda_rc(e);
+  uint8_t* xq = ws + L.xq;
+  uint8_t* xs = ws + L.xs;
+  moe::launch_dependent(moe::split_rows_kernel, dim3(rows), dim3(256), 0, stream, static_cast<const bf16*>(latent),
+                        static_cast<const int32_t*>(row_token), static_cast<const int32_t*>(offsets + E), tokens, LH, xq, xs);
+  ++launches;
+
+  // 4. gate/up with situ, split again; down into slot rows (megabench/tasks/kimi_layer.py:175-186)
+  moe::MxGemmArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.tile = L.tile;
+  a.n_experts = E;
+  a.total_rows = L.rows2;
+  a.chunks = g.chunks;
+  a.n_chunks = g.n_chunks;
+  a.status = status;
+  a.pairs = true;
+  int driver_error = 0;
+  a.dual = true;
+  a.k = LH; a.m = I;
+  a.max_units = L.max_chunks * (I / 128);
+  a.act = xq; a.act_scales = xs;
+  a.w_blocks = w->gate_blocks; a.w_scales = w->gate_scales;
+  a.w_blocks_b = w->up_blocks; a.w_scales_b = w->up_scales;
+  a.aq = ws + L.aq; a.as = ws + L.as;
+  a.row_dest = row_dest;
+  a.activation = 1;
+  e = moe::launch_gemm_mx(a, stream, &launches, &driver_error);
+  if (driver_error) return MOE_ERR_DRIVER;
+  if (e != cudaSuccess) return cuda_rc(e);
+  a.dual = false;
+  a.k = I; a.m = LH;
+  a.max_units = L.max_chunks * (LH / 128);
+  a.act = ws + L.aq; a.act_scales = ws + L.as;
+  a.w_blocks = w->down_blocks; a.w_scales = w->down_scales;
+  a.w_blocks_b = nullptr; a.w_scales_b = nullptr;
+  a.aq = nullptr; a.as = nullptr;
+  a.out = slots;
+  e = moe::launch_gemm_mx(a, stream, &launches, &driver_error);
+  if (driver_error) return MOE_ERR_DRIVER;
+  if (e != cudaSuccess) return cuda_rc(e);
+
+  // 5. fp32 slot-order weighted sum rounded to bf16, latent RMSNorm (megabench/tasks/kimi_layer.py:222-227)
+  e = moe::launch_combine(slots, tw, tokens, K, LH, 0, sum, stream, &launches);
+  if (e != cudaSuccess) return cuda_rc(e);
+  e = moe::launch_rmsnorm(sum, static_cast<const bf16*>(w->latent_norm), cfg->latent_eps, 0, tokens, LH, normed, stream, &launches);
+  if (e != cudaSuccess) return cuda_rc(e);
+
+  // 6. shared experts on the full-width token (megabench/tasks/kimi_layer.py:228), then latent_up + shared
+  e = moe::launch_dense<1>(static_cast<const bf16*>(w->shared_gate), static_cast<const bf16*>(w->shared_up), x, tokens,
+                           cfg->n_shared * I, H, nullptr, act, stream, &launches);
+  if (e != cudaSuccess) return cuda_rc(e);
+  e = moe::launch_dense<0>(static_cast<const bf16*>(w->shared_down), nullptr, act, tokens, H, cfg->n_shared * I, nullptr, shared,
+                           stream, &launches);
+  if (e != cudaSuccess) return cuda_rc(e);
+  e = moe::launch_dense<2>(static_cast<const bf16*>(w->latent_up), nullptr, normed, tokens, H, LH, shared,
+                           static_cast<bf16*>(y_bf16), stream, &launches);
+  moe::note_launches(launches);
+  return cuda_rc(e);
+}
+
+}  // extern "C"

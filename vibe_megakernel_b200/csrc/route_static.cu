@@ -9,7 +9,7 @@
 // exits, whether or not this entry point is ever called.
 //
 // What follows from that:
-//   * sizes are capped (MOE_STATIC_ROUTE_MAX_TOKENS tokens, MOE_MAX_EXPERTS experts, MOE_MAX_TOPK
+//   * sizes are capped (MOE_STATIC_ROUTE_MAX_TOKENS tokens, MOE_STATIC_ROUTE_MAX_EXPERTS experts, MOE_MAX_TOPK
 //     picks); larger requests are refused with MOE_ERR_TOO_LARGE, nothing is launched;
 //   * all calls on one GPU share the array. It keeps whatever the previous call left; the router
 //     writes every element it later reads, so nothing has to be cleared first. Two calls whose
@@ -24,7 +24,7 @@
 
 namespace {
 
-constexpr size_t kLogitFloats = static_cast<size_t>(MOE_STATIC_ROUTE_MAX_TOKENS) * MOE_MAX_EXPERTS;
+constexpr size_t kLogitFloats = static_cast<size_t>(MOE_STATIC_ROUTE_MAX_TOKENS) * MOE_STATIC_ROUTE_MAX_EXPERTS;
 constexpr size_t kPickWords = static_cast<size_t>(MOE_STATIC_ROUTE_MAX_TOKENS) * MOE_MAX_TOPK;
 constexpr size_t kStaticBytes = (kLogitFloats + 2 * kPickWords) * 4;     // 557,056 bytes
 
@@ -61,7 +61,7 @@ extern "C" int moe_route_static(const moe_config_t* cfg, const void* x_bf16, con
                                 void* stream) {
   if (!cfg || !x_bf16 || !router) return MOE_ERR_BAD_ARG;
   if (tokens < 1) return MOE_ERR_BAD_ARG;
-  if (tokens > MOE_STATIC_ROUTE_MAX_TOKENS || cfg->n_experts > MOE_MAX_EXPERTS || cfg->topk > MOE_MAX_TOPK)
+  if (tokens > MOE_STATIC_ROUTE_MAX_TOKENS || cfg->n_experts > MOE_STATIC_ROUTE_MAX_EXPERTS || cfg->topk > MOE_MAX_TOPK)
     return MOE_ERR_TOO_LARGE;
   const int rc = moe_workspace_layout(cfg, tokens, nullptr);   // same geometry checks as moe_route
   if (rc != MOE_OK) return rc;

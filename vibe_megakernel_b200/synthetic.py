@@ -192,3 +192,34 @@ def megamoe_inputs(tokens: int, experts: int, topk: int, hidden: int, inter: int
     values["l2_blocks"] = codes(experts, hidden, inter // 32, 16)
     values["l2_scales"] = scales(121, experts, hidden, inter // 32)
     return values
+
+
+def kimi_latent_inputs(tokens: int, experts: int, topk: int, hidden: int, latent: int, inter: int, shared: int, seed: int,
+                       device) -> tuple[dict, torch.Tensor]:
+    """Seeded random inputs of the Kimi-K3 latent MoE block made on ``device``: (values, normalized).
+    Tensor names, layouts and scales follow megabench/tasks/kimi_layer.py:107-125 (dense matrices bf16
+    ~N(0, 1/fan_in), router logits of unit variance, a small selection bias); the MXFP4 expert matrices
+    are random codes with E8M0 scales around the value that gives them the same spread."""
+    import math
+    gen = torch.Generator(device=device).manual_seed(seed)
+    bf = torch.bfloat16
+
+    def dense(rows, cols, fan_in):
+        return (torch.randn((rows, cols), device=device, generator=gen) * fan_in ** -0.5).to(bf)
+
+    def mx(rows, cols):
+        center = 127 + round(math.log2(cols ** -0.5 / 2.9))       # E2M1 codes have an rms of about 2.9
+        blocks = torch.randint(0, 256, (experts, rows, cols // 32, 16), dtype=torch.uint8, device=device, generator=gen)
+        scales = torch.randint(center - 1, center + 2, (experts, rows, cols // 32), dtype=torch.uint8, device=device, generator=gen)
+        return blocks, scales
+
+    values = {"router": dense(experts, hidden, hidden),
+              "router_bias": torch.randn((experts,), device=device, generator=gen) * 0.1,
+              "latent_down": dense(latent, hidden, hidden), "latent_up": dense(hidden, latent, latent),
+              "latent_norm": (torch.randn((latent,), device=device, generator=gen) / 10 + 1).to(bf),
+              "shared_gate": dense(shared * inter, hidden, hidden), "shared_up": dense(shared * inter, hidden, hidden),
+              "shared_down": dense(hidden, shared * inter, shared * inter)}
+    for name, rows, cols in (("gate", inter, latent), ("up", inter, latent), ("down", latent, inter)):
+        values[name + "_blocks"], values[name + "_scales"] = mx(rows, cols)
+    normalized = torch.randn((tokens, hidden), device=device, generator=gen).to(bf)
+    return values, normalized
