@@ -279,8 +279,18 @@ def test_bad_arguments_are_refused(api):
         api.MoeLayer(api.LayerConfig(hidden=100, inter=128, experts=8, topk=2), max_tokens=1)
 
 
-@pytest.mark.parametrize("name,tokens", [("qwen_small", 300), ("mixtral_small", 257), ("ds_small", 128)])
+@pytest.mark.parametrize("name,tokens", [("qwen_small", 300), ("mixtral_small", 257), ("ds_small", 128),
+                                         ("mixtral_small", 600), ("long_k", 300), ("qwen_small", 1000)])
 def test_experts_with_more_rows_than_one_tile(api, name, tokens):
+    # several chunks per expert and channel tile (a split contraction in long_k)
     geo = H.small_geometries()[name]
-    values, _ = H.audited_inputs(geo, tokens)
+    values, _ = H.audited_inputs(geo, tokens, max_tries=64)
     check_against_oracle(api, geo, values, "tcgen05")
+    if tokens >= 600:
+        check_against_oracle(api, geo, values, "simt")
+        # a row's result does not depend on the tile it was multiplied in: the same tokens, fewer at a time
+        full = api.MoeLayer(api.LayerConfig.from_geometry(geo), max_tokens=tokens).forward(H.to_device(values, "cuda"))
+        few = dict(values)
+        few["x"] = values["x"][:40].contiguous()
+        part = api.MoeLayer(api.LayerConfig.from_geometry(geo), max_tokens=40).forward(H.to_device(few, "cuda"))
+        assert torch.equal(part["y"], full["y"][:40])
