@@ -394,13 +394,14 @@ static bool regs_variant_fits(const moe_config_t& cfg, int epl) {
 }
 
 static int regs_variant_of(const moe_config_t& cfg) {
-  for (int epl : {1, 2, 4, 8, 12, 16})
+  for (int epl : {1, 2, 4, 8, 12, 16, 28})
     if (regs_variant_fits(cfg, epl)) return epl;
   return 0;
 }
 
 bool fused_route_fits(const moe_config_t& cfg, int tokens) {
-  return tokens >= 1 && tokens <= kFusedMaxTokens && tokens * cfg.topk <= kFusedMaxRows && regs_variant_of(cfg) != 0;
+  const int epl = regs_variant_of(cfg);       // (28 values per lane leave the 1024-thread kernel no registers)
+  return tokens >= 1 && tokens <= kFusedMaxTokens && tokens * cfg.topk <= kFusedMaxRows && epl != 0 && epl <= 16;
 }
 
 template <int EPL>
@@ -456,6 +457,7 @@ cudaError_t launch_router(const moe_config_t& cfg, const __nv_bfloat16* x, const
   else if (regs_variant_fits(cfg, 8)) kernel = route_select_regs_kernel<8>;
   else if (regs_variant_fits(cfg, 12)) kernel = route_select_regs_kernel<12>;
   else if (regs_variant_fits(cfg, 16)) kernel = route_select_regs_kernel<16>;
+  else if (regs_variant_fits(cfg, 28)) kernel = route_select_regs_kernel<28>;      // 896 experts
   launch_dependent(kernel, dim3(blocks), dim3(threads), 0, stream, a);
   if (launches) *launches += 2;
   return cudaGetLastError();

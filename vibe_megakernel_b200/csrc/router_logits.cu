@@ -264,7 +264,9 @@ cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* router, in
   } else if (tokens <= 4 || rows_smem(8) > smem_limit) {
     cudaError_t e = launch_rows(router_logits_rows_kernel<4>, 4);
     if (e != cudaSuccess) return e;
-  } else if (tokens <= 8 || !tiled_ok) {
+  } else if ((tokens <= 8 && row_blocks <= 2 * 148) || !tiled_ok) {
+    // (with many hundreds of experts the rows kernel's blocks, each holding the 8 token rows and two
+    // router rows, run in several waves: the tiled kernel below streams the router rows instead)
     cudaError_t e = launch_rows(router_logits_rows_kernel<8>, 8);
     if (e != cudaSuccess) return e;
   } else {
@@ -279,8 +281,11 @@ cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* router, in
     // 8 token rows per block: 12 (the most that fit at H = 7168) measured 15-25 % slower, the extra
     // accumulators costing more than the saved passes over the router rows
     const long long wide_grid = static_cast<long long>((experts + 31) / 32) * ((tokens + 7) / 8);
+    // experts per warp: as many as still leave about a hundred blocks
+    const long long mid_grid = static_cast<long long>((experts + 15) / 16) * ((tokens + 7) / 8);
     cudaError_t e = wide_grid >= 148 ? launch_tiled(router_logits_tiled_kernel<8, 4>, 8, 32)
-                                     : launch_tiled(router_logits_tiled_kernel<8, 2>, 8, 16);
+                  : mid_grid >= 100  ? launch_tiled(router_logits_tiled_kernel<8, 2>, 8, 16)
+                                     : launch_tiled(router_logits_tiled_kernel<8, 1>, 8, 8);
     if (e != cudaSuccess) return e;
   }
   return cudaGetLastError();
