@@ -76,6 +76,91 @@ __device__ __forceinline__ void epilogue_swiglu_requant(float (&gate)[CPT], cons
   epilogue_sync<THREADS>();   // s_amax may be reused by the next work item
 }
 
+// The same arithmetic for the tensor-core kernel, laid out for a persistent CTA whose epilogue warps
+// also fold the next item's K blocks, so every cycle here delays the tensor pipe:
+//   * the activations of a thread's columns are computed first, independent chains the scheduler can
+//     interleave (a warp reduction per column in the same loop serialised them);
+//   * one thread per token computes the scale (a division) instead of all 128 of the column;
+//   * the e4m3 bytes are collected in shared memory as [token][128 channels] and leave as whole rows,
+//     16 bytes per thread, instead of one byte per thread and token;
+//   * no thread fences: whoever announces the tile does, after the closing barrier.
+//   tid: 0..THREADS-1; rend: end of this thread's valid columns; rows: the chunk's rows;
+//   s_amax: float[4][nt]; s_scale: float[nt]; s_tile: uint8_t[nt][128], 16-byte aligned.
+template <int CPT, int THREADS>
+__device__ __forceinline__ void epilogue_swiglu_requant_tile(float (&gate)[CPT], const float (&up)[CPT], int tid, int m,
+                                                             int col0, int nt, int rend, int rows, int row0, int tile_m,
+                                                             int inter, float* s_amax, float* s_scale, uint8_t* s_tile,
+                                                             uint8_t* __restrict__ aq, float* __restrict__ as,
+                                                             const SwigluMode& mode) {
+  const int quarter = m >> 5, lane = m & 31;
+#pragma unroll
+  for (int n = 0; n < CPT; ++n) {
+    if (col0 + n < rend) {      // uniform across the warp
+      float g = bf16_round(gate[n]);
+      float u = bf16_round(up[n]);
+      if (mode.limit > 0.f) {
+        g = fminf(g, mode.limit);
+        u = fminf(fmaxf(u, -mode.limit), mode.limit);
+      }
+      float a = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.f, expf(-g))), u);
+      if (mode.slot_weight) {
+        const int dest = mode.row_dest[row0 + col0 + n];
+        if (dest < mode.routed_rows) a = __fmul_rn(a, mode.slot_weight[dest]);
+      }
+      gate[n] = a;
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < CPT; ++n) {
+    if (col0 + n < rend) {
+      const unsigned bits = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(gate[n])));
+      if (lane == 0) s_amax[quarter * nt + col0 + n] = __uint_as_float(bits);
+    }
+  }
+  epilogue_sync<THREADS>();
+  const int groups = inter / kGroup;
+  for (int c = tid; c < rows; c += THREADS) {
+    const float amax = fmaxf(fmaxf(s_amax[c], s_amax[nt + c]), fmaxf(s_amax[2 * nt + c], s_amax[3 * nt + c]));
+    const float scale = group_scale(amax);
+    s_scale[c] = scale;
+    as[static_cast<size_t>(row0 + c) * groups + tile_m] = scale;
+  }
+  epilogue_sync<THREADS>();
+#pragma unroll
+  for (int n = 0; n < CPT; ++n) {
+    const int c = col0 + n;
+    if (c < rend) s_tile[c * kGroup + m] = to_e4m3(gate[n], s_scale[c]);
+  }
+  epilogue_sync<THREADS>();
+  for (int i = tid; i < rows * (kGroup / 16); i += THREADS) {
+    const int r = i >> 3, part = i & 7;
+    *reinterpret_cast<uint4*>(aq + static_cast<size_t>(row0 + r) * inter + tile_m * kGroup + part * 16) =
+        *reinterpret_cast<const uint4*>(s_tile + r * kGroup + part * 16);
+  }
+  epilogue_sync<THREADS>();   // every row is on its way: the tile may be announced, the scratch reused
+}
+
+// Down projection in the tensor-core kernel: the bf16 roundings of a work item collected in shared
+// memory as [token][128 channels] and stored as whole 256-byte row pieces, 16 bytes per thread.
+//   dest: shared int[nt], destination row of every token column; s_tile: bf16 [nt][128].
+// The caller's next barrier over the epilogue threads protects the tile against reuse.
+template <int CPT, int THREADS>
+__device__ __forceinline__ void epilogue_store_tile(const float (&sum)[CPT], int tid, int m, int col0, int rend, int rows,
+                                                    int tile_m, int hidden, const int* dest, __nv_bfloat16* s_tile,
+                                                    __nv_bfloat16* __restrict__ out) {
+#pragma unroll
+  for (int n = 0; n < CPT; ++n) {
+    const int c = col0 + n;
+    if (c < rend) s_tile[c * kGroup + m] = __float2bfloat16_rn(sum[n]);
+  }
+  epilogue_sync<THREADS>();
+  for (int i = tid; i < rows * (kGroup / 8); i += THREADS) {
+    const int r = i >> 4, part = i & 15;
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(dest[r]) * hidden + tile_m * kGroup + part * 8) =
+        *reinterpret_cast<const uint4*>(s_tile + r * kGroup + part * 8);
+  }
+}
+
 // Down projection: one bf16 rounding of the fp32 accumulator, stored at the row's slot.
 // Reference: megabench/tasks/megamoe.py:149 (`@ w2.T` with a bf16 result).
 template <int CPT>

@@ -45,18 +45,29 @@ namespace moe {
 // CTAs into the spare status words in units of 256 cycles: [2] producer for a free stage, [3] MMA
 // for a free accumulator, [4] MMA for data, [5] epilogue for an accumulator, [6] epilogue for
 // scales, [7] lifetime of the CTA. MOE_GEMM_PROBE=1 records the gate/up GEMM, =2 the down GEMM.
-// Off by default: the words stay zero.
+// With -DMOE_GEMM_PROBE_EPI besides, words [2], [3], [4] and [6] hold the first epilogue thread's
+// cycles instead: reading the accumulators, releasing them, folding them, and the item's closing
+// epilogue (activation, requantisation, stores). Off by default: the words stay zero.
 #ifdef MOE_GEMM_PROBE
 #define PROBE_DECL(name) long long name = 0
 #define PROBE_START(t) const long long t = clock64()
 #define PROBE_ADD(name, t) name += clock64() - t
 #define PROBE_FLUSH(status, slot, name) \
   if (DUAL == (MOE_GEMM_PROBE == 1)) atomicAdd((status) + (slot), static_cast<int>((name) >> 8))
+#ifdef MOE_GEMM_PROBE_EPI
+#define PROBE_FLUSH_ROLE(status, slot, name)
+#define PROBE_FLUSH_EPI(status, slot, name) PROBE_FLUSH(status, slot, name)
+#else
+#define PROBE_FLUSH_ROLE(status, slot, name) PROBE_FLUSH(status, slot, name)
+#define PROBE_FLUSH_EPI(status, slot, name)
+#endif
 #else
 #define PROBE_DECL(name)
 #define PROBE_START(t)
 #define PROBE_ADD(name, t)
 #define PROBE_FLUSH(status, slot, name)
+#define PROBE_FLUSH_ROLE(status, slot, name)
+#define PROBE_FLUSH_EPI(status, slot, name)
 #endif
 
 // TMEM accumulators in flight (per configuration: as many as fit in the 512 columns, at most 8).
@@ -87,13 +98,20 @@ struct GemmCfg {
   static constexpr int kAcc = 512 / kAccCols < kMaxAccStages ? 512 / kAccCols : kMaxAccStages;
   static constexpr int kTmemCols = kAcc * kAccCols < 32 ? 32 : kAcc * kAccCols;   // a power of two
   // Shared memory after the stage ring, for a contraction of kb K blocks:
-  //   2 buffers of { x scales [kb][NT], weight scales [2][kb] }, amax scratch [4][NT],
+  //   the output tile [NT][128] (e4m3 for gate/up, bf16 for down) the epilogue collects an item's
+  //   results in, 2 buffers of { scale table [kb][NT], gate/up: weight scales [2][kb], destination
+  //   rows [NT] }, amax scratch [4][NT] and the token scales [NT],
   //   barriers (2*kMaxStages + 2*kMaxAccStages + 2 + 2 + 2*kQueue), the item queue, 8 words of flags.
   // (every part a multiple of four floats, so the token scales can be read 16 bytes at a time)
-  static constexpr int weight_scale_floats(int kb) { return (2 * kb + 3) & ~3; }
+  // Down GEMM: the table holds the products w_scale * x_scale (computed once by the scale loader
+  // instead of by each of the 128 threads that own a channel of the column). Gate/up: the token
+  // scales, with the two weight scales of every K block behind them (two product tables would
+  // double the broadcast loads of the fold, which the shared-memory pipe, not the FP pipe, limits).
+  static constexpr int weight_scale_floats(int kb) { return DUAL ? (2 * kb + 3) & ~3 : 0; }
   static constexpr int scale_floats(int kb) { return kb * NT + weight_scale_floats(kb) + NT; }   // + destination rows [NT]
+  static constexpr int kTileBytes = NT * 128 * (DUAL ? 1 : 2);
   static constexpr int tail_bytes(int kb) {
-    return 2 * scale_floats(kb) * 4 + 4 * NT * 4 + (2 * kMaxStages + 2 * kMaxAccStages + 4 + 2 * kQueue) * 8 + kQueue * 16 + 64;
+    return kTileBytes + 2 * scale_floats(kb) * 4 + 5 * NT * 4 + (2 * kMaxStages + 2 * kMaxAccStages + 4 + 2 * kQueue) * 8 + kQueue * 16 + 64;
   }
   static constexpr int stages_for(int kb) {
     const int s = (kMaxSmem - 1024 - tail_bytes(kb)) / kStageBytes;
@@ -185,10 +203,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const int S = p.stages;
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* stages = base;
-  float* s_scales = reinterpret_cast<float*>(base + S * C::kStageBytes);     // [2][scale_floats(KB)]
+  uint8_t* s_tile = base + S * C::kStageBytes;                               // [NT][128] e4m3 or bf16
+  float* s_scales = reinterpret_cast<float*>(s_tile + C::kTileBytes);        // [2][scale_floats(KB)]
   const int sf = C::scale_floats(KB);
-  float* s_amax = s_scales + 2 * sf;
-  uint64_t* bar_full = reinterpret_cast<uint64_t*>(s_amax + 4 * NT);
+  float* s_amax = s_scales + 2 * sf;                                         // [4][NT], then the token scales [NT]
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(s_amax + 5 * NT);
   uint64_t* bar_empty = bar_full + kMaxStages;
   uint64_t* bar_tfull = bar_empty + kMaxStages;
   uint64_t* bar_tempty = bar_tfull + kMaxAccStages;
@@ -309,7 +328,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           __syncwarp();
         }
         if (u < 0) {
-          if (lane == 0) { PROBE_FLUSH(p.status, 2, probe_stage); }
+          if (lane == 0) { PROBE_FLUSH_ROLE(p.status, 2, probe_stage); }
           break;
         }
         u_next = next_unit(item + 1);                          // both in flight during this item
@@ -382,7 +401,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           break;
         }
         if (u < 0) {
-          if (lane == 0) { PROBE_FLUSH(p.status, 3, probe_acc); PROBE_FLUSH(p.status, 4, probe_data); }
+          if (lane == 0) { PROBE_FLUSH_ROLE(p.status, 3, probe_acc); PROBE_FLUSH_ROLE(p.status, 4, probe_data); }
           break;
         }
         const uint32_t idesc = idesc_e4m3(128, ((ch.rows + 15) >> 4) * 16);
@@ -454,8 +473,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       ready_chunk = u / p.tiles_m;
       const int mt = u % p.tiles_m;
       const bool shared_e = ch.expert >= p.n_local;
-      float* xs = s_scales + b * sf;            // [kb][NT]
-      float* ws = xs + KB * NT;                 // [2][kb]
+      // The table [kb][NT]: the token's scale (gate/up), or its product with the weight block's scale (down)
+      float* ta = s_scales + b * sf;
+      float* ws = ta + KB * NT;                                      // gate/up: weight scales [2][kb]
       int* sd = reinterpret_cast<int*>(ws + C::weight_scale_floats(KB));   // [NT] destination row of every token column
       const int cols = ((ch.rows + 15) >> 4) * 16;
       if constexpr (!DUAL) {
@@ -465,12 +485,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       int kb_lo, kb_hi;
       item_range(ch.pad, kb_lo, kb_hi);
       const int nk = kb_hi - kb_lo;
-      // Token scales, transposed to [K block][column]. Read at L2: a line shared with a
-      // neighbouring chunk may have been fetched before that chunk's scales were written.
+      const float* wa = (shared_e ? p.s_a_scale : p.w_a_scale + static_cast<size_t>(ch.expert) * p.tiles_m * KB) +
+                        static_cast<size_t>(mt) * KB;
+      const float* wb = wa;
+      if constexpr (DUAL)
+        wb = (shared_e ? p.s_b_scale : p.w_b_scale + static_cast<size_t>(ch.expert) * p.tiles_m * KB) +
+             static_cast<size_t>(mt) * KB;
+      // Token scales are read at L2: a line shared with a neighbouring chunk may have been fetched
+      // before that chunk's scales were written.
       if (((KB | kb_lo | nk) & 3) == 0) {
         // a lane takes a row (the transposed stores then fall in different banks), four K blocks
         // per load, eight loads in flight
         const int quads = nk >> 2;
+        const float4* wa4 = reinterpret_cast<const float4*>(wa + kb_lo);
         for (int n = lane; n < cols; n += 32) {
           const bool live = n < ch.rows;
           const float4* src =
@@ -478,15 +505,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           for (int q0 = 0; q0 < quads; q0 += 8) {
             float4 v[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __ldcg(src + min(q0 + j, quads - 1));
+            for (int j = 0; j < 8; ++j) {
+              v[j] = __ldcg(src + min(q0 + j, quads - 1));
+              if (!live) v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               if (q0 + j < quads) {
-                float* dst = xs + (kb_lo + 4 * (q0 + j)) * NT + n;
-                dst[0] = live ? v[j].x : 0.f;
-                dst[NT] = live ? v[j].y : 0.f;
-                dst[2 * NT] = live ? v[j].z : 0.f;
-                dst[3 * NT] = live ? v[j].w : 0.f;
+                float* dst = ta + (kb_lo + 4 * (q0 + j)) * NT + n;
+                const float4 a4 = DUAL ? make_float4(1.f, 1.f, 1.f, 1.f) : __ldg(wa4 + q0 + j);
+                dst[0] = __fmul_rn(a4.x, v[j].x);
+                dst[NT] = __fmul_rn(a4.y, v[j].y);
+                dst[2 * NT] = __fmul_rn(a4.z, v[j].z);
+                dst[3 * NT] = __fmul_rn(a4.w, v[j].w);
               }
             }
           }
@@ -494,16 +525,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       } else {
         for (int i = lane; i < cols * nk; i += 32) {
           const int n = i / nk, kb = kb_lo + i - n * nk;
-          xs[kb * NT + n] = n < ch.rows ? __ldcg(p.act_scale + static_cast<size_t>(ch.row0 + n) * KB + kb) : 0.f;
+          const float x = n < ch.rows ? __ldcg(p.act_scale + static_cast<size_t>(ch.row0 + n) * KB + kb) : 0.f;
+          ta[kb * NT + n] = DUAL ? x : __fmul_rn(__ldg(wa + kb), x);
         }
       }
-      const float* wa = (shared_e ? p.s_a_scale : p.w_a_scale + static_cast<size_t>(ch.expert) * p.tiles_m * KB) +
-                        static_cast<size_t>(mt) * KB;
-      for (int kb = kb_lo + lane; kb < kb_hi; kb += 32) ws[kb] = wa[kb];
       if constexpr (DUAL) {
-        const float* wb = (shared_e ? p.s_b_scale : p.w_b_scale + static_cast<size_t>(ch.expert) * p.tiles_m * KB) +
-                          static_cast<size_t>(mt) * KB;
-        for (int kb = kb_lo + lane; kb < kb_hi; kb += 32) ws[KB + kb] = wb[kb];
+        for (int kb = kb_lo + lane; kb < kb_hi; kb += 32) {
+          ws[kb] = wa[kb];
+          ws[KB + kb] = wb[kb];
+        }
       }
       mbar_arrive(bar_scfull + b);
     }
@@ -518,6 +548,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     bool failed = false;
     PROBE_DECL(probe_tfull);
     PROBE_DECL(probe_scales);
+    PROBE_DECL(probe_read);
+    PROBE_DECL(probe_release);
+    PROBE_DECL(probe_fold);
+    PROBE_DECL(probe_close);
     for (uint32_t un = 0;; ++un) {
       int u = -1;
       Chunk ch;
@@ -527,7 +561,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
       // one decision for all epilogue threads (the item is the same for all of them unless one failed)
       if (epilogue_any<C::kEpiThreads>(failed) || u < 0) {
-        if (threadIdx.x == 96) { PROBE_FLUSH(p.status, 5, probe_tfull); PROBE_FLUSH(p.status, 6, probe_scales); }
+        if (threadIdx.x == 96) {
+          PROBE_FLUSH(p.status, 5, probe_tfull);
+          PROBE_FLUSH_ROLE(p.status, 6, probe_scales);
+          PROBE_FLUSH_EPI(p.status, 2, probe_read);
+          PROBE_FLUSH_EPI(p.status, 3, probe_release);
+          PROBE_FLUSH_EPI(p.status, 4, probe_fold);
+          PROBE_FLUSH_EPI(p.status, 6, probe_close);
+        }
         break;
       }
       const int mt = u % p.tiles_m;
@@ -539,8 +580,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const int cend = (C::kEpiWarps == 8 && group == 0) ? min(split, cols) : cols;
       const int rend = min(ch.rows, cend);                     // ... and the rows among them that exist
       const uint32_t b = un & 1u, sph = (un >> 1) & 1u;
-      const float* xs_all = s_scales + b * sf;
-      const float* ws = xs_all + KB * NT;
+      const float* tab = s_scales + b * sf;         // [kb][NT]: token scales (gate/up) or scale products (down)
+      const float* ws = tab + KB * NT;              // gate/up: weight scales [2][kb]
       const int* sd = reinterpret_cast<const int*>(ws + C::weight_scale_floats(KB));
       PROBE_START(t_scales);
       if (!failed && !mbar_wait(bar_scfull + b, sph, s_abort)) {
@@ -569,6 +610,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         PROBE_ADD(probe_tfull, t_tfull);
         if (failed) { kb += len; continue; }   // keep in step with the other epilogue threads up to the item's end
         tc_fence_after();
+        PROBE_START(t_read);
         const bool active = col0 < cend;      // uniform per warp
         uint32_t ra[C::kCpt], rb[C::kCpt];
         if (active) {
@@ -584,45 +626,51 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
         // The values are in registers: hand the accumulators back before folding them, which
         // shortens the round trip that bounds the K blocks per microsecond.
+        PROBE_ADD(probe_read, t_read);
+        PROBE_START(t_release);
         tc_fence_before();
         mbar_arrive(bar_tempty + as);
         if (m == 0 && epi < 4) *s_drained = it + 1;
+        PROBE_ADD(probe_release, t_release);
+        PROBE_START(t_fold);
         if (active) {
-          // DUAL: gate and up of K block kb share the token scales; else K blocks kb and kb + 1 of
-          // the down projection, folded one after the other into the same sums
-          const float wa = ws[kb];
-          const float wb = DUAL ? ws[KB + kb] : (second ? ws[kb + 1] : 0.f);
-          const float* xs = xs_all + kb * NT + col0;
-          const float* xs2 = DUAL ? xs : xs + NT;
+          // acc += D * (w_scale * x_scale), the product rounded once. Gate/up: gate and up of K block
+          // kb share the token scales, the two products are formed here. Down: K blocks kb and kb + 1,
+          // folded one after the other into the same sums, their products read from the table.
+          const float* sa = tab + kb * NT + col0;
 #pragma unroll
           for (int g = 0; g < C::kCpt; g += 16) {
             if (col0 + g < cend) {
-              // 16 token scales as four 16-byte loads (col0 and NT are multiples of 16)
-              float x16[16];
+              // 16 table entries as four 16-byte loads (col0 and NT are multiples of 16), two columns per instruction
+              float s16[16];
 #pragma unroll
               for (int j = 0; j < 16; j += 4)
-                *reinterpret_cast<float4*>(x16 + j) = *reinterpret_cast<const float4*>(xs + g + j);
-              // two columns per instruction: acc += D * (w_scale * x_scale), every step rounded as before
+                *reinterpret_cast<float4*>(s16 + j) = *reinterpret_cast<const float4*>(sa + g + j);
+              if constexpr (DUAL) {
+                const float wa = ws[kb], wb = ws[KB + kb];
 #pragma unroll
-              for (int j = 0; j < 16; j += 2) {
-                float s0, s1;
-                mul2(wa, wa, x16[j], x16[j + 1], s0, s1);
-                fma2(__uint_as_float(ra[g + j]), __uint_as_float(ra[g + j + 1]), s0, s1, acc_a[g + j], acc_a[g + j + 1]);
-              }
-              if (second) {
-                if constexpr (!DUAL) {
-#pragma unroll
-                  for (int j = 0; j < 16; j += 4)
-                    *reinterpret_cast<float4*>(x16 + j) = *reinterpret_cast<const float4*>(xs2 + g + j);
+                for (int j = 0; j < 16; j += 2) {
+                  float s0, s1;
+                  mul2(wa, wa, s16[j], s16[j + 1], s0, s1);
+                  fma2(__uint_as_float(ra[g + j]), __uint_as_float(ra[g + j + 1]), s0, s1, acc_a[g + j], acc_a[g + j + 1]);
                 }
 #pragma unroll
                 for (int j = 0; j < 16; j += 2) {
                   float s0, s1;
-                  mul2(wb, wb, x16[j], x16[j + 1], s0, s1);
-                  if constexpr (DUAL)
-                    fma2(__uint_as_float(rb[g + j]), __uint_as_float(rb[g + j + 1]), s0, s1, acc_b[g + j], acc_b[g + j + 1]);
-                  else
-                    fma2(__uint_as_float(rb[g + j]), __uint_as_float(rb[g + j + 1]), s0, s1, acc_a[g + j], acc_a[g + j + 1]);
+                  mul2(wb, wb, s16[j], s16[j + 1], s0, s1);
+                  fma2(__uint_as_float(rb[g + j]), __uint_as_float(rb[g + j + 1]), s0, s1, acc_b[g + j], acc_b[g + j + 1]);
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; j += 2)
+                  fma2(__uint_as_float(ra[g + j]), __uint_as_float(ra[g + j + 1]), s16[j], s16[j + 1], acc_a[g + j], acc_a[g + j + 1]);
+                if (second) {
+#pragma unroll
+                  for (int j = 0; j < 16; j += 4)
+                    *reinterpret_cast<float4*>(s16 + j) = *reinterpret_cast<const float4*>(sa + NT + g + j);
+#pragma unroll
+                  for (int j = 0; j < 16; j += 2)
+                    fma2(__uint_as_float(rb[g + j]), __uint_as_float(rb[g + j + 1]), s16[j], s16[j + 1], acc_a[g + j], acc_a[g + j + 1]);
                 }
               }
             }
@@ -638,26 +686,28 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
           }
         }
+        PROBE_ADD(probe_fold, t_fold);
         kb += len;
       }
+      PROBE_START(t_close);
       // One decision for all epilogue threads: nobody may be left alone at a later barrier.
       if (epilogue_any<C::kEpiThreads>(failed || *s_abort)) break;
       if constexpr (DUAL) {
-        epilogue_swiglu_requant<C::kCpt, C::kEpiThreads>(acc_a, acc_b, m, col0, NT, rend, ch.row0, mt, p.m, s_amax,
-                                                         p.aq, p.as, p.swiglu);
-        // every thread's stores were fenced before the epilogue's closing barrier: announce the tile
+        epilogue_swiglu_requant_tile<C::kCpt, C::kEpiThreads>(acc_a, acc_b, static_cast<int>(threadIdx.x) - 96, m, col0, NT,
+                                                              rend, ch.rows, ch.row0, mt, p.m, s_amax, s_amax + 4 * NT,
+                                                              s_tile, p.aq, p.as, p.swiglu);
+        // Every epilogue thread's stores precede the closing barrier of the call above, so one
+        // thread's fence and release cover them all (the readers are plain loads and TMA).
         if (p.progress && epi == 0 && lane == 0) {
           __threadfence();
+          fence_async_global();
           atomicAdd(p.progress + u / p.tiles_m, 1);
         }
       } else {
         if (spread) {
           // This part's fp32 sums go to global memory; the CTA that finishes a tile's last part adds
           // all parts in part order (so the result does not depend on which one that is) and rounds.
-          // destination rows were staged by the scale loader together with the scales
-          int dest[C::kCpt];
-#pragma unroll
-          for (int n = 0; n < C::kCpt; ++n) dest[n] = sd[col0 + n];
+          // (destination rows were staged by the scale loader together with the scales)
           const size_t tile_floats = static_cast<size_t>(NT) * 128;
           float* parts = p.partial + static_cast<size_t>(u) * ksplit * tile_floats;
 #pragma unroll
@@ -673,26 +723,29 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           }
           epilogue_sync<C::kEpiThreads>();
           if (*s_last_part) {
+            float sums[C::kCpt];
 #pragma unroll
             for (int n = 0; n < C::kCpt; ++n) {
+              sums[n] = 0.f;
               if (col0 + n < rend) {
-                float sum = 0.f;
                 for (int part = 0; part < ksplit; ++part)
-                  sum = __fadd_rn(sum, __ldcg(parts + part * tile_floats + (col0 + n) * 128 + m));
-                p.out[static_cast<size_t>(dest[n]) * p.m + mt * kGroup + m] = __float2bfloat16_rn(sum);
+                  sums[n] = __fadd_rn(sums[n], __ldcg(parts + part * tile_floats + (col0 + n) * 128 + m));
               }
             }
+            epilogue_store_tile<C::kCpt, C::kEpiThreads>(sums, static_cast<int>(threadIdx.x) - 96, m, col0, rend, ch.rows, mt,
+                                                         p.m, sd, reinterpret_cast<__nv_bfloat16*>(s_tile), p.out);
           }
         } else {
-#pragma unroll
-          for (int n = 0; n < C::kCpt; ++n) {
-            if (col0 + n < rend) {   // one bf16 rounding of the fp32 sum (megabench/tasks/megamoe.py:149)
-              const float sum = parts_here ? acc_b[n] : acc_a[n];
-              p.out[static_cast<size_t>(sd[col0 + n]) * p.m + mt * kGroup + m] = __float2bfloat16_rn(sum);
-            }
-          }
+          // one bf16 rounding of the fp32 sum (megabench/tasks/megamoe.py:149)
+          if (parts_here)
+            epilogue_store_tile<C::kCpt, C::kEpiThreads>(acc_b, static_cast<int>(threadIdx.x) - 96, m, col0, rend, ch.rows, mt,
+                                                         p.m, sd, reinterpret_cast<__nv_bfloat16*>(s_tile), p.out);
+          else
+            epilogue_store_tile<C::kCpt, C::kEpiThreads>(acc_a, static_cast<int>(threadIdx.x) - 96, m, col0, rend, ch.rows, mt,
+                                                         p.m, sd, reinterpret_cast<__nv_bfloat16*>(s_tile), p.out);
         }
       }
+      PROBE_ADD(probe_close, t_close);
       mbar_arrive(bar_scempty + b);   // this item's scales are no longer needed
     }
   }
