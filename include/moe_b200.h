@@ -110,7 +110,7 @@ typedef struct moe_workspace_layout {
   uint64_t slots;         /* bf16 [T*topk + T, H] down-projection rows in slot order */
   int32_t rows;           /* T*topk + T*n_shared */
   int32_t max_chunks;
-  int32_t token_tile;     /* tokens per MMA tile (16, 32 or 64) chosen for this T */
+  int32_t token_tile;     /* token rows per MMA tile (16, 32, 64 or 128) chosen for this T */
   int32_t reserved;
 } moe_workspace_layout_t;
 

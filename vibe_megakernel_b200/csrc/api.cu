@@ -56,7 +56,7 @@ int layout_of(const moe_config_t* c, int tokens, moe_workspace_layout_t* L) {
   const int n_local = c->n_experts / c->ep_world;
   const int routed = tokens * c->topk;
   const int rows = routed + tokens * c->n_shared;
-  const int tile = moe::pick_token_tile(routed, n_local);
+  const int tile = moe::pick_token_tile(routed, n_local, c->gemm_impl == MOE_GEMM_TCGEN05 && c->ep_world == 1 ? 128 : 64);
   const int max_chunks = std::min(routed, n_local) + routed / tile + (tokens + tile - 1) / tile + 1;
   const uint64_t H = c->hidden, I = c->inter;
   uint64_t off = 0;
@@ -296,7 +296,8 @@ static int layer_forward_impl(const moe_config_t* cfg, const moe_weights_t* w, c
   a.chunks = chunks;
   a.n_chunks = n_chunks;
   a.status = status;
-  a.progress = g_profile ? nullptr : g.progress;   // per-stage timing wants the two GEMMs apart
+  // per-stage timing wants the two GEMMs apart; 128-row tiles run them one after the other as well
+  a.progress = g_profile || L.token_tile == 128 ? nullptr : g.progress;
   a.max_chunks = L.max_chunks;
   a.tiles_before = cfg->inter / 128;
   int driver_error = 0;

@@ -119,8 +119,11 @@ cudaError_t launch_gather_rows(const GatherArgs& a, int row_blocks, cudaStream_t
 // A tile wider than the chunks it meets costs shared memory per pipeline stage and epilogue
 // registers for columns that are never used; a narrower one only splits the few large chunks
 // (the shared expert, hot experts), whose weight tiles are then re-read from the L2.
-inline int pick_token_tile(long long routed_rows, int experts) {
+// With widest = 128 (callers whose GEMM arm has the kernel for it): 128-row tiles with the tokens on
+// the MMA's M side once an expert can expect more rows than the widest N tile holds.
+inline int pick_token_tile(long long routed_rows, int experts, int widest = 64) {
   const long long expected = (routed_rows + experts - 1) / (experts > 0 ? experts : 1);
+  if (widest >= 128 && expected > 64) return 128;
   return expected <= 8 ? 16 : expected <= 16 ? 32 : 64;
 }
 
@@ -157,7 +160,7 @@ inline WorkListLayout work_list_layout(int max_chunks, int hidden, int inter, in
   uint64_t off = w.counters + 4ull * w.counters_len;
   off = (off + 255) / 256 * 256;
   w.partial = off;
-  if (ksplit > 1) off += 4ull * max_chunks * tiles_down * ksplit * tile * 128;
+  if (ksplit > 1 && tile < 128) off += 4ull * max_chunks * tiles_down * ksplit * tile * 128;   // 128-row tiles sum their parts in registers
   w.bytes = off;
   return w;
 }
@@ -226,6 +229,8 @@ struct GemmArgs {
   bool bf16_operands;        // CUDA-core arm only: operands dequantised and rounded to bf16 first (MOE_GEMM_SIMT_BF16)
 };
 cudaError_t launch_gemm_tc(const GemmArgs& a, cudaStream_t stream, int* launches, int* driver_error);
+// tile == 128: tokens on the MMA's M side (gemm_wide.cu); no hand-over, no folded combine
+cudaError_t launch_gemm_wide(const GemmArgs& a, cudaStream_t stream, int* launches, int* driver_error);
 
 // Grouped GEMM in the MegaMoE-native formats (MXFP4 weights, E4M3 rows, E8M0 scales per 32 channels
 // on both sides), block-scaled tensor-core MMA. dual: linear1 ([E, 2m, k]: gate rows then up rows) with
@@ -268,6 +273,7 @@ cudaError_t launch_gather_mx_rows(const uint8_t* x, const uint8_t* x_scales, con
 cudaError_t launch_gemm_simt(const GemmArgs& a, cudaStream_t stream, int* launches);
 // The arm `impl` (MOE_GEMM_*) asks for.
 inline cudaError_t launch_gemm(int impl, GemmArgs& a, cudaStream_t stream, int* launches, int* driver_error) {
+  if (impl == MOE_GEMM_TCGEN05 && a.tile == 128) return launch_gemm_wide(a, stream, launches, driver_error);
   if (impl == MOE_GEMM_TCGEN05) return launch_gemm_tc(a, stream, launches, driver_error);
   a.bf16_operands = impl == MOE_GEMM_SIMT_BF16;
   return launch_gemm_simt(a, stream, launches);
