@@ -371,6 +371,14 @@ int moe_ep_buffer_free(void* ptr);
  * refused an out-of-range index. *detail (may be NULL) receives a code naming the place. */
 int moe_device_status(const void* workspace, void* stream, int32_t* detail);
 
+/* Self-check of the epilogue arithmetic (no counterpart in the reference; test infrastructure). The
+ * tensor-core epilogues divide without the math library's range check and slow path (a reciprocal
+ * and fused residual corrections); this runs n (even) gate/up value pairs and n/2 group scales (device
+ * pointers, fp32) through both forms of SwiGLU and of the e4m3 quantisation and writes to counts
+ * (device int32[3]): SwiGLU values whose bits differ, e4m3 code pairs that differ, pairs checked. */
+int moe_selfcheck_divisions(const float* gate, const float* up, const float* scales, int32_t n, int32_t* counts,
+                            void* stream);
+
 /* Number of kernels the last layer call of this thread launched (moe_layer_forward, moe_block_forward,
  * moe_ep_forward, moe_experts_forward, moe_mx_forward, moe_mx_ep_forward, moe_latent_forward). */
 int moe_last_launch_count(void);

@@ -242,3 +242,36 @@ def test_ue8m0_quantiser_matches_oracle(api, rows, width, block, dtype):
     wq, ws = O.quantize_activation(x, group=block, scale_format="e8m0")
     assert torch.equal(q.view(torch.uint8).cpu(), wq.view(torch.uint8))
     assert torch.equal(s.cpu(), ws)
+
+
+def test_epilogue_divisions_match_the_library_divisions(api):
+    # The tensor-core epilogues divide by a reciprocal plus fused residual corrections instead of the
+    # math library's division (no range check, no slow path). Both forms are run on the device over
+    # four million value pairs: normal GEMM outputs, zeros of both signs, tiny and huge values, gates
+    # far below the point where exp(-g) overflows, group scales at and above their floor.
+    import ctypes as C
+    from vibe_megakernel_b200 import _cabi
+    lib = _cabi.load()
+    n = 1 << 22
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    g = (torch.randn(n, device="cuda", generator=gen) * 3).to(torch.bfloat16).float()
+    u = (torch.randn(n, device="cuda", generator=gen) * 3).to(torch.bfloat16).float()
+    edge = torch.tensor([0.0, -0.0, 1e-30, -1e-30, 1e-20, -1e-20, 87.0, -87.0, -88.0, -89.0, -100.0, -300.0, 300.0, 1e4,
+                         -1e4, 3.0e38, -3.0e38, 1.0, -1.0, 448.0], device="cuda").to(torch.bfloat16).float()
+    g[: edge.numel() * edge.numel()] = edge.repeat_interleave(edge.numel())
+    u[: edge.numel() * edge.numel()] = edge.repeat(edge.numel())
+    act = (g / (1 + torch.exp(-g)) * u).abs()
+    amax = torch.maximum(act[0::2], act[1::2])
+    amax = torch.where(torch.isfinite(amax), amax, torch.ones_like(amax))
+    spread = torch.rand(n // 2, device="cuda", generator=gen) * 4 + 0.25      # some groups saturate, most do not
+    scales = torch.clamp(amax * spread, min=1e-4) / torch.tensor(448.0, device="cuda")
+    scales = scales.clamp(max=1e30).contiguous()
+    counts = torch.zeros(3, dtype=torch.int32, device="cuda")
+    rc = lib.moe_selfcheck_divisions(g.data_ptr(), u.data_ptr(), scales.data_ptr(), n, counts.data_ptr(),
+                                     torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    differing_values, differing_codes, seen = counts.tolist()
+    assert seen == n // 2
+    assert differing_values == 0
+    assert differing_codes == 0

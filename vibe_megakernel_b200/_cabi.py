@@ -110,6 +110,7 @@ EXPORTS = {
                                      C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "moe_device_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]),
     "moe_last_launch_count": (C.c_int, []),
+    "moe_selfcheck_divisions": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "moe_profile_enable": (C.c_int, [C.c_int32]),
     "moe_profile_read": (C.c_int, [C.POINTER(C.c_float), C.c_int32]),
 }

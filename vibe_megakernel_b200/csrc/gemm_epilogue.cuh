@@ -83,9 +83,12 @@ __device__ __forceinline__ void epilogue_swiglu_requant(float (&gate)[CPT], cons
 //   * one thread per token computes the scale (a division) instead of all 128 of the column;
 //   * the e4m3 bytes are collected in shared memory as [token][128 channels] and leave as whole rows,
 //     16 bytes per thread, instead of one byte per thread and token;
+//   * the divisions (SwiGLU, quantisation) take the forms without range check and slow path
+//     (common.cuh), the quantisation's with the reciprocal of the token's scale computed once;
 //   * no thread fences: whoever announces the tile does, after the closing barrier.
 //   tid: 0..THREADS-1; rend: end of this thread's valid columns; rows: the chunk's rows;
-//   s_amax: float[4][nt]; s_scale: float[nt]; s_tile: uint8_t[nt][128], 16-byte aligned.
+//   s_amax: float[4][nt]; s_scale: float[2][nt] (scales, then their reciprocals);
+//   s_tile: uint8_t[nt][128], 16-byte aligned.
 template <int CPT, int THREADS>
 __device__ __forceinline__ void epilogue_swiglu_requant_tile(float (&gate)[CPT], const float (&up)[CPT], int tid, int m,
                                                              int col0, int nt, int rend, int rows, int row0, int tile_m,
@@ -102,7 +105,7 @@ __device__ __forceinline__ void epilogue_swiglu_requant_tile(float (&gate)[CPT],
         g = fminf(g, mode.limit);
         u = fminf(fmaxf(u, -mode.limit), mode.limit);
       }
-      float a = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.f, expf(-g))), u);
+      float a = silu_times(g, u);
       if (mode.slot_weight) {
         const int dest = mode.row_dest[row0 + col0 + n];
         if (dest < mode.routed_rows) a = __fmul_rn(a, mode.slot_weight[dest]);
@@ -123,13 +126,14 @@ __device__ __forceinline__ void epilogue_swiglu_requant_tile(float (&gate)[CPT],
     const float amax = fmaxf(fmaxf(s_amax[c], s_amax[nt + c]), fmaxf(s_amax[2 * nt + c], s_amax[3 * nt + c]));
     const float scale = group_scale(amax);
     s_scale[c] = scale;
+    s_scale[nt + c] = __frcp_rn(scale);
     as[static_cast<size_t>(row0 + c) * groups + tile_m] = scale;
   }
   epilogue_sync<THREADS>();
 #pragma unroll
   for (int n = 0; n < CPT; ++n) {
     const int c = col0 + n;
-    if (c < rend) s_tile[c * kGroup + m] = to_e4m3(gate[n], s_scale[c]);
+    if (c < rend) s_tile[c * kGroup + m] = to_e4m3_near(gate[n], s_scale[c], s_scale[nt + c]);
   }
   epilogue_sync<THREADS>();
   for (int i = tid; i < rows * (kGroup / 16); i += THREADS) {

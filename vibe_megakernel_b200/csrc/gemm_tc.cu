@@ -71,7 +71,7 @@ struct GemmCfg {
   // Shared memory after the stage ring, for a contraction of kb K blocks:
   //   the output tile [NT][128] (e4m3 for gate/up, bf16 for down) the epilogue collects an item's
   //   results in, 2 buffers of { scale table [kb][NT], gate/up: weight scales [2][kb], destination
-  //   rows [NT] }, amax scratch [4][NT] and the token scales [NT],
+  //   rows [NT] }, amax scratch [4][NT], the token scales and their reciprocals [2][NT],
   //   barriers (2*kMaxStages + 2*kMaxAccStages + 2 + 2 + 2*kQueue), the item queue, 8 words of flags.
   // (every part a multiple of four floats, so the token scales can be read 16 bytes at a time)
   // Down GEMM: the table holds the products w_scale * x_scale (computed once by the scale loader
@@ -82,7 +82,7 @@ struct GemmCfg {
   static constexpr int scale_floats(int kb) { return kb * NT + weight_scale_floats(kb) + NT; }   // + destination rows [NT]
   static constexpr int kTileBytes = NT * 128 * (DUAL ? 1 : 2);
   static constexpr int tail_bytes(int kb) {
-    return kTileBytes + 2 * scale_floats(kb) * 4 + 5 * NT * 4 + (2 * kMaxStages + 2 * kMaxAccStages + 4 + 2 * kQueue) * 8 + kQueue * 16 + 64;
+    return kTileBytes + 2 * scale_floats(kb) * 4 + 6 * NT * 4 + (2 * kMaxStages + 2 * kMaxAccStages + 4 + 2 * kQueue) * 8 + kQueue * 16 + 64;
   }
   static constexpr int stages_for(int kb) {
     const int s = (kMaxSmem - 1024 - tail_bytes(kb)) / kStageBytes;
@@ -127,8 +127,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   uint8_t* s_tile = base + S * C::kStageBytes;                               // [NT][128] e4m3 or bf16
   float* s_scales = reinterpret_cast<float*>(s_tile + C::kTileBytes);        // [2][scale_floats(KB)]
   const int sf = C::scale_floats(KB);
-  float* s_amax = s_scales + 2 * sf;                                         // [4][NT], then the token scales [NT]
-  uint64_t* bar_full = reinterpret_cast<uint64_t*>(s_amax + 5 * NT);
+  float* s_amax = s_scales + 2 * sf;                                         // [4][NT], then scales and reciprocals [2][NT]
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(s_amax + 6 * NT);
   uint64_t* bar_empty = bar_full + kMaxStages;
   uint64_t* bar_tfull = bar_empty + kMaxStages;
   uint64_t* bar_tempty = bar_tfull + kMaxAccStages;
