@@ -26,6 +26,8 @@ CASES = {
     "ragged_scale_rows": (200, 4, 2, 384, 640, 3.0),           # 3 and 5 K blocks: scale rows of 12 and 20 bytes; tiles of 64
     "idle_experts": (3, 64, 2, 256, 256, 0.0),                 # most experts get no row; no clamp
     "catalog_width": (3, 2, 2, 7168, 3072, 10.0),              # megabench/cases.py:384-385: 56 and 24 K blocks per row
+    "rows_on_m": (300, 4, 2, 512, 256, 10.0),                  # 150 rows per expert: 128-row tiles, tokens on the MMA's M side
+    "rows_on_m_ragged": (520, 2, 2, 768, 640, 3.0),            # 520 rows per expert (4 full tiles + 8 rows), 6 and 5 K blocks
 }
 
 
@@ -140,3 +142,22 @@ def test_call_can_be_captured_in_a_cuda_graph(api):
         graph.replay()
         torch.cuda.synchronize()
         assert torch.equal(out, expect)
+
+
+@pytest.mark.parametrize("name", ["rows_on_m", "rows_on_m_ragged"])
+def test_rows_on_the_mma_m_side_give_the_bits_of_the_other_kernel(api, name):
+    # more than 64 rows per expert in sight: 128-row tiles with the tokens on M (gemm_mx_wide.cu). The same
+    # tokens sixteen at a time meet the kernel with the weights on M: every row must be bit-identical.
+    tokens, experts, topk, hidden, inter, limit = CASES[name]
+    values = H.to_device(H.megamoe_inputs(tokens, experts, topk, hidden, inter, seed=len(name)), "cuda")
+    wide = api.MegaMoe(api.MegaMoeConfig(hidden, inter, experts, topk, limit), max_tokens=tokens)
+    full = wide.run(values, check_status=True)
+    small = api.MegaMoe(api.MegaMoeConfig(hidden, inter, experts, topk, limit), max_tokens=16)
+    per_token = [k for k, v in values.items() if v.shape[0] == tokens]
+    assert "x" in per_token or len(per_token) >= 2
+    for lo in range(0, tokens, 16):
+        few = dict(values)
+        for k in per_token:
+            few[k] = values[k][lo:lo + 16].contiguous()
+        part = small.run(few, check_status=True)
+        assert torch.equal(part["y"], full["y"][lo:lo + 16]), lo

@@ -283,7 +283,7 @@ static void mx_ep_layouts(const moe_config_t& c, int max_tokens, moe_ep_layout_t
   const uint64_t H = c.hidden, I = c.inter;
   const int cap = max_tokens * c.topk;
   const int rows = world * cap;
-  const int tile = moe::pick_token_tile(rows, c.n_experts);
+  const int tile = moe::pick_token_tile(rows, c.n_experts, c.hidden % 256 == 0 ? 128 : 64, moe::kMxWideAbove);
   const int max_chunks = std::min(rows, n_local) + rows / tile + 1;
   uint64_t off = 0;
   auto take = [&](uint64_t bytes) { const uint64_t at = off; off = up256(off + bytes); return at; };

@@ -121,11 +121,15 @@ cudaError_t launch_gather_rows(const GatherArgs& a, int row_blocks, cudaStream_t
 // (the shared expert, hot experts), whose weight tiles are then re-read from the L2.
 // With widest = 128 (callers whose GEMM arm has the kernel for it): 128-row tiles with the tokens on
 // the MMA's M side once an expert can expect more rows than the widest N tile holds.
-inline int pick_token_tile(long long routed_rows, int experts, int widest = 64) {
+inline int pick_token_tile(long long routed_rows, int experts, int widest = 64, int wide_above = 64) {
   const long long expected = (routed_rows + experts - 1) / (experts > 0 ? experts : 1);
-  if (widest >= 128 && expected > 64) return 128;
+  if (widest >= 128 && expected > wide_above) return 128;
   return expected <= 8 ? 16 : expected <= 16 ? 32 : 64;
 }
+
+// MegaMoE-native GEMMs: expected rows per expert above which the 128-row kernel is taken (its MMAs cost
+// the same whether a tile's 128 rows are all there or not, the 64-token kernel's grow with the rows)
+constexpr int kMxWideAbove = 32;
 
 // Parts the down projection's contraction is cut in, from the geometry alone (never from the
 // batch, so that a token's result does not depend on what else is in flight): contractions
@@ -237,7 +241,7 @@ cudaError_t launch_gemm_wide(const GemmArgs& a, cudaStream_t stream, int* launch
 // clamped SwiGLU, routing weight and requantisation; else linear2 ([E, m, k]) into bf16 slot rows.
 struct MxGemmArgs {
   bool dual;
-  int tile;                   // tokens per MMA tile: 16, 32 or 64
+  int tile;                   // tokens per MMA tile: 16, 32 or 64 (weights on M), or 128 (tokens on M)
   int k, m;                   // contraction length; output channels per expert (I for linear1, H for linear2)
   int n_experts;
   int total_rows;             // rows of the activation buffer
@@ -266,6 +270,8 @@ struct MxGemmArgs {
   bool pairs;
 };
 cudaError_t launch_gemm_mx(const MxGemmArgs& a, cudaStream_t stream, int* launches, int* driver_error);
+// tile == 128: tokens on the MMA's M side (gemm_mx_wide.cu); plain rows, gate and up rows in one tensor, m % 256 == 0 for linear2
+cudaError_t launch_gemm_mx_wide(const MxGemmArgs& a, cudaStream_t stream, int* launches, int* driver_error);
 // Grouped row r < *kept <- row row_token[r] of e4m3 [tokens, hidden] with its hidden/32 scale bytes.
 cudaError_t launch_gather_mx_rows(const uint8_t* x, const uint8_t* x_scales, const int32_t* row_token, const int32_t* kept,
                                   int rows, int tokens, int hidden, uint8_t* xg, uint8_t* xgs, cudaStream_t stream,

@@ -64,7 +64,7 @@ int mx_layout(const moe_config_t* c, int tokens, MxLayout* L) {
   const uint64_t H = c->hidden, I = c->inter;
   MxLayout l;
   l.rows = rows;
-  l.tile = moe::pick_token_tile(rows, c->n_experts);
+  l.tile = moe::pick_token_tile(rows, c->n_experts, c->hidden % 256 == 0 ? 128 : 64, moe::kMxWideAbove);
   l.max_chunks = std::min(rows, c->n_experts) + rows / l.tile + 1;
   uint64_t off = 0;
   auto take = [&](uint64_t bytes) { const uint64_t at = off; off = align_up(off + bytes, 256); return at; };
