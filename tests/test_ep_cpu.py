@@ -66,7 +66,7 @@ def test_megamoe_exchange_layout_through_the_c_abi():
     cfg = _cabi.Config(7168, 3072, 384, 6, 0, 0, 1, 1, 1.0, 8, 5, 0, 10.0, 1)
     lay = _cabi.EpLayout()
     assert lib.moe_mx_ep_layout(C.byref(cfg), 512, C.byref(lay)) == 0
-    assert lay.cap == 512 * 6 and lay.rows == 8 * lay.cap and lay.token_tile == 64
+    assert lay.cap == 512 * 6 and lay.rows == 8 * lay.cap and lay.token_tile == 128
     offsets = [getattr(lay, n) for n in _cabi.EP_LAYOUT_OFFSETS[2:]]
     assert offsets == sorted(offsets) and all(o % 256 == 0 for o in offsets)
     assert lay.recv_s - lay.recv_q >= lay.rows * 7168 and lay.slots - lay.recv_s >= lay.rows * 7168 // 32
