@@ -94,14 +94,15 @@ def run(args, geo, metric: str, peak: float, peak_kind: str, clock_sampler, conf
     values = synthetic.make_inputs(geo, max(batches) // world, args.seed, dev, rank=rank, world=world)
     torch.cuda.synchronize()
     gen_s = time.time() - t0
-    x_all = values["x"]
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
     local = geo.experts // world
 
     def measure(batch: int, steps: int, warmup: int, full: bool):
         tokens = batch // world
         inputs = dict(values)
-        inputs["x"] = x_all[:tokens].contiguous()
+        # this rank's rows of THIS batch (global rows rank*tokens..): what the one-GPU run of the same batch sees
+        inputs["x"] = synthetic.normal_rows(args.seed, "x", batch, geo.hidden, 1.0, dev,
+                                            row_range=(rank * tokens, (rank + 1) * tokens)).to(torch.bfloat16)
         layer = EpMoeLayer(config, max_tokens=tokens, device=dev)
         out = layer.forward(inputs, check_status=True)
         ids_all = [None] * world
@@ -146,12 +147,16 @@ def run(args, geo, metric: str, peak: float, peak_kind: str, clock_sampler, conf
             # correctness across GPUs at full geometry: rank 0 runs the whole batch on one GPU
             ys = [None] * world
             dist.all_gather_object(ys, out["y"].cpu())
-            equal_one_gpu = None
+            equal_one_gpu, differing = None, None
             if rank == 0:
-                equal_one_gpu = bool(torch.equal(torch.cat(ys), one_gpu_result(geo, config, args, batch, dev)))
+                alone = one_gpu_result(geo, config, args, batch, dev)
+                together = torch.cat(ys)
+                equal_one_gpu = bool(torch.equal(together, alone))
+                gap = (together.float() - alone.float()).abs()
+                differing = {"elements": int((gap > 0).sum()), "rows": int((gap > 0).any(1).sum()), "max_abs": float(gap.max())}
             extra = {"e2e_us": e2e_ms * 1e3, "io_bytes": _reduce(float(x_host.numel() * 2), dist.ReduceOp.SUM),
                      "agree": _reduce(1.0 if same else 0.0, dist.ReduceOp.SUM) == world, "busiest": busiest, "ms": ms,
-                     "equal_one_gpu": equal_one_gpu, "launches": launches}
+                     "equal_one_gpu": equal_one_gpu, "differing": differing, "launches": launches}
             dist.barrier()
         layer.close()
         collective = EpCollectiveLayer(config, max_tokens=tokens, device=dev)
@@ -184,7 +189,7 @@ def run(args, geo, metric: str, peak: float, peak_kind: str, clock_sampler, conf
                          "input_generation_s": round(gen_s, 1)},
             "e2e": {"value": round(extra["e2e_us"], 2), "unit": "us", "h2d_bytes_per_step": int(extra["io_bytes"]),
                     "d2h_bytes_per_step": int(extra["io_bytes"]), "plugin_path_equals_direct_path": extra["agree"]},
-            "ep_equals_one_gpu": extra["equal_one_gpu"],
+            "ep_equals_one_gpu": extra["equal_one_gpu"], "ep_vs_one_gpu_differing": extra["differing"],
             "gpu_launches": extra["launches"] * args.steps * world, "launches_per_step_per_gpu": extra["launches"],
             "clocks": clocks.summary(),
             "roofline": {"bound": "hbm", "kernel": "whole layer on the busiest rank (weights of the experts it is hit on)",
