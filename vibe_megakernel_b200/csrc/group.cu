@@ -12,6 +12,7 @@ namespace moe {
 
 constexpr int kGroupWarps = 8;
 constexpr int kMaxGroupRows = 32768;   // ids are staged in shared memory as int16
+constexpr int kMaxSegments = 8;        // segments of a segmented input (one per source rank)
 
 __global__ void __launch_bounds__(kGroupWarps * 32) group_rows_kernel(GroupArgs a) {
   extern __shared__ int16_t s_ids[];                       // [n]
@@ -25,19 +26,35 @@ __global__ void __launch_bounds__(kGroupWarps * 32) group_rows_kernel(GroupArgs 
   if (a.zero_status && a.status && blockIdx.x == 0 && tid < 8) a.status[tid] = 0;   // only block 0 reports, later
   wait_for_peers(a.wait);
 
+  // Segmented input (expert-parallel arrivals: segment s holds seg_counts[s] rows at s * seg_cap): only
+  // the rows that exist are walked, in row order, through a compact index c -> row.
+  int first_c[kMaxSegments + 1];      // (every index below is a compile-time constant: registers)
+  int n_rows = a.n;
+  const int segments = a.seg_counts ? min(a.n / a.seg_cap, kMaxSegments) : 0;
+  first_c[0] = 0;
+#pragma unroll
+  for (int sgm = 0; sgm < kMaxSegments; ++sgm)
+    first_c[sgm + 1] = first_c[sgm] + (sgm < segments ? min(max(a.seg_counts[sgm], 0), a.seg_cap) : 0);
+  if (a.seg_counts) n_rows = first_c[kMaxSegments];
+  auto row_of = [&](int c) {
+    int r = c;
+#pragma unroll
+    for (int sgm = 1; sgm < kMaxSegments; ++sgm)
+      if (sgm < segments && c >= first_c[sgm]) r = sgm * a.seg_cap + (c - first_c[sgm]);
+    return r;
+  };
+
   for (int i = tid; i < groups; i += blockDim.x) s_count[i] = 0;
   __syncthreads();
-  for (int r0 = warp * 32; r0 < a.n; r0 += blockDim.x) {     // whole warps, so that the lanes can vote
-    const int r = r0 + lane;
+  for (int c0 = warp * 32; c0 < n_rows; c0 += blockDim.x) {     // whole warps, so that the lanes can vote
+    const int c = c0 + lane;
     int key = -1;                                             // local expert of a kept row
-    if (r < a.n) {
+    if (c < n_rows) {
+      const int r = row_of(c);
       const long long id = a.ids32 ? static_cast<long long>(a.ids32[r]) : a.ids64[r];
       const long long local = id - a.id_base;
-      // segmented input (expert-parallel arrivals): row r of segment r / seg_cap exists only below
-      // that segment's count
-      const bool present = !a.seg_counts || (r % a.seg_cap) < a.seg_counts[r / a.seg_cap];
-      if (present && local >= 0 && local < a.n_local) key = static_cast<int>(local);
-      s_ids[r] = static_cast<int16_t>(key);
+      if (local >= 0 && local < a.n_local) key = static_cast<int>(local);
+      s_ids[c] = static_cast<int16_t>(key);
     }
     // one shared-memory atomic per distinct expert of the warp: a hot expert (skewed routing) would
     // otherwise serialise hundreds of them on one address, in every block
@@ -55,11 +72,12 @@ __global__ void __launch_bounds__(kGroupWarps * 32) group_rows_kernel(GroupArgs 
   if (e < a.n_local && s_count[e] > 0) {
     int placed = 0;
     const int base = s_offset[e];
-    for (int r0 = 0; r0 < a.n; r0 += 32) {
-      const int r = r0 + lane;
-      const bool hit = r < a.n && s_ids[r] == e;
+    for (int c0 = 0; c0 < n_rows; c0 += 32) {
+      const int c = c0 + lane;
+      const bool hit = c < n_rows && s_ids[c] == e;
       const unsigned m = __ballot_sync(0xffffffffu, hit);
       if (hit) {
+        const int r = row_of(c);
         const int pos = base + placed + __popc(m & ((1u << lane) - 1u));
         if (a.order) a.order[pos] = r;
         if (a.row_token) a.row_token[pos] = r / a.topk;
