@@ -38,6 +38,7 @@ __global__ void __launch_bounds__(kGroupWarps * 32) group_rows_kernel(GroupArgs 
   if (a.seg_counts) n_rows = first_c[kMaxSegments];
   auto row_of = [&](int c) {
     int r = c;
+    if (segments == 0) return r;      // uniform: plain input
 #pragma unroll
     for (int sgm = 1; sgm < kMaxSegments; ++sgm)
       if (sgm < segments && c >= first_c[sgm]) r = sgm * a.seg_cap + (c - first_c[sgm]);
