@@ -120,8 +120,10 @@ cudaError_t launch_gather_rows(const GatherArgs& a, int row_blocks, cudaStream_t
 // registers for columns that are never used; a narrower one only splits the few large chunks
 // (the shared expert, hot experts), whose weight tiles are then re-read from the L2.
 // With widest = 128 (callers whose GEMM arm has the kernel for it): 128-row tiles with the tokens on
-// the MMA's M side once an expert can expect more rows than the widest N tile holds.
-inline int pick_token_tile(long long routed_rows, int experts, int widest = 64, int wide_above = 64) {
+// the MMA's M side once an expert can expect more than `wide_above` rows (measured on the Mixtral
+// shape: 64 rows per expert 418 -> 375 us with them; at 32 and fewer rows per expert, there and on
+// the Qwen and Kimi shapes, the 16..64-token tiles are as fast or faster).
+inline int pick_token_tile(long long routed_rows, int experts, int widest = 64, int wide_above = 32) {
   const long long expected = (routed_rows + experts - 1) / (experts > 0 ? experts : 1);
   if (widest >= 128 && expected > wide_above) return 128;
   return expected <= 8 ? 16 : expected <= 16 ? 32 : 64;
