@@ -37,7 +37,7 @@ static void ep_layouts(const moe_config_t& c, int max_tokens, moe_ep_layout_t* L
   const uint64_t H = c.hidden, I = c.inter;
   const int cap = max_tokens * c.topk;
   const int rows = world * cap + max_tokens;
-  const int tile = moe::pick_token_tile(static_cast<long long>(world) * cap, c.n_experts);
+  const int tile = moe::pick_token_tile(static_cast<long long>(world) * cap, c.n_experts, c.gemm_impl == MOE_GEMM_TCGEN05 ? 128 : 64);
   const int max_chunks = std::min(world * cap, n_local) + world * cap / tile + (max_tokens + tile - 1) / tile + 1;
   uint64_t off = 0;
   auto take = [&](uint64_t bytes) { const uint64_t at = off; off = up256(off + bytes); return at; };
@@ -559,7 +559,7 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* 
   a.chunks = g.chunks;
   a.n_chunks = g.n_chunks;
   a.status = status;
-  a.progress = g.progress;
+  a.progress = L.token_tile == 128 ? nullptr : g.progress;      // 128-row tiles run the two GEMMs one after the other
   a.max_chunks = L.max_chunks;
   a.tiles_before = cfg->inter / 128;
   int driver_error = 0;
