@@ -587,22 +587,38 @@ int moe_ep_forward(const moe_config_t* cfg, const moe_weights_t* w, const void* 
   a.swiglu = moe::SwigluMode{};
   a.out = reinterpret_cast<__nv_bfloat16*>(ws + P.out);
   a.row_dest = nullptr;
+  // 5. rows go home as peer stores, flags raised when all are on their way: from the down GEMM's own
+  // epilogue and last CTA (the weights-on-M tensor-core kernel), else by a copy kernel behind it
+  const bool fold_return = cfg->gemm_impl == MOE_GEMM_TCGEN05 && L.token_tile != 128;
+  if (fold_return) {
+    for (int r = 0; r < 8; ++r) a.ret.base[r] = r < world ? peers.base[r] : nullptr;
+    a.ret.row_source = row_source;
+    a.ret.recv_slot = reinterpret_cast<const int32_t*>(mine + L.recv_slot);
+    a.ret.offsets = offsets;
+    a.ret.n_local = n_local; a.ret.cap = L.cap; a.ret.world = world; a.ret.rank = rank;
+    a.ret.home_tokens = tokens; a.ret.topk = cfg->topk;
+    a.ret.off_slots = L.slots; a.ret.off_flags = L.flags_return;
+    a.ret.done = counters + 1;
+    a.ret.epoch = epoch;
+  }
   e = moe::launch_gemm(cfg->gemm_impl, a, stream, &launches, &driver_error);
   if (driver_error) return MOE_ERR_DRIVER;
   if (e != cudaSuccess) return cuda_rc(e);
 
-  // 5. rows go home (peer stores), flags raised by the last block; 6. wait for all owners, combine
-  moe::ReturnArgs r;
-  r.out = a.out; r.row_source = row_source; r.offsets = offsets;
-  r.recv_slot = reinterpret_cast<const int32_t*>(mine + L.recv_slot);
-  r.n_local = n_local; r.shared_rows = g.shared_rows; r.hidden = H; r.cap = L.cap; r.world = world; r.rank = rank;
-  r.home_tokens = tokens; r.topk = cfg->topk;
-  r.peers = peers;
-  r.off_slots = L.slots; r.off_flags = L.flags_return;
-  r.done = counters + 1;
-  r.epoch = epoch;
-  moe::launch_dependent(moe::ep_return_kernel, dim3(row_blocks), dim3(128), 0, stream, r);
-  ++launches;
+  if (!fold_return) {
+    moe::ReturnArgs r;
+    r.out = a.out; r.row_source = row_source; r.offsets = offsets;
+    r.recv_slot = reinterpret_cast<const int32_t*>(mine + L.recv_slot);
+    r.n_local = n_local; r.shared_rows = g.shared_rows; r.hidden = H; r.cap = L.cap; r.world = world; r.rank = rank;
+    r.home_tokens = tokens; r.topk = cfg->topk;
+    r.peers = peers;
+    r.off_slots = L.slots; r.off_flags = L.flags_return;
+    r.done = counters + 1;
+    r.epoch = epoch;
+    moe::launch_dependent(moe::ep_return_kernel, dim3(row_blocks), dim3(128), 0, stream, r);
+    ++launches;
+  }
+  // 6. wait for all owners, combine
   const moe::FlagWait home{reinterpret_cast<const uint64_t*>(mine + L.flags_return), world, epoch, moe::kWaitNs, status, 300};
   e = moe::launch_combine(reinterpret_cast<const __nv_bfloat16*>(mine + L.slots), tw, tokens, cfg->topk, H, cfg->n_shared,
                           static_cast<__nv_bfloat16*>(y_bf16), stream, &launches, nullptr, &home);

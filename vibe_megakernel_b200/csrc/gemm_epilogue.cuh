@@ -148,10 +148,13 @@ __device__ __forceinline__ void epilogue_swiglu_requant_tile(float (&gate)[CPT],
 // memory as [token][128 channels] and stored as whole 256-byte row pieces, 16 bytes per thread.
 //   dest: shared int[nt], destination row of every token column; s_tile: bf16 [nt][128].
 // The caller's next barrier over the epilogue threads protects the tile against reuse.
+//   row_ptr (optional, shared uint64[nt]): the address of every token column's output row instead of
+//   dest/out (rows that live in other GPUs' memory).
 template <int CPT, int THREADS>
 __device__ __forceinline__ void epilogue_store_tile(const float (&sum)[CPT], int tid, int m, int col0, int rend, int rows,
                                                     int tile_m, int hidden, const int* dest, __nv_bfloat16* s_tile,
-                                                    __nv_bfloat16* __restrict__ out) {
+                                                    __nv_bfloat16* __restrict__ out,
+                                                    const unsigned long long* row_ptr = nullptr) {
 #pragma unroll
   for (int n = 0; n < CPT; ++n) {
     const int c = col0 + n;
@@ -160,8 +163,8 @@ __device__ __forceinline__ void epilogue_store_tile(const float (&sum)[CPT], int
   epilogue_sync<THREADS>();
   for (int i = tid; i < rows * (kGroup / 8); i += THREADS) {
     const int r = i >> 4, part = i & 15;
-    *reinterpret_cast<uint4*>(out + static_cast<size_t>(dest[r]) * hidden + tile_m * kGroup + part * 8) =
-        *reinterpret_cast<const uint4*>(s_tile + r * kGroup + part * 8);
+    __nv_bfloat16* row = row_ptr ? reinterpret_cast<__nv_bfloat16*>(row_ptr[r]) : out + static_cast<size_t>(dest[r]) * hidden;
+    *reinterpret_cast<uint4*>(row + tile_m * kGroup + part * 8) = *reinterpret_cast<const uint4*>(s_tile + r * kGroup + part * 8);
   }
 }
 

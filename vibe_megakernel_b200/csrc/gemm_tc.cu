@@ -79,7 +79,7 @@ struct GemmCfg {
   // scales, with the two weight scales of every K block behind them (two product tables would
   // double the broadcast loads of the fold, which the shared-memory pipe, not the FP pipe, limits).
   static constexpr int weight_scale_floats(int kb) { return DUAL ? (2 * kb + 3) & ~3 : 0; }
-  static constexpr int scale_floats(int kb) { return kb * NT + weight_scale_floats(kb) + NT; }   // + destination rows [NT]
+  static constexpr int scale_floats(int kb) { return kb * NT + weight_scale_floats(kb) + NT + (DUAL ? 0 : 2 * NT); }   // + destination rows [NT], down: + row addresses [NT] x 8 bytes
   static constexpr int kTileBytes = NT * 128 * (DUAL ? 1 : 2);
   static constexpr int tail_bytes(int kb) {
     return kTileBytes + 2 * scale_floats(kb) * 4 + 6 * NT * 4 + (2 * kMaxStages + 2 * kMaxAccStages + 4 + 2 * kQueue) * 8 + kQueue * 16 + 64;
@@ -111,6 +111,7 @@ struct GemmDev {
   int32_t* parts_done;     // ksplit > 1: per (chunk, channel tile) count of finished parts, zero on entry
   SwigluMode swiglu;       // DUAL: clamp and routing weight of the MegaMoE form, off by default
   FoldCombine fold;        // !DUAL: the combine, done by whoever stores a token's last slot row of a channel tile
+  PeerReturn ret;          // !DUAL: rows stored into their sources' slot buffers, flags raised by the last CTA
 };
 
 template <int NT, bool DUAL>
@@ -402,6 +403,27 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if constexpr (!DUAL) {
         for (int n = lane; n < NT; n += 32)
           sd[n] = n < ch.rows ? (p.row_dest ? p.row_dest[ch.row0 + n] : ch.row0 + n) : 0;
+        if (p.ret.base[0]) {
+          // expert-parallel return: where every row of the chunk goes home to (its source's slot buffer)
+          unsigned long long* sp = reinterpret_cast<unsigned long long*>(sd + NT);
+          const int kept = p.ret.offsets[p.ret.n_local];
+          for (int n = lane; n < NT; n += 32) {
+            unsigned long long at = 0;
+            if (n < ch.rows) {
+              const int pos = ch.row0 + n;
+              const int src = p.ret.row_source[pos];
+              const bool routed = pos < kept;
+              const int owner = routed ? src / p.ret.cap : p.ret.rank;
+              const size_t slot = routed ? static_cast<size_t>(p.ret.recv_slot[src])
+                                         : static_cast<size_t>(p.ret.home_tokens) * p.ret.topk + src;
+              uint8_t* peer = p.ret.base[0];
+#pragma unroll
+              for (int r = 1; r < 8; ++r) peer = owner == r ? p.ret.base[r] : peer;
+              at = reinterpret_cast<unsigned long long>(peer + p.ret.off_slots + slot * p.m * 2);
+            }
+            sp[n] = at;
+          }
+        }
       }
       int kb_lo, kb_hi;
       item_range(ch.pad, kb_lo, kb_hi);
@@ -504,6 +526,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const float* tab = s_scales + b * sf;         // [kb][NT]: token scales (gate/up) or scale products (down)
       const float* ws = tab + KB * NT;              // gate/up: weight scales [2][kb]
       const int* sd = reinterpret_cast<const int*>(ws + C::weight_scale_floats(KB));
+      // down GEMM of an expert-parallel call: the rows' addresses in their sources' slot buffers
+      const unsigned long long* sp = (!DUAL && p.ret.base[0]) ? reinterpret_cast<const unsigned long long*>(sd + NT) : nullptr;
       PROBE_START(t_scales);
       if (!failed && !mbar_wait(bar_scfull + b, sph, s_abort)) {
         if (!*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 5); *s_abort = 1; }
@@ -654,16 +678,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               }
             }
             epilogue_store_tile<C::kCpt, C::kEpiThreads>(sums, static_cast<int>(threadIdx.x) - 96, m, col0, rend, ch.rows, mt,
-                                                         p.m, sd, reinterpret_cast<__nv_bfloat16*>(s_tile), p.out);
+                                                         p.m, sd, reinterpret_cast<__nv_bfloat16*>(s_tile), p.out, sp);
           }
         } else {
           // one bf16 rounding of the fp32 sum (megabench/tasks/megamoe.py:149)
           if (parts_here)
             epilogue_store_tile<C::kCpt, C::kEpiThreads>(acc_b, static_cast<int>(threadIdx.x) - 96, m, col0, rend, ch.rows, mt,
-                                                         p.m, sd, reinterpret_cast<__nv_bfloat16*>(s_tile), p.out);
+                                                         p.m, sd, reinterpret_cast<__nv_bfloat16*>(s_tile), p.out, sp);
           else
             epilogue_store_tile<C::kCpt, C::kEpiThreads>(acc_a, static_cast<int>(threadIdx.x) - 96, m, col0, rend, ch.rows, mt,
-                                                         p.m, sd, reinterpret_cast<__nv_bfloat16*>(s_tile), p.out);
+                                                         p.m, sd, reinterpret_cast<__nv_bfloat16*>(s_tile), p.out, sp);
         }
       }
       PROBE_ADD(probe_close, t_close);
@@ -741,6 +765,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
     }
   }
+  if constexpr (!DUAL) {
+    if (p.ret.base[0] && threadIdx.x == 0) {
+      // Expert-parallel return: every row this CTA stored into a peer's slot buffer precedes the
+      // barrier above; one system-wide fence covers them, and the CTA that is through last tells every
+      // source that this owner's rows are home.
+      __threadfence_system();
+      if (atomicAdd(p.ret.done, 1) == static_cast<int>(gridDim.x) - 1) {
+        __threadfence_system();
+        for (int r = 0; r < p.ret.world; ++r) {
+          uint8_t* peer = p.ret.base[0];
+#pragma unroll
+          for (int q = 1; q < 8; ++q) peer = r == q ? p.ret.base[q] : peer;
+          store_release_sys(reinterpret_cast<uint64_t*>(peer + p.ret.off_flags) + p.ret.rank, p.ret.epoch);
+        }
+        *p.ret.done = 0;
+      }
+    }
+  }
   // Keep the stream's ordering for whatever follows: this grid does not complete before the
   // gate/up grid has (a CTA that found the dispenser empty idles here until that grid's last
   // tiles are done; one that did work finds it finished).
@@ -792,7 +834,7 @@ cudaError_t launch_gemm_tc(const GemmArgs& a, cudaStream_t stream, int* launches
   }
   GemmDev dev{a.chunks, a.n_chunks, a.m / 128, a.k / 128, a.m, a.n_local, a.max_stages, a.act_scale, a.w_a_scale, a.w_b_scale,
               a.s_a_scale, a.s_b_scale, a.aq, a.as, a.out, a.row_dest, a.status, a.progress, a.max_chunks,
-              a.tiles_before, 1, nullptr, nullptr, a.swiglu, a.dual ? FoldCombine{} : a.fold};
+              a.tiles_before, 1, nullptr, nullptr, a.swiglu, a.dual ? FoldCombine{} : a.fold, a.dual ? PeerReturn{} : a.ret};
   if (!a.dual && a.ksplit > 1) {
     const int per = (a.k / 128 + a.ksplit - 1) / a.ksplit;
     if (!a.partial || !a.parts_done || (a.ksplit - 1) * per >= a.k / 128 || a.ksplit > 255) return cudaErrorInvalidValue;

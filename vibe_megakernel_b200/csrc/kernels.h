@@ -191,6 +191,20 @@ struct FoldCombine {
   int tokens = 0, topk = 0, shared = 0;
 };
 
+// Down GEMM of an expert-parallel call: finished rows go straight into their sources' slot buffers
+// (peer stores from the epilogue) instead of a local buffer that a copy kernel would read again, and
+// the kernel's last CTA raises the return flags. base[0] == NULL: off.
+struct PeerReturn {
+  uint8_t* base[8];           // every rank's exchange buffer
+  const int32_t* row_source;  // grouped position -> arrival index (routed) or home token (shared expert)
+  const int32_t* recv_slot;   // arrival index -> slot at its source
+  const int32_t* offsets;     // offsets[n_local] = routed rows kept
+  int n_local, cap, world, rank, home_tokens, topk;
+  uint64_t off_slots, off_flags;
+  int32_t* done;              // counter of CTAs that are through: zero on entry, left at zero
+  uint64_t epoch;
+};
+
 struct GemmArgs {
   bool dual;                 // true: gate+up with SwiGLU + requantisation; false: down projection
   int tile;                  // tokens per MMA tile: 16, 32 or 64
@@ -233,6 +247,7 @@ struct GemmArgs {
   FoldCombine fold;          // down GEMM only: the combine done by the last tile of every token (y == NULL: off)
   int max_stages;            // > 0: cap of the shared-memory ring, so that the CTAs of the call's two GEMMs fit on an SM together
   bool bf16_operands;        // CUDA-core arm only: operands dequantised and rounded to bf16 first (MOE_GEMM_SIMT_BF16)
+  PeerReturn ret;            // down GEMM of the weights-on-M tensor-core kernel only (tile <= 64)
 };
 cudaError_t launch_gemm_tc(const GemmArgs& a, cudaStream_t stream, int* launches, int* driver_error);
 // tile == 128: tokens on the MMA's M side (gemm_wide.cu); no hand-over, no folded combine
