@@ -74,7 +74,7 @@ __global__ void duplicate_ids_kernel(const int32_t* __restrict__ ids, int n, int
 constexpr int kDenseTokens = 8;
 constexpr int kDenseWarps = 8;
 
-template <int ROWS, int MODE>
+template <int ROWS, int MODE, int TOK>
 __global__ void __launch_bounds__(kDenseWarps * 32) dense_rows_kernel(const __nv_bfloat16* __restrict__ w,
                                                                       const __nv_bfloat16* __restrict__ w2,
                                                                       const __nv_bfloat16* __restrict__ x, int tokens, int n, int k,
@@ -86,14 +86,16 @@ __global__ void __launch_bounds__(kDenseWarps * 32) dense_rows_kernel(const __nv
   dependents_may_launch();
   if (n0 >= n) return;
   constexpr int MATS = MODE == 1 ? 2 : 1;
-  for (int t0 = 0; t0 < tokens; t0 += kDenseTokens) {
-    float acc[MATS][ROWS][kDenseTokens];
+  for (int t0 = 0; t0 < tokens; t0 += TOK) {
+    float acc[MATS][ROWS][TOK];
 #pragma unroll
     for (int a = 0; a < MATS; ++a)
 #pragma unroll
       for (int r = 0; r < ROWS; ++r)
 #pragma unroll
-        for (int t = 0; t < kDenseTokens; ++t) acc[a][r][t] = 0.f;
+        for (int t = 0; t < TOK; ++t) acc[a][r][t] = 0.f;
+    // (few tokens leave registers free: several trips' weight loads are then in flight at once)
+#pragma unroll(TOK <= 2 ? 4 : 1)
     for (int c = lane * 8; c < k; c += 32 * 8) {
       uint4 wv[MATS][ROWS];
 #pragma unroll
@@ -102,8 +104,25 @@ __global__ void __launch_bounds__(kDenseWarps * 32) dense_rows_kernel(const __nv
         wv[0][r] = __ldg(reinterpret_cast<const uint4*>(w + static_cast<size_t>(row) * k + c));
         if constexpr (MODE == 1) wv[1][r] = __ldg(reinterpret_cast<const uint4*>(w2 + static_cast<size_t>(row) * k + c));
       }
+      if constexpr (TOK == 1) {
+        // one token: plain fused multiply-adds (each half of the packed form below is the same operation)
+        const uint4 xa = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(t0) * k + c);
+        const uint32_t* pa = reinterpret_cast<const uint32_t*>(&xa);
 #pragma unroll
-      for (int t = 0; t < kDenseTokens; t += 2) {
+        for (int j = 0; j < 4; ++j) {
+          const float a0 = __uint_as_float(pa[j] << 16), a1 = __uint_as_float(pa[j] & 0xffff0000u);
+#pragma unroll
+          for (int a = 0; a < MATS; ++a)
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+              const uint32_t word = reinterpret_cast<const uint32_t*>(&wv[a][r])[j];
+              acc[a][r][0] = __fmaf_rn(__uint_as_float(word << 16), a0, acc[a][r][0]);
+              acc[a][r][0] = __fmaf_rn(__uint_as_float(word & 0xffff0000u), a1, acc[a][r][0]);
+            }
+        }
+      }
+#pragma unroll
+      for (int t = 0; t + 1 < TOK; t += 2) {
         const int ta = min(t0 + t, tokens - 1), tb = min(t0 + t + 1, tokens - 1);
         const uint4 xa = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(ta) * k + c);
         const uint4 xb = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(tb) * k + c);
@@ -130,7 +149,7 @@ __global__ void __launch_bounds__(kDenseWarps * 32) dense_rows_kernel(const __nv
 #pragma unroll
       for (int r = 0; r < ROWS; ++r)
 #pragma unroll
-        for (int t = 0; t < kDenseTokens; ++t)
+        for (int t = 0; t < TOK; ++t)
 #pragma unroll
           for (int off = 16; off > 0; off >>= 1) acc[a][r][t] = __fadd_rn(acc[a][r][t], __shfl_xor_sync(0xffffffffu, acc[a][r][t], off));
     if (lane == 0) {
@@ -138,7 +157,7 @@ __global__ void __launch_bounds__(kDenseWarps * 32) dense_rows_kernel(const __nv
       for (int r = 0; r < ROWS; ++r) {
         if (n0 + r >= n) break;
 #pragma unroll
-        for (int t = 0; t < kDenseTokens; ++t) {
+        for (int t = 0; t < TOK; ++t) {
           if (t0 + t >= tokens) break;
           const size_t at = static_cast<size_t>(t0 + t) * n + n0 + r;
           float v = bf16_round(acc[0][r][t]);
@@ -158,7 +177,15 @@ static cudaError_t launch_dense(const __nv_bfloat16* w, const __nv_bfloat16* w2,
     return cudaErrorInvalidValue;
   constexpr int ROWS = MODE == 1 ? 2 : 4;
   const int blocks = (n + kDenseWarps * ROWS - 1) / (kDenseWarps * ROWS);
-  launch_dependent(dense_rows_kernel<ROWS, MODE>, dim3(blocks), dim3(kDenseWarps * 32), 0, stream, w, w2, x, tokens, n, k, other, y);
+  // tokens per pass: no more than there are (a pass of eight for one token did eight tokens' arithmetic)
+  if (tokens <= 1)
+    launch_dependent(dense_rows_kernel<ROWS, MODE, 1>, dim3(blocks), dim3(kDenseWarps * 32), 0, stream, w, w2, x, tokens, n, k, other, y);
+  else if (tokens <= 2)
+    launch_dependent(dense_rows_kernel<ROWS, MODE, 2>, dim3(blocks), dim3(kDenseWarps * 32), 0, stream, w, w2, x, tokens, n, k, other, y);
+  else if (tokens <= 4)
+    launch_dependent(dense_rows_kernel<ROWS, MODE, 4>, dim3(blocks), dim3(kDenseWarps * 32), 0, stream, w, w2, x, tokens, n, k, other, y);
+  else
+    launch_dependent(dense_rows_kernel<ROWS, MODE, kDenseTokens>, dim3(blocks), dim3(kDenseWarps * 32), 0, stream, w, w2, x, tokens, n, k, other, y);
   if (launches) *launches += 1;
   return cudaGetLastError();
 }
