@@ -10,7 +10,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "lib" / "libmoe_b200.so"
-SOURCES = ("api.cu", "megamoe.cu", "gemm_mx.cu", "gemm_mx_wide.cu", "route.cu", "router_logits.cu", "route_static.cu","group.cu", "quant.cu", "combine.cu", "rmsnorm.cu", "gemm_tc.cu", "gemm_wide.cu", "gemm_simt.cu", "ep.cu", "experts.cu", "latent.cu", "selfcheck.cu")
+SOURCES = ("api.cu", "megamoe.cu", "gemm_mx.cu", "gemm_mx_wide.cu", "route.cu", "router_logits.cu", "route_static.cu","group.cu", "quant.cu", "combine.cu", "rmsnorm.cu", "gemm_tc.cu", "gemm_wide.cu", "gemm_simt.cu", "ep.cu", "experts.cu", "latent.cu", "dense_tc.cu", "selfcheck.cu")
 FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "--expt-relaxed-constexpr")
 

@@ -302,4 +302,17 @@ inline cudaError_t launch_gemm(int impl, GemmArgs& a, cudaStream_t stream, int* 
   return launch_gemm_simt(a, stream, launches);
 }
 
+// Dense bf16 projection y = f(x W^T) on tensor cores (dense_tc.cu; the Kimi latent block above eight
+// tokens). mode 0: bf16(sum); 1: situ(bf16(sum over w), bf16(sum over w2)); 2: bf16(bf16(sum) + other).
+// n % 128 == 0, k % 64 == 0, 16-byte aligned pointers. The contraction is cut in plan.ksplit parts that
+// meet in `partial` (plan.partial_bytes) and `parts_done` (plan.tiles counters, zero on entry, left at zero).
+struct DenseTcPlan {
+  int tiles, ksplit;
+  uint64_t partial_bytes;
+};
+DenseTcPlan dense_tc_plan(int tokens, int n, int k);
+cudaError_t launch_dense_tc(int mode, const __nv_bfloat16* w, const __nv_bfloat16* w2, const __nv_bfloat16* x, int tokens, int n,
+                            int k, const __nv_bfloat16* other, __nv_bfloat16* y, float* partial, int32_t* parts_done,
+                            int32_t* status, cudaStream_t stream, int* launches, int* driver_error);
+
 }  // namespace moe

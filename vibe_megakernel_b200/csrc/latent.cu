@@ -201,8 +201,9 @@ inline uint64_t up256(uint64_t v) { return (v + 255) / 256 * 256; }
 inline int cuda_rc(cudaError_t e) { return e == cudaSuccess ? MOE_OK : static_cast<int>(e); }
 
 struct LatentLayout {
-  uint64_t status, logits, ids32, weights, ids2, counts, offsets, n_chunks, chunks, row_token, row_dest, latent, xq, xs, aq, as,
-      slots, sum, normed, act, shared, total;
+  uint64_t status, dense_parts, logits, ids32, weights, ids2, counts, offsets, n_chunks, chunks, row_token, row_dest, latent, xq,
+      xs, aq, as, slots, sum, normed, act, shared, dense_partial, total;
+  int dense_parts_len;
   int rows2, tile, max_chunks;
 };
 
@@ -223,6 +224,20 @@ int latent_layout(const moe_latent_config_t* c, int tokens, LatentLayout* L) {
   uint64_t off = 0;
   auto take = [&](uint64_t bytes) { const uint64_t at = off; off = up256(off + bytes); return at; };
   l.status = take(32);
+  // the tensor-core dense projections (above kDenseTokens tokens): per-tile counters of finished parts and
+  // the fp32 partial tiles of a split contraction, shared by the four projections (they run one after another)
+  const moe::DenseTcPlan plans[4] = {moe::dense_tc_plan(tokens, c->latent, c->hidden),
+                                     moe::dense_tc_plan(tokens, c->n_shared * c->inter, c->hidden),
+                                     moe::dense_tc_plan(tokens, c->hidden, c->n_shared * c->inter),
+                                     moe::dense_tc_plan(tokens, c->hidden, c->latent)};
+  int most_tiles = 1;
+  uint64_t most_partial = 0;
+  for (const moe::DenseTcPlan& plan : plans) {
+    most_tiles = std::max(most_tiles, plan.tiles);
+    most_partial = std::max(most_partial, plan.partial_bytes);
+  }
+  l.dense_parts_len = most_tiles;
+  l.dense_parts = take(4ull * most_tiles);
   l.logits = take(4ull * tokens * E);
   l.ids32 = take(4ull * rows);
   l.weights = take(4ull * rows);
@@ -243,6 +258,7 @@ int latent_layout(const moe_latent_config_t* c, int tokens, LatentLayout* L) {
   l.normed = take(2ull * tokens * LH);
   l.act = take(2ull * tokens * c->n_shared * I);
   l.shared = take(2ull * tokens * H);
+  l.dense_partial = take(most_partial);
   l.total = off;
   *L = l;
   return MOE_OK;
@@ -299,8 +315,25 @@ int moe_latent_forward(const moe_latent_config_t* cfg, const moe_latent_weights_
   const int H = cfg->hidden, LH = cfg->latent, I = cfg->inter, E = cfg->n_experts, K = cfg->topk;
   const int rows = tokens * K;
   int launches = 0;
-  cudaError_t e = cudaMemsetAsync(status, 0, 32, stream);
+  // status word, and the dense projections' part counters behind it (left at zero by the kernels, but the
+  // workspace arrives uninitialised)
+  cudaError_t e = cudaMemsetAsync(status, 0, L.dense_parts + 4ull * L.dense_parts_len, stream);
   if (e != cudaSuccess) return cuda_rc(e);
+  int driver_error = 0;
+  float* dense_partial = reinterpret_cast<float*>(ws + L.dense_partial);
+  int32_t* dense_parts = reinterpret_cast<int32_t*>(ws + L.dense_parts);
+  const int dense_tc_above = 0;
+  // a dense projection: CUDA cores up to dense_tc_above tokens, tensor cores above
+  auto dense = [&](int mode, const void* wm, const void* wm2, const bf16* in, int n, int k, const bf16* other, bf16* out) {
+    if (tokens > dense_tc_above && n % 128 == 0 && k % 64 == 0)
+      return moe::launch_dense_tc(mode, static_cast<const bf16*>(wm), static_cast<const bf16*>(wm2), in, tokens, n, k, other, out,
+                                  dense_partial, dense_parts, status, stream, &launches, &driver_error);
+    if (mode == 0) return moe::launch_dense<0>(static_cast<const bf16*>(wm), nullptr, in, tokens, n, k, nullptr, out, stream, &launches);
+    if (mode == 1)
+      return moe::launch_dense<1>(static_cast<const bf16*>(wm), static_cast<const bf16*>(wm2), in, tokens, n, k, nullptr, out, stream,
+                                  &launches);
+    return moe::launch_dense<2>(static_cast<const bf16*>(wm), nullptr, in, tokens, n, k, other, out, stream, &launches);
+  };
 
   // 1. router: sigmoid scores plus selection bias, no groups, weights normalised with scaling 1
   //    (megabench/tasks/kimi_layer.py:200-201)
@@ -313,7 +346,8 @@ int moe_latent_forward(const moe_latent_config_t* cfg, const moe_latent_weights_
   if (e != cudaSuccess) return cuda_rc(e);
 
   // 2. latent rows (megabench/tasks/kimi_layer.py:203)
-  e = moe::launch_dense<0>(static_cast<const bf16*>(w->latent_down), nullptr, x, tokens, LH, H, nullptr, latent, stream, &launches);
+  e = dense(0, w->latent_down, nullptr, x, LH, H, nullptr, latent);
+  if (driver_error) return MOE_ERR_DRIVER;
   if (e != cudaSuccess) return cuda_rc(e);
 
   // 3. every routed row becomes a pair of E4M3 rows; the pairs are grouped by expert
@@ -353,7 +387,6 @@ int moe_latent_forward(const moe_latent_config_t* cfg, const moe_latent_weights_
   a.n_chunks = g.n_chunks;
   a.status = status;
   a.pairs = true;
-  int driver_error = 0;
   a.dual = true;
   a.k = LH; a.m = I;
   a.max_units = L.max_chunks * (I / 128);
@@ -385,14 +418,14 @@ int moe_latent_forward(const moe_latent_config_t* cfg, const moe_latent_weights_
   if (e != cudaSuccess) return cuda_rc(e);
 
   // 6. shared experts on the full-width token (megabench/tasks/kimi_layer.py:228), then latent_up + shared
-  e = moe::launch_dense<1>(static_cast<const bf16*>(w->shared_gate), static_cast<const bf16*>(w->shared_up), x, tokens,
-                           cfg->n_shared * I, H, nullptr, act, stream, &launches);
+  e = dense(1, w->shared_gate, w->shared_up, x, cfg->n_shared * I, H, nullptr, act);
+  if (driver_error) return MOE_ERR_DRIVER;
   if (e != cudaSuccess) return cuda_rc(e);
-  e = moe::launch_dense<0>(static_cast<const bf16*>(w->shared_down), nullptr, act, tokens, H, cfg->n_shared * I, nullptr, shared,
-                           stream, &launches);
+  e = dense(0, w->shared_down, nullptr, act, H, cfg->n_shared * I, nullptr, shared);
+  if (driver_error) return MOE_ERR_DRIVER;
   if (e != cudaSuccess) return cuda_rc(e);
-  e = moe::launch_dense<2>(static_cast<const bf16*>(w->latent_up), nullptr, normed, tokens, H, LH, shared,
-                           static_cast<bf16*>(y_bf16), stream, &launches);
+  e = dense(2, w->latent_up, nullptr, normed, H, LH, shared, static_cast<bf16*>(y_bf16));
+  if (driver_error) return MOE_ERR_DRIVER;
   moe::note_launches(launches);
   return cuda_rc(e);
 }
