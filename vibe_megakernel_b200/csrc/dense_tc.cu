@@ -8,8 +8,9 @@
 // once per tile of 64 tokens. There are no scales: a work item accumulates its whole K range in one TMEM
 // accumulator (two for the gate/up pair) and the epilogue reads it once. A projection has only
 // N / 128 = 28..56 weight tiles, too few for 148 SMs, so the contraction is cut in parts that are work
-// items of their own: fp32 partial tiles in global memory, the CTA that finishes a tile's last part adds
-// them in part order (the result does not depend on which one that is) and applies f.
+// items of their own: fp32 partial tiles in global memory; at the kernel's end the grid meets (one
+// counter, bounded wait) and all CTAs share out the sums, every element's parts added in part order,
+// and apply f.
 //
 //   mode 0: y = bf16(sum)
 //   mode 1: y = situ(bf16(sum over W), bf16(sum over W2))     (gate and up rows of the shared experts)
@@ -47,7 +48,7 @@ struct DtDev {
   const __nv_bfloat16* other;
   __nv_bfloat16* y;
   float* partial;          // ksplit > 1: [tile][part][matrix][token column][128 channels]
-  int32_t* parts_done;     // ksplit > 1: per tile, zero on entry, left at zero
+  int32_t* parts_done;     // ksplit > 1: two counters (CTAs whose parts are stored, CTAs that have left), zero on entry, left at zero
   int32_t* status;
 };
 
@@ -61,6 +62,15 @@ __device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+
+// One output element from its complete fp32 sums (a: the projection, b: the up projection of the pair).
+template <bool DUAL>
+__device__ __forceinline__ __nv_bfloat16 dense_value(float a, float b, float other, int mode) {
+  float v = bf16_round(a);
+  if constexpr (DUAL) v = bf16_round(situ_f32(v, bf16_round(b)));
+  else if (mode == 2) v = bf16_round(__fadd_rn(v, other));
+  return __float2bfloat16_rn(v);
 }
 
 template <bool DUAL>
@@ -208,10 +218,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       const int channel = mt * 128 + m;
       auto finish = [&](int col, float a, float b) {      // one output element from its complete fp32 sums
         const size_t at = static_cast<size_t>(tt * kDtTokens + col) * p.n + channel;
-        float v = bf16_round(a);
-        if constexpr (DUAL) v = bf16_round(situ_f32(v, bf16_round(b)));
-        else if (p.mode == 2) v = bf16_round(__fadd_rn(v, __bfloat162float(p.other[at])));
-        p.y[at] = __float2bfloat16_rn(v);
+        p.y[at] = dense_value<DUAL>(a, b, p.mode == 2 ? __bfloat162float(p.other[at]) : 0.f, p.mode);
       };
       for (int j = 0; j < n16; ++j) {
         uint32_t g[16], v[16];
@@ -235,52 +242,6 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
           }
         }
       }
-      if (p.ksplit > 1) {
-        // the CTA that finishes the tile's last part adds all parts in part order and stores the result
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (tid == 0) {
-          __threadfence();
-          const int before = atomicAdd(p.parts_done + tile, 1);
-          __threadfence();
-          *s_last = before == p.ksplit - 1 ? 1 : 0;
-          if (before == p.ksplit - 1) p.parts_done[tile] = 0;      // left at zero for the next call
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*s_last) {
-          const float* parts = p.partial + static_cast<size_t>(tile) * p.ksplit * (MATS * kDtTokens * 128);
-          // four columns at a time: all their parts' loads are issued before the first sum (one
-          // dependent load per addition made this loop a chain of cols * parts L2 latencies)
-          constexpr int kMaxParts = 8;
-          for (int col0 = 0; col0 < cols; col0 += 4) {
-            float va[4][kMaxParts], vb[4][kMaxParts];
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-#pragma unroll
-              for (int q = 0; q < kMaxParts; ++q) {
-                const bool live = col0 + c < cols && q < p.ksplit;
-                const float* src = parts + static_cast<size_t>(live ? q : 0) * (MATS * kDtTokens * 128);
-                const int col = live ? col0 + c : 0;
-                va[c][q] = __ldcg(src + col * 128 + m);
-                if constexpr (DUAL) vb[c][q] = __ldcg(src + (kDtTokens + col) * 128 + m);
-              }
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              if (col0 + c >= cols) break;
-              float a = 0.f, b = 0.f;
-#pragma unroll
-              for (int q = 0; q < kMaxParts; ++q) {
-                if (q < p.ksplit) {
-                  a = __fadd_rn(a, va[c][q]);
-                  if constexpr (DUAL) b = __fadd_rn(b, vb[c][q]);
-                }
-              }
-              finish(col0 + c, a, b);
-            }
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");      // s_last may be rewritten by the next item
-      }
     }
   }
 
@@ -295,6 +256,56 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+  }
+  if (p.ksplit > 1) {
+    // The parts meet. Every CTA of this grid is resident (at most one per SM, and nothing it waits for
+    // depends on a CTA that is not), so the grid can meet here: each CTA announces that its partial
+    // tiles are stored, waits (bounded) for all the others, and then adds up its share of the outputs,
+    // every element's parts in part order. (One CTA per tile adding 64 columns x 8 parts on its own took
+    // longer than streaming the weights.)
+    if (threadIdx.x == 0) {
+      __threadfence();
+      atomicAdd(p.parts_done, 1);
+      if (!wait_counter(p.parts_done, static_cast<int>(gridDim.x))) report(p.status, MOE_ERR_DEVICE_TIMEOUT, 46);
+      __threadfence();
+    }
+    __syncthreads();
+    constexpr int kTileFloats = MATS * kDtTokens * 128;
+    const long long elements = static_cast<long long>(p.tiles_m) * p.token_tiles * kDtTokens * 128;
+    for (long long e = static_cast<long long>(blockIdx.x) * kDtThreads + threadIdx.x; e < elements;
+         e += static_cast<long long>(gridDim.x) * kDtThreads) {
+      const int m = static_cast<int>(e & 127), col = static_cast<int>((e >> 7) & (kDtTokens - 1));
+      const int tile = static_cast<int>(e >> 13);          // 128 channels x 64 columns per tile
+      const int tt = tile % p.token_tiles, mt = tile / p.token_tiles;
+      const int token = tt * kDtTokens + col;
+      if (token >= p.tokens) continue;
+      const float* parts = p.partial + static_cast<size_t>(tile) * p.ksplit * kTileFloats + col * 128 + m;
+      const size_t at = static_cast<size_t>(token) * p.n + mt * 128 + m;
+      constexpr int kMaxParts = 8;
+      float va[kMaxParts], vb[kMaxParts];
+#pragma unroll
+      for (int q = 0; q < kMaxParts; ++q) {      // all loads first, then the sums in part order
+        const float* src = parts + static_cast<size_t>(q < p.ksplit ? q : 0) * kTileFloats;
+        va[q] = __ldcg(src);
+        vb[q] = DUAL ? __ldcg(src + kDtTokens * 128) : 0.f;
+      }
+      const float other = p.mode == 2 ? __bfloat162float(p.other[at]) : 0.f;
+      float a = 0.f, b = 0.f;
+#pragma unroll
+      for (int q = 0; q < kMaxParts; ++q) {
+        if (q < p.ksplit) {
+          a = __fadd_rn(a, va[q]);
+          if constexpr (DUAL) b = __fadd_rn(b, vb[q]);
+        }
+      }
+      p.y[at] = dense_value<DUAL>(a, b, other, p.mode);
+    }
+    // the last CTA to leave puts the two counters back to zero for the next launch
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(p.parts_done + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+      p.parts_done[0] = 0;
+      p.parts_done[1] = 0;
+    }
   }
 }
 
