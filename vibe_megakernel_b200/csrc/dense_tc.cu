@@ -1,5 +1,4 @@
-// Dense bf16 projections of the Kimi-K3 latent block on tcgen05 tensor cores, for more tokens than the
-// CUDA-core rows kernel of latent.cu takes in a pass:
+// Dense bf16 projections of the Kimi-K3 latent block on tcgen05 tensor cores:
 //
 //   y[t][n] = f( sum_k W[n][k] x[t][k] )        W bf16 [N, K] row-major, x bf16 [T, K], fp32 accumulation
 //

@@ -63,133 +63,6 @@ __global__ void duplicate_ids_kernel(const int32_t* __restrict__ ids, int n, int
   if (i < 2 * n) ids2[i] = ids[i >> 1];
 }
 
-// ---- dense bf16 rows: y[t][n] = f( sum_k W[n][k] x[t][k] ) for a handful of tokens --------------------
-// W bf16 [N, K] row-major, x bf16 [T, K]; fp32 accumulation, bf16 results (`W @ token` of the
-// reference, megabench/tasks/kimi_layer.py:203,227-228). Decode batches: the weights stream once from
-// HBM, the token rows sit in L1. A warp owns kDenseRows output channels (lane-strided 16-byte weight
-// loads, lane partial sums added by a butterfly) for up to kDenseTokens tokens per pass.
-//   MODE 0: y = bf16(sum)
-//   MODE 1: y = situ(bf16(sum over W), bf16(sum over W2))     (gate and up rows of the shared experts)
-//   MODE 2: y = bf16(bf16(sum) + other[t][n])                 (routed + shared)
-constexpr int kDenseTokens = 8;
-constexpr int kDenseWarps = 8;
-
-template <int ROWS, int MODE, int TOK>
-__global__ void __launch_bounds__(kDenseWarps * 32) dense_rows_kernel(const __nv_bfloat16* __restrict__ w,
-                                                                      const __nv_bfloat16* __restrict__ w2,
-                                                                      const __nv_bfloat16* __restrict__ x, int tokens, int n, int k,
-                                                                      const __nv_bfloat16* __restrict__ other,
-                                                                      __nv_bfloat16* __restrict__ y) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = (blockIdx.x * kDenseWarps + warp) * ROWS;      // first output channel of this warp
-  dependent_wait();
-  dependents_may_launch();
-  if (n0 >= n) return;
-  constexpr int MATS = MODE == 1 ? 2 : 1;
-  for (int t0 = 0; t0 < tokens; t0 += TOK) {
-    float acc[MATS][ROWS][TOK];
-#pragma unroll
-    for (int a = 0; a < MATS; ++a)
-#pragma unroll
-      for (int r = 0; r < ROWS; ++r)
-#pragma unroll
-        for (int t = 0; t < TOK; ++t) acc[a][r][t] = 0.f;
-    // (few tokens leave registers free: several trips' weight loads are then in flight at once)
-#pragma unroll(TOK <= 2 ? 4 : 1)
-    for (int c = lane * 8; c < k; c += 32 * 8) {
-      uint4 wv[MATS][ROWS];
-#pragma unroll
-      for (int r = 0; r < ROWS; ++r) {
-        const int row = min(n0 + r, n - 1);
-        wv[0][r] = __ldg(reinterpret_cast<const uint4*>(w + static_cast<size_t>(row) * k + c));
-        if constexpr (MODE == 1) wv[1][r] = __ldg(reinterpret_cast<const uint4*>(w2 + static_cast<size_t>(row) * k + c));
-      }
-      if constexpr (TOK == 1) {
-        // one token: plain fused multiply-adds (each half of the packed form below is the same operation)
-        const uint4 xa = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(t0) * k + c);
-        const uint32_t* pa = reinterpret_cast<const uint32_t*>(&xa);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float a0 = __uint_as_float(pa[j] << 16), a1 = __uint_as_float(pa[j] & 0xffff0000u);
-#pragma unroll
-          for (int a = 0; a < MATS; ++a)
-#pragma unroll
-            for (int r = 0; r < ROWS; ++r) {
-              const uint32_t word = reinterpret_cast<const uint32_t*>(&wv[a][r])[j];
-              acc[a][r][0] = __fmaf_rn(__uint_as_float(word << 16), a0, acc[a][r][0]);
-              acc[a][r][0] = __fmaf_rn(__uint_as_float(word & 0xffff0000u), a1, acc[a][r][0]);
-            }
-        }
-      }
-#pragma unroll
-      for (int t = 0; t + 1 < TOK; t += 2) {
-        const int ta = min(t0 + t, tokens - 1), tb = min(t0 + t + 1, tokens - 1);
-        const uint4 xa = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(ta) * k + c);
-        const uint4 xb = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(tb) * k + c);
-        const uint32_t* pa = reinterpret_cast<const uint32_t*>(&xa);
-        const uint32_t* pb = reinterpret_cast<const uint32_t*>(&xb);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float a0 = __uint_as_float(pa[j] << 16), a1 = __uint_as_float(pa[j] & 0xffff0000u);
-          const float b0 = __uint_as_float(pb[j] << 16), b1 = __uint_as_float(pb[j] & 0xffff0000u);
-#pragma unroll
-          for (int a = 0; a < MATS; ++a)
-#pragma unroll
-            for (int r = 0; r < ROWS; ++r) {
-              const uint32_t word = reinterpret_cast<const uint32_t*>(&wv[a][r])[j];
-              const float w0 = __uint_as_float(word << 16), w1 = __uint_as_float(word & 0xffff0000u);
-              fma2(w0, w0, a0, b0, acc[a][r][t], acc[a][r][t + 1]);
-              fma2(w1, w1, a1, b1, acc[a][r][t], acc[a][r][t + 1]);
-            }
-        }
-      }
-    }
-#pragma unroll
-    for (int a = 0; a < MATS; ++a)
-#pragma unroll
-      for (int r = 0; r < ROWS; ++r)
-#pragma unroll
-        for (int t = 0; t < TOK; ++t)
-#pragma unroll
-          for (int off = 16; off > 0; off >>= 1) acc[a][r][t] = __fadd_rn(acc[a][r][t], __shfl_xor_sync(0xffffffffu, acc[a][r][t], off));
-    if (lane == 0) {
-#pragma unroll
-      for (int r = 0; r < ROWS; ++r) {
-        if (n0 + r >= n) break;
-#pragma unroll
-        for (int t = 0; t < TOK; ++t) {
-          if (t0 + t >= tokens) break;
-          const size_t at = static_cast<size_t>(t0 + t) * n + n0 + r;
-          float v = bf16_round(acc[0][r][t]);
-          if constexpr (MODE == 1) v = bf16_round(situ_f32(v, bf16_round(acc[1][r][t])));
-          if constexpr (MODE == 2) v = bf16_round(__fadd_rn(v, __bfloat162float(other[at])));
-          y[at] = __float2bfloat16_rn(v);
-        }
-      }
-    }
-  }
-}
-
-template <int MODE>
-static cudaError_t launch_dense(const __nv_bfloat16* w, const __nv_bfloat16* w2, const __nv_bfloat16* x, int tokens, int n, int k,
-                                const __nv_bfloat16* other, __nv_bfloat16* y, cudaStream_t stream, int* launches) {
-  if (k % 8 || ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w2)) & 15))
-    return cudaErrorInvalidValue;
-  constexpr int ROWS = MODE == 1 ? 2 : 4;
-  const int blocks = (n + kDenseWarps * ROWS - 1) / (kDenseWarps * ROWS);
-  // tokens per pass: no more than there are (a pass of eight for one token did eight tokens' arithmetic)
-  if (tokens <= 1)
-    launch_dependent(dense_rows_kernel<ROWS, MODE, 1>, dim3(blocks), dim3(kDenseWarps * 32), 0, stream, w, w2, x, tokens, n, k, other, y);
-  else if (tokens <= 2)
-    launch_dependent(dense_rows_kernel<ROWS, MODE, 2>, dim3(blocks), dim3(kDenseWarps * 32), 0, stream, w, w2, x, tokens, n, k, other, y);
-  else if (tokens <= 4)
-    launch_dependent(dense_rows_kernel<ROWS, MODE, 4>, dim3(blocks), dim3(kDenseWarps * 32), 0, stream, w, w2, x, tokens, n, k, other, y);
-  else
-    launch_dependent(dense_rows_kernel<ROWS, MODE, kDenseTokens>, dim3(blocks), dim3(kDenseWarps * 32), 0, stream, w, w2, x, tokens, n, k, other, y);
-  if (launches) *launches += 1;
-  return cudaGetLastError();
-}
-
 }  // namespace moe
 
 // ---------------------------------------------------------------------------------------------
@@ -224,8 +97,8 @@ int latent_layout(const moe_latent_config_t* c, int tokens, LatentLayout* L) {
   uint64_t off = 0;
   auto take = [&](uint64_t bytes) { const uint64_t at = off; off = up256(off + bytes); return at; };
   l.status = take(32);
-  // the tensor-core dense projections (above kDenseTokens tokens): per-tile counters of finished parts and
-  // the fp32 partial tiles of a split contraction, shared by the four projections (they run one after another)
+  // the dense projections: the two counters of their grid meeting and the fp32 partial tiles of a split
+  // contraction, shared by the four projections (they run one after another)
   const moe::DenseTcPlan plans[4] = {moe::dense_tc_plan(tokens, c->latent, c->hidden),
                                      moe::dense_tc_plan(tokens, c->n_shared * c->inter, c->hidden),
                                      moe::dense_tc_plan(tokens, c->hidden, c->n_shared * c->inter),
@@ -322,17 +195,10 @@ int moe_latent_forward(const moe_latent_config_t* cfg, const moe_latent_weights_
   int driver_error = 0;
   float* dense_partial = reinterpret_cast<float*>(ws + L.dense_partial);
   int32_t* dense_parts = reinterpret_cast<int32_t*>(ws + L.dense_parts);
-  const int dense_tc_above = 0;
-  // a dense projection: CUDA cores up to dense_tc_above tokens, tensor cores above
+  // a dense bf16 projection (dense_tc.cu): every width of this block is a multiple of 128
   auto dense = [&](int mode, const void* wm, const void* wm2, const bf16* in, int n, int k, const bf16* other, bf16* out) {
-    if (tokens > dense_tc_above && n % 128 == 0 && k % 64 == 0)
-      return moe::launch_dense_tc(mode, static_cast<const bf16*>(wm), static_cast<const bf16*>(wm2), in, tokens, n, k, other, out,
-                                  dense_partial, dense_parts, status, stream, &launches, &driver_error);
-    if (mode == 0) return moe::launch_dense<0>(static_cast<const bf16*>(wm), nullptr, in, tokens, n, k, nullptr, out, stream, &launches);
-    if (mode == 1)
-      return moe::launch_dense<1>(static_cast<const bf16*>(wm), static_cast<const bf16*>(wm2), in, tokens, n, k, nullptr, out, stream,
-                                  &launches);
-    return moe::launch_dense<2>(static_cast<const bf16*>(wm), nullptr, in, tokens, n, k, other, out, stream, &launches);
+    return moe::launch_dense_tc(mode, static_cast<const bf16*>(wm), static_cast<const bf16*>(wm2), in, tokens, n, k, other, out,
+                                dense_partial, dense_parts, status, stream, &launches, &driver_error);
   };
 
   // 1. router: sigmoid scores plus selection bias, no groups, weights normalised with scaling 1
