@@ -658,23 +658,41 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
           for (int n = 0; n < C::kCpt; ++n)
             if (col0 + n < rend) __stcg(parts + ch.pad * tile_floats + (col0 + n) * 128 + m, acc_a[n]);
-          __threadfence();
           epilogue_sync<C::kEpiThreads>();
           if (epi == 0 && lane == 0) {
-            __threadfence();
+            __threadfence();      // after the barrier: this one fence and release cover every thread's stores
             const int before = atomicAdd(p.parts_done + u, 1);
             __threadfence();
             *s_last_part = before == ksplit - 1 ? 1 : 0;
           }
           epilogue_sync<C::kEpiThreads>();
           if (*s_last_part) {
+            // eight columns at a time: the loads of all their parts are issued before the first sum (one
+            // dependent load per addition made this a chain of columns x parts L2 latencies, 45 us for a
+            // 16-row chunk of the Mixtral shape)
             float sums[C::kCpt];
+            constexpr int kBatch = 8, kBatchParts = 4;
 #pragma unroll
-            for (int n = 0; n < C::kCpt; ++n) {
-              sums[n] = 0.f;
-              if (col0 + n < rend) {
-                for (int part = 0; part < ksplit; ++part)
-                  sums[n] = __fadd_rn(sums[n], __ldcg(parts + part * tile_floats + (col0 + n) * 128 + m));
+            for (int n0 = 0; n0 < C::kCpt; n0 += kBatch) {
+              float v[kBatch][kBatchParts];
+#pragma unroll
+              for (int c = 0; c < kBatch; ++c)
+#pragma unroll
+                for (int q = 0; q < kBatchParts; ++q) {
+                  const bool live = col0 + n0 + c < rend && q < ksplit;
+                  v[c][q] = __ldcg(parts + (live ? q : 0) * tile_floats + (live ? col0 + n0 + c : 0) * 128 + m);
+                }
+#pragma unroll
+              for (int c = 0; c < kBatch; ++c) {
+                float sum = 0.f;
+                if (col0 + n0 + c < rend) {
+#pragma unroll
+                  for (int q = 0; q < kBatchParts; ++q)
+                    if (q < ksplit) sum = __fadd_rn(sum, v[c][q]);
+                  for (int part = kBatchParts; part < ksplit; ++part)
+                    sum = __fadd_rn(sum, __ldcg(parts + part * tile_floats + (col0 + n0 + c) * 128 + m));
+                }
+                sums[n0 + c] = sum;
               }
             }
             epilogue_store_tile<C::kCpt, C::kEpiThreads>(sums, static_cast<int>(threadIdx.x) - 96, m, col0, rend, ch.rows, mt,
