@@ -25,13 +25,25 @@ __global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __res
   float acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-  for (int s = 0; s < topk; ++s) {
-    const size_t row = static_cast<size_t>(t) * topk + s;
-    const float w = weights ? weights[row] : 1.f;   // null: the rows carry their weight already
-    const uint4 raw = *reinterpret_cast<const uint4*>(slots + row * hidden + c);
-    const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&raw);
+  // eight slots at a time: their loads are issued before the first addition (a load per addition made
+  // the sum a chain of topk memory latencies); the additions keep the slot order
+  for (int s0 = 0; s0 < topk; s0 += 8) {
+    uint4 raw[8];
+    float w[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(__bfloat162float(v[i]), w));
+    for (int j = 0; j < 8; ++j) {
+      const size_t row = static_cast<size_t>(t) * topk + min(s0 + j, topk - 1);
+      w[j] = weights ? weights[row] : 1.f;   // null: the rows carry their weight already
+      raw[j] = *reinterpret_cast<const uint4*>(slots + row * hidden + c);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (s0 + j < topk) {
+        const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&raw[j]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(__bfloat162float(v[i]), w[j]));
+      }
+    }
   }
   if (shared) {
     const size_t row = static_cast<size_t>(tokens) * topk + t;

@@ -755,13 +755,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         float acc[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-        for (int slot = 0; slot < p.fold.topk; ++slot) {
-          const size_t row = static_cast<size_t>(t) * p.fold.topk + slot;
-          const float w = p.fold.weights ? p.fold.weights[row] : 1.f;
-          const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(p.out + row * p.m + c));
-          const __nv_bfloat16* x8 = reinterpret_cast<const __nv_bfloat16*>(&raw);
+        // eight slots' loads are issued before the first addition; the additions keep the slot order
+        for (int s0 = 0; s0 < p.fold.topk; s0 += 8) {
+          uint4 raw[8];
+          float w[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(__bfloat162float(x8[i]), w));
+          for (int j = 0; j < 8; ++j) {
+            const size_t row = static_cast<size_t>(t) * p.fold.topk + min(s0 + j, p.fold.topk - 1);
+            w[j] = p.fold.weights ? p.fold.weights[row] : 1.f;
+            raw[j] = __ldcg(reinterpret_cast<const uint4*>(p.out + row * p.m + c));
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (s0 + j < p.fold.topk) {
+              const __nv_bfloat16* x8 = reinterpret_cast<const __nv_bfloat16*>(&raw[j]);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(__bfloat162float(x8[i]), w[j]));
+            }
+          }
         }
         if (p.fold.shared) {
           const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(p.out + (static_cast<size_t>(routed) + t) * p.m + c));
