@@ -182,10 +182,11 @@ __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(c
   for (int j = 0; j < kTiledExpertsPerWarp; ++j)
 #pragma unroll
     for (int t = 0; t < TOK; ++t) acc[j][t] = 0.f;
-  // Two pieces per trip: all router loads of a trip (8 x 16 bytes per lane) are issued before the
+  // Several pieces per trip: all router loads of a trip (8 x 16 bytes per lane) are issued before the
   // first use. The token values are converted once per piece and shared by the warp's four
   // experts; two tokens go through every packed FMA (each half is the scalar chain of fma4).
-  constexpr int kAhead = 2;
+  // (with one or two experts per warp more pieces per trip keep as many bytes in flight as four experts do)
+  constexpr int kAhead = kTiledExpertsPerWarp >= 4 ? 2 : 8 / kTiledExpertsPerWarp;
   for (int q0 = lane; q0 < quads; q0 += 32 * kAhead) {
     float4 r[kAhead][kTiledExpertsPerWarp];
 #pragma unroll
