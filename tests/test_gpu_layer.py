@@ -316,3 +316,36 @@ def test_rows_on_the_mma_m_side_give_the_bits_of_the_decode_kernel(api, name, to
         part = small.forward(few, check_status=True)
         assert torch.equal(part["expert_ids"], full["expert_ids"][lo:lo + 40])
         assert torch.equal(part["y"], full["y"][lo:lo + 40]), lo
+
+
+def test_quantising_from_the_token_side_leaves_the_bytes_of_the_gathering_kernel(api):
+    # From 8,192 (token, group of 128 channels) pairs on, a layer call quantises each token once and
+    # stores the bytes and scales to all of its grouped rows (found through the inverse of the
+    # permutation), instead of gathering and quantising every grouped row. The grouped rows left in the
+    # workspace must be, byte for byte, what the gathering kernel makes of the same permutation.
+    geo = H.small_geometries()["kimi_small"]
+    tokens = 1100                                   # x 8 groups of 128 channels
+    values = synthetic.make_inputs(geo, tokens, 0, "cpu")    # (not audited: nothing here is compared with the oracle)
+    dev = H.to_device(values, "cuda")
+    layer = api.MoeLayer(api.LayerConfig.from_geometry(geo), max_tokens=tokens)
+    out = layer.forward(dev, check_status=True)
+    ws, lay = layer.workspace(tokens)
+    rows, groups = int(lay.rows), geo.hidden // 128
+    assert rows == tokens * (geo.topk + 1)
+    row_token = ws[int(lay.row_token):int(lay.row_token) + 4 * rows].view(torch.int32).clone()
+    assert torch.equal(torch.bincount(row_token[:tokens * geo.topk].long(), minlength=tokens),
+                       torch.full((tokens,), geo.topk, device="cuda"))
+    assert torch.equal(row_token[tokens * geo.topk:], torch.arange(tokens, dtype=torch.int32, device="cuda"))
+    xq = ws[int(lay.xq):int(lay.xq) + rows * geo.hidden].view(rows, geo.hidden)
+    xs = ws[int(lay.xs):int(lay.xs) + 4 * rows * groups].view(torch.float32).view(rows, groups)
+    q, s = api.quantize_rows(dev["x"], gather=row_token)
+    assert torch.equal(q.view(torch.uint8), xq)
+    assert torch.equal(s, xs)
+    # and the call's result is that of the same tokens sixty-four at a time (the small-batch kernels)
+    small = api.MoeLayer(api.LayerConfig.from_geometry(geo), max_tokens=64)
+    for lo in range(0, tokens, 64):
+        few = dict(dev)
+        few["x"] = dev["x"][lo:lo + 64].contiguous()
+        part = small.forward(few, check_status=True)
+        assert torch.equal(part["expert_ids"], out["expert_ids"][lo:lo + 64])
+        assert torch.equal(part["y"], out["y"][lo:lo + 64]), lo

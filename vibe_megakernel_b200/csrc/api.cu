@@ -79,6 +79,7 @@ int layout_of(const moe_config_t* c, int tokens, moe_workspace_layout_t* L) {
   l.as = take(4ull * rows * (I / 128));
   l.slots = take(2ull * rows * H);
   take(2ull * tokens * H);               // normalised token rows of moe_block_forward (see norm_offset)
+  take(4ull * routed);                   // grouped row of every routed row (see slot_pos_offset)
   l.total_bytes = off;
   l.rows = rows;
   l.max_chunks = max_chunks;
@@ -90,6 +91,11 @@ int layout_of(const moe_config_t* c, int tokens, moe_workspace_layout_t* L) {
 // bf16 [T, H] behind the slot rows: the RMSNorm output when the call covers the whole block
 inline uint64_t norm_offset(const moe_workspace_layout_t& L, int hidden) {
   return align_up(L.slots + 2ull * L.rows * hidden, 256);
+}
+
+// int32 [T * topk] behind those: where the permutation put each routed row (large batches quantise from the token side)
+inline uint64_t slot_pos_offset(const moe_workspace_layout_t& L, int hidden, int tokens) {
+  return align_up(norm_offset(L, hidden) + 2ull * tokens * hidden, 256);
 }
 
 int sm_count() {
@@ -263,8 +269,13 @@ static int layer_forward_impl(const moe_config_t* cfg, const moe_weights_t* w, c
     warm.ptr[2] = w->shared_down; warm.bytes[2] = bytes;
   }
 
+  // Large batches quantise from the token side (every routed row is kept here: all experts are local).
+  const bool fused_route = !g_profile && moe::fused_route_fits(*cfg, tokens);
+  const bool scatter = !fused_route && cfg->topk <= 16 && moe::quantize_scatter_fits(tokens, cfg->hidden, x_bf16);
+  if (scatter) g.slot_pos = reinterpret_cast<int32_t*>(ws + slot_pos_offset(L, cfg->hidden, tokens));
+
   mark(0, stream);
-  if (!g_profile && moe::fused_route_fits(*cfg, tokens)) {
+  if (fused_route) {
     // small batch: logits, then selection + permutation + quantiser in one launch (steps 1-3 below)
     e = moe::launch_router_fused(*cfg, static_cast<const __nv_bfloat16*>(x_bf16), w->router, w->router_bias, tokens,
                                  logits, ids32, tw, expert_ids, topk_weights, g, xq, xs, stream, &launches, &warm);
@@ -282,7 +293,11 @@ static int layer_forward_impl(const moe_config_t* cfg, const moe_weights_t* w, c
 
     // 3. activation quantiser, gathering each grouped row from its token
     mark(2, stream);
-    e = moe::launch_quantize(x_bf16, 0, L.rows, cfg->hidden, row_token, xq, xs, stream, &launches);
+    if (scatter)
+      e = moe::launch_quantize_scatter(static_cast<const __nv_bfloat16*>(x_bf16), tokens, cfg->hidden, cfg->topk,
+                                       g.slot_pos, cfg->n_shared ? routed : -1, xq, xs, stream, &launches);
+    else
+      e = moe::launch_quantize(x_bf16, 0, L.rows, cfg->hidden, row_token, xq, xs, stream, &launches);
     if (e != cudaSuccess) return from_cuda(e);
   }
 

@@ -83,6 +83,7 @@ __global__ void __launch_bounds__(kGroupWarps * 32) group_rows_kernel(GroupArgs 
         if (a.order) a.order[pos] = r;
         if (a.row_token) a.row_token[pos] = r / a.topk;
         if (a.row_dest) a.row_dest[pos] = r;
+        if (a.slot_pos) a.slot_pos[r] = pos;
       }
       placed += __popc(m);
     }

@@ -67,6 +67,7 @@ struct GroupArgs {
   int32_t* row_token;     // optional
   int32_t* row_dest;      // optional
   int64_t* order;         // optional, [n]
+  int32_t* slot_pos;      // optional, [n]: the grouped row a kept routed row went to (rows not kept are not written)
   int32_t* status;        // optional
   int zero_status;        // the kernel clears the 8 status words itself (it is the call's first that may report)
   const int32_t* seg_counts;  // optional: rows come in segments of seg_cap, segment s holds seg_counts[s] rows
@@ -89,6 +90,12 @@ cudaError_t launch_quantize(const void* x, int dtype, int rows, int width, const
                             float* scales, cudaStream_t stream, int* launches);
 
 // e4m3 payload with one power-of-two scale (biased exponent, uint8) per `block` = 32 or 128 channels
+// The same rows from the token side, for large batches in which every routed row is kept: a token's
+// groups are quantised once and stored to each of its `topk` grouped rows slot_pos[token * topk + k]
+// and, with `shared_base` >= 0, to row shared_base + token (bf16 rows of whole groups only).
+bool quantize_scatter_fits(int tokens, int width, const void* x);
+cudaError_t launch_quantize_scatter(const __nv_bfloat16* x, int tokens, int width, int topk, const int32_t* slot_pos,
+                                    int shared_base, uint8_t* q, float* scales, cudaStream_t stream, int* launches);
 cudaError_t launch_quantize_ue8m0(const void* x, int dtype, int rows, int width, int block, uint8_t* q, uint8_t* scales,
                                   cudaStream_t stream);
 

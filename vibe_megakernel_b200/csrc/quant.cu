@@ -86,6 +86,89 @@ __global__ void __launch_bounds__(256) quantize_rows_stream_kernel(const __nv_bf
   }
 }
 
+// The token side of the same work, when every routed row is kept: each (token, run of four groups)
+// is loaded and quantised once and its bytes and scales are stored to the token's topk grouped rows
+// (and its shared-expert row). The gathering kernel above re-reads and re-quantises a token once per
+// grouped row: nine times the loads and the arithmetic for the same 66 MB of stores at 1,024 tokens of
+// 7,168 channels, top-8 and a shared expert.
+constexpr int kScatterMaxTopk = 16;
+
+__global__ void __launch_bounds__(256) quantize_scatter_kernel(const __nv_bfloat16* __restrict__ x, int tokens, int width,
+                                                               int topk, const int32_t* __restrict__ slot_pos,
+                                                               int shared_base, uint8_t* __restrict__ q,
+                                                               float* __restrict__ scales) {
+  dependent_wait();
+  dependents_may_launch();
+  const int groups = width / kGroup;
+  const int runs = (groups + kStreamGroups - 1) / kStreamGroups;
+  const long long items = static_cast<long long>(tokens) * runs;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long stride = static_cast<long long>(gridDim.x) * 8;
+  const int dests = topk + (shared_base >= 0 ? 1 : 0);
+  auto fetch = [&](long long item, uint2 (&raw)[kStreamGroups], int& dest) {
+    const int token = static_cast<int>(item / runs), g0 = static_cast<int>(item % runs) * kStreamGroups;
+    // lane k < topk holds the token's k-th grouped row, lane topk the shared expert's
+    dest = lane < topk ? __ldg(slot_pos + static_cast<size_t>(token) * topk + lane) : shared_base + token;
+    const uint2* in = reinterpret_cast<const uint2*>(x + static_cast<size_t>(token) * width);
+#pragma unroll
+    for (int u = 0; u < kStreamGroups; ++u) raw[u] = __ldg(in + min(g0 + u, groups - 1) * 32 + lane);
+  };
+  long long item = static_cast<long long>(blockIdx.x) * 8 + warp;
+  uint2 cur[kStreamGroups], nxt[kStreamGroups];
+  int dest = 0, dest_next = 0;
+  if (item < items) fetch(item, cur, dest);
+  for (; item < items; item += stride) {
+    if (item + stride < items) fetch(item + stride, nxt, dest_next);
+    const int g0 = static_cast<int>(item % runs) * kStreamGroups;
+    uint32_t bytes[kStreamGroups];
+    float scale[kStreamGroups];
+#pragma unroll
+    for (int u = 0; u < kStreamGroups; ++u) {
+      const float v[4] = {__uint_as_float(cur[u].x << 16), __uint_as_float(cur[u].x & 0xffff0000u),
+                          __uint_as_float(cur[u].y << 16), __uint_as_float(cur[u].y & 0xffff0000u)};
+      scale[u] = quantize_values(v, bytes[u]);
+    }
+    for (int k = 0; k < dests; ++k) {
+      const size_t row = static_cast<size_t>(__shfl_sync(0xffffffffu, dest, k));
+      uint32_t* out = reinterpret_cast<uint32_t*>(q + row * width);
+#pragma unroll
+      for (int u = 0; u < kStreamGroups; ++u)
+        if (g0 + u < groups) out[(g0 + u) * 32 + lane] = bytes[u];
+      if (lane < kStreamGroups && g0 + lane < groups) {
+        float mine = scale[0];
+#pragma unroll
+        for (int u = 1; u < kStreamGroups; ++u) mine = lane == u ? scale[u] : mine;
+        scales[row * groups + g0 + lane] = mine;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kStreamGroups; ++u) cur[u] = nxt[u];
+    dest = dest_next;
+  }
+}
+
+bool quantize_scatter_fits(int tokens, int width, const void* x) {
+  // (below this size the gathering kernels' many short blocks are as fast, and small batches take the fused routing kernel)
+  return width % kGroup == 0 && (reinterpret_cast<uintptr_t>(x) & 7) == 0 &&
+         static_cast<long long>(tokens) * (width / kGroup) >= 8192;
+}
+
+cudaError_t launch_quantize_scatter(const __nv_bfloat16* x, int tokens, int width, int topk, const int32_t* slot_pos,
+                                    int shared_base, uint8_t* q, float* scales, cudaStream_t stream, int* launches) {
+  if (tokens <= 0) return cudaSuccess;
+  if (topk < 1 || topk > kScatterMaxTopk || !quantize_scatter_fits(tokens, width, x)) return cudaErrorInvalidValue;
+  const int groups = width / kGroup;
+  const long long items = static_cast<long long>(tokens) * ((groups + kStreamGroups - 1) / kStreamGroups);
+  int device = 0, sms = 148;
+  cudaGetDevice(&device);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  const long long blocks = std::min((items + 7) / 8, static_cast<long long>(sms) * 8);
+  launch_dependent(quantize_scatter_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, x, tokens, width,
+                   topk, slot_pos, shared_base, q, scales);
+  if (launches) *launches += 1;
+  return cudaGetLastError();
+}
+
 template <typename T>
 static void launch_quantize_typed(const T* x, int rows, int width, const int32_t* gather, uint8_t* q, float* scales,
                                   cudaStream_t stream) {

@@ -43,6 +43,19 @@ __device__ __forceinline__ float quantize_loaded(const float (&v)[4], uint8_t* o
   return scale;
 }
 
+// The same arithmetic for a whole group whose bytes the caller stores itself (to several rows):
+// the lane's four e4m3 bytes in `packed`, the scale returned.
+__device__ __forceinline__ float quantize_values(const float (&v)[4], uint32_t& packed) {
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  const float scale = group_scale(amax);
+  packed = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) packed |= static_cast<uint32_t>(to_e4m3(v[j], scale)) << (8 * j);
+  return scale;
+}
+
 template <typename T>
 __device__ __forceinline__ float quantize_group(const T* in, uint8_t* out, int g, int width, int lane) {
   float v[4];

@@ -136,102 +136,168 @@ __device__ __forceinline__ void unpack4(const uint2& raw, float (&v)[4]) {
   v[3] = __uint_as_float(raw.y & 0xffff0000u);
 }
 
-// Larger batches: a block keeps TOK token rows in shared memory and streams the router rows of
-// 8 * kTiledExpertsPerWarp experts against them, so x is read from L2 once per block. Four experts
-// per warp halve the instructions per FMA (the token values are unpacked once for all of them);
-// two give twice the blocks, which wins while the grid would not fill the SMs.
-constexpr int kTiledWarps = 8;
+// The totals of N per-lane sums (N a power of two, at most 32), by the same tree as warp_total
+// (partners 16, 8, 4, 2, 1 lanes apart, the symmetric two-float merge at every node, so the bits
+// are those of warp_total), but as a reduce-scatter: at every level a lane keeps half of its values
+// and hands the other half to its partner: about 2 N shuffles instead of 10 N. Lane l returns the
+// total of value l * N / 32.
+template <int N>
+__device__ __forceinline__ float warp_totals(const float (&v)[N], int lane) {
+  static_assert(N >= 1 && N <= 32 && (N & (N - 1)) == 0, "a power of two up to the warp size");
+  float hi[N], lo[N];
+#pragma unroll
+  for (int i = 0; i < N; ++i) hi[i] = v[i], lo[i] = 0.f;
+  int off = 16;
+#pragma unroll
+  for (int count = N; count > 1; count >>= 1) {
+    const int half = count >> 1;
+    const bool upper = (lane & off) != 0;
+#pragma unroll
+    for (int i = 0; i < half; ++i) {
+      const Sum2 mine{upper ? hi[i + half] : hi[i], upper ? lo[i + half] : lo[i]};
+      const float send_hi = upper ? hi[i] : hi[i + half], send_lo = upper ? lo[i] : lo[i + half];
+      Sum2 other;
+      other.hi = __shfl_xor_sync(0xffffffffu, send_hi, off);
+      other.lo = count == N ? 0.f : __shfl_xor_sync(0xffffffffu, send_lo, off);   // the lane sums have no low part yet
+      const Sum2 m = sum2_merge(mine, other);
+      hi[i] = m.hi, lo[i] = m.lo;
+    }
+    off >>= 1;
+  }
+  Sum2 s{hi[0], lo[0]};
+#pragma unroll
+  for (int o = 16 / N; o > 0; o >>= 1) {      // the levels left when N < 32: every partner holds the same value index
+    Sum2 other;
+    other.hi = __shfl_xor_sync(0xffffffffu, s.hi, o);
+    other.lo = __shfl_xor_sync(0xffffffffu, s.lo, o);
+    s = sum2_merge(s, other);
+  }
+  return __fadd_rn(s.hi, s.lo);
+}
 
-template <int TOK, int kTiledExpertsPerWarp>
+// Larger batches: a block takes TOK token rows against the router rows of 8 * EPW experts. The token
+// rows pass through shared memory in pieces of 1,024 channels, two pieces in flight (a piece is
+// requested as soon as all warps have left its buffer), so a block holds 32 KB instead of whole rows
+// and several blocks share an SM; the router rows stream through registers, the loads of a trip
+// issued one trip ahead of their use (with them issued at the top of the trip that uses them, the
+// two warps a scheduler had spent most of their time waiting for the L2). Four experts per warp halve
+// the instructions per FMA (the token values are unpacked once for all of them); fewer give more
+// blocks, which wins while the grid would not fill the SMs. The order of a lane's additions is that
+// of the rows kernel whatever the piece size.
+constexpr int kTiledWarps = 8;
+constexpr int kPieceQuads = 256;                      // four channels per quad
+
+template <int TOK, int EPW>
 __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(const __nv_bfloat16* __restrict__ x,
                                                                                const float* __restrict__ router,
                                                                                int tokens, int experts, int hidden,
                                                                                float* __restrict__ logits,
                                                                                const L2Warm warm, int logit_blocks) {
-  extern __shared__ __align__(128) uint2 s_x[];        // [8][hidden / 4], four bf16 per entry
+  extern __shared__ __align__(128) uint2 s_x[];        // [2][TOK][kPieceQuads], four bf16 per entry
   if (static_cast<int>(blockIdx.x) >= logit_blocks) {
     if (blockIdx.y == 0) warm_l2(warm, blockIdx.x - logit_blocks, gridDim.x - logit_blocks);
     return;
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int quads = hidden / 4;
+  const int pieces = (quads + kPieceQuads - 1) / kPieceQuads;
   const int t0 = blockIdx.y * TOK;
   const int tcount = min(TOK, tokens - t0);
-  // Token rows arrive by bulk async copies (one per row, 16-byte aligned by the launcher's check);
-  // rows past the batch are zero-filled by the threads.
-  __shared__ uint64_t bar;
+  // Bulk async copies, one per row and piece (16-byte aligned: the launcher checks the base, and
+  // hidden is a multiple of 8); rows past the batch are zero-filled by the threads, once.
+  __shared__ uint64_t bar[2];
+  auto request = [&](int piece) {
+    const int first = piece * kPieceQuads;
+    const uint32_t bytes = static_cast<uint32_t>(min(kPieceQuads, quads - first)) * 8u;
+    uint64_t* b = &bar[piece & 1];
+    mbar_expect_tx(b, bytes * tcount);
+    for (int t = 0; t < tcount; ++t)
+      bulk_copy_g2s(s_x + static_cast<size_t>((piece & 1) * TOK + t) * kPieceQuads,
+                    x + static_cast<size_t>(t0 + t) * hidden + 4 * first, bytes, b);
+  };
   if (threadIdx.x == 0) {
-    mbar_init(&bar, 1);
+    mbar_init(&bar[0], 1);
+    mbar_init(&bar[1], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  dependent_wait();
-  dependents_may_launch();
-  if (threadIdx.x == 0) {
-    const uint32_t row_bytes = static_cast<uint32_t>(hidden) * 2u;
-    mbar_expect_tx(&bar, row_bytes * tcount);
-    for (int t = 0; t < tcount; ++t)
-      bulk_copy_g2s(s_x + static_cast<size_t>(t) * quads, x + static_cast<size_t>(t0 + t) * hidden, row_bytes, &bar);
-  }
-  for (int i = tcount * quads + threadIdx.x; i < TOK * quads; i += blockDim.x) s_x[i] = make_uint2(0u, 0u);
-  mbar_wait(&bar, 0);           // bounded; a copy that never lands leaves wrong logits, not a hang
-  __syncthreads();
-  const int e0 = (blockIdx.x * kTiledWarps + warp) * kTiledExpertsPerWarp;
-  float acc[kTiledExpertsPerWarp][TOK];
-#pragma unroll
-  for (int j = 0; j < kTiledExpertsPerWarp; ++j)
-#pragma unroll
-    for (int t = 0; t < TOK; ++t) acc[j][t] = 0.f;
-  // Several pieces per trip: all router loads of a trip (8 x 16 bytes per lane) are issued before the
-  // first use. The token values are converted once per piece and shared by the warp's four
-  // experts; two tokens go through every packed FMA (each half is the scalar chain of fma4).
-  // (with one or two experts per warp more pieces per trip keep as many bytes in flight as four experts do)
-  constexpr int kAhead = kTiledExpertsPerWarp >= 4 ? 2 : 8 / kTiledExpertsPerWarp;
-  for (int q0 = lane; q0 < quads; q0 += 32 * kAhead) {
-    float4 r[kAhead][kTiledExpertsPerWarp];
+  const int e0 = (blockIdx.x * kTiledWarps + warp) * EPW;
+  // Several quads per trip: all router loads of a trip (8 x 16 bytes per lane) are in flight together.
+  // The token values are converted once per quad and shared by the warp's experts; two tokens
+  // go through every packed FMA (each half is the scalar chain of fma4).
+  constexpr int kAhead = EPW >= 4 ? 2 : 8 / EPW;
+  static_assert(kPieceQuads % (32 * kAhead) == 0, "a trip never straddles two pieces");
+  auto fetch = [&](int q0, float4 (&r)[kAhead][EPW]) {
 #pragma unroll
     for (int u = 0; u < kAhead; ++u)
 #pragma unroll
-      for (int j = 0; j < kTiledExpertsPerWarp; ++j) {
+      for (int j = 0; j < EPW; ++j) {
         const int q = min(q0 + 32 * u, quads - 1);       // clamped, unconditional (see the rows kernel)
         const int e = min(e0 + j, experts - 1);
         r[u][j] = __ldg(reinterpret_cast<const float4*>(router + static_cast<size_t>(e) * hidden + 4 * q));
       }
+  };
+  float4 r[kAhead][EPW];
+  fetch(lane, r);                                        // weights: nothing to wait for
+  dependent_wait();
+  dependents_may_launch();
+  if (threadIdx.x == 0) {
+    request(0);
+    if (pieces > 1) request(1);
+  }
+  for (int i = threadIdx.x; i < 2 * (TOK - tcount) * kPieceQuads; i += blockDim.x) {
+    const int row = tcount + (i / kPieceQuads) % (TOK - tcount), buf = i / ((TOK - tcount) * kPieceQuads);
+    s_x[static_cast<size_t>(buf * TOK + row) * kPieceQuads + i % kPieceQuads] = make_uint2(0u, 0u);
+  }
+  __syncthreads();
+  float acc[EPW * TOK];
 #pragma unroll
-    for (int u = 0; u < kAhead; ++u) {
-      const int q = q0 + 32 * u;
-      if (q < quads) {
+  for (int i = 0; i < EPW * TOK; ++i) acc[i] = 0.f;
+  for (int piece = 0; piece < pieces; ++piece) {
+    mbar_wait(&bar[piece & 1], (piece >> 1) & 1);   // bounded; a copy that never lands leaves wrong logits, not a hang
+    const uint2* xs = s_x + static_cast<size_t>(piece & 1) * TOK * kPieceQuads;
+    const int first = piece * kPieceQuads, end = min(first + kPieceQuads, quads);
+    for (int q0 = first + lane; q0 < end; q0 += 32 * kAhead) {
+      float4 rn[kAhead][EPW];
+      fetch(q0 + 32 * kAhead, rn);
 #pragma unroll
-        for (int t = 0; t < TOK; t += 2) {
-          float xa[4], xb[4];
-          unpack4(s_x[t * quads + q], xa);
-          unpack4(s_x[(t + 1) * quads + q], xb);
+      for (int u = 0; u < kAhead; ++u) {
+        const int q = q0 + 32 * u;
+        if (q < end) {
 #pragma unroll
-          for (int j = 0; j < kTiledExpertsPerWarp; ++j) {
-            const float4 w = r[u][j];
-            fma2(w.x, w.x, xa[0], xb[0], acc[j][t], acc[j][t + 1]);
-            fma2(w.y, w.y, xa[1], xb[1], acc[j][t], acc[j][t + 1]);
-            fma2(w.z, w.z, xa[2], xb[2], acc[j][t], acc[j][t + 1]);
-            fma2(w.w, w.w, xa[3], xb[3], acc[j][t], acc[j][t + 1]);
+          for (int t = 0; t < TOK; t += 2) {
+            float xa[4], xb[4];
+            unpack4(xs[t * kPieceQuads + q - first], xa);
+            unpack4(xs[(t + 1) * kPieceQuads + q - first], xb);
+#pragma unroll
+            for (int j = 0; j < EPW; ++j) {
+              const float4 w = r[u][j];
+              fma2(w.x, w.x, xa[0], xb[0], acc[j * TOK + t], acc[j * TOK + t + 1]);
+              fma2(w.y, w.y, xa[1], xb[1], acc[j * TOK + t], acc[j * TOK + t + 1]);
+              fma2(w.z, w.z, xa[2], xb[2], acc[j * TOK + t], acc[j * TOK + t + 1]);
+              fma2(w.w, w.w, xa[3], xb[3], acc[j * TOK + t], acc[j * TOK + t + 1]);
+            }
           }
         }
       }
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u)
+#pragma unroll
+        for (int j = 0; j < EPW; ++j) r[u][j] = rn[u][j];
     }
+    __syncthreads();                                  // every warp has left this piece's buffer
+    if (threadIdx.x == 0 && piece + 2 < pieces) request(piece + 2);
   }
-#pragma unroll
-  for (int j = 0; j < kTiledExpertsPerWarp; ++j)
-#pragma unroll
-    for (int t = 0; t < TOK; ++t) {
-      if (t < tcount) {
-        const float v = warp_total(acc[j][t]);
-        if (lane == 0 && e0 + j < experts) logits[static_cast<size_t>(t0 + t) * experts + e0 + j] = v;
-      }
-    }
+  const float total = warp_totals<EPW * TOK>(acc, lane);
+  constexpr int kLanesPerValue = 32 / (EPW * TOK);
+  const int value = lane / kLanesPerValue, j = value / TOK, t = value % TOK;
+  if (lane % kLanesPerValue == 0 && t < tcount && e0 + j < experts)
+    logits[static_cast<size_t>(t0 + t) * experts + e0 + j] = total;
 }
 
 cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* router, int tokens, int experts, int hidden,
                                  float* logits, cudaStream_t stream, const L2Warm* warm_request) {
-  auto tile_smem = [&](int tok) { return static_cast<size_t>(tok) * hidden * sizeof(__nv_bfloat16); };
+  auto tile_smem = [&](int tok) { return static_cast<size_t>(2) * tok * kPieceQuads * sizeof(uint2); };
   const int row_blocks = (experts + kRowsWarps - 1) / kRowsWarps;
   const bool tiled_ok = tile_smem(8) <= kLogitsSmemLimit && hidden % 8 == 0;
   const dim3 rows_block(kRowsWarps * 32);
@@ -284,9 +350,10 @@ cudaError_t launch_router_logits(const __nv_bfloat16* x, const float* router, in
     const long long wide_grid = static_cast<long long>((experts + 31) / 32) * ((tokens + 7) / 8);
     // experts per warp: as many as still leave about a hundred blocks
     const long long mid_grid = static_cast<long long>((experts + 15) / 16) * ((tokens + 7) / 8);
-    cudaError_t e = wide_grid >= 148 ? launch_tiled(router_logits_tiled_kernel<8, 4>, 8, 32)
-                  : mid_grid >= 100  ? launch_tiled(router_logits_tiled_kernel<8, 2>, 8, 16)
-                                     : launch_tiled(router_logits_tiled_kernel<8, 1>, 8, 8);
+    // (and never more experts per block than there are: Mixtral's 8 take one per warp)
+    cudaError_t e = wide_grid >= 148 && experts > 16 ? launch_tiled(router_logits_tiled_kernel<8, 4>, 8, 32)
+                  : mid_grid >= 100 && experts > 8   ? launch_tiled(router_logits_tiled_kernel<8, 2>, 8, 16)
+                                                     : launch_tiled(router_logits_tiled_kernel<8, 1>, 8, 8);
     if (e != cudaSuccess) return e;
   }
   return cudaGetLastError();
