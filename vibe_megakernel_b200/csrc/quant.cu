@@ -95,7 +95,7 @@ constexpr int kScatterMaxTopk = 16;
 
 __global__ void __launch_bounds__(256) quantize_scatter_kernel(const __nv_bfloat16* __restrict__ x, int tokens, int width,
                                                                int topk, const int32_t* __restrict__ slot_pos,
-                                                               int shared_base, uint8_t* __restrict__ q,
+                                                               int shared_base, int rows, uint8_t* __restrict__ q,
                                                                float* __restrict__ scales) {
   dependent_wait();
   dependents_may_launch();
@@ -129,7 +129,9 @@ __global__ void __launch_bounds__(256) quantize_scatter_kernel(const __nv_bfloat
       scale[u] = quantize_values(v, bytes[u]);
     }
     for (int k = 0; k < dests; ++k) {
-      const size_t row = static_cast<size_t>(__shfl_sync(0xffffffffu, dest, k));
+      const int to = __shfl_sync(0xffffffffu, dest, k);
+      if (to < 0 || to >= rows) continue;      // (every routed row is kept by contract; a position outside the buffers is never written)
+      const size_t row = static_cast<size_t>(to);
       uint32_t* out = reinterpret_cast<uint32_t*>(q + row * width);
 #pragma unroll
       for (int u = 0; u < kStreamGroups; ++u)
@@ -163,8 +165,9 @@ cudaError_t launch_quantize_scatter(const __nv_bfloat16* x, int tokens, int widt
   cudaGetDevice(&device);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   const long long blocks = std::min((items + 7) / 8, static_cast<long long>(sms) * 8);
+  const int rows = tokens * topk + (shared_base >= 0 ? tokens : 0);
   launch_dependent(quantize_scatter_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, x, tokens, width,
-                   topk, slot_pos, shared_base, q, scales);
+                   topk, slot_pos, shared_base, rows, q, scales);
   if (launches) *launches += 1;
   return cudaGetLastError();
 }

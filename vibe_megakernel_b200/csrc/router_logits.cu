@@ -225,19 +225,21 @@ __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(c
   // Several quads per trip: all router loads of a trip (8 x 16 bytes per lane) are in flight together.
   // The token values are converted once per quad and shared by the warp's experts; two tokens
   // go through every packed FMA (each half is the scalar chain of fma4).
-  constexpr int kAhead = EPW >= 4 ? 2 : 8 / EPW;
-  static_assert(kPieceQuads % (32 * kAhead) == 0, "a trip never straddles two pieces");
+  constexpr int kAhead = EPW >= 4 ? 2 : 4 / EPW;      // (two register sets are in flight)
+  static_assert(kPieceQuads % (64 * kAhead) == 0, "a round of two trips never straddles two pieces");
+  const float4* row[EPW];                                // this warp's router rows (clamped: see the rows kernel)
+#pragma unroll
+  for (int j = 0; j < EPW; ++j)
+    row[j] = reinterpret_cast<const float4*>(router + static_cast<size_t>(min(e0 + j, experts - 1)) * hidden);
   auto fetch = [&](int q0, float4 (&r)[kAhead][EPW]) {
 #pragma unroll
-    for (int u = 0; u < kAhead; ++u)
+    for (int u = 0; u < kAhead; ++u) {
+      const int q = min(q0 + 32 * u, quads - 1);         // clamped, unconditional
 #pragma unroll
-      for (int j = 0; j < EPW; ++j) {
-        const int q = min(q0 + 32 * u, quads - 1);       // clamped, unconditional (see the rows kernel)
-        const int e = min(e0 + j, experts - 1);
-        r[u][j] = __ldg(reinterpret_cast<const float4*>(router + static_cast<size_t>(e) * hidden + 4 * q));
-      }
+      for (int j = 0; j < EPW; ++j) r[u][j] = __ldg(row[j] + q);
+    }
   };
-  float4 r[kAhead][EPW];
+  float4 r[kAhead][EPW], r_odd[kAhead][EPW];
   fetch(lane, r);                                        // weights: nothing to wait for
   dependent_wait();
   dependents_may_launch();
@@ -257,9 +259,7 @@ __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(c
     mbar_wait(&bar[piece & 1], (piece >> 1) & 1);   // bounded; a copy that never lands leaves wrong logits, not a hang
     const uint2* xs = s_x + static_cast<size_t>(piece & 1) * TOK * kPieceQuads;
     const int first = piece * kPieceQuads, end = min(first + kPieceQuads, quads);
-    for (int q0 = first + lane; q0 < end; q0 += 32 * kAhead) {
-      float4 rn[kAhead][EPW];
-      fetch(q0 + 32 * kAhead, rn);
+    auto trip = [&](int q0, const float4 (&w4)[kAhead][EPW]) {
 #pragma unroll
       for (int u = 0; u < kAhead; ++u) {
         const int q = q0 + 32 * u;
@@ -271,7 +271,7 @@ __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(c
             unpack4(xs[(t + 1) * kPieceQuads + q - first], xb);
 #pragma unroll
             for (int j = 0; j < EPW; ++j) {
-              const float4 w = r[u][j];
+              const float4 w = w4[u][j];
               fma2(w.x, w.x, xa[0], xb[0], acc[j * TOK + t], acc[j * TOK + t + 1]);
               fma2(w.y, w.y, xa[1], xb[1], acc[j * TOK + t], acc[j * TOK + t + 1]);
               fma2(w.z, w.z, xa[2], xb[2], acc[j * TOK + t], acc[j * TOK + t + 1]);
@@ -280,10 +280,14 @@ __global__ void __launch_bounds__(kTiledWarps * 32) router_logits_tiled_kernel(c
           }
         }
       }
-#pragma unroll
-      for (int u = 0; u < kAhead; ++u)
-#pragma unroll
-        for (int j = 0; j < EPW; ++j) r[u][j] = rn[u][j];
+    };
+    // two trips per round, the two register sets taking turns (no copies from the set that was fetched
+    // ahead into the set that is used)
+    for (int q0 = first + lane; q0 < end; q0 += 64 * kAhead) {
+      fetch(q0 + 32 * kAhead, r_odd);
+      trip(q0, r);
+      fetch(q0 + 64 * kAhead, r);
+      trip(q0 + 32 * kAhead, r_odd);
     }
     __syncthreads();                                  // every warp has left this piece's buffer
     if (threadIdx.x == 0 && piece + 2 < pieces) request(piece + 2);
