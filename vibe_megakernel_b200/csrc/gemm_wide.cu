@@ -341,9 +341,30 @@ grouped_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       float acc_a[64], acc_b[64];
 #pragma unroll
       for (int n = 0; n < 64; ++n) { acc_a[n] = 0.f; acc_b[n] = 0.f; }
-      // the scales of a step are read one step ahead (token scales at L2: the kernel before wrote them)
-      float x0 = __ldcg(xs), w0 = __ldg(wa);
-      float x1 = DUAL ? x0 : (KB > 1 ? __ldcg(xs + 1) : 0.f);
+      // The scales of a step are read one step ahead (token scales at L2: the kernel before wrote them).
+      // A thread's token scales are KB consecutive floats of its own row, so each 4-byte load is a
+      // 32-byte sector of its own from the L2: where the rows are 16-byte aligned (KB a multiple of 4)
+      // they come four K blocks per load, one group ahead (a quarter of the requests; with a load per
+      // K block the scale reads were a sixth of the SM's L2 traffic beside the operand tiles).
+      const bool by_four = (KB & 3) == 0 && (reinterpret_cast<uintptr_t>(p.act_scale) & 15) == 0;
+      float4 x_now = make_float4(0.f, 0.f, 0.f, 0.f), x_ahead = x_now;
+      int x_group = 0;
+      if (by_four) {
+        x_now = __ldcg(reinterpret_cast<const float4*>(xs));
+        x_ahead = KB > 4 ? __ldcg(reinterpret_cast<const float4*>(xs) + 1) : x_now;
+      }
+      auto token_scale = [&](int k) -> float {      // k never decreases and advances by at most two
+        if (!by_four) return __ldcg(xs + k);
+        if ((k >> 2) != x_group) {
+          x_group = k >> 2;
+          x_now = x_ahead;
+          if (4 * (x_group + 1) < KB) x_ahead = __ldcg(reinterpret_cast<const float4*>(xs) + x_group + 1);
+        }
+        const int i = k & 3;
+        return i == 0 ? x_now.x : i == 1 ? x_now.y : i == 2 ? x_now.z : x_now.w;
+      };
+      float x0 = token_scale(0), w0 = __ldg(wa);
+      float x1 = DUAL ? x0 : (KB > 1 ? token_scale(1) : 0.f);
       float w1 = DUAL ? __ldg(wb) : (KB > 1 ? __ldg(wa + 1) : 0.f);
       for (int kb = 0; kb < KB; ++it) {
         const int len = step_blocks<DUAL>(kb, KB, part_len);
@@ -352,9 +373,9 @@ grouped_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         {
           const int nb = kb + len;                     // first K block of the next step
           if (nb < KB) {
-            x0 = __ldcg(xs + nb); w0 = __ldg(wa + nb);
+            x0 = token_scale(nb); w0 = __ldg(wa + nb);
             if constexpr (DUAL) { x1 = x0; w1 = __ldg(wb + nb); }
-            else if (nb + 1 < KB) { x1 = __ldcg(xs + nb + 1); w1 = __ldg(wa + nb + 1); }
+            else if (nb + 1 < KB) { x1 = token_scale(nb + 1); w1 = __ldg(wa + nb + 1); }
           }
         }
         const uint32_t as = it % kWideAcc, aph = (it / kWideAcc) & 1u;
