@@ -84,7 +84,8 @@ __device__ __forceinline__ void tmem_ld32_mx(uint32_t taddr, uint32_t* r) {
 
 template <bool DUAL>
 __global__ void __launch_bounds__(kMxwThreads, 1)
-mx_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const MxWideDev p) {
+mx_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                    const __grid_constant__ CUtensorMap tm_xw, const MxWideDev p) {
   constexpr int S = kMxwStages;
   extern __shared__ uint8_t smem_raw[];
   const int KB = p.kblocks;
@@ -112,7 +113,7 @@ mx_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     for (int s = 0; s < kMxSfSlots; ++s) { mbar_init(bar_sffull + s, 4); mbar_init(bar_sfempty + s, 1); }   // four scale warps
     *s_abort = 0; *s_issued = 0; *s_consumed = 0; *s_committed = 0; *s_drained = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    prefetch_tmap(&tm_w); prefetch_tmap(&tm_x);
+    prefetch_tmap(&tm_w); prefetch_tmap(&tm_x); prefetch_tmap(&tm_xw);
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)), "r"(512) : "memory");
@@ -156,7 +157,8 @@ mx_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             tma_load_3d(st + kMxwTile, &tm_w, kx, tile * 128, 2 * ch.expert, bar_full + s, pol_w);
           else                      // 256 consecutive rows
             tma_load_2d(st + kMxwTile, &tm_w, kx, ch.expert * p.rows_per_expert + tile * 256, bar_full + s, pol_w);
-          for (int j = 0; j < n16; ++j) tma_load_2d(st + j * 2048, &tm_x, kx, ch.row0 + j * 16, bar_full + s, pol_x);
+          if (n16 == 8) tma_load_2d(st, &tm_xw, kx, ch.row0, bar_full + s, pol_x);      // a full tile: one request
+          else for (int j = 0; j < n16; ++j) tma_load_2d(st + j * 2048, &tm_x, kx, ch.row0 + j * 16, bar_full + s, pol_x);
           *s_issued = it + 1;
         }
         __syncwarp();
@@ -409,7 +411,7 @@ static cudaError_t mx_wide_launch_typed(const MxWideDev& dev, const CUtensorMap*
   }
   constexpr int smem = 1024 + kMxwStages * kMxwStageBytes + kMxSfRing * kMxwSfSlotBytes + kMxwTailBytes;
   static_assert(smem <= kMxSmem, "shared memory of one CTA");
-  return launch_dependent(mx_gemm_wide_kernel<DUAL>, dim3(grid), dim3(kMxwThreads), smem, stream, maps[0], maps[1], dev);
+  return launch_dependent(mx_gemm_wide_kernel<DUAL>, dim3(grid), dim3(kMxwThreads), smem, stream, maps[0], maps[1], maps[2], dev);
 }
 
 cudaError_t launch_gemm_mx_wide(const MxGemmArgs& a, cudaStream_t stream, int* launches, int* driver_error) {
@@ -418,10 +420,11 @@ cudaError_t launch_gemm_mx_wide(const MxGemmArgs& a, cudaStream_t stream, int* l
       (!a.dual && a.m % 256))
     return cudaErrorInvalidValue;
   const int rows_per_expert = a.dual ? 2 * a.m : a.m;
-  CUtensorMap maps[2];
+  CUtensorMap maps[3];
   int rc = a.dual ? mx_make_pair_map(&maps[0], a.w_blocks, a.n_experts, a.m, a.k)
                   : mx_make_map(&maps[0], a.w_blocks, static_cast<uint64_t>(a.n_experts) * rows_per_expert, a.k, true, 256);
-  rc = rc ? rc : mx_make_map(&maps[1], a.act, a.total_rows, a.k, false, 16);      // token rows move in boxes of 16
+  rc = rc ? rc : mx_make_map(&maps[1], a.act, a.total_rows, a.k, false, 16);      // token rows of a ragged chunk move in boxes of 16,
+  rc = rc ? rc : mx_make_map(&maps[2], a.act, a.total_rows, a.k, false, 128);     // a full tile's in one of 128
   if (rc) {
     if (driver_error) *driver_error = rc;
     return cudaErrorUnknown;

@@ -102,7 +102,8 @@ template <bool DUAL>
 __global__ void __launch_bounds__(kWideThreads, 1)
 grouped_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                          const __grid_constant__ CUtensorMap tm_sa, const __grid_constant__ CUtensorMap tm_sb,
-                         const __grid_constant__ CUtensorMap tm_x, const WideDev p) {
+                         const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_xw,
+                         const WideDev p) {
   using C = WideCfg<DUAL>;
   constexpr int S = C::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -132,7 +133,7 @@ grouped_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     for (int s = 0; s < kQueue; ++s) { mbar_init(bar_qfull + s, 1); mbar_init(bar_qempty + s, 32 + kWideEpiThreads); }
     *s_abort = 0; *s_issued = 0; *s_consumed = 0; *s_committed = 0; *s_drained = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    prefetch_tmap(&tm_a); prefetch_tmap(&tm_x);
+    prefetch_tmap(&tm_a); prefetch_tmap(&tm_x); prefetch_tmap(&tm_xw);
     if (DUAL) prefetch_tmap(&tm_b);
   }
   if (warp == 1) {
@@ -215,11 +216,13 @@ grouped_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
           if constexpr (DUAL) {
             tma_load_2d(st + kWideTile, ma, kb * 128, wrow, bar_full + s, pol_w);
             tma_load_2d(st + 2 * kWideTile, mb, kb * 128, wrow, bar_full + s, pol_w);
-            for (int j = 0; j < n16; ++j) tma_load_2d(st + j * 2048, &tm_x, kb * 128, ch.row0 + j * 16, bar_full + s, pol_x);
+            if (n16 == 8) tma_load_2d(st, &tm_xw, kb * 128, ch.row0, bar_full + s, pol_x);     // a full tile: one request
+            else for (int j = 0; j < n16; ++j) tma_load_2d(st + j * 2048, &tm_x, kb * 128, ch.row0 + j * 16, bar_full + s, pol_x);
           } else {
             for (int l = 0; l < len; ++l) {
               tma_load_2d(st + (2 + l) * kWideTile, ma, (kb + l) * 128, wrow, bar_full + s, pol_w);
-              for (int j = 0; j < n16; ++j)
+              if (n16 == 8) tma_load_2d(st + l * kWideTile, &tm_xw, (kb + l) * 128, ch.row0, bar_full + s, pol_x);
+              else for (int j = 0; j < n16; ++j)
                 tma_load_2d(st + l * kWideTile + j * 2048, &tm_x, (kb + l) * 128, ch.row0 + j * 16, bar_full + s, pol_x);
             }
           }
@@ -535,12 +538,12 @@ static cudaError_t launch_wide_typed(const WideDev& dev, const CUtensorMap* maps
   if (cached && configured[device] < 0) return cudaErrorInvalidConfiguration;
   const int smem = 1024 + C::kStages * C::kStageBytes + C::kTailBytes;
   return launch_dependent(grouped_gemm_wide_kernel<DUAL>, dim3(grid), dim3(kWideThreads), smem, stream, maps[0], maps[1],
-                          maps[2], maps[3], maps[4], dev);
+                          maps[2], maps[3], maps[4], maps[5], dev);
 }
 
 cudaError_t launch_gemm_wide(const GemmArgs& a, cudaStream_t stream, int* launches, int* driver_error) {
   if (a.tile != 128 || a.k % 128 || a.m % 128 || a.k / 128 > 112 || a.progress || a.fold.y) return cudaErrorInvalidValue;
-  CUtensorMap maps[5];
+  CUtensorMap maps[6];
   int rc = 0;
   const uint64_t wrows = static_cast<uint64_t>(a.n_local) * a.m;
   // With no routed experts on this rank the routed maps alias the shared ones (never dereferenced).
@@ -552,7 +555,8 @@ cudaError_t launch_gemm_wide(const GemmArgs& a, cudaStream_t stream, int* launch
   const uint8_t* sb = a.dual ? (a.s_b ? a.s_b : wb) : sa;
   rc |= make_map(&maps[2], sa, a.s_a ? a.m : wrows, a.k, 128);
   rc |= make_map(&maps[3], sb, a.s_a ? a.m : wrows, a.k, 128);
-  rc |= make_map(&maps[4], a.act, a.total_rows, a.k, 16);      // token rows move in boxes of 16
+  rc |= make_map(&maps[4], a.act, a.total_rows, a.k, 16);      // token rows of a ragged chunk move in boxes of 16,
+  rc |= make_map(&maps[5], a.act, a.total_rows, a.k, 128);     // a full tile's in one of 128 (a tenth of the requests per K block)
   if (rc) {
     if (driver_error) *driver_error = rc;
     return cudaErrorUnknown;
