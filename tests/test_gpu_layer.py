@@ -77,7 +77,8 @@ def check_against_oracle(api, geo, values, gemm):
 @pytest.mark.parametrize("name", ["tiny", "ds_small", "qwen_small", "kimi_small", "mixtral_small", "long_k"])
 def test_small_layers_match_the_oracle(api, name, gemm):
     geo = H.small_geometries()[name]
-    for tokens in (1, 4, 19, 40):
+    # (33 tokens: with top-2 the permutation kernel gets a row count that is no multiple of four)
+    for tokens in (1, 4, 19, 33, 40):
         values, _ = H.audited_inputs(geo, tokens)
         check_against_oracle(api, geo, values, gemm)
 
