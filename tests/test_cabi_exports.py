@@ -39,7 +39,8 @@ def test_workspace_layout_and_argument_checks_need_no_gpu():
     assert lay.rows == 64 * 9 and lay.token_tile == 16          # 512 routed rows over 256 experts: narrow tiles
     offsets = [getattr(lay, n) for n in _cabi.LAYOUT_OFFSETS[1:]]
     assert offsets == sorted(offsets) and all(o % 256 == 0 for o in offsets)
-    assert lay.total_bytes >= lay.slots + 2 * lay.rows * 7168
+    # behind the slot rows: the block entry point's normalised rows and the inverse permutation of large batches
+    assert lay.total_bytes >= lay.slots + 2 * lay.rows * 7168 + 2 * 64 * 7168 + 4 * 64 * 8
     assert lib.moe_workspace_layout(C.byref(cfg), 1, C.byref(lay)) == 0 and lay.token_tile == 16
     assert lib.moe_workspace_layout(C.byref(cfg), 1024, C.byref(lay)) == 0 and lay.token_tile == 64   # 32 rows per expert
     dense = _cabi.Config(4096, 14336, 8, 2, 0, 0, 1, 1, 1.0, 1, 0, 0)     # long down contraction: room for partial tiles
