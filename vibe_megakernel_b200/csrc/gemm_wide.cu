@@ -42,8 +42,15 @@ namespace moe {
 
 constexpr int kWideThreads = 384;
 constexpr int kWideEpiThreads = 256;
+#ifndef MOE_WIDE_CLOSERS
+#define MOE_WIDE_CLOSERS 1               // gate/up: warps 2-3 close the work items (SwiGLU + requantisation), see below
+#endif
 constexpr int kWideServiceRegs = 40;     // registers per thread the first warp group keeps
 constexpr int kWideEpiRegs = 232;        // ... and the epilogue warp groups rise to: 128*40 + 256*232 = 384*168
+// gate/up with a fourth warp group that closes the items: 128*40 + 256*200 + 128*72 = 512*128
+constexpr int kWideCloserRegs = 72;
+constexpr int kWideEpiRegsWithClosers = 200;
+constexpr int kWideCloseTile = 128 * 128 * 4;                    // a work item's bf16 (gate, up) pairs, [row][channel]
 constexpr int kWideLaunchRegs = 168;     // what the kernel must have been given per thread for that to add up
 constexpr int kWideSmem = 232448;
 constexpr int kWideAcc = 2;              // accumulator stages of 256 TMEM columns
@@ -55,9 +62,16 @@ struct WideCfg {
   // gate/up: tokens, gate tile, up tile of one K block; down: tokens and weights of two K blocks
   static constexpr int kStageBytes = (DUAL ? 3 : 4) * kWideTile;
   // after the ring: barriers, the item queue, amax exchange [2 items][2 halves][128], flags
-  static constexpr int kTailBytes = (2 * kWideMaxStages + 2 * kWideAcc + 2 * kQueue) * 8 + kQueue * 16 + 2 * 2 * 128 * 4 + 64;
-  static constexpr int kStages = (kWideSmem - 1024 - kTailBytes) / kStageBytes < kWideMaxStages
-                                     ? (kWideSmem - 1024 - kTailBytes) / kStageBytes
+  static constexpr int kTailBytes = (2 * kWideMaxStages + 2 * kWideAcc + 2 * kQueue + 2) * 8 + kQueue * 16 + 2 * 2 * 128 * 4 + 64 + 16;
+  // gate/up with closing warps: the tile the epilogue hands them sits between the ring and the tail
+  static constexpr bool kClosers = DUAL && MOE_WIDE_CLOSERS;
+  static constexpr int kCloseBytes = kClosers ? kWideCloseTile : 0;
+  static constexpr int kThreads = kClosers ? 512 : kWideThreads;
+  static constexpr int kEpiRegs = kClosers ? kWideEpiRegsWithClosers : kWideEpiRegs;
+  static constexpr int kLaunchRegs = kClosers ? 128 : kWideLaunchRegs;
+  static constexpr int kRegsNeeded = 128 * kWideServiceRegs + kWideEpiThreads * kEpiRegs + (kClosers ? 128 * kWideCloserRegs : 0);
+  static constexpr int kStages = (kWideSmem - 1024 - kTailBytes - kCloseBytes) / kStageBytes < kWideMaxStages
+                                     ? (kWideSmem - 1024 - kTailBytes - kCloseBytes) / kStageBytes
                                      : kWideMaxStages;
 };
 
@@ -99,7 +113,7 @@ __device__ __forceinline__ void fold32(const uint32_t* d, float s, float* acc) {
 }
 
 template <bool DUAL>
-__global__ void __launch_bounds__(kWideThreads, 1)
+__global__ void __launch_bounds__(WideCfg<DUAL>::kThreads, 1)
 grouped_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                          const __grid_constant__ CUtensorMap tm_sa, const __grid_constant__ CUtensorMap tm_sb,
                          const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_xw,
@@ -110,15 +124,19 @@ grouped_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   const int KB = p.kblocks;
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* stages = base;
-  uint64_t* bar_full = reinterpret_cast<uint64_t*>(base + S * C::kStageBytes);
+  uint4* s_close = reinterpret_cast<uint4*>(base + S * C::kStageBytes);      // [128 rows][32 chunks of four (gate, up) pairs], swizzled
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(base + S * C::kStageBytes + C::kCloseBytes);
   uint64_t* bar_empty = bar_full + kWideMaxStages;
   uint64_t* bar_tfull = bar_empty + kWideMaxStages;
   uint64_t* bar_tempty = bar_tfull + kWideAcc;
   uint64_t* bar_qfull = bar_tempty + kWideAcc;
   uint64_t* bar_qempty = bar_qfull + kQueue;
-  int4* s_queue = reinterpret_cast<int4*>(bar_qempty + kQueue);
+  uint64_t* bar_cfull = bar_qempty + kQueue;       // the closing warps' tile is written / has been read
+  uint64_t* bar_cempty = bar_cfull + 1;
+  int4* s_queue = reinterpret_cast<int4*>(bar_cempty + 1);
   float* s_amax = reinterpret_cast<float*>(s_queue + kQueue);            // [2][2][128]
-  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_amax + 2 * 2 * 128);
+  int4* s_close_item = reinterpret_cast<int4*>(s_amax + 2 * 2 * 128);      // {channel tile, first row, rows, 1 = no more items}
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_close_item + 1);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   volatile uint32_t* s_issued = reinterpret_cast<volatile uint32_t*>(s_tmem + 2);    // steps whose TMA was issued
   volatile uint32_t* s_consumed = reinterpret_cast<volatile uint32_t*>(s_tmem + 3);  // steps whose data arrived
@@ -131,6 +149,8 @@ grouped_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     for (int s = 0; s < S; ++s) { mbar_init(bar_full + s, 1); mbar_init(bar_empty + s, 1); }
     for (int s = 0; s < kWideAcc; ++s) { mbar_init(bar_tfull + s, 1); mbar_init(bar_tempty + s, kWideEpiThreads); }
     for (int s = 0; s < kQueue; ++s) { mbar_init(bar_qfull + s, 1); mbar_init(bar_qempty + s, 32 + kWideEpiThreads); }
+    mbar_init(bar_cfull, kWideEpiThreads);
+    mbar_init(bar_cempty, 128);
     *s_abort = 0; *s_issued = 0; *s_consumed = 0; *s_committed = 0; *s_drained = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tmap(&tm_a); prefetch_tmap(&tm_x); prefetch_tmap(&tm_xw);
@@ -295,8 +315,61 @@ grouped_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     }
     __syncwarp();
   }
+  } else if (warp >= 12) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kWideCloserRegs));
+    // ------------------------------ closing warps (gate/up) -------------------
+    // SwiGLU on the bf16-rounded GEMM outputs and requantisation of each row's 128 channels of the tile
+    // (megabench/tasks/megamoe.py:116-128, megabench/tasks/quantization.py:87-109), off the epilogue
+    // warps: those hand over a finished item as bf16 (gate, up) pairs in shared memory and go on folding
+    // the next item's K blocks, so the accumulators keep coming back while an item is closed (with the
+    // epilogue threads closing their own rows the MMAs stood still for most of the 11,000 cycles it
+    // took: TMEM holds two accumulators). Warps 12-15: a warp takes a row at a time, a lane four channels.
+    const SwigluMode& mode = p.swiglu;
+    for (uint32_t k = 0;; ++k) {
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_cfull, k & 1u, s_abort))) {
+        if (lane == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 35); *s_abort = 1; }
+        break;
+      }
+      const int4 item = *s_close_item;
+      if (item.w) break;                                   // the CTA's last item is behind us
+      const int mt = item.x, row0 = item.y, rows = item.z;
+      for (int r = warp - 12; r < rows; r += 4) {
+        const uint4 v = s_close[r * 32 + (lane ^ (r & 31))];
+        const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+        float weight = 1.f;
+        bool weighted = false;
+        if (mode.slot_weight) {
+          const int dest = mode.row_dest[row0 + r];
+          if (dest < mode.routed_rows) { weight = mode.slot_weight[dest]; weighted = true; }
+        }
+        float a[4];
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float g = __uint_as_float(w4[j] << 16);            // a bf16 is the upper half of an fp32
+          float u = __uint_as_float(w4[j] & 0xffff0000u);
+          if (mode.limit > 0.f) {
+            g = fminf(g, mode.limit);
+            u = fminf(fmaxf(u, -mode.limit), mode.limit);
+          }
+          a[j] = silu_times(g, u);
+          if (weighted) a[j] = __fmul_rn(a[j], weight);
+          amax = fmaxf(amax, fabsf(a[j]));
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        const float scale = group_scale(amax);
+        const float rcp = __frcp_rn(scale);
+        const uint32_t bytes = to_e4m3_pair(a[0], a[1], scale, rcp) | to_e4m3_pair(a[2], a[3], scale, rcp) << 16;
+        *reinterpret_cast<uint32_t*>(p.aq + static_cast<size_t>(row0 + r) * p.m + mt * kGroup + 4 * lane) = bytes;
+        if (lane == 0) p.as[static_cast<size_t>(row0 + r) * (p.m / kGroup) + mt] = scale;
+      }
+      mbar_arrive(bar_cempty);                             // this thread has read what it needed of the tile
+    }
+    __syncwarp();
+    __syncwarp();
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kWideEpiRegs));
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::kEpiRegs));
     // ------------------------------ epilogue ----------------------------------
     const int tid = static_cast<int>(threadIdx.x) - 128;
     const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
@@ -319,7 +392,15 @@ grouped_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
         failed = true;
       }
       // one decision for all epilogue threads (the item is the same for all of them unless one failed)
-      if (epilogue_any<kWideEpiThreads>(failed) || u < 0) {
+      const bool any_failed = epilogue_any<kWideEpiThreads>(failed);
+      if (any_failed || u < 0) {
+        if constexpr (DUAL && MOE_WIDE_CLOSERS) {
+          if (!any_failed) {      // tell the closing warps that nothing follows (they have a bounded wait otherwise)
+            mbar_wait(bar_cempty, (un & 1u) ^ 1u, s_abort);
+            if (tid == 0) *s_close_item = make_int4(0, 0, 0, 1);
+            mbar_arrive(bar_cfull);
+          }
+        }
         if (tid == 0) {
           PROBE_ADD(probe_cta, t_cta);
           PROBE_FLUSH(p.status, 5, probe_tfull);
@@ -429,7 +510,27 @@ grouped_gemm_wide_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       PROBE_START(t_close);
       // One decision for all epilogue threads: nobody may be left alone at a later barrier.
       if (epilogue_any<kWideEpiThreads>(failed || *s_abort)) break;
-      if constexpr (DUAL) {
+      if constexpr (DUAL && MOE_WIDE_CLOSERS) {
+        // The item goes to the closing warps as bf16 (gate, up) pairs, four channels per 16-byte chunk,
+        // chunk c of row t at position c ^ (t & 31) of the row: the lanes of a warp (32 rows, the same
+        // chunk) and the lanes of a closing warp (one row, 32 chunks) both touch every bank once.
+        const bool late = !mbar_wait(bar_cempty, (un & 1u) ^ 1u, s_abort);     // the previous item's tile has been read
+        if (epilogue_any<kWideEpiThreads>(late)) {
+          if (tid == 0 && !*s_abort) { report(p.status, MOE_ERR_DEVICE_TIMEOUT, 36); *s_abort = 1; }
+          break;
+        }
+#pragma unroll
+        for (int n = 0; n < 64; n += 4) {
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            w[j] = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(acc_a[n + j]))) |
+                   static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(acc_b[n + j]))) << 16;
+          s_close[t * 32 + ((half * 16 + (n >> 2)) ^ (t & 31))] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        if (tid == 0) *s_close_item = make_int4(mt, ch.row0, ch.rows, 0);
+        mbar_arrive(bar_cfull);                    // (release: the stores above are visible to who waits on it)
+      } else if constexpr (DUAL) {
         // SwiGLU on the bf16-rounded GEMM outputs and requantisation of the row's 128 channels of this
         // tile (megabench/tasks/megamoe.py:116-128, megabench/tasks/quantization.py:87-109); the row's
         // two threads exchange their maxima through shared memory (a buffer per item parity, so one
@@ -528,16 +629,15 @@ static cudaError_t launch_wide_typed(const WideDev& dev, const CUtensorMap* maps
     cudaFuncAttributes attr;
     cudaError_t e = cudaFuncGetAttributes(&attr, grouped_gemm_wide_kernel<DUAL>);
     if (e != cudaSuccess) return e;
-    const bool fits = attr.numRegs * kWideThreads >= 128 * kWideServiceRegs + kWideEpiThreads * kWideEpiRegs &&
-                      attr.numRegs >= kWideLaunchRegs;
+    const bool fits = attr.numRegs * C::kThreads >= C::kRegsNeeded && attr.numRegs >= C::kLaunchRegs;
     if (fits) e = cudaFuncSetAttribute(grouped_gemm_wide_kernel<DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, kWideSmem);
     if (e != cudaSuccess) return e;
     if (cached) configured[device] = fits ? 1 : -1;
     if (!fits) return cudaErrorInvalidConfiguration;
   }
   if (cached && configured[device] < 0) return cudaErrorInvalidConfiguration;
-  const int smem = 1024 + C::kStages * C::kStageBytes + C::kTailBytes;
-  return launch_dependent(grouped_gemm_wide_kernel<DUAL>, dim3(grid), dim3(kWideThreads), smem, stream, maps[0], maps[1],
+  const int smem = 1024 + C::kStages * C::kStageBytes + C::kCloseBytes + C::kTailBytes;
+  return launch_dependent(grouped_gemm_wide_kernel<DUAL>, dim3(grid), dim3(C::kThreads), smem, stream, maps[0], maps[1],
                           maps[2], maps[3], maps[4], maps[5], dev);
 }
 
