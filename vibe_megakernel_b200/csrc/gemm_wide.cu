@@ -24,7 +24,10 @@
 // warp group that gives its registers away), warps 4-11 = epilogue: warp w reads TMEM lanes
 // 32*(w%4).., the first four warps take columns 0-63 of each 128-column accumulator, the last four
 // columns 64-127. An epilogue thread keeps 128 fp32 sums, which is why the epilogue warp groups raise
-// their register allowance (setmaxnreg) from what the other warp group releases.
+// their register allowance (setmaxnreg) from what the other warp groups release. The gate/up kernel has
+// a fourth warp group, warps 12-15, that closes the work items (SwiGLU + requantisation) from a tile of
+// bf16 (gate, up) pairs the epilogue warps leave in shared memory, so that those go straight on to the
+// next item's K blocks and the accumulators keep coming back to the MMAs.
 //
 // Every wait is bounded, as in the decode kernel: on expiry the role records
 // MOE_ERR_DEVICE_TIMEOUT, raises the CTA's abort flag, and all roles fall through to the common exit.
