@@ -297,19 +297,23 @@ def test_experts_with_more_rows_than_one_tile(api, name, tokens):
         assert torch.equal(part["y"], full["y"][:40])
 
 
-@pytest.mark.parametrize("name,tokens", [("mixtral_small", 600), ("long_k", 300)])
-def test_rows_on_the_mma_m_side_give_the_bits_of_the_decode_kernel(api, name, tokens):
+@pytest.mark.parametrize("name,tokens,megamoe_form", [("mixtral_small", 600, False), ("long_k", 300, False),
+                                                      ("mixtral_small", 600, True)])
+def test_rows_on_the_mma_m_side_give_the_bits_of_the_decode_kernel(api, name, tokens, megamoe_form):
     # With more than 64 rows per expert in sight the tensor-core path multiplies 128-row tiles with the
     # tokens on the MMA's M side (another kernel, another epilogue, divisions without the library's
     # slow path). The same tokens forty at a time meet the decode kernel (16-token tiles, weights on
     # M): every row must come out bit-identical (long_k: a contraction summed in parts).
+    # megamoe_form: the clamp and the routing weight inside SwiGLU (megabench/tasks/megamoe.py:116-122), which
+    # the 128-row gate/up kernel applies in its closing warps
     geo = H.small_geometries()[name]
     values, _ = H.audited_inputs(geo, tokens, max_tries=64)
     dev = H.to_device(values, "cuda")
-    wide = api.MoeLayer(api.LayerConfig.from_geometry(geo), max_tokens=tokens)
+    form = dict(swiglu_limit=1.0, weight_before_requant=True) if megamoe_form else {}
+    wide = api.MoeLayer(api.LayerConfig.from_geometry(geo, **form), max_tokens=tokens)
     assert wide.workspace(tokens)[1].token_tile == 128
     full = wide.forward(dev, check_status=True)
-    small = api.MoeLayer(api.LayerConfig.from_geometry(geo), max_tokens=40)
+    small = api.MoeLayer(api.LayerConfig.from_geometry(geo, **form), max_tokens=40)
     assert small.workspace(40)[1].token_tile <= 64
     for lo in range(0, tokens, 40):
         few = dict(dev)
